@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""Headline benchmark: greedy decode tokens/s of a Llama-3-8B-architecture Q4_K model (synthetic
+seeded weights, 512-token random-id prompt, paged fp16 KV with 16-token pages, context 4096) and
+the achieved HBM bandwidth of the quantised matrix-vector kernel against the measured peak.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--batch B] [--format Q4_K|Q8_0|Q4_0] [--arch 8b|1b|tiny] [--prompt P]
+
+One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE). Rank 0 prints ONE JSON line.
+
+value  : tokens/s with token feedback resident on the device (jl_generate: no host round trip).
+e2e    : tokens/s through the reference-facing call (BatchExecutor.decodeStep -> jl_decode) with
+         host token/position arrays going in and sampled ids coming back every step.
+roofline: the dominant kernel (RMSNorm + gate/up + SwiGLU matrix-vector launch) timed alone with
+         CUDA events over all layers' weights (2.1 GB for the 8B shape, so every launch reads HBM),
+         algorithmic bytes / time against MEASURED_PEAKS.json.
+cpu_baseline / --impl reference: the C restatement of jitLLM's CPU path (oracle/) on the host
+         cores, a bounded number of decode steps of the same model.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ARCHS = {
+    # dim, hidden, layers, heads, kv_heads, vocab, ctx, tied
+    "8b": (4096, 14336, 32, 32, 8, 128256, 4096, False),
+    "1b": (2048, 8192, 16, 32, 8, 128256, 2048, True),
+    "tiny": (512, 1024, 4, 8, 2, 4096, 1024, False),
+}
+BYTES_PER_EL = {"Q4_K": 144 / 256, "Q4_0": 18 / 32, "Q8_0": 34 / 32}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--format", default="Q4_K", choices=list(BYTES_PER_EL))
+    ap.add_argument("--arch", default="8b", choices=list(ARCHS))
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--seed", type=int, default=20261125)
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs (read-only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        inside = [r for ts, r in self.rows if t0 - 0.05 <= ts <= t1 + 0.15 and len(r) >= 8] or \
+                 [r for _, r in self.rows if len(r) >= 8]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(r[1]) for r in inside)
+        reasons = []
+        for name, col in (("hw_slowdown", 4), ("hw_thermal_slowdown", 5), ("sw_thermal_slowdown", 6),
+                          ("sw_power_cap", 7)):
+            if any(r[col].lower().startswith("active") for r in inside):
+                reasons.append(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(inside[0][2]), "reasons": reasons,
+                "samples": len(inside), "power_w_max": max(float(r[3]) for r in inside)}
+
+
+def model_bytes(cfg, fmt):
+    """Algorithmic bytes one decode step must read: every weight matrix once."""
+    bpe = BYTES_PER_EL[fmt]
+    dim, hid, L, kv = cfg.dim, cfg.hiddenDim, cfg.numberOfLayers, cfg.kvDim
+    per_layer = dim * dim * 2 + kv * dim * 2 + hid * dim * 3
+    return (per_layer * L + cfg.vocabularySize * dim) * bpe
+
+
+def op_bytes(cfg, fmt, op):
+    bpe = BYTES_PER_EL[fmt]
+    dim, hid, kv, V = cfg.dim, cfg.hiddenDim, cfg.kvDim, cfg.vocabularySize
+    rows, cols = {0: (dim + 2 * kv, dim), 1: (dim, dim), 2: (2 * hid, dim), 3: (dim, hid), 4: (V, dim)}[op]
+    out_rows = hid if op == 2 else rows
+    return rows * cols * bpe + 4 * cols + 4 * out_rows
+
+
+def cpu_decode_rate(cfg, tensors, budget_s, max_steps, seed):
+    """tokens/s of the oracle's forwardJava on this host, decode steps from position 0."""
+    from oracle import binding as oracle
+    om = oracle.Model(cfg, tensors)
+    rng = np.random.default_rng(seed)
+    toks = rng.integers(0, cfg.vocabularySize, size=max_steps + 1)
+    om.forward(int(toks[0]), 0)  # untimed warm-up, as JitllmBench does
+    t0 = time.perf_counter()
+    done = 0
+    while done < max_steps:
+        om.forward(int(toks[done + 1]), done + 1)
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    cores = oracle.lib().orc_get_threads()
+    om.close()
+    return done / dt, cores, done, dt
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    n_gpus = args.gpus
+
+    import jitllm_b200 as jl
+
+    dims = ARCHS[args.arch]
+    cfg = jl.Configuration(dim=dims[0], hiddenDim=dims[1], numberOfLayers=dims[2], numberOfHeads=dims[3],
+                           numberOfKeyValueHeads=dims[4], vocabularySize=dims[5], contextLength=dims[6],
+                           tiedEmbeddings=dims[7])
+    fmt = jl.GGMLType[args.format]
+    B, K, W, P = args.batch, args.steps, args.warmup, args.prompt
+    workload = f"llama3-{args.arch}-arch {args.format} greedy decode, B={B}, {P}-token prompt, ctx {cfg.contextLength}, 16-token fp16 KV pages"
+    config = {"workload": workload, "batch": B, "prompt_len": P, "format": args.format,
+              "cache": "weights of one step (%.2f GB) exceed L2; no flush needed" % (model_bytes(cfg, args.format) / 1e9)}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        t0 = time.time()
+        tensors = jl.synth_model_tensors(cfg, fmt, args.seed)
+        budget = min(150.0, max(10.0, 1.5 * K))
+        rate, cores, done, dt = cpu_decode_rate(cfg, tensors, budget, max(1, K), args.seed)
+        line = {"impl": "reference", "metric": "decode tok/s", "value": rate, "unit": "tok/s", "n_gpus": n_gpus,
+                "steps": done, "steps_requested": K, "warmup": 1, "ms_per_step": 1000.0 / rate,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": rate, "unit": "tok/s", "cores": cores, "kind": "port",
+                                 "sample": f"{done} single-sequence decode steps from position 1, all layers, "
+                                           f"scalar summation mode, {dt:.1f} s; model built in {time.time() - t0 - dt:.0f} s"},
+                "e2e": {"value": rate, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line), flush=True)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    distributed = world > 1
+    if distributed:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+
+    t_build = time.time()
+    tensors = jl.synth_model_tensors(cfg, fmt, args.seed)
+    cr, ci = jl.precomputeFreqsCis(cfg.contextLength, cfg.headSize, cfg.ropeTheta)
+    dev = jl.Device(local_rank)
+    model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=B)
+    t_build = time.time() - t_build
+
+    # KV pool: only the pages this run touches are mapped; the rest stay UNMAPPED (scratch block).
+    bps = cfg.contextLength // 16
+    total_tokens = P + W + 3 * K + 64
+    if total_tokens > cfg.contextLength:
+        raise SystemExit(f"prompt + steps ({total_tokens}) exceed the context ({cfg.contextLength})")
+    need = (total_tokens + 15) // 16
+    kv = model.createKvStorage(jl.KvStorageRequest(B * need, bps, B, 16, cfg.numberOfLayers, cfg.kvDim))
+    table = np.full(B * bps, jl.UNMAPPED, dtype=np.int32)
+    for b in range(B):
+        table[b * bps:b * bps + need] = np.arange(b * need, (b + 1) * need)
+    kv.publishBlockTable(table)
+    ex = jl.B200BatchExecutor(model)
+
+    rng = np.random.default_rng(args.seed + rank)
+    prompts = rng.integers(0, cfg.vocabularySize, size=(B, P))
+    t_prefill = time.perf_counter()
+    for b in range(B):
+        jl.B200InvocationBoundary(model, kvSlot=b, copyLogits=False).prefill(prompts[b, :P - 1], 0)
+    dev.synchronize()
+    t_prefill = time.perf_counter() - t_prefill
+
+    active = [True] * B
+    slots = list(range(B))
+    pos = P - 1
+    last = [int(t) for t in prompts[:, P - 1]]
+
+    # warm-up (also captures the step graph)
+    hist = ex.generate(jl.BatchSlots(active, last, [pos] * B, slots), max(W, 3))
+    pos += max(W, 3)
+    last = [int(t) for t in hist[-1]]
+
+    # ---- timed region 1: device-resident token feedback
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    c0 = dev.counters()
+    barrier()
+    dev.synchronize()
+    wall0 = time.time()
+    dev.timer_start()
+    hist = ex.generate(jl.BatchSlots(active, last, [pos] * B, slots), K)
+    ms = dev.timer_stop()
+    wall1 = time.time()
+    barrier()
+    c1 = dev.counters()
+    clocks = sampler.stop(wall0, wall1)
+    mid_pos = pos + K // 2
+    pos += K
+    last = [int(t) for t in hist[-1]]
+    if distributed:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- timed region 2: end to end through decodeStep with host arrays every step
+    tok = list(last)
+    for _ in range(3):
+        out = ex.decodeStep(jl.BatchSlots(active, tok, [pos] * B, slots))
+        tok = [int(t) for t in out]
+        pos += 1
+    barrier()
+    dev.synchronize()
+    e0 = time.perf_counter()
+    for _ in range(K):
+        out = ex.decodeStep(jl.BatchSlots(active, tok, [pos] * B, slots))
+        tok = [int(t) for t in out]
+        pos += 1
+    dev.synchronize()
+    e_ms = (time.perf_counter() - e0) * 1000.0
+    if distributed:
+        t = torch.tensor([e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e_ms = float(t.item())
+
+    # ---- per-kernel roofline: each matrix-vector launch shape alone, over all layers' weights
+    peak, peak_kind = measured_peak()
+    names = {0: "rmsnorm+qkv", 1: "attn-out+residual", 2: "rmsnorm+gate/up+swiglu", 3: "down+residual",
+             4: "rmsnorm+vocab+argmax"}
+    ops = []
+    for op in (2, 0, 1, 3, 4):
+        reps = cfg.numberOfLayers * (2 if op != 4 else 1) if op != 4 else 8
+        model.benchOp(op, 0, cfg.numberOfLayers if op != 4 else 3)  # warm-up
+        dev.synchronize()
+        if op == 4:
+            dev.flush_l2()  # one matrix only: start it cold
+        dev.timer_start()
+        model.benchOp(op, 0, reps)
+        t_ms = dev.timer_stop()
+        by = op_bytes(cfg, args.format, op)
+        us = t_ms * 1000.0 / reps
+        ops.append({"kernel": names[op], "bytes_per_launch": by, "us_per_launch": round(us, 3),
+                    "gbs": round(by / us / 1e3, 1), "frac": round(by / us / 1e3 / peak, 4), "launches": reps})
+    dom = ops[0]
+
+    weights_b = model_bytes(cfg, args.format)
+    kv_b = B * (mid_pos + 1) * cfg.numberOfLayers * cfg.kvDim * 2 * 2
+    step_ms = ms / K
+    tokens = B * K
+    replicas = world if distributed else 1
+    value = tokens * replicas / (ms / 1000.0)
+    line = {
+        "metric": "decode tok/s", "value": value, "unit": "tok/s", "n_gpus": n_gpus, "steps": K, "warmup": max(W, 3),
+        "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": "weak" if replicas > 1 else "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": dict(config, parallelism="replicas x%d" % replicas if replicas > 1 else "single GPU"),
+        "clocks": clocks,
+        "e2e": {"value": tokens * replicas / (e_ms / 1000.0), "unit": "tok/s", "h2d_bytes_per_step": 13 * B,
+                "d2h_bytes_per_step": 4 * B + 4, "ms_per_step": e_ms / K},
+        "gpu_launches": int(c1["kernel_launches"] - c0["kernel_launches"]),
+        "roofline": {"bound": "hbm", "kernel": "gemv_kernel<%s> %s" % (args.format, dom["kernel"]),
+                     "achieved": dom["gbs"], "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": dom["frac"], "traffic": None, "bytes_per_launch": dom["bytes_per_launch"],
+                     "us_per_launch": dom["us_per_launch"]},
+        "step_roofline": {"weight_bytes": weights_b, "kv_bytes": kv_b, "achieved_gbs": (weights_b + kv_b) / step_ms / 1e6,
+                          "frac_of_measured_peak": (weights_b + kv_b) / step_ms / 1e6 / peak,
+                          "frac_of_8tbs": (weights_b + kv_b) / step_ms / 1e6 / 8000.0},
+        "kernels": ops,
+        "setup": {"synth_and_upload_s": round(t_build, 1), "prefill_tok_s": round(B * (P - 1) / t_prefill, 1)},
+    }
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+        rate, cores, done, dt = cpu_decode_rate(cfg, tensors, args.cpu_seconds, 64, args.seed)
+        line["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": cores, "kind": "port",
+                                "sample": f"{done} single-sequence decode steps from position 1, all layers, "
+                                          f"scalar summation mode, {dt:.1f} s"}
+    else:
+        line["cpu_baseline"] = None
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,177 @@
+/*
+ * jitllm_b200 -- C ABI of the B200 (sm_100a) CUDA library that stands in for jitLLM's TornadoVM
+ * TaskGraph + kernel layer on the Llama decode / prefill hot path.
+ *
+ * Plain pointers and sizes only; every function returns a jl_status (0 = OK) and leaves a
+ * human-readable message, prefixed with the reference's diagnostic code (GPUL-CFG-002,
+ * GPUL-MEM-001, ...; runtime/diagnostics/DiagnosticCode.java:26-60), retrievable through
+ * jl_last_error(). There is no CPU fallback: without a usable CUDA device jl_init fails.
+ *
+ * Ownership: the caller owns every host buffer (the mmapped GGUF slices, token arrays, output
+ * arrays); the library copies what it needs and owns all device memory until jl_destroy. This is
+ * the contract of lowering/InvocationBoundary.java:6-24 ("results copied out into session-owned
+ * storage").
+ *
+ * Threading: one jl_ctx per model per GPU; calls on one context must be serialised by the
+ * caller, as runtime/batch/BatchExecutor.java:17-18 and InvocationBoundary.java:13-21 already
+ * require of the code this replaces.
+ *
+ * Reference paths below are relative to src/main/java/org/beehive/jitllm/.
+ */
+#ifndef JITLLM_B200_H
+#define JITLLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct jl_ctx jl_ctx;
+typedef struct jl_tensor jl_tensor;
+
+typedef enum {
+    JL_OK = 0,
+    JL_ERR_INVALID = 1,     /* GPUL-CFG-002: bad argument / unsupported combination */
+    JL_ERR_OOM = 2,         /* GPUL-MEM-001: device memory exhausted */
+    JL_ERR_CUDA = 3,        /* a CUDA runtime call failed */
+    JL_ERR_STATE = 4,       /* GPUL-LIFE-001: call out of order (no model, no KV store, closed) */
+    JL_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up */
+    JL_ERR_UNSUPPORTED = 6  /* GPUL-CFG-002: format or shape this build does not handle */
+} jl_status;
+
+/* GGML type ids as stored in GGUF (format/GGMLType.java:7,13,18-20). */
+typedef enum { JL_F32 = 0, JL_F16 = 1, JL_Q4_0 = 2, JL_Q8_0 = 8, JL_Q4_K = 12 } jl_ggml_type;
+
+/* Tensor roles: the subset of runtime/tensor/TensorRole.java:17-59 a Llama file uses; this is
+ * the key of TornadoWeights.tensor(role, layer) (inference/weights/tornado/TornadoWeights.java:95-109). */
+typedef enum {
+    JL_ROLE_TOKEN_EMBEDDING = 0,
+    JL_ROLE_ATTENTION_NORM = 1,
+    JL_ROLE_ATTENTION_QUERY = 2,
+    JL_ROLE_ATTENTION_KEY = 3,
+    JL_ROLE_ATTENTION_VALUE = 4,
+    JL_ROLE_ATTENTION_OUTPUT = 5,
+    JL_ROLE_FFN_NORM = 6,
+    JL_ROLE_FFN_GATE = 7,
+    JL_ROLE_FFN_UP = 8,
+    JL_ROLE_FFN_DOWN = 9,
+    JL_ROLE_OUTPUT_NORM = 10,
+    JL_ROLE_OUTPUT = 11,
+    JL_ROLE_COUNT = 12
+} jl_tensor_role;
+
+/* model/llama/LlamaConfiguration.java:5-16 plus the tensor-parallel placement of this GPU. */
+typedef struct {
+    int32_t dim, hidden, layers, heads, kv_heads, head_dim, vocab, ctx_len;
+    float rms_eps;
+    int32_t tied_embeddings; /* 1: no output.weight, logits use token_embd (AbstractModelLoader.java:255-266) */
+    int32_t max_batch;       /* widest BatchSlots this context will be asked to decode */
+    int32_t tp_rank, tp_size; /* 0,1 for a single GPU */
+} jl_model_desc;
+
+/* Counters for a MetricsSink adapter (runtime/metrics/MetricsSink.java;
+ * backend/tornado/TornadoMetricsReporter.java:52-78). */
+typedef struct {
+    uint64_t decode_calls, prefill_calls, kernel_launches;
+    uint64_t h2d_bytes, d2h_bytes;
+    uint64_t weight_bytes, kv_bytes, workspace_bytes;
+    float last_step_ms; /* device time of the last jl_decode / jl_prefill, CUDA events */
+} jl_counters;
+
+/* ---- lifecycle: replaces TornadoVMMasterPlan.initializeTornadoVMPlan / freeTornadoExecutionPlan
+ * (backend/tornado/TornadoVMMasterPlan.java:59-83,131-180). */
+int32_t jl_init(int32_t device_id, jl_ctx **out);
+int32_t jl_destroy(jl_ctx *ctx);
+/* Message of the last failing call on this context (ctx == NULL: last failing jl_init). */
+const char *jl_last_error(jl_ctx *ctx);
+
+/* ---- weights: replaces the device half of ModelLoader.loadTornadoTensorNative
+ * (model/loader/ModelLoader.java:246-290). Bytes stay in GGUF block layout on the device. */
+int32_t jl_model_create(jl_ctx *ctx, const jl_model_desc *desc);
+int32_t jl_upload_tensor(jl_ctx *ctx, int32_t role, int32_t layer, int32_t ggml_type, int64_t rows,
+                         int64_t cols, const void *host_bytes, size_t nbytes);
+/* RoPE tables as computed by model/loader/RopeFrequencies.java:14-54, [ctx_len][head_dim/2]. */
+int32_t jl_upload_rope(jl_ctx *ctx, const float *cos_table, const float *sin_table, int64_t n);
+/* Checks that every tensor of every layer is present and builds the per-step launch plan;
+ * replaces forceCopyInReadOnlyData + createExecutionPlan (TornadoVMMasterPlan.java:131-180). */
+int32_t jl_model_finalize(jl_ctx *ctx);
+
+/* ---- paged KV store: replaces backend/tornado/kv/TornadoKvStore.java behind
+ * runtime/kv/KvStorageFactory.create(KvStorageRequest) (runtime/kv/KvStorageRequest.java:5-12).
+ * One extra, never-leased scratch block is allocated for UNMAPPED (-1) table entries. */
+int32_t jl_kv_create(jl_ctx *ctx, int32_t total_blocks, int32_t blocks_per_slot, int32_t max_slots,
+                     int32_t block_size_tokens, int32_t fp16_key_value);
+/* KvStorage.publishBlockTable (TornadoKvStore.java publishBlockTable): n must equal
+ * max_slots * blocks_per_slot. */
+int32_t jl_kv_publish_block_table(jl_ctx *ctx, const int32_t *table, int64_t n);
+int64_t jl_kv_bytes_per_block(jl_ctx *ctx);
+/* Test / checkpoint access to one position's K or V row (kv_dim halfs) of a layer. */
+int32_t jl_kv_read_row(jl_ctx *ctx, int32_t which /*0=K,1=V*/, int32_t slot, int32_t layer,
+                       int32_t pos, uint16_t *out_halfs);
+
+/* ---- the step: replaces TornadoVMMasterPlan.tornadoVMForwardDecode(position)
+ * (backend/tornado/TornadoVMMasterPlanSingleToken.java:134-171) for width 1 and
+ * BatchExecutor.decodeStep(BatchSlots) (backend/tornado/batch/TornadoBatchExecutor.java:294-347)
+ * for width > 1. Arrays have `width` entries; inactive slots are skipped and get token -1.
+ * out_tokens: greedy argmax, first index on ties (inference/Logits.java:49-60).
+ * out_logits: NULL, or width * vocab floats. */
+int32_t jl_decode(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32_t *positions,
+                  const int32_t *kv_slots, const uint8_t *active, int32_t *out_tokens,
+                  float *out_logits);
+/* n_steps greedy steps without a host round trip between them: each active row's sampled token is
+ * fed back on the device and its position advances (the device-side sampling the reference turns
+ * on with -Djitllm.deviceSample, inference/TokenGenerationLoop.java:111-128, carried one step
+ * further). out_history receives n_steps * width token ids, step-major; inactive rows get -1. */
+int32_t jl_generate(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32_t *positions,
+                    const int32_t *kv_slots, const uint8_t *active, int32_t n_steps,
+                    int32_t *out_history);
+/* Replaces BatchPrefillDecodePlan.tornadoVMForwardBatchPrefill (backend/tornado/
+ * BatchPrefillDecodePlan.java:12-64): n prompt tokens of one sequence at start_pos.., KV pages
+ * written, no logits (backend/cpu/InferenceCoreBatchPrefillDecode.java:189-191). */
+int32_t jl_prefill(jl_ctx *ctx, int32_t kv_slot, const int32_t *tokens, int32_t start_pos,
+                   int32_t n);
+/* Reads a named per-step buffer ("x","q","k","v","xb","hb","logits") of batch row `row` after a
+ * step; for per-operation parity tests. */
+int32_t jl_debug_read(jl_ctx *ctx, const char *name, int32_t row, float *out, int64_t n);
+
+/* ---- standalone operators (the sweep of quantised GEMV/GEMM shapes) */
+/* Host blocks in, host floats out: element-exact FloatTensor.getFloat
+ * (tensor/standard/Q8_0FloatTensor.java:53-61, Q4_0FloatTensor.java:56-79, Q4_KFloatTensor.java:88-122). */
+int32_t jl_dequant(jl_ctx *ctx, int32_t ggml_type, const void *blocks, int64_t n_elements,
+                   float *out);
+/* y[n][rows] = W[rows][cols] . x[n][cols]; FloatTensor.matmul (tensor/standard/FloatTensor.java:123-140).
+ * Host buffers; copies are part of the call. */
+int32_t jl_gemv(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t cols, const void *w_host,
+                const float *x_host, int32_t n, float *y_host);
+/* Device-resident form: upload once, multiply many times. x_dev / y_dev are device pointers. */
+int32_t jl_tensor_upload(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t cols,
+                         const void *host_bytes, size_t nbytes, jl_tensor **out);
+int32_t jl_tensor_free(jl_ctx *ctx, jl_tensor *t);
+int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t n, float *y_dev);
+
+/* ---- plumbing */
+void *jl_device_alloc(jl_ctx *ctx, size_t nbytes);
+int32_t jl_device_free(jl_ctx *ctx, void *p);
+int32_t jl_memcpy_h2d(jl_ctx *ctx, void *dst_dev, const void *src_host, size_t nbytes);
+int32_t jl_memcpy_d2h(jl_ctx *ctx, void *dst_host, const void *src_dev, size_t nbytes);
+int32_t jl_synchronize(jl_ctx *ctx);
+/* The cudaStream_t every launch of this context goes to. */
+void *jl_stream(jl_ctx *ctx);
+/* CUDA-event stopwatch on that stream. */
+int32_t jl_timer_start(jl_ctx *ctx);
+int32_t jl_timer_stop(jl_ctx *ctx, float *elapsed_ms);
+/* Launches one operator of the loaded model `iters` times on successive layers (wrapping) with
+ * the step workspace as input and output, for per-kernel timing: op 0 = RMSNorm+QKV, 1 = attention
+ * output projection, 2 = RMSNorm+gate/up+SwiGLU, 3 = down projection, 4 = RMSNorm+vocabulary.
+ * The measuring counterpart of backend/tornado/bench/SyntheticKernelBench.java:87-161. */
+int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters);
+int32_t jl_get_counters(jl_ctx *ctx, jl_counters *out);
+/* Overwrites a 256 MiB scratch buffer (larger than L2) so that the next kernel starts cold. */
+int32_t jl_flush_l2(jl_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

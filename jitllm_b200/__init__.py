@@ -1,0 +1,24 @@
+"""B200-native (sm_100a) CUDA implementation of jitLLM's Llama decode / prefill hot path behind a
+C ABI (include/jitllm_b200.h), with a Python mirror of the reference's host interfaces."""
+from .api import (  # noqa: F401
+    B200BatchExecutor,
+    B200InvocationBoundary,
+    B200Model,
+    BatchSlots,
+    Configuration,
+    Device,
+    DeviceTimeoutError,
+    GGMLType,
+    IllegalStateError,
+    InsufficientDeviceMemoryError,
+    KvStorage,
+    KvStorageRequest,
+    TensorRole,
+    UNMAPPED,
+    argmax,
+    load_model,
+    precomputeFreqsCis,
+    quantize,
+    synth_model_tensors,
+    synth_tensor,
+)

@@ -1,0 +1,92 @@
+"""In-tree build of the native libraries.
+
+`python -m jitllm_b200.build` compiles
+
+* ``jitllm_b200/lib/libjitllm_b200.so`` -- the sm_100a CUDA library behind the C ABI of
+  ``include/jitllm_b200.h`` (nvcc cross-compiles without a GPU);
+* ``jitllm_b200/lib/libjl_synth.so``    -- the host-side synthetic weight generator / encoders.
+
+Nothing is installed outside the tree; the built files are what a GPU machine loads.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB = PKG / "lib"
+
+CUDA_SOURCES = ["gemv.cu", "ops.cu", "engine.cu"]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+    "-shared",
+]
+HOST_CC = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
+HOST_CFLAGS = ["-O2", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared", "-std=c11", "-Wall"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc", shutil.which("nvcc")):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or install the CUDA toolkit")
+
+
+def _stale(target: Path, sources: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(s.stat().st_mtime > t for s in sources)
+
+
+def _run(cmd: list[str], verbose: bool) -> None:
+    if verbose:
+        print("+", " ".join(cmd), flush=True)
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout)
+        sys.stderr.write(proc.stderr)
+        raise RuntimeError(f"build step failed: {' '.join(cmd)}")
+    if verbose and proc.stderr:
+        sys.stderr.write(proc.stderr)
+
+
+def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
+    LIB.mkdir(exist_ok=True)
+    target = LIB / "libjitllm_b200.so"
+    deps = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [
+        PKG.parent / "include" / "jitllm_b200.h"
+    ]
+    if force or _stale(target, deps):
+        cmd = [_nvcc(), *NVCC_FLAGS]
+        if ptxas_info:
+            cmd += ["-Xptxas", "-v"]
+        cmd += ["-o", str(target), *[str(CSRC / s) for s in CUDA_SOURCES]]
+        _run(cmd, verbose or ptxas_info)
+    return target
+
+
+def build_synth(force: bool = False, verbose: bool = False) -> Path:
+    LIB.mkdir(exist_ok=True)
+    target = LIB / "libjl_synth.so"
+    src = CSRC / "synth.c"
+    if force or _stale(target, [src]):
+        _run([HOST_CC, *HOST_CFLAGS, "-o", str(target), str(src), "-lm"], verbose)
+    return target
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    build_cuda(force, verbose)
+    build_synth(force, verbose)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose=True)
+    if "--ptxas" in sys.argv:
+        build_cuda(force=True, ptxas_info=True)

@@ -1,0 +1,1237 @@
+// Context, device-resident model, paged KV store, the decode step and the C ABI of
+// include/jitllm_b200.h. Host-side logic only; the kernels live in gemv.cu / ops.cu.
+#include "../../include/jitllm_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "gemv.cuh"
+#include "ops.cuh"
+
+using namespace jl;
+
+namespace {
+
+thread_local std::string g_init_error;
+
+struct DevTensor {
+    uint8_t *data = nullptr;
+    int type = -1;
+    int64_t rows = 0, cols = 0;
+    size_t bytes = 0;
+};
+
+struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    uint64_t launches = 0;
+};
+
+}  // namespace
+
+struct jl_tensor {
+    DevTensor t;
+};
+
+struct jl_ctx {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, tev0 = nullptr, tev1 = nullptr;
+    std::string err;
+    bool use_graph = true, use_pdl = true;
+
+    bool has_model = false, finalized = false;
+    jl_model_desc desc = {};
+    int kv_dim = 0;
+    DevTensor global[JL_ROLE_COUNT];
+    std::vector<DevTensor> layer[JL_ROLE_COUNT];
+    float *rope_cos = nullptr, *rope_sin = nullptr;
+
+    // paged KV
+    bool has_kv = false;
+    __half *kpool = nullptr, *vpool = nullptr;
+    int32_t *block_table = nullptr;
+    int total_blocks = 0, blocks_per_slot = 0, max_slots = 0, block_tokens = 0;
+    std::vector<int32_t> host_table;
+
+    // per-step workspace, [max_batch] rows each
+    float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *xb = nullptr, *hb = nullptr,
+          *logits = nullptr;
+    int32_t *d_tokens = nullptr, *d_positions = nullptr, *d_slots = nullptr, *d_out = nullptr;
+    uint8_t *d_active = nullptr;
+    float *att_partial = nullptr;
+    unsigned *att_count = nullptr;
+    float *amax_val = nullptr;
+    int *amax_idx = nullptr;
+    unsigned *amax_count = nullptr;
+    int *d_status = nullptr;
+    int attn_nsplit = 1;
+    int32_t *d_history = nullptr, *d_step = nullptr;
+    size_t history_cap = 0;
+    // pinned host staging: tokens | positions | slots | out | active | status
+    int32_t *h_stage = nullptr;
+
+    std::map<int, StepGraph> graphs;  // key: width
+    uint32_t *flush_buf = nullptr;
+    size_t flush_words = 0;
+    std::vector<void *> user_allocs;
+    jl_counters counters = {};
+};
+
+namespace {
+
+int fail(jl_ctx *ctx, int code, const char *fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    const char *prefix = "";
+    switch (code) {
+        case JL_ERR_INVALID: prefix = "GPUL-CFG-002: "; break;
+        case JL_ERR_UNSUPPORTED: prefix = "GPUL-CFG-002: unsupported: "; break;
+        case JL_ERR_OOM: prefix = "GPUL-MEM-001: "; break;
+        case JL_ERR_STATE: prefix = "GPUL-LIFE-001: "; break;
+        case JL_ERR_TIMEOUT: prefix = "device wait timed out: "; break;
+        case JL_ERR_CUDA: prefix = "CUDA: "; break;
+        default: break;
+    }
+    std::string msg = std::string(prefix) + buf;
+    if (ctx)
+        ctx->err = msg;
+    else
+        g_init_error = msg;
+    return code;
+}
+
+#define JL_CUDA(ctx, call)                                                                   \
+    do {                                                                                     \
+        cudaError_t e_ = (call);                                                             \
+        if (e_ != cudaSuccess) {                                                             \
+            int code_ = (e_ == cudaErrorMemoryAllocation) ? JL_ERR_OOM : JL_ERR_CUDA;        \
+            return fail(ctx, code_, "%s failed: %s", #call, cudaGetErrorString(e_));         \
+        }                                                                                    \
+    } while (0)
+
+#define JL_REQUIRE(ctx, cond, code, ...) \
+    do {                                 \
+        if (!(cond)) return fail(ctx, code, __VA_ARGS__); \
+    } while (0)
+
+int dev_alloc(jl_ctx *ctx, void **p, size_t bytes) {
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ctx, e == cudaErrorMemoryAllocation ? JL_ERR_OOM : JL_ERR_CUDA,
+                    "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    }
+    return JL_OK;
+}
+
+bool env_flag(const char *name, bool dflt) {
+    const char *v = getenv(name);
+    if (!v || !*v) return dflt;
+    return !(v[0] == '0' || v[0] == 'n' || v[0] == 'N' || v[0] == 'f' || v[0] == 'F');
+}
+
+int check_shape(jl_ctx *ctx, int type, int64_t rows, int64_t cols, size_t nbytes) {
+    JL_REQUIRE(ctx, rows > 0 && cols > 0, JL_ERR_INVALID, "rows and cols must be positive, got %lld x %lld",
+               (long long)rows, (long long)cols);
+    JL_REQUIRE(ctx, type == kF32 || type == kF16 || is_quant(type), JL_ERR_UNSUPPORTED,
+               "GGML type %d (supported: F32=0, F16=1, Q4_0=2, Q8_0=8, Q4_K=12)", type);
+    if (is_quant(type))
+        JL_REQUIRE(ctx, cols % 256 == 0, JL_ERR_UNSUPPORTED,
+                   "quantised rows must be a multiple of 256 columns, got %lld", (long long)cols);
+    const int64_t need = rows * row_bytes(type, cols);
+    JL_REQUIRE(ctx, int64_t(nbytes) == need, JL_ERR_INVALID,
+               "tensor of %lld x %lld type %d needs %lld bytes, got %zu", (long long)rows,
+               (long long)cols, type, (long long)need, nbytes);
+    return JL_OK;
+}
+
+int upload(jl_ctx *ctx, DevTensor *t, int type, int64_t rows, int64_t cols, const void *host,
+           size_t nbytes) {
+    if (t->data) {
+        cudaFree(t->data);
+        ctx->counters.weight_bytes -= t->bytes;
+        *t = DevTensor();
+    }
+    void *p = nullptr;
+    int rc = dev_alloc(ctx, &p, nbytes);
+    if (rc) return rc;
+    cudaError_t e = cudaMemcpyAsync(p, host, nbytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(ctx, JL_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(e));
+    }
+    t->data = static_cast<uint8_t *>(p);
+    t->type = type;
+    t->rows = rows;
+    t->cols = cols;
+    t->bytes = nbytes;
+    ctx->counters.weight_bytes += nbytes;
+    ctx->counters.h2d_bytes += nbytes;
+    return JL_OK;
+}
+
+void drop_graphs(jl_ctx *ctx) {
+    for (auto &kv : ctx->graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    ctx->graphs.clear();
+}
+
+void free_model(jl_ctx *ctx) {
+    drop_graphs(ctx);
+    for (int r = 0; r < JL_ROLE_COUNT; ++r) {
+        if (ctx->global[r].data) cudaFree(ctx->global[r].data);
+        ctx->global[r] = DevTensor();
+        for (auto &t : ctx->layer[r])
+            if (t.data) cudaFree(t.data);
+        ctx->layer[r].clear();
+    }
+    void *bufs[] = {ctx->rope_cos, ctx->rope_sin, ctx->x,       ctx->q,        ctx->k,
+                    ctx->v,        ctx->xb,       ctx->hb,      ctx->logits,   ctx->d_tokens,
+                    ctx->d_positions, ctx->d_slots, ctx->d_out, ctx->d_active, ctx->att_partial,
+                    ctx->att_count, ctx->amax_val, ctx->amax_idx, ctx->amax_count};
+    for (void *b : bufs)
+        if (b) cudaFree(b);
+    ctx->rope_cos = ctx->rope_sin = ctx->x = ctx->q = ctx->k = ctx->v = ctx->xb = ctx->hb =
+        ctx->logits = nullptr;
+    ctx->d_tokens = ctx->d_positions = ctx->d_slots = ctx->d_out = nullptr;
+    ctx->d_active = nullptr;
+    ctx->att_partial = nullptr;
+    ctx->att_count = nullptr;
+    ctx->amax_val = nullptr;
+    ctx->amax_idx = nullptr;
+    ctx->amax_count = nullptr;
+    if (ctx->d_history) cudaFree(ctx->d_history);
+    if (ctx->d_step) cudaFree(ctx->d_step);
+    ctx->d_history = ctx->d_step = nullptr;
+    ctx->history_cap = 0;
+    ctx->counters.weight_bytes = 0;
+    ctx->counters.workspace_bytes = 0;
+    ctx->has_model = ctx->finalized = false;
+}
+
+void free_kv(jl_ctx *ctx) {
+    drop_graphs(ctx);
+    if (ctx->kpool) cudaFree(ctx->kpool);
+    if (ctx->vpool) cudaFree(ctx->vpool);
+    if (ctx->block_table) cudaFree(ctx->block_table);
+    ctx->kpool = ctx->vpool = nullptr;
+    ctx->block_table = nullptr;
+    ctx->has_kv = false;
+    ctx->counters.kv_bytes = 0;
+}
+
+const DevTensor &wcls_of(const jl_ctx *ctx) {
+    return ctx->global[JL_ROLE_OUTPUT].data ? ctx->global[JL_ROLE_OUTPUT]
+                                            : ctx->global[JL_ROLE_TOKEN_EMBEDDING];
+}
+
+// One quantised matrix-vector launch for batch row `row`.
+int launch_gemv(jl_ctx *ctx, GemvArgs &a, int total_rows, uint64_t *launches) {
+    GemvPlan plan;
+    if (!gemv_plan(a.type, a.cols, total_rows, a.mode, ctx->sm_count, &plan))
+        return fail(ctx, JL_ERR_UNSUPPORTED, "no launch plan for type %d with %d columns", a.type,
+                    a.cols);
+    a.status = ctx->d_status;
+    cudaError_t e = gemv_launch(a, plan, ctx->stream, ctx->use_pdl);
+    if (e != cudaSuccess)
+        return fail(ctx, JL_ERR_CUDA, "matrix-vector launch failed: %s", cudaGetErrorString(e));
+    ++*launches;
+    return JL_OK;
+}
+
+// Enqueues the kernels of one decode step for `width` batch rows on ctx->stream.
+// Order of operations per layer: backend/cpu/InferenceCore.java:72-141 of the reference.
+int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_t *launches) {
+    const jl_model_desc &d = ctx->desc;
+    const int dim = d.dim, kv_dim = ctx->kv_dim, hidden = d.hidden;
+    const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
+    cudaError_t e = embedding_launch(emb.type, emb.data, ctx->d_tokens, ctx->d_active, ctx->x, dim,
+                                     width, ctx->stream, false);
+    if (e != cudaSuccess)
+        return fail(ctx, JL_ERR_CUDA, "embedding launch failed: %s", cudaGetErrorString(e));
+    ++*launches;
+    int rc;
+    for (int l = 0; l < d.layers; ++l) {
+        const DevTensor &wq = ctx->layer[JL_ROLE_ATTENTION_QUERY][l];
+        const DevTensor &wk = ctx->layer[JL_ROLE_ATTENTION_KEY][l];
+        const DevTensor &wv = ctx->layer[JL_ROLE_ATTENTION_VALUE][l];
+        const DevTensor &wo = ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l];
+        const DevTensor &w1 = ctx->layer[JL_ROLE_FFN_GATE][l];
+        const DevTensor &w3 = ctx->layer[JL_ROLE_FFN_UP][l];
+        const DevTensor &w2 = ctx->layer[JL_ROLE_FFN_DOWN][l];
+        const float *attn_norm =
+            reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
+        const float *ffn_norm =
+            reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
+        for (int b = 0; b < width; ++b) {
+            GemvArgs a = {};
+            a.nseg = 3;
+            a.seg[0] = {wq.data, ctx->q + size_t(b) * dim, nullptr, int(wq.rows)};
+            a.seg[1] = {wk.data, ctx->k + size_t(b) * kv_dim, nullptr, int(wk.rows)};
+            a.seg[2] = {wv.data, ctx->v + size_t(b) * kv_dim, nullptr, int(wv.rows)};
+            a.cols = dim;
+            a.type = wq.type;
+            a.mode = kGemvPlain;
+            a.x = ctx->x + size_t(b) * dim;
+            a.norm_w = attn_norm;
+            a.eps = d.rms_eps;
+            a.active = ctx->d_active + b;
+            if ((rc = launch_gemv(ctx, a, int(wq.rows + wk.rows + wv.rows), launches))) return rc;
+        }
+        {
+            AttnArgs a = {};
+            a.q = ctx->q;
+            a.k = ctx->k;
+            a.v = ctx->v;
+            a.out = ctx->xb;
+            a.rope_cos = ctx->rope_cos;
+            a.rope_sin = ctx->rope_sin;
+            a.positions = ctx->d_positions;
+            a.slots = ctx->d_slots;
+            a.active = ctx->d_active;
+            a.kv = {ctx->kpool, ctx->vpool, ctx->block_table, ctx->blocks_per_slot,
+                    ctx->block_tokens, d.layers, kv_dim};
+            a.layer = l;
+            a.heads = d.heads;
+            a.kv_heads = d.kv_heads;
+            a.head_dim = d.head_dim;
+            a.dim = dim;
+            a.nsplit = ctx->attn_nsplit;
+            a.partial = ctx->att_partial;
+            a.counters = ctx->att_count;
+            e = attention_launch(a, width, ctx->stream, ctx->use_pdl);
+            if (e != cudaSuccess)
+                return fail(ctx, JL_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
+            ++*launches;
+        }
+        for (int b = 0; b < width; ++b) {
+            GemvArgs a = {};
+            a.nseg = 1;
+            float *xr = ctx->x + size_t(b) * dim;
+            a.seg[0] = {wo.data, xr, xr, int(wo.rows)};
+            a.cols = int(wo.cols);
+            a.type = wo.type;
+            a.mode = kGemvPlain;
+            a.x = ctx->xb + size_t(b) * dim;
+            a.active = ctx->d_active + b;
+            if ((rc = launch_gemv(ctx, a, int(wo.rows), launches))) return rc;
+        }
+        for (int b = 0; b < width; ++b) {
+            GemvArgs a = {};
+            a.nseg = 2;
+            a.seg[0] = {w1.data, ctx->hb + size_t(b) * hidden, nullptr, int(w1.rows)};
+            a.seg[1] = {w3.data, nullptr, nullptr, int(w3.rows)};
+            a.cols = dim;
+            a.type = w1.type;
+            a.mode = kGemvGateUp;
+            a.x = ctx->x + size_t(b) * dim;
+            a.norm_w = ffn_norm;
+            a.eps = d.rms_eps;
+            a.active = ctx->d_active + b;
+            if ((rc = launch_gemv(ctx, a, int(w1.rows + w3.rows), launches))) return rc;
+        }
+        for (int b = 0; b < width; ++b) {
+            GemvArgs a = {};
+            a.nseg = 1;
+            float *xr = ctx->x + size_t(b) * dim;
+            a.seg[0] = {w2.data, xr, xr, int(w2.rows)};
+            a.cols = int(w2.cols);
+            a.type = w2.type;
+            a.mode = kGemvPlain;
+            a.x = ctx->hb + size_t(b) * hidden;
+            a.active = ctx->d_active + b;
+            if ((rc = launch_gemv(ctx, a, int(w2.rows), launches))) return rc;
+        }
+    }
+    if (with_logits) {
+        const DevTensor &wc = wcls_of(ctx);
+        for (int b = 0; b < width; ++b) {
+            GemvArgs a = {};
+            a.nseg = 1;
+            a.seg[0] = {wc.data, ctx->logits + size_t(b) * d.vocab, nullptr, int(wc.rows)};
+            a.cols = dim;
+            a.type = wc.type;
+            a.mode = kGemvPlain;
+            a.x = ctx->x + size_t(b) * dim;
+            a.norm_w = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
+            a.eps = d.rms_eps;
+            a.active = ctx->d_active + b;
+            a.argmax_val = ctx->amax_val + size_t(b) * ctx->sm_count;
+            a.argmax_idx = ctx->amax_idx + size_t(b) * ctx->sm_count;
+            a.argmax_count = ctx->amax_count + b;
+            a.out_token = ctx->d_out + b;
+            if ((rc = launch_gemv(ctx, a, int(wc.rows), launches))) return rc;
+        }
+    }
+    if (advance) {
+        e = advance_launch(ctx->d_tokens, ctx->d_positions, ctx->d_out, ctx->d_active, ctx->d_history,
+                           ctx->d_step, width, ctx->stream, ctx->use_pdl);
+        if (e != cudaSuccess)
+            return fail(ctx, JL_ERR_CUDA, "advance launch failed: %s", cudaGetErrorString(e));
+        ++*launches;
+    }
+    return JL_OK;
+}
+
+// Runs one step: replays the captured graph for this width, capturing it on first use.
+int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
+    const int key = width * 4 + (with_logits ? 1 : 0) + (advance ? 2 : 0);
+    uint64_t launches = 0;
+    if (!ctx->use_graph) {
+        int rc = enqueue_step(ctx, width, with_logits, advance, &launches);
+        ctx->counters.kernel_launches += launches;
+        return rc;
+    }
+    auto it = ctx->graphs.find(key);
+    if (it == ctx->graphs.end()) {
+        cudaGraph_t graph = nullptr;
+        JL_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        int rc = enqueue_step(ctx, width, with_logits, advance, &launches);
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+        if (rc) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc;
+        }
+        if (e != cudaSuccess)
+            return fail(ctx, JL_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+        StepGraph sg;
+        e = cudaGraphInstantiate(&sg.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess)
+            return fail(ctx, e == cudaErrorMemoryAllocation ? JL_ERR_OOM : JL_ERR_CUDA,
+                        "graph instantiation failed: %s", cudaGetErrorString(e));
+        sg.launches = launches;
+        it = ctx->graphs.emplace(key, sg).first;
+    }
+    JL_CUDA(ctx, cudaGraphLaunch(it->second.exec, ctx->stream));
+    ctx->counters.kernel_launches += it->second.launches;
+    return JL_OK;
+}
+
+int check_status(jl_ctx *ctx) {
+    int st = ctx->h_stage[5 * ctx->desc.max_batch];
+    if (st == kDevTimeout) {
+        cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+        return fail(ctx, JL_ERR_TIMEOUT, "a kernel gave up waiting for an asynchronous copy");
+    }
+    return JL_OK;
+}
+
+}  // namespace
+
+// =================================================================================== C ABI
+
+extern "C" {
+
+int32_t jl_init(int32_t device_id, jl_ctx **out) {
+    if (!out) return fail(nullptr, JL_ERR_INVALID, "out must not be NULL");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(nullptr, JL_ERR_CUDA,
+                    "no usable CUDA device (%s); this library has no CPU fallback",
+                    e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+    }
+    if (device_id < 0 || device_id >= count)
+        return fail(nullptr, JL_ERR_INVALID, "device %d out of range (0..%d)", device_id, count - 1);
+    cudaDeviceProp prop;
+    JL_CUDA(nullptr, cudaSetDevice(device_id));
+    JL_CUDA(nullptr, cudaGetDeviceProperties(&prop, device_id));
+    if (prop.major != 10)
+        return fail(nullptr, JL_ERR_UNSUPPORTED,
+                    "device %d is sm_%d%d; this build carries sm_100a code only", device_id,
+                    prop.major, prop.minor);
+    jl_ctx *ctx = new jl_ctx();
+    ctx->device = device_id;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->use_graph = env_flag("JITLLM_B200_GRAPH", true);
+    ctx->use_pdl = env_flag("JITLLM_B200_PDL", true);
+    e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev0);
+    if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev1);
+    if (e == cudaSuccess) e = cudaEventCreate(&ctx->tev0);
+    if (e == cudaSuccess) e = cudaEventCreate(&ctx->tev1);
+    if (e == cudaSuccess) e = gemv_configure();
+    if (e == cudaSuccess) e = attention_configure();
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->d_status), sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        int rc = fail(nullptr, JL_ERR_CUDA, "context set-up failed: %s", cudaGetErrorString(e));
+        jl_destroy(ctx);
+        return rc;
+    }
+    *out = ctx;
+    return JL_OK;
+}
+
+int32_t jl_destroy(jl_ctx *ctx) {
+    if (!ctx) return JL_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    free_model(ctx);
+    free_kv(ctx);
+    for (void *p : ctx->user_allocs) cudaFree(p);
+    if (ctx->flush_buf) cudaFree(ctx->flush_buf);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
+    if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+    if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+    if (ctx->tev0) cudaEventDestroy(ctx->tev0);
+    if (ctx->tev1) cudaEventDestroy(ctx->tev1);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return JL_OK;
+}
+
+const char *jl_last_error(jl_ctx *ctx) { return ctx ? ctx->err.c_str() : g_init_error.c_str(); }
+
+int32_t jl_model_create(jl_ctx *ctx, const jl_model_desc *desc) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, desc != nullptr, JL_ERR_INVALID, "desc must not be NULL");
+    const jl_model_desc &d = *desc;
+    JL_REQUIRE(ctx, d.dim > 0 && d.hidden > 0 && d.layers > 0 && d.heads > 0 && d.kv_heads > 0 &&
+                        d.head_dim > 0 && d.vocab > 0 && d.ctx_len > 0,
+               JL_ERR_INVALID, "every model dimension must be positive");
+    JL_REQUIRE(ctx, d.heads % d.kv_heads == 0, JL_ERR_INVALID,
+               "heads (%d) must be a multiple of kv_heads (%d)", d.heads, d.kv_heads);
+    JL_REQUIRE(ctx, d.heads * d.head_dim == d.dim, JL_ERR_UNSUPPORTED,
+               "heads * head_dim (%d) must equal dim (%d) for the Llama layout", d.heads * d.head_dim,
+               d.dim);
+    JL_REQUIRE(ctx, d.head_dim == 64 || d.head_dim == 128, JL_ERR_UNSUPPORTED,
+               "head_dim %d (supported: 64, 128)", d.head_dim);
+    const int gq = d.heads / d.kv_heads;
+    JL_REQUIRE(ctx, gq == 1 || gq == 2 || gq == 4 || gq == 8, JL_ERR_UNSUPPORTED,
+               "heads / kv_heads = %d (supported: 1, 2, 4, 8)", gq);
+    JL_REQUIRE(ctx, d.dim % 256 == 0 && d.hidden % 256 == 0, JL_ERR_UNSUPPORTED,
+               "dim and hidden must be multiples of 256");
+    JL_REQUIRE(ctx, d.max_batch >= 1 && d.max_batch <= 256, JL_ERR_INVALID,
+               "max_batch must be in 1..256, got %d", d.max_batch);
+    JL_REQUIRE(ctx, d.tp_size <= 1 && d.tp_rank == 0, JL_ERR_UNSUPPORTED,
+               "tensor parallel placement %d/%d", d.tp_rank, d.tp_size);
+    cudaSetDevice(ctx->device);
+    free_model(ctx);
+    ctx->desc = d;
+    if (ctx->desc.tp_size < 1) ctx->desc.tp_size = 1;
+    ctx->kv_dim = d.kv_heads * d.head_dim;
+    for (int r = 0; r < JL_ROLE_COUNT; ++r) ctx->layer[r].assign(d.layers, DevTensor());
+    ctx->has_model = true;
+    return JL_OK;
+}
+
+int32_t jl_upload_tensor(jl_ctx *ctx, int32_t role, int32_t layer, int32_t ggml_type, int64_t rows,
+                         int64_t cols, const void *host_bytes, size_t nbytes) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->has_model, JL_ERR_STATE, "jl_model_create must come first");
+    JL_REQUIRE(ctx, role >= 0 && role < JL_ROLE_COUNT, JL_ERR_INVALID, "unknown tensor role %d", role);
+    JL_REQUIRE(ctx, host_bytes != nullptr, JL_ERR_INVALID, "host_bytes must not be NULL");
+    const jl_model_desc &d = ctx->desc;
+    const bool per_layer = !(role == JL_ROLE_TOKEN_EMBEDDING || role == JL_ROLE_OUTPUT_NORM ||
+                             role == JL_ROLE_OUTPUT);
+    if (per_layer)
+        JL_REQUIRE(ctx, layer >= 0 && layer < d.layers, JL_ERR_INVALID, "layer %d out of range 0..%d",
+                   layer, d.layers - 1);
+    int64_t er = 0, ec = 0;
+    bool norm = false;
+    switch (role) {
+        case JL_ROLE_TOKEN_EMBEDDING: er = d.vocab; ec = d.dim; break;
+        case JL_ROLE_OUTPUT: er = d.vocab; ec = d.dim; break;
+        case JL_ROLE_ATTENTION_QUERY: er = d.dim; ec = d.dim; break;
+        case JL_ROLE_ATTENTION_KEY:
+        case JL_ROLE_ATTENTION_VALUE: er = ctx->kv_dim; ec = d.dim; break;
+        case JL_ROLE_ATTENTION_OUTPUT: er = d.dim; ec = d.dim; break;
+        case JL_ROLE_FFN_GATE:
+        case JL_ROLE_FFN_UP: er = d.hidden; ec = d.dim; break;
+        case JL_ROLE_FFN_DOWN: er = d.dim; ec = d.hidden; break;
+        default: er = 1; ec = d.dim; norm = true; break;
+    }
+    JL_REQUIRE(ctx, rows == er && cols == ec, JL_ERR_INVALID,
+               "role %d expects %lld x %lld, got %lld x %lld", role, (long long)er, (long long)ec,
+               (long long)rows, (long long)cols);
+    if (norm)
+        JL_REQUIRE(ctx, ggml_type == kF32, JL_ERR_UNSUPPORTED, "norm weights must be F32, got type %d",
+                   ggml_type);
+    else
+        JL_REQUIRE(ctx, is_quant(ggml_type), JL_ERR_UNSUPPORTED,
+                   "matrix role %d must be Q8_0, Q4_0 or Q4_K, got type %d", role, ggml_type);
+    int rc = check_shape(ctx, ggml_type, rows, cols, nbytes);
+    if (rc) return rc;
+    cudaSetDevice(ctx->device);
+    drop_graphs(ctx);
+    ctx->finalized = false;
+    DevTensor *t = per_layer ? &ctx->layer[role][layer] : &ctx->global[role];
+    return upload(ctx, t, ggml_type, rows, cols, host_bytes, nbytes);
+}
+
+int32_t jl_upload_rope(jl_ctx *ctx, const float *cos_table, const float *sin_table, int64_t n) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->has_model, JL_ERR_STATE, "jl_model_create must come first");
+    const int64_t need = int64_t(ctx->desc.ctx_len) * (ctx->desc.head_dim / 2);
+    JL_REQUIRE(ctx, cos_table && sin_table && n == need, JL_ERR_INVALID,
+               "RoPE tables must hold ctx_len * head_dim / 2 = %lld floats, got %lld",
+               (long long)need, (long long)n);
+    cudaSetDevice(ctx->device);
+    if (!ctx->rope_cos) {
+        int rc;
+        if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->rope_cos), n * 4))) return rc;
+        if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->rope_sin), n * 4))) return rc;
+    }
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->rope_cos, cos_table, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->rope_sin, sin_table, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->counters.h2d_bytes += n * 8;
+    return JL_OK;
+}
+
+int32_t jl_model_finalize(jl_ctx *ctx) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->has_model, JL_ERR_STATE, "jl_model_create must come first");
+    const jl_model_desc &d = ctx->desc;
+    JL_REQUIRE(ctx, ctx->global[JL_ROLE_TOKEN_EMBEDDING].data, JL_ERR_STATE, "token embedding missing");
+    JL_REQUIRE(ctx, ctx->global[JL_ROLE_OUTPUT_NORM].data, JL_ERR_STATE, "output norm missing");
+    JL_REQUIRE(ctx, d.tied_embeddings || ctx->global[JL_ROLE_OUTPUT].data, JL_ERR_STATE,
+               "output.weight missing and embeddings are not tied");
+    JL_REQUIRE(ctx, ctx->rope_cos != nullptr, JL_ERR_STATE, "RoPE tables missing");
+    static const int per_layer_roles[] = {JL_ROLE_ATTENTION_NORM,  JL_ROLE_ATTENTION_QUERY,
+                                          JL_ROLE_ATTENTION_KEY,   JL_ROLE_ATTENTION_VALUE,
+                                          JL_ROLE_ATTENTION_OUTPUT, JL_ROLE_FFN_NORM,
+                                          JL_ROLE_FFN_GATE,        JL_ROLE_FFN_UP,
+                                          JL_ROLE_FFN_DOWN};
+    for (int l = 0; l < d.layers; ++l) {
+        for (int r : per_layer_roles)
+            JL_REQUIRE(ctx, ctx->layer[r][l].data, JL_ERR_STATE, "layer %d is missing tensor role %d", l, r);
+        const int tq = ctx->layer[JL_ROLE_ATTENTION_QUERY][l].type;
+        JL_REQUIRE(ctx, ctx->layer[JL_ROLE_ATTENTION_KEY][l].type == tq &&
+                            ctx->layer[JL_ROLE_ATTENTION_VALUE][l].type == tq,
+                   JL_ERR_UNSUPPORTED, "layer %d: Q, K and V must share one quantisation type", l);
+        JL_REQUIRE(ctx, ctx->layer[JL_ROLE_FFN_GATE][l].type == ctx->layer[JL_ROLE_FFN_UP][l].type,
+                   JL_ERR_UNSUPPORTED, "layer %d: gate and up must share one quantisation type", l);
+    }
+    if (ctx->finalized) return JL_OK;
+    cudaSetDevice(ctx->device);
+    const size_t B = d.max_batch;
+    int rc;
+    size_t ws = 0;
+    auto alloc = [&](void **p, size_t bytes) {
+        ws += bytes;
+        return dev_alloc(ctx, p, bytes);
+    };
+    // A single-row step has (pos+1) keys to cover with ~2 CTAs per SM; wider batches already
+    // fill the grid with rows.
+    int nsplit = (2 * ctx->sm_count + int(B) * d.kv_heads - 1) / (int(B) * d.kv_heads);
+    if (nsplit > 32) nsplit = 32;
+    if (nsplit < 1) nsplit = 1;
+    ctx->attn_nsplit = nsplit;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->x), B * d.dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->q), B * d.dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->k), B * ctx->kv_dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->v), B * ctx->kv_dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->xb), B * d.dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb), B * d.hidden * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->logits), B * d.vocab * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_tokens), B * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_positions), B * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_slots), B * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_out), B * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_active), B))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_partial),
+                    attention_partial_floats(int(B), d.heads, nsplit, d.head_dim) * 4)))
+        return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_count), B * d.kv_heads * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_val), B * ctx->sm_count * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_idx), B * ctx->sm_count * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_count), B * 4))) return rc;
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->att_count, 0, B * d.kv_heads * 4, ctx->stream));
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->amax_count, 0, B * 4, ctx->stream));
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->d_active, 0, B, ctx->stream));
+    if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
+    ctx->h_stage = nullptr;
+    JL_CUDA(ctx, cudaMallocHost(reinterpret_cast<void **>(&ctx->h_stage), (5 * B + 1) * 4));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->counters.workspace_bytes = ws;
+    ctx->finalized = true;
+    return JL_OK;
+}
+
+int32_t jl_kv_create(jl_ctx *ctx, int32_t total_blocks, int32_t blocks_per_slot, int32_t max_slots,
+                     int32_t block_size_tokens, int32_t fp16_key_value) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->has_model, JL_ERR_STATE, "jl_model_create must come first");
+    // runtime/kv/KvStorageRequest.java:5-12: every pool dimension must be positive.
+    JL_REQUIRE(ctx, total_blocks > 0 && blocks_per_slot > 0 && max_slots > 0 && block_size_tokens > 0,
+               JL_ERR_INVALID,
+               "every key/value pool dimension must be positive, got totalBlocks=%d blocksPerSlot=%d "
+               "maxSlots=%d blockSizeTokens=%d",
+               total_blocks, blocks_per_slot, max_slots, block_size_tokens);
+    JL_REQUIRE(ctx, fp16_key_value != 0, JL_ERR_UNSUPPORTED, "fp32 key/value pages; the pool is fp16");
+    cudaSetDevice(ctx->device);
+    free_kv(ctx);
+    const jl_model_desc &d = ctx->desc;
+    // One block beyond the leasable range is the scratch block for UNMAPPED entries.
+    const size_t elems = size_t(total_blocks + 1) * d.layers * block_size_tokens * ctx->kv_dim;
+    int rc;
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->kpool), elems * 2))) return rc;
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->vpool), elems * 2))) {
+        free_kv(ctx);
+        return rc;
+    }
+    const size_t entries = size_t(max_slots) * blocks_per_slot;
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->block_table), entries * 4))) {
+        free_kv(ctx);
+        return rc;
+    }
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->kpool, 0, elems * 2, ctx->stream));
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->vpool, 0, elems * 2, ctx->stream));
+    ctx->total_blocks = total_blocks;
+    ctx->blocks_per_slot = blocks_per_slot;
+    ctx->max_slots = max_slots;
+    ctx->block_tokens = block_size_tokens;
+    ctx->host_table.assign(entries, total_blocks);  // everything unmapped -> scratch
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->block_table, ctx->host_table.data(), entries * 4,
+                                 cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->counters.kv_bytes = elems * 4 + entries * 4;
+    ctx->has_kv = true;
+    return JL_OK;
+}
+
+int32_t jl_kv_publish_block_table(jl_ctx *ctx, const int32_t *table, int64_t n) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->has_kv, JL_ERR_STATE, "this KV store is closed");
+    const int64_t entries = int64_t(ctx->max_slots) * ctx->blocks_per_slot;
+    JL_REQUIRE(ctx, table != nullptr && n == entries, JL_ERR_INVALID,
+               "block table shape changed: manager has %lld entries, the device mirror has %lld",
+               (long long)n, (long long)entries);
+    for (int64_t i = 0; i < n; ++i) {
+        const int32_t entry = table[i];
+        JL_REQUIRE(ctx, entry >= -1 && entry < ctx->total_blocks, JL_ERR_INVALID,
+                   "block table entry %lld = %d is outside the pool of %d blocks", (long long)i, entry,
+                   ctx->total_blocks);
+        ctx->host_table[i] = entry < 0 ? ctx->total_blocks : entry;  // UNMAPPED -> scratch block
+    }
+    cudaSetDevice(ctx->device);
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->block_table, ctx->host_table.data(), n * 4,
+                                 cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->counters.h2d_bytes += n * 4;
+    return JL_OK;
+}
+
+int64_t jl_kv_bytes_per_block(jl_ctx *ctx) {
+    if (!ctx || !ctx->has_kv) return 0;
+    return 2LL * ctx->kv_dim * ctx->block_tokens * ctx->desc.layers * 2LL;
+}
+
+int32_t jl_kv_read_row(jl_ctx *ctx, int32_t which, int32_t slot, int32_t layer, int32_t pos,
+                       uint16_t *out_halfs) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->has_kv, JL_ERR_STATE, "this KV store is closed");
+    JL_REQUIRE(ctx, out_halfs && slot >= 0 && slot < ctx->max_slots && layer >= 0 &&
+                        layer < ctx->desc.layers && pos >= 0 &&
+                        pos < ctx->blocks_per_slot * ctx->block_tokens,
+               JL_ERR_INVALID, "slot/layer/pos out of range");
+    const int64_t phys = ctx->host_table[size_t(slot) * ctx->blocks_per_slot + pos / ctx->block_tokens];
+    const int64_t off = phys * (int64_t(ctx->desc.layers) * ctx->block_tokens * ctx->kv_dim) +
+                        int64_t(layer) * ctx->block_tokens * ctx->kv_dim +
+                        int64_t(pos % ctx->block_tokens) * ctx->kv_dim;
+    cudaSetDevice(ctx->device);
+    const __half *pool = which == 0 ? ctx->kpool : ctx->vpool;
+    JL_CUDA(ctx, cudaMemcpyAsync(out_halfs, pool + off, size_t(ctx->kv_dim) * 2, cudaMemcpyDeviceToHost,
+                                 ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return JL_OK;
+}
+
+static int validate_rows(jl_ctx *ctx, int width, const int32_t *tokens, const int32_t *positions,
+                         const int32_t *kv_slots, const uint8_t *active) {
+    const jl_model_desc &d = ctx->desc;
+    const int capacity = ctx->blocks_per_slot * ctx->block_tokens;
+    for (int b = 0; b < width; ++b) {
+        if (active && !active[b]) continue;
+        JL_REQUIRE(ctx, tokens[b] >= 0 && tokens[b] < d.vocab, JL_ERR_INVALID,
+                   "row %d: token %d outside vocabulary of %d", b, tokens[b], d.vocab);
+        JL_REQUIRE(ctx, positions[b] >= 0 && positions[b] < d.ctx_len && positions[b] < capacity,
+                   JL_ERR_INVALID, "row %d: position %d outside context %d / slot capacity %d", b,
+                   positions[b], d.ctx_len, capacity);
+        JL_REQUIRE(ctx, kv_slots[b] >= 0 && kv_slots[b] < ctx->max_slots, JL_ERR_INVALID,
+                   "row %d: kv slot %d outside 0..%d", b, kv_slots[b], ctx->max_slots - 1);
+        for (int c = b + 1; c < width; ++c)
+            JL_REQUIRE(ctx, (active && !active[c]) || kv_slots[c] != kv_slots[b], JL_ERR_INVALID,
+                       "rows %d and %d share kv slot %d in one step", b, c, kv_slots[b]);
+    }
+    return JL_OK;
+}
+
+int32_t jl_decode(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32_t *positions,
+                  const int32_t *kv_slots, const uint8_t *active, int32_t *out_tokens,
+                  float *out_logits) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->finalized, JL_ERR_STATE, "jl_model_finalize must come first");
+    JL_REQUIRE(ctx, ctx->has_kv, JL_ERR_STATE, "jl_kv_create must come first");
+    JL_REQUIRE(ctx, width >= 1 && width <= ctx->desc.max_batch, JL_ERR_INVALID,
+               "a batch is fixed width: got %d, this context was sized for 1..%d", width,
+               ctx->desc.max_batch);
+    JL_REQUIRE(ctx, tokens && positions && kv_slots && out_tokens, JL_ERR_INVALID,
+               "tokens, positions, kv_slots and out_tokens must not be NULL");
+    int rc = validate_rows(ctx, width, tokens, positions, kv_slots, active);
+    if (rc) return rc;
+    cudaSetDevice(ctx->device);
+    const size_t B = ctx->desc.max_batch;
+    int32_t *h_tok = ctx->h_stage, *h_pos = h_tok + B, *h_slot = h_pos + B, *h_out = h_slot + B;
+    uint8_t *h_act = reinterpret_cast<uint8_t *>(h_out + B);
+    int32_t *h_status = ctx->h_stage + 5 * B;
+    for (int b = 0; b < width; ++b) {
+        const bool on = !active || active[b];
+        h_tok[b] = on ? tokens[b] : 0;
+        h_pos[b] = on ? positions[b] : 0;
+        h_slot[b] = on ? kv_slots[b] : 0;
+        h_act[b] = on ? 1 : 0;
+    }
+    JL_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_tokens, h_tok, width * 4, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_positions, h_pos, width * 4, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_slots, h_slot, width * 4, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_active, h_act, width, cudaMemcpyHostToDevice, ctx->stream));
+    if ((rc = run_step(ctx, width, true, false))) return rc;
+    JL_CUDA(ctx, cudaMemcpyAsync(h_out, ctx->d_out, width * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(h_status, ctx->d_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (out_logits)
+        JL_CUDA(ctx, cudaMemcpyAsync(out_logits, ctx->logits, size_t(width) * ctx->desc.vocab * 4,
+                                     cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if ((rc = check_status(ctx))) return rc;
+    for (int b = 0; b < width; ++b) out_tokens[b] = h_act[b] ? h_out[b] : -1;
+    cudaEventElapsedTime(&ctx->counters.last_step_ms, ctx->ev0, ctx->ev1);
+    ctx->counters.decode_calls++;
+    ctx->counters.h2d_bytes += width * 13;
+    ctx->counters.d2h_bytes += width * 4 + 4 + (out_logits ? size_t(width) * ctx->desc.vocab * 4 : 0);
+    return JL_OK;
+}
+
+int32_t jl_prefill(jl_ctx *ctx, int32_t kv_slot, const int32_t *tokens, int32_t start_pos, int32_t n) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->finalized, JL_ERR_STATE, "jl_model_finalize must come first");
+    JL_REQUIRE(ctx, ctx->has_kv, JL_ERR_STATE, "jl_kv_create must come first");
+    JL_REQUIRE(ctx, tokens != nullptr && n >= 0 && start_pos >= 0, JL_ERR_INVALID,
+               "tokens must not be NULL, n and start_pos must not be negative");
+    if (n == 0) return JL_OK;
+    cudaSetDevice(ctx->device);
+    const size_t B = ctx->desc.max_batch;
+    int32_t *h_tok = ctx->h_stage, *h_pos = h_tok + B, *h_slot = h_pos + B, *h_out = h_slot + B;
+    uint8_t *h_act = reinterpret_cast<uint8_t *>(h_out + B);
+    int32_t *h_status = ctx->h_stage + 5 * B;
+    JL_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+    // Token-at-a-time through the decode kernels without the vocabulary projection; the values
+    // are those of batchForwardJavaPrefill, which is the per-token layer stack row by row.
+    for (int i = 0; i < n; ++i) {
+        const int32_t one_tok = tokens[i], one_pos = start_pos + i;
+        const uint8_t on = 1;
+        int rc = validate_rows(ctx, 1, &one_tok, &one_pos, &kv_slot, &on);
+        if (rc) return rc;
+        h_tok[0] = one_tok;
+        h_pos[0] = one_pos;
+        h_slot[0] = kv_slot;
+        h_act[0] = 1;
+        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_tokens, h_tok, 4, cudaMemcpyHostToDevice, ctx->stream));
+        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_positions, h_pos, 4, cudaMemcpyHostToDevice, ctx->stream));
+        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_slots, h_slot, 4, cudaMemcpyHostToDevice, ctx->stream));
+        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_active, h_act, 1, cudaMemcpyHostToDevice, ctx->stream));
+        if ((rc = run_step(ctx, 1, false, false))) return rc;
+        // The staging words are reused by the next token's copies.
+        JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    JL_CUDA(ctx, cudaMemcpyAsync(h_status, ctx->d_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    int rc = check_status(ctx);
+    if (rc) return rc;
+    cudaEventElapsedTime(&ctx->counters.last_step_ms, ctx->ev0, ctx->ev1);
+    ctx->counters.prefill_calls++;
+    ctx->counters.h2d_bytes += size_t(n) * 13;
+    return JL_OK;
+}
+
+int32_t jl_generate(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32_t *positions,
+                    const int32_t *kv_slots, const uint8_t *active, int32_t n_steps,
+                    int32_t *out_history) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->finalized, JL_ERR_STATE, "jl_model_finalize must come first");
+    JL_REQUIRE(ctx, ctx->has_kv, JL_ERR_STATE, "jl_kv_create must come first");
+    JL_REQUIRE(ctx, width >= 1 && width <= ctx->desc.max_batch, JL_ERR_INVALID,
+               "a batch is fixed width: got %d, this context was sized for 1..%d", width,
+               ctx->desc.max_batch);
+    JL_REQUIRE(ctx, tokens && positions && kv_slots && out_history && n_steps >= 0, JL_ERR_INVALID,
+               "NULL argument or negative step count");
+    if (n_steps == 0) return JL_OK;
+    int rc = validate_rows(ctx, width, tokens, positions, kv_slots, active);
+    if (rc) return rc;
+    const int capacity = ctx->blocks_per_slot * ctx->block_tokens;
+    for (int b = 0; b < width; ++b) {
+        if (active && !active[b]) continue;
+        const int last = positions[b] + n_steps - 1;
+        JL_REQUIRE(ctx, last < ctx->desc.ctx_len && last < capacity, JL_ERR_INVALID,
+                   "row %d: %d steps from position %d run past context %d / slot capacity %d", b,
+                   n_steps, positions[b], ctx->desc.ctx_len, capacity);
+    }
+    cudaSetDevice(ctx->device);
+    const size_t need = size_t(n_steps) * width;
+    if (need > ctx->history_cap) {
+        drop_graphs(ctx);  // captured graphs hold the old history pointer
+        if (ctx->d_history) cudaFree(ctx->d_history);
+        ctx->d_history = nullptr;
+        ctx->history_cap = 0;
+        if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_history), need * 4))) return rc;
+        ctx->history_cap = need;
+    }
+    if (!ctx->d_step && (rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_step), 4))) return rc;
+    const size_t B = ctx->desc.max_batch;
+    int32_t *h_tok = ctx->h_stage, *h_pos = h_tok + B, *h_slot = h_pos + B, *h_out = h_slot + B;
+    uint8_t *h_act = reinterpret_cast<uint8_t *>(h_out + B);
+    int32_t *h_status = ctx->h_stage + 5 * B;
+    for (int b = 0; b < width; ++b) {
+        const bool on = !active || active[b];
+        h_tok[b] = on ? tokens[b] : 0;
+        h_pos[b] = on ? positions[b] : 0;
+        h_slot[b] = on ? kv_slots[b] : 0;
+        h_act[b] = on ? 1 : 0;
+    }
+    JL_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_tokens, h_tok, width * 4, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_positions, h_pos, width * 4, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_slots, h_slot, width * 4, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_active, h_act, width, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->d_step, 0, 4, ctx->stream));
+    for (int s = 0; s < n_steps; ++s)
+        if ((rc = run_step(ctx, width, true, true))) return rc;
+    JL_CUDA(ctx, cudaMemcpyAsync(out_history, ctx->d_history, need * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(h_status, ctx->d_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if ((rc = check_status(ctx))) return rc;
+    cudaEventElapsedTime(&ctx->counters.last_step_ms, ctx->ev0, ctx->ev1);
+    ctx->counters.decode_calls += n_steps;
+    ctx->counters.h2d_bytes += width * 13;
+    ctx->counters.d2h_bytes += need * 4 + 4;
+    return JL_OK;
+}
+
+int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->finalized, JL_ERR_STATE, "jl_model_finalize must come first");
+    JL_REQUIRE(ctx, op >= 0 && op <= 4 && iters >= 0 && first_layer >= 0, JL_ERR_INVALID,
+               "op must be 0..4 (qkv, attn-out, gate/up, down, vocabulary)");
+    cudaSetDevice(ctx->device);
+    const jl_model_desc &d = ctx->desc;
+    uint64_t launches = 0;
+    for (int i = 0; i < iters; ++i) {
+        const int l = (first_layer + i) % d.layers;
+        GemvArgs a = {};
+        a.cols = d.dim;
+        a.mode = kGemvPlain;
+        a.eps = d.rms_eps;
+        int total = 0;
+        if (op == 0) {
+            const DevTensor &wq = ctx->layer[JL_ROLE_ATTENTION_QUERY][l];
+            const DevTensor &wk = ctx->layer[JL_ROLE_ATTENTION_KEY][l];
+            const DevTensor &wv = ctx->layer[JL_ROLE_ATTENTION_VALUE][l];
+            a.nseg = 3;
+            a.seg[0] = {wq.data, ctx->q, nullptr, int(wq.rows)};
+            a.seg[1] = {wk.data, ctx->k, nullptr, int(wk.rows)};
+            a.seg[2] = {wv.data, ctx->v, nullptr, int(wv.rows)};
+            a.type = wq.type;
+            a.x = ctx->x;
+            a.norm_w = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
+            total = int(wq.rows + wk.rows + wv.rows);
+        } else if (op == 1) {
+            const DevTensor &wo = ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l];
+            a.nseg = 1;
+            a.seg[0] = {wo.data, ctx->q, nullptr, int(wo.rows)};
+            a.type = wo.type;
+            a.x = ctx->xb;
+            total = int(wo.rows);
+        } else if (op == 2) {
+            const DevTensor &w1 = ctx->layer[JL_ROLE_FFN_GATE][l];
+            const DevTensor &w3 = ctx->layer[JL_ROLE_FFN_UP][l];
+            a.nseg = 2;
+            a.seg[0] = {w1.data, ctx->hb, nullptr, int(w1.rows)};
+            a.seg[1] = {w3.data, nullptr, nullptr, int(w3.rows)};
+            a.type = w1.type;
+            a.mode = kGemvGateUp;
+            a.x = ctx->x;
+            a.norm_w = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
+            total = int(w1.rows + w3.rows);
+        } else if (op == 3) {
+            const DevTensor &w2 = ctx->layer[JL_ROLE_FFN_DOWN][l];
+            a.nseg = 1;
+            a.seg[0] = {w2.data, ctx->q, nullptr, int(w2.rows)};
+            a.cols = int(w2.cols);
+            a.type = w2.type;
+            a.x = ctx->hb;
+            total = int(w2.rows);
+        } else {
+            const DevTensor &wc = wcls_of(ctx);
+            a.nseg = 1;
+            a.seg[0] = {wc.data, ctx->logits, nullptr, int(wc.rows)};
+            a.type = wc.type;
+            a.x = ctx->x;
+            a.norm_w = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
+            total = int(wc.rows);
+        }
+        int rc = launch_gemv(ctx, a, total, &launches);
+        if (rc) return rc;
+    }
+    ctx->counters.kernel_launches += launches;
+    return JL_OK;
+}
+
+int32_t jl_debug_read(jl_ctx *ctx, const char *name, int32_t row, float *out, int64_t n) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->finalized, JL_ERR_STATE, "jl_model_finalize must come first");
+    JL_REQUIRE(ctx, name && out && row >= 0 && row < ctx->desc.max_batch, JL_ERR_INVALID,
+               "bad name, out or row");
+    const jl_model_desc &d = ctx->desc;
+    const float *src = nullptr;
+    int64_t width = 0;
+    if (!strcmp(name, "x")) { src = ctx->x; width = d.dim; }
+    else if (!strcmp(name, "q")) { src = ctx->q; width = d.dim; }
+    else if (!strcmp(name, "k")) { src = ctx->k; width = ctx->kv_dim; }
+    else if (!strcmp(name, "v")) { src = ctx->v; width = ctx->kv_dim; }
+    else if (!strcmp(name, "xb")) { src = ctx->xb; width = d.dim; }
+    else if (!strcmp(name, "hb")) { src = ctx->hb; width = d.hidden; }
+    else if (!strcmp(name, "logits")) { src = ctx->logits; width = d.vocab; }
+    JL_REQUIRE(ctx, src != nullptr, JL_ERR_INVALID, "unknown buffer '%s'", name);
+    JL_REQUIRE(ctx, n >= 0 && n <= width, JL_ERR_INVALID, "buffer '%s' has %lld floats per row", name,
+               (long long)width);
+    cudaSetDevice(ctx->device);
+    JL_CUDA(ctx, cudaMemcpyAsync(out, src + size_t(row) * width, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return JL_OK;
+}
+
+// ---- standalone operators ---------------------------------------------------------------------
+
+int32_t jl_dequant(jl_ctx *ctx, int32_t ggml_type, const void *blocks, int64_t n_elements, float *out) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, n_elements >= 0, JL_ERR_INVALID, "n_elements must not be negative");
+    if (n_elements == 0) return JL_OK;
+    JL_REQUIRE(ctx, blocks && out, JL_ERR_INVALID, "blocks and out must not be NULL");
+    JL_REQUIRE(ctx, is_quant(ggml_type), JL_ERR_UNSUPPORTED, "GGML type %d", ggml_type);
+    const int blk = ggml_type == kQ4_K ? 256 : 32;
+    JL_REQUIRE(ctx, n_elements % blk == 0, JL_ERR_INVALID,
+               "n_elements (%lld) must be a whole number of %d-element blocks", (long long)n_elements, blk);
+    cudaSetDevice(ctx->device);
+    const size_t in_bytes = size_t(n_elements / blk) * (ggml_type == kQ4_K ? 144 : ggml_type == kQ8_0 ? 34 : 18);
+    void *d_in = nullptr, *d_out = nullptr;
+    int rc;
+    if ((rc = dev_alloc(ctx, &d_in, in_bytes))) return rc;
+    if ((rc = dev_alloc(ctx, &d_out, size_t(n_elements) * 4))) {
+        cudaFree(d_in);
+        return rc;
+    }
+    cudaError_t e = cudaMemcpyAsync(d_in, blocks, in_bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess)
+        e = dequant_launch(ggml_type, static_cast<uint8_t *>(d_in), n_elements,
+                           static_cast<float *>(d_out), ctx->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(out, d_out, size_t(n_elements) * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(d_in);
+    cudaFree(d_out);
+    if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "dequant failed: %s", cudaGetErrorString(e));
+    ctx->counters.kernel_launches++;
+    ctx->counters.h2d_bytes += in_bytes;
+    ctx->counters.d2h_bytes += size_t(n_elements) * 4;
+    return JL_OK;
+}
+
+int32_t jl_tensor_upload(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t cols,
+                         const void *host_bytes, size_t nbytes, jl_tensor **out) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, out != nullptr && host_bytes != nullptr, JL_ERR_INVALID, "NULL argument");
+    *out = nullptr;
+    JL_REQUIRE(ctx, is_quant(ggml_type), JL_ERR_UNSUPPORTED, "GGML type %d", ggml_type);
+    int rc = check_shape(ctx, ggml_type, rows, cols, nbytes);
+    if (rc) return rc;
+    JL_REQUIRE(ctx, rows <= INT32_MAX && cols <= INT32_MAX, JL_ERR_UNSUPPORTED, "matrix too large");
+    cudaSetDevice(ctx->device);
+    jl_tensor *t = new jl_tensor();
+    rc = upload(ctx, &t->t, ggml_type, rows, cols, host_bytes, nbytes);
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    *out = t;
+    return JL_OK;
+}
+
+int32_t jl_tensor_free(jl_ctx *ctx, jl_tensor *t) {
+    if (!ctx || !t) return JL_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (t->t.data) {
+        cudaFree(t->t.data);
+        ctx->counters.weight_bytes -= t->t.bytes;
+    }
+    delete t;
+    return JL_OK;
+}
+
+int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t n, float *y_dev) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, w && x_dev && y_dev, JL_ERR_INVALID, "NULL argument");
+    JL_REQUIRE(ctx, n >= 0, JL_ERR_INVALID, "n must not be negative");
+    cudaSetDevice(ctx->device);
+    uint64_t launches = 0;
+    for (int b = 0; b < n; ++b) {
+        GemvArgs a = {};
+        a.nseg = 1;
+        a.seg[0] = {w->t.data, y_dev + size_t(b) * w->t.rows, nullptr, int(w->t.rows)};
+        a.cols = int(w->t.cols);
+        a.type = w->t.type;
+        a.mode = kGemvPlain;
+        a.x = x_dev + size_t(b) * w->t.cols;
+        int rc = launch_gemv(ctx, a, int(w->t.rows), &launches);
+        if (rc) return rc;
+    }
+    ctx->counters.kernel_launches += launches;
+    return JL_OK;
+}
+
+int32_t jl_gemv(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t cols, const void *w_host,
+                const float *x_host, int32_t n, float *y_host) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, w_host && x_host && y_host, JL_ERR_INVALID, "NULL argument");
+    JL_REQUIRE(ctx, n >= 0, JL_ERR_INVALID, "n must not be negative");
+    JL_REQUIRE(ctx, is_quant(ggml_type), JL_ERR_UNSUPPORTED, "GGML type %d", ggml_type);
+    JL_REQUIRE(ctx, rows > 0 && cols > 0 && cols % 256 == 0, JL_ERR_UNSUPPORTED,
+               "rows must be positive and cols a positive multiple of 256");
+    if (n == 0) return JL_OK;
+    jl_tensor *t = nullptr;
+    int rc = jl_tensor_upload(ctx, ggml_type, rows, cols, w_host, size_t(rows * row_bytes(ggml_type, cols)), &t);
+    if (rc) return rc;
+    void *dx = nullptr, *dy = nullptr;
+    if ((rc = dev_alloc(ctx, &dx, size_t(n) * cols * 4)) || (rc = dev_alloc(ctx, &dy, size_t(n) * rows * 4))) {
+        if (dx) cudaFree(dx);
+        jl_tensor_free(ctx, t);
+        return rc;
+    }
+    cudaError_t e = cudaMemcpyAsync(dx, x_host, size_t(n) * cols * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) {
+        rc = jl_gemv_dev(ctx, t, static_cast<float *>(dx), n, static_cast<float *>(dy));
+        if (!rc) e = cudaMemcpyAsync(y_host, dy, size_t(n) * rows * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    }
+    int32_t status = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&status, ctx->d_status, 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(dx);
+    cudaFree(dy);
+    jl_tensor_free(ctx, t);
+    if (rc) return rc;
+    if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-vector product failed: %s", cudaGetErrorString(e));
+    if (status == kDevTimeout) {
+        cudaMemset(ctx->d_status, 0, 4);
+        return fail(ctx, JL_ERR_TIMEOUT, "a kernel gave up waiting for an asynchronous copy");
+    }
+    ctx->counters.h2d_bytes += size_t(n) * cols * 4;
+    ctx->counters.d2h_bytes += size_t(n) * rows * 4;
+    return JL_OK;
+}
+
+// ---- plumbing ---------------------------------------------------------------------------------
+
+void *jl_device_alloc(jl_ctx *ctx, size_t nbytes) {
+    if (!ctx) return nullptr;
+    cudaSetDevice(ctx->device);
+    void *p = nullptr;
+    if (dev_alloc(ctx, &p, nbytes)) return nullptr;
+    ctx->user_allocs.push_back(p);
+    return p;
+}
+
+int32_t jl_device_free(jl_ctx *ctx, void *p) {
+    if (!ctx || !p) return JL_OK;
+    cudaSetDevice(ctx->device);
+    for (size_t i = 0; i < ctx->user_allocs.size(); ++i)
+        if (ctx->user_allocs[i] == p) {
+            cudaStreamSynchronize(ctx->stream);
+            cudaFree(p);
+            ctx->user_allocs.erase(ctx->user_allocs.begin() + i);
+            return JL_OK;
+        }
+    return fail(ctx, JL_ERR_INVALID, "pointer was not allocated by jl_device_alloc");
+}
+
+int32_t jl_memcpy_h2d(jl_ctx *ctx, void *dst_dev, const void *src_host, size_t nbytes) {
+    if (!ctx) return JL_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    JL_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->counters.h2d_bytes += nbytes;
+    return JL_OK;
+}
+
+int32_t jl_memcpy_d2h(jl_ctx *ctx, void *dst_host, const void *src_dev, size_t nbytes) {
+    if (!ctx) return JL_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    JL_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->counters.d2h_bytes += nbytes;
+    return JL_OK;
+}
+
+int32_t jl_synchronize(jl_ctx *ctx) {
+    if (!ctx) return JL_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return JL_OK;
+}
+
+void *jl_stream(jl_ctx *ctx) { return ctx ? static_cast<void *>(ctx->stream) : nullptr; }
+
+int32_t jl_timer_start(jl_ctx *ctx) {
+    if (!ctx) return JL_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    JL_CUDA(ctx, cudaEventRecord(ctx->tev0, ctx->stream));
+    return JL_OK;
+}
+
+int32_t jl_timer_stop(jl_ctx *ctx, float *elapsed_ms) {
+    if (!ctx || !elapsed_ms) return JL_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    JL_CUDA(ctx, cudaEventRecord(ctx->tev1, ctx->stream));
+    JL_CUDA(ctx, cudaEventSynchronize(ctx->tev1));
+    JL_CUDA(ctx, cudaEventElapsedTime(elapsed_ms, ctx->tev0, ctx->tev1));
+    return JL_OK;
+}
+
+int32_t jl_get_counters(jl_ctx *ctx, jl_counters *out) {
+    if (!ctx || !out) return JL_ERR_INVALID;
+    *out = ctx->counters;
+    return JL_OK;
+}
+
+int32_t jl_flush_l2(jl_ctx *ctx) {
+    if (!ctx) return JL_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    if (!ctx->flush_buf) {
+        ctx->flush_words = size_t(256) * 1024 * 1024 / 4;  // 256 MiB > 126 MB of L2
+        int rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->flush_buf), ctx->flush_words * 4);
+        if (rc) return rc;
+    }
+    JL_CUDA(ctx, fill_launch(ctx->flush_buf, ctx->flush_words, 0u, ctx->stream));
+    return JL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,81 @@
+// GGUF block formats kept in their on-disk layout (format/GGMLType.java:7,13,18-20 of the
+// reference): geometry constants and element-exact device decoders.
+#pragma once
+
+#include "common.cuh"
+
+namespace jl {
+
+enum : int { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ8_0 = 8, kQ4_K = 12 };
+
+constexpr int kQ8_0Block = 32, kQ8_0Bytes = 34;
+constexpr int kQ4_0Block = 32, kQ4_0Bytes = 18;
+constexpr int kQ4_KBlock = 256, kQ4_KBytes = 144;
+
+// Every format packs 256 consecutive elements into a 16-byte-aligned group:
+// Q4_K 144 B (one super-block), Q4_0 8 x 18 = 144 B, Q8_0 8 x 34 = 272 B.
+__host__ __device__ inline int64_t row_bytes(int type, int64_t cols) {
+    switch (type) {
+        case kF32: return cols * 4;
+        case kF16: return cols * 2;
+        case kQ8_0: return cols / kQ8_0Block * kQ8_0Bytes;
+        case kQ4_0: return cols / kQ4_0Block * kQ4_0Bytes;
+        case kQ4_K: return cols / kQ4_KBlock * kQ4_KBytes;
+        default: return -1;
+    }
+}
+__host__ __device__ inline bool is_quant(int type) {
+    return type == kQ8_0 || type == kQ4_0 || type == kQ4_K;
+}
+
+__device__ __forceinline__ float f16_at(const uint8_t *p) {
+    return half_bits_to_float(uint32_t(p[0]) | (uint32_t(p[1]) << 8));
+}
+
+// Element-exact decoders: the same binary32 operations in the same order as the reference's
+// FloatTensor.getFloat, with explicit round-to-nearest intrinsics so nothing is contracted to FMA.
+// tensor/standard/Q8_0FloatTensor.java:53-61
+__device__ __forceinline__ float decode_q8_0(const uint8_t *data, int64_t index) {
+    const uint8_t *blk = data + (index / kQ8_0Block) * kQ8_0Bytes;
+    int q = static_cast<int8_t>(blk[2 + index % kQ8_0Block]);
+    return __fmul_rn(static_cast<float>(q), f16_at(blk));
+}
+// tensor/standard/Q4_0FloatTensor.java:56-79
+__device__ __forceinline__ float decode_q4_0(const uint8_t *data, int64_t index) {
+    const uint8_t *blk = data + (index / kQ4_0Block) * kQ4_0Bytes;
+    int w = static_cast<int>(index % kQ4_0Block);
+    int q = w < 16 ? (blk[2 + w] & 0x0F) : (blk[2 + w - 16] >> 4);
+    return __fmul_rn(static_cast<float>(q - 8), f16_at(blk));
+}
+// tensor/standard/Q4_KFloatTensor.java:68-122: ((d * sc) * q) - (dmin * m)
+__device__ __forceinline__ float decode_q4_k(const uint8_t *data, int64_t index) {
+    const uint8_t *blk = data + (index / kQ4_KBlock) * kQ4_KBytes;
+    int within = static_cast<int>(index % kQ4_KBlock);
+    float d = f16_at(blk), dmin = f16_at(blk + 2);
+    const uint8_t *s = blk + 4, *qs = blk + 16;
+    int pair = within >> 6, pos = within & 63;
+    int sub = pair * 2 + (pos >> 5);
+    int byte = qs[pair * 32 + (pos & 31)];
+    int q = (pos < 32) ? (byte & 0xF) : (byte >> 4);
+    int sc, m;
+    if (sub < 4) {
+        sc = s[sub] & 63;
+        m = s[sub + 4] & 63;
+    } else {
+        sc = (s[sub + 4] & 0xF) | ((s[sub - 4] >> 6) << 4);
+        m = (s[sub + 4] >> 4) | ((s[sub] >> 6) << 4);
+    }
+    float t = __fmul_rn(__fmul_rn(d, static_cast<float>(sc)), static_cast<float>(q));
+    return __fsub_rn(t, __fmul_rn(dmin, static_cast<float>(m)));
+}
+__device__ __forceinline__ float decode_any(int type, const uint8_t *data, int64_t index) {
+    switch (type) {
+        case kQ8_0: return decode_q8_0(data, index);
+        case kQ4_0: return decode_q4_0(data, index);
+        case kQ4_K: return decode_q4_k(data, index);
+        case kF16: return __half2float(reinterpret_cast<const __half *>(data)[index]);
+        default: return reinterpret_cast<const float *>(data)[index];
+    }
+}
+
+}  // namespace jl

@@ -1,0 +1,317 @@
+// Per-layer kernels around the matrix products (see ops.cuh).
+#include "ops.cuh"
+
+namespace jl {
+
+namespace {
+
+// ---- embedding -------------------------------------------------------------------------------
+__global__ void embedding_kernel(int type, const uint8_t *table, const int32_t *tokens,
+                                 const uint8_t *active, float *x, int dim) {
+    const int row = blockIdx.x;
+    const bool on = active == nullptr || active[row] != 0;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (!on) return;
+    const int token = tokens[row];
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        x[size_t(row) * dim + i] = decode_any(type, table, int64_t(token) * dim + i);
+}
+
+// ---- dequant ---------------------------------------------------------------------------------
+__global__ void dequant_kernel(int type, const uint8_t *blocks, int64_t n, float *out) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = decode_any(type, blocks, i);
+}
+
+__global__ void fill_kernel(uint32_t *buf, size_t words, uint32_t value) {
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += stride)
+        buf[i] = value;
+}
+
+__global__ void advance_kernel(int32_t *tokens, int32_t *positions, const int32_t *sampled,
+                               const uint8_t *active, int32_t *history, int32_t *step_counter,
+                               int width) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int b = threadIdx.x;
+    const int step = *step_counter;
+    __syncthreads();
+    if (b < width) {
+        const bool on = active[b] != 0;
+        const int32_t tok = on ? sampled[b] : -1;
+        history[size_t(step) * width + b] = tok;
+        if (on) {
+            tokens[b] = tok;
+            positions[b] += 1;
+        }
+    }
+    if (b == 0) *step_counter = step + 1;
+}
+
+// ---- RoPE + KV append + paged decode attention -------------------------------------------------
+__device__ __forceinline__ int64_t kv_offset(const KvGeom &g, int slot, int pos, int layer) {
+    const int blk = pos / g.block_tokens;
+    const int within = pos - blk * g.block_tokens;
+    const int64_t phys = g.block_table[int64_t(slot) * g.blocks_per_slot + blk];
+    const int64_t block_stride = int64_t(g.layers) * g.block_tokens * g.kv_dim;
+    return phys * block_stride + int64_t(layer) * g.block_tokens * g.kv_dim +
+           int64_t(within) * g.kv_dim;
+}
+
+template <int VEC>
+__device__ __forceinline__ void load_halfs(const __half *p, float (&f)[VEC]) {
+    if constexpr (VEC == 4) {
+        const uint2 u = *reinterpret_cast<const uint2 *>(p);
+        const __half2 a = *reinterpret_cast<const __half2 *>(&u.x);
+        const __half2 b = *reinterpret_cast<const __half2 *>(&u.y);
+        const float2 fa = __half22float2(a), fb = __half22float2(b);
+        f[0] = fa.x; f[1] = fa.y; f[2] = fb.x; f[3] = fb.y;
+    } else {
+        const __half2 a = *reinterpret_cast<const __half2 *>(p);
+        const float2 fa = __half22float2(a);
+        f[0] = fa.x; f[1] = fa.y;
+    }
+}
+
+constexpr int kAttnThreads = 128;
+constexpr int kAttnWarps = kAttnThreads / 32;
+
+// One CTA = (split of the position range, KV head, batch row). The G query heads that share the
+// KV head are processed together so each K/V row is read once. What it computes is
+// CpuOperations.rope + appendKeyValue + attention (inference/op/CpuOperations.java:94-204) with
+// the softmax evaluated online; K and V are rounded to binary16 on append exactly as
+// ArrayHalfFloatTensor.setFloat does (tensor/standard/ArrayHalfFloatTensor.java:33-40).
+template <int HD, int G>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
+    constexpr int VEC = HD / 32;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool on = a.active == nullptr || a.active[b] != 0;
+    const int pos = on ? a.positions[b] : 0;
+    const int slot = on ? a.slots[b] : 0;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (!on) return;
+
+    __shared__ float q_s[G][HD];
+    __shared__ float red[kAttnWarps][G][HD + 2];
+    __shared__ int is_last;
+
+    const float *cr = a.rope_cos + size_t(pos) * (HD / 2);
+    const float *ci = a.rope_sin + size_t(pos) * (HD / 2);
+    for (int idx = tid; idx < G * (HD / 2); idx += kAttnThreads) {
+        const int g = idx / (HD / 2), i = idx - g * (HD / 2);
+        const float *qh = a.q + size_t(b) * a.dim + size_t(kvh * G + g) * HD;
+        const float v0 = qh[2 * i], v1 = qh[2 * i + 1];
+        q_s[g][2 * i] = __fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]));
+        q_s[g][2 * i + 1] = __fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]));
+    }
+    const int n = pos + 1;
+    const int chunk = (n + a.nsplit - 1) / a.nsplit;
+    const int start = split * chunk;
+    const int end = min(n, start + chunk);
+    if (start <= pos && pos < end) {
+        // This CTA owns the new position: rotate k, round k and v to fp16, append to the page.
+        const int64_t off = kv_offset(a.kv, slot, pos, a.layer) + int64_t(kvh) * HD;
+        const float *kh = a.k + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
+        const float *vh = a.v + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
+        for (int i = tid; i < HD / 2; i += kAttnThreads) {
+            const float v0 = kh[2 * i], v1 = kh[2 * i + 1];
+            const float r0 = __fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]));
+            const float r1 = __fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]));
+            a.kv.kpool[off + 2 * i] = __float2half_rn(r0);
+            a.kv.kpool[off + 2 * i + 1] = __float2half_rn(r1);
+            a.kv.vpool[off + 2 * i] = __float2half_rn(vh[2 * i]);
+            a.kv.vpool[off + 2 * i + 1] = __float2half_rn(vh[2 * i + 1]);
+        }
+    }
+    __syncthreads();
+
+    float m[G], l[G], acc[G][VEC], qr[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            acc[g][j] = 0.f;
+            qr[g][j] = q_s[g][lane * VEC + j];
+        }
+    }
+    const float inv_sqrt = 1.0f / sqrtf(static_cast<float>(HD));
+    for (int t = start + warp; t < end; t += kAttnWarps) {
+        const int64_t off = kv_offset(a.kv, slot, t, a.layer) + int64_t(kvh) * HD + lane * VEC;
+        float kf[VEC], vf[VEC];
+        load_halfs<VEC>(a.kv.kpool + off, kf);
+        load_halfs<VEC>(a.kv.vpool + off, vf);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) s += qr[g][j] * kf[j];
+            s = warp_sum(s) * inv_sqrt;
+            const float mn = fmaxf(m[g], s);
+            const float corr = expf(m[g] - mn);
+            const float p = expf(s - mn);
+            l[g] = l[g] * corr + p;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[g][j] = acc[g][j] * corr + p * vf[j];
+            m[g] = mn;
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) red[warp][g][lane * VEC + j] = acc[g][j];
+        if (lane == 0) {
+            red[warp][g][HD] = m[g];
+            red[warp][g][HD + 1] = l[g];
+        }
+    }
+    __syncthreads();
+
+    const size_t pstride = size_t(HD + 2);
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, d = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, red[w][g][HD]);
+        float val = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float mw = red[w][g][HD];
+            const float wgt = (mw == -INFINITY) ? 0.f : expf(mw - M);
+            val += red[w][g][d] * wgt;
+            L += red[w][g][HD + 1] * wgt;
+        }
+        const int h = kvh * G + g;
+        if (a.nsplit == 1) {
+            a.out[size_t(b) * a.dim + size_t(h) * HD + d] = val / L;
+        } else {
+            float *p = a.partial + ((size_t(b) * a.heads + h) * a.nsplit + split) * pstride;
+            p[d] = val;
+            if (d == 0) {
+                p[HD] = M;
+                p[HD + 1] = L;
+            }
+        }
+    }
+    if (a.nsplit == 1) return;
+
+    // The last CTA of this (row, KV head) to finish folds the splits together.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(a.counters + size_t(b) * a.kv_heads + kvh, 1u);
+        is_last = (prev == unsigned(a.nsplit) - 1u);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, d = idx - g * HD;
+        const int h = kvh * G + g;
+        const float *p = a.partial + (size_t(b) * a.heads + h) * a.nsplit * pstride;
+        float M = -INFINITY;
+        for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, __ldcg(p + s * pstride + HD));
+        float val = 0.f, L = 0.f;
+        for (int s = 0; s < a.nsplit; ++s) {
+            const float ms = __ldcg(p + s * pstride + HD);
+            const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M);
+            val += __ldcg(p + s * pstride + d) * wgt;
+            L += __ldcg(p + s * pstride + HD + 1) * wgt;
+        }
+        a.out[size_t(b) * a.dim + size_t(h) * HD + d] = val / L;
+    }
+    if (tid == 0) a.counters[size_t(b) * a.kv_heads + kvh] = 0u;
+}
+
+template <int HD, int G>
+cudaError_t attn_launch_t(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.nsplit, a.kv_heads, width);
+    cfg.blockDim = dim3(kAttnThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, G>, a);
+}
+
+template <int HD>
+cudaError_t attn_launch_hd(const AttnArgs &a, int width, cudaStream_t s, bool pdl) {
+    switch (a.heads / a.kv_heads) {
+        case 1: return attn_launch_t<HD, 1>(a, width, s, pdl);
+        case 2: return attn_launch_t<HD, 2>(a, width, s, pdl);
+        case 4: return attn_launch_t<HD, 4>(a, width, s, pdl);
+        case 8: return attn_launch_t<HD, 8>(a, width, s, pdl);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace
+
+cudaError_t attention_configure() { return cudaSuccess; }
+
+size_t attention_partial_floats(int width, int heads, int nsplit, int head_dim) {
+    return size_t(width) * heads * nsplit * (head_dim + 2);
+}
+
+cudaError_t attention_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
+    if (a.head_dim == 128) return attn_launch_hd<128>(a, width, stream, programmatic);
+    if (a.head_dim == 64) return attn_launch_hd<64>(a, width, stream, programmatic);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t embedding_launch(int type, const uint8_t *table, const int32_t *tokens,
+                             const uint8_t *active, float *x, int dim, int width,
+                             cudaStream_t stream, bool programmatic) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(width);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, embedding_kernel, type, table, tokens, active, x, dim);
+}
+
+cudaError_t dequant_launch(int type, const uint8_t *blocks, int64_t n, float *out,
+                           cudaStream_t stream) {
+    if (n <= 0) return cudaSuccess;
+    int64_t blocks_needed = (n + 255) / 256;
+    int grid = static_cast<int>(blocks_needed < 148 * 16 ? blocks_needed : 148 * 16);
+    dequant_kernel<<<grid, 256, 0, stream>>>(type, blocks, n, out);
+    return cudaGetLastError();
+}
+
+cudaError_t advance_launch(int32_t *tokens, int32_t *positions, const int32_t *sampled,
+                           const uint8_t *active, int32_t *history, int32_t *step_counter, int width,
+                           cudaStream_t stream, bool programmatic) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, advance_kernel, tokens, positions, sampled, active, history,
+                              step_counter, width);
+}
+
+cudaError_t fill_launch(uint32_t *buf, size_t words, uint32_t value, cudaStream_t stream) {
+    fill_kernel<<<148 * 8, 256, 0, stream>>>(buf, words, value);
+    return cudaGetLastError();
+}
+
+}  // namespace jl

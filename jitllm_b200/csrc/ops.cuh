@@ -1,0 +1,52 @@
+// Per-layer kernels around the matrix products: embedding lookup, RoPE + KV page append + paged
+// decode attention, block dequantisation.
+#pragma once
+
+#include "formats.cuh"
+
+namespace jl {
+
+// Geometry of the paged fp16 KV store (backend/tornado/kernels/KvBlockAddress.java:59-71 of the
+// reference): element offset = table[slot*blocks_per_slot + pos/block_tokens] * block_stride
+//   + layer * block_tokens * kv_dim + (pos % block_tokens) * kv_dim + c, 64-bit here.
+struct KvGeom {
+    __half *kpool, *vpool;
+    const int32_t *block_table;
+    int blocks_per_slot, block_tokens, layers, kv_dim;
+};
+
+struct AttnArgs {
+    const float *q, *k, *v;  // [width][dim], [width][kv_dim]: projections before RoPE
+    float *out;              // [width][dim]
+    const float *rope_cos, *rope_sin;  // [ctx][head_dim/2]
+    const int32_t *positions, *slots;
+    const uint8_t *active;
+    KvGeom kv;
+    int layer, heads, kv_heads, head_dim, dim;
+    int nsplit;
+    float *partial;     // scratch [width][heads][nsplit][head_dim + 2]
+    unsigned *counters; // scratch [width][kv_heads], zero between launches
+};
+
+cudaError_t attention_configure();
+cudaError_t attention_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic);
+size_t attention_partial_floats(int width, int heads, int nsplit, int head_dim);
+
+// x[row] = getFloat of embedding row tokens[row] (inference/op/CpuOperations.java:30-32).
+cudaError_t embedding_launch(int type, const uint8_t *table, const int32_t *tokens,
+                             const uint8_t *active, float *x, int dim, int width,
+                             cudaStream_t stream, bool programmatic);
+
+// out[i] = getFloat(i), element-exact.
+cudaError_t dequant_launch(int type, const uint8_t *blocks, int64_t n, float *out,
+                           cudaStream_t stream);
+
+// After a step: feeds each active row's sampled token back as its next input, advances its
+// position and appends the token to history[step][row] (step counter kept on the device).
+cudaError_t advance_launch(int32_t *tokens, int32_t *positions, const int32_t *sampled,
+                           const uint8_t *active, int32_t *history, int32_t *step_counter, int width,
+                           cudaStream_t stream, bool programmatic);
+
+cudaError_t fill_launch(uint32_t *buf, size_t words, uint32_t value, cudaStream_t stream);
+
+}  // namespace jl

@@ -1,0 +1,183 @@
+"""The decode step through the C ABI against the oracle's forwardJava on small synthetic models:
+logits within 1e-2 max-abs (stated bar; ~1e-5 expected), identical greedy tokens, identical KV
+pages up to binary16 rounding of nearly-equal inputs."""
+import numpy as np
+import pytest
+
+import jitllm_b200 as jl
+from jitllm_b200 import GGMLType
+from tests.util import Pair, rel_l2, small_config
+
+pytestmark = pytest.mark.gpu
+FORMATS = [GGMLType.Q8_0, GGMLType.Q4_0, GGMLType.Q4_K]
+LOGIT_BAR = 1e-2
+LOGIT_EXPECT = 2e-4
+
+
+def _half_close(a_bits, b_bits, ulps=1):
+    a = a_bits.view(np.float16).astype(np.float32)
+    b = b_bits.view(np.float16).astype(np.float32)
+    same = a_bits == b_bits
+    # values that differ must be neighbours in binary16
+    tol = np.maximum(np.abs(a), 2.0 ** -14) * 2.0 ** -10 * ulps
+    return bool(np.all(same | (np.abs(a - b) <= tol))), float(np.mean(same))
+
+
+@pytest.mark.parametrize("t", FORMATS)
+@pytest.mark.parametrize("head", [64, 128])
+def test_teacher_forced_logits_and_kv(dev, oracle, t, head):
+    cfg = small_config(layers=2, ctx=64, head=head)
+    p = Pair(dev, oracle, cfg, t, seed=21 + head, std=0.05)
+    tokens = np.random.default_rng(5).integers(0, cfg.vocabularySize, size=40)
+    for pos, tok in enumerate(tokens):
+        want = p.oracle_model.forward(int(tok), pos)
+        res = p.boundary.invoke(int(tok), pos)
+        err = float(np.max(np.abs(res.logits - want)))
+        assert err < LOGIT_BAR and err < LOGIT_EXPECT, (pos, err)
+        assert res.sampledToken == int(np.argmax(want)) == jl.argmax(res.logits)
+        for l in range(cfg.numberOfLayers):
+            ok, frac = _half_close(p.kv.readRow("k", 0, l, pos), p.oracle_model.kcache(l, pos))
+            assert ok and frac > 0.98
+            ok, frac = _half_close(p.kv.readRow("v", 0, l, pos), p.oracle_model.vcache(l, pos))
+            assert ok and frac > 0.98
+    # per-operation buffers of the last step
+    for name, n in (("q", cfg.dim), ("k", cfg.kvDim), ("v", cfg.kvDim), ("hb", cfg.hiddenDim)):
+        if name in ("q", "k"):
+            continue  # the oracle rotates q and k in place; the device keeps them un-rotated
+        assert rel_l2(p.model.debugRead(name), p.oracle_model.buffer(name, n)) < 1e-4
+
+
+@pytest.mark.parametrize("t", FORMATS)
+def test_greedy_tokens_identical(dev, oracle, t):
+    cfg = small_config(layers=3, ctx=96, tied=True)
+    p = Pair(dev, oracle, cfg, t, seed=77, std=0.05)
+    prompt = [int(v) for v in np.random.default_rng(8).integers(0, cfg.vocabularySize, size=8)]
+    cpu, gpu, gaps = [], [], []
+    tok_c = tok_g = None
+    for pos in range(72):
+        feed_c = prompt[pos] if pos < len(prompt) else tok_c
+        feed_g = prompt[pos] if pos < len(prompt) else tok_g
+        logits = p.oracle_model.forward(feed_c, pos)
+        tok_c = int(np.argmax(logits))
+        top2 = np.partition(logits, -2)[-2:]
+        gaps.append(float(top2[1] - top2[0]))
+        tok_g = p.boundary.invoke(feed_g, pos).sampledToken
+        cpu.append(tok_c)
+        gpu.append(tok_g)
+    assert cpu == gpu, f"first divergence at {next(i for i, (a, b) in enumerate(zip(cpu, gpu)) if a != b)}, min top-2 gap {min(gaps):.3g}"
+
+
+def test_paged_block_table_remapping_and_unmapped_entries(dev, oracle):
+    cfg = small_config(layers=2, ctx=64)
+    bps = 4
+    # slot 0 -> physical blocks in scrambled order, slot 1 unmapped (scratch), slot 2 -> the rest
+    table = np.array([5, 2, 7, 0, -1, -1, -1, -1, 1, 3, 4, 6], dtype=np.int32)
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=31, max_batch=1, slots=3, block_table=table, total_blocks=8, std=0.05)
+    toks = np.random.default_rng(2).integers(0, cfg.vocabularySize, size=36)
+    bound = jl.B200InvocationBoundary(p.model, kvSlot=2)
+    for pos, tok in enumerate(toks):
+        want = p.oracle_model.forward(int(tok), pos)
+        got = bound.invoke(int(tok), pos)
+        assert float(np.max(np.abs(got.logits - want))) < LOGIT_EXPECT
+    with pytest.raises(ValueError, match="block table shape changed"):
+        p.kv.publishBlockTable(np.zeros(5, dtype=np.int32))
+    with pytest.raises(ValueError, match="outside the pool"):
+        p.kv.publishBlockTable(np.full(12, 99, dtype=np.int32))
+
+
+def test_batched_decode_matches_independent_sequences(dev, oracle):
+    cfg = small_config(layers=2, ctx=64)
+    width = 4
+    p = Pair(dev, oracle, cfg, GGMLType.Q8_0, seed=41, max_batch=width, std=0.05)
+    seqs = [p.new_oracle_sequence() for _ in range(width)]
+    rng = np.random.default_rng(3)
+    positions = [0, 0, 0, 0]
+    # ragged: rows advance at different rates, one row goes inactive half way
+    for step in range(24):
+        active = [True, step % 2 == 0, step < 10, True]
+        toks = [int(v) for v in rng.integers(0, cfg.vocabularySize, size=width)]
+        out, logits = p.executor.decodeStep(jl.BatchSlots(active, toks, positions, [0, 1, 2, 3]), wantLogits=True)
+        for b in range(width):
+            if not active[b]:
+                assert out[b] == -1
+                continue
+            want = seqs[b].forward(toks[b], positions[b])
+            assert float(np.max(np.abs(logits[b] - want))) < LOGIT_EXPECT
+            assert out[b] == int(np.argmax(want))
+            positions[b] += 1
+    assert p.executor.maxBatchSize() == width
+
+
+def test_prefill_then_decode_equals_token_by_token(dev, oracle):
+    cfg = small_config(layers=2, ctx=64)
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_0, seed=51, std=0.05)
+    prompt = [int(v) for v in np.random.default_rng(4).integers(0, cfg.vocabularySize, size=20)]
+    for pos, tok in enumerate(prompt[:-1]):
+        p.oracle_model.forward_no_logits(tok, pos)
+    want = p.oracle_model.forward(prompt[-1], len(prompt) - 1)
+    p.boundary.prefill(prompt[:-1], 0)
+    got = p.boundary.invoke(prompt[-1], len(prompt) - 1)
+    assert float(np.max(np.abs(got.logits - want))) < LOGIT_EXPECT
+    assert got.sampledToken == int(np.argmax(want))
+
+
+def test_argmax_ties_take_the_first_index(dev, oracle):
+    """All-zero activations cannot happen, but identical embedding rows can: rows 10 and 20 of a
+    tied embedding are made identical, so their logits tie exactly and index 10 must win."""
+    cfg = small_config(layers=1, ctx=32, tied=True, vocab=512)
+    tensors = jl.synth_model_tensors(cfg, GGMLType.Q8_0, seed=61, std=0.05)
+    t, emb = tensors[(jl.TensorRole.TOKEN_EMBEDDING, -1)]
+    rb = cfg.dim // 32 * 34
+    emb = emb.copy()
+    big = jl.quantize(GGMLType.Q8_0, np.full(cfg.dim, 3.0, dtype=np.float32) * np.sign(np.random.default_rng(1).standard_normal(cfg.dim)).astype(np.float32))
+    emb[10 * rb:11 * rb] = big
+    emb[20 * rb:21 * rb] = big
+    tensors[(jl.TensorRole.TOKEN_EMBEDDING, -1)] = (t, emb)
+    om = oracle.Model(cfg, tensors)
+    cr, ci = om.rope_tables()
+    model = jl.load_model(dev, cfg, tensors, cr, ci)
+    kv = model.createKvStorage(jl.KvStorageRequest(2, 2, 1, 16, cfg.numberOfLayers, cfg.kvDim))
+    kv.publishBlockTable(np.arange(2, dtype=np.int32))
+    res = jl.B200InvocationBoundary(model).invoke(10, 0)
+    want = om.forward(10, 0)
+    assert int(np.argmax(want)) == res.sampledToken
+    if want[10] == want[20] == want.max():
+        assert res.sampledToken == 10
+
+
+def test_lifecycle_and_argument_errors(dev, oracle):
+    cfg = small_config(layers=1, ctx=32)
+    model = jl.B200Model(dev, cfg)
+    ex = jl.B200BatchExecutor(model)
+    with pytest.raises(jl.IllegalStateError, match="jl_model_finalize"):
+        ex.decodeStep(jl.BatchSlots([True], [1], [0], [0]))
+    with pytest.raises(jl.IllegalStateError, match="missing"):
+        model.finalize()
+    with pytest.raises(ValueError, match="expects"):
+        dev._check(dev._lib.jl_upload_tensor(dev.handle, 2, 0, 8, 5, 256, np.zeros(5 * 272, dtype=np.uint8).ctypes.data, 5 * 272))
+    p = Pair(dev, oracle, cfg, GGMLType.Q8_0, seed=1)
+    with pytest.raises(ValueError, match="outside vocabulary"):
+        p.executor.decodeStep(jl.BatchSlots([True], [cfg.vocabularySize], [0], [0]))
+    with pytest.raises(ValueError, match="position"):
+        p.executor.decodeStep(jl.BatchSlots([True], [1], [cfg.contextLength], [0]))
+    with pytest.raises(ValueError, match="fixed width"):
+        p.executor.decodeStep(jl.BatchSlots([True, True], [1, 1], [0, 0], [0, 1]))
+    with pytest.raises(ValueError, match="head_dim"):
+        jl.B200Model(dev, jl.Configuration(256, 512, 1, 8, 8, 512, 32))
+
+
+def test_device_resident_generation_equals_host_driven_steps(dev, oracle):
+    cfg = small_config(layers=2, ctx=96)
+    width = 2
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=71, max_batch=width, std=0.05)
+    seqs = [p.new_oracle_sequence() for _ in range(width)]
+    first = [5, 900]
+    hist = p.executor.generate(jl.BatchSlots([True, True], first, [0, 0], [0, 1]), 40)
+    assert hist.shape == (40, width)
+    for b in range(width):
+        tok = first[b]
+        for step in range(40):
+            tok = int(np.argmax(seqs[b].forward(tok, step)))
+            assert hist[step, b] == tok, (b, step)
+    with pytest.raises(ValueError, match="run past context"):
+        p.executor.generate(jl.BatchSlots([True, True], first, [90, 0], [0, 1]), 10)

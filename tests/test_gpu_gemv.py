@@ -1,0 +1,89 @@
+"""Quantised matrix-vector products through the C ABI against the oracle: per-matmul relative L2
+<= 1e-3 is the stated bar; the kernels are expected (and required here) to be near 1e-6."""
+import numpy as np
+import pytest
+
+import jitllm_b200 as jl
+from jitllm_b200 import GGMLType
+from tests.util import rel_l2
+
+pytestmark = pytest.mark.gpu
+BAR = 1e-3       # north-star tolerance per matmul
+EXPECT = 2e-5    # what fp32-equivalent arithmetic should deliver
+FORMATS = [GGMLType.Q8_0, GGMLType.Q4_0, GGMLType.Q4_K]
+
+
+@pytest.mark.parametrize("t", FORMATS)
+@pytest.mark.parametrize("rows,cols", [(1, 256), (3, 256), (64, 512), (257, 1024), (1000, 2048), (512, 1792),
+                                       (96, 14336)])
+def test_small_and_ragged_shapes(dev, oracle, t, rows, cols):
+    w = jl.synth_tensor(t, rows * cols, seed=rows * 31 + cols)
+    x = np.random.default_rng(rows + cols).standard_normal(cols).astype(np.float32)
+    got, want = dev.matmul(t, w, rows, cols, x), oracle.matmul(t, w, x, rows, cols)
+    err = rel_l2(got, want)
+    assert err < BAR and err < EXPECT, err
+
+
+@pytest.mark.parametrize("t", FORMATS)
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (14336, 4096), (4096, 14336)])
+def test_sweep_shapes_single_vector(dev, oracle, t, rows, cols):
+    w = jl.synth_tensor(t, rows * cols, seed=rows + cols + int(t))
+    x = np.random.default_rng(1).standard_normal(cols).astype(np.float32)
+    got, want = dev.matmul(t, w, rows, cols, x), oracle.matmul(t, w, x, rows, cols)
+    err = rel_l2(got, want)
+    assert err < BAR and err < EXPECT, err
+
+
+def test_vocabulary_shape_q4_k(dev, oracle):
+    rows, cols, t = 128256, 4096, GGMLType.Q4_K
+    w = jl.synth_tensor(t, rows * cols, seed=99)
+    x = np.random.default_rng(2).standard_normal(cols).astype(np.float32)
+    got, want = dev.matmul(t, w, rows, cols, x), oracle.matmul(t, w, x, rows, cols)
+    assert rel_l2(got, want) < EXPECT
+    assert int(np.argmax(got)) == int(np.argmax(want))
+
+
+@pytest.mark.parametrize("t", FORMATS)
+def test_batch_of_activations(dev, oracle, t):
+    rows, cols, n = 768, 1024, 8
+    w = jl.synth_tensor(t, rows * cols, seed=5)
+    x = np.random.default_rng(4).standard_normal((n, cols)).astype(np.float32)
+    got, want = dev.matmul(t, w, rows, cols, x), oracle.matmul(t, w, x, rows, cols)
+    assert got.shape == (n, rows)
+    assert rel_l2(got, want) < EXPECT
+
+
+@pytest.mark.parametrize("t", FORMATS)
+def test_properties_at_full_size(dev, t):
+    """Size-independent properties: linearity in x, zero maps to zero, determinism."""
+    rows, cols = 14336, 4096
+    w = jl.synth_tensor(t, rows * cols, seed=8)
+    rng = np.random.default_rng(6)
+    a, b = rng.standard_normal(cols).astype(np.float32), rng.standard_normal(cols).astype(np.float32)
+    ya, yb, yab = dev.matmul(t, w, rows, cols, a), dev.matmul(t, w, rows, cols, b), dev.matmul(t, w, rows, cols, a + b)
+    assert rel_l2(yab, ya + yb) < 5e-6
+    assert np.array_equal(dev.matmul(t, w, rows, cols, np.zeros(cols, dtype=np.float32)), np.zeros(rows, dtype=np.float32))
+    assert np.array_equal(dev.matmul(t, w, rows, cols, a), ya)  # run twice, same bits
+    y2 = dev.matmul(t, w, rows, cols, 2.0 * a)
+    assert rel_l2(y2, 2.0 * ya) < 1e-6
+
+
+def test_activation_dynamic_range(dev, oracle):
+    """One huge element per block must not wipe out its small neighbours beyond fp32-like error."""
+    rows, cols, t = 256, 2048, GGMLType.Q4_K
+    w = jl.synth_tensor(t, rows * cols, seed=12)
+    x = np.random.default_rng(9).standard_normal(cols).astype(np.float32)
+    x[::32] *= 1000.0
+    got, want = dev.matmul(t, w, rows, cols, x), oracle.matmul(t, w, x, rows, cols)
+    assert rel_l2(got, want) < EXPECT
+
+
+def test_argument_errors(dev):
+    with pytest.raises(ValueError, match="multiple of 256"):
+        dev.matmul(GGMLType.Q8_0, np.zeros(34 * 4, dtype=np.uint8), 1, 128, np.zeros(128, dtype=np.float32))
+    with pytest.raises(ValueError, match="needs"):
+        dev.matmul(GGMLType.Q8_0, np.zeros(10, dtype=np.uint8), 1, 256, np.zeros(256, dtype=np.float32))
+    with pytest.raises(ValueError, match="GGML type"):
+        dev._check(dev._lib.jl_gemv(dev.handle, 1, 1, 256, np.zeros(512, dtype=np.uint8).ctypes.data,
+                                    np.zeros(256, dtype=np.float32).ctypes.data, 1,
+                                    np.zeros(1, dtype=np.float32).ctypes.data))
