@@ -29,21 +29,24 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
                  "r"(bytes)
                  : "memory");
 }
+// try_wait may block in hardware for up to the hinted time, so a waiting warp does not spend
+// issue slots polling.
+constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
 // Bounded wait: gives up after `limit` polls (each poll may itself suspend for a
 // hardware-defined time), so a copy that never lands cannot hang the GPU.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
-                                                  uint32_t limit = (1u << 22)) {
+                                                  uint32_t limit = (1u << 16)) {
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
     }

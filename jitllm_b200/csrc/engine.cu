@@ -366,8 +366,8 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.norm_w = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
             a.eps = d.rms_eps;
             a.active = ctx->d_active + b;
-            a.argmax_val = ctx->amax_val + size_t(b) * ctx->sm_count;
-            a.argmax_idx = ctx->amax_idx + size_t(b) * ctx->sm_count;
+            a.argmax_val = ctx->amax_val + size_t(b) * 4 * ctx->sm_count;
+            a.argmax_idx = ctx->amax_idx + size_t(b) * 4 * ctx->sm_count;
             a.argmax_count = ctx->amax_count + b;
             a.out_token = ctx->d_out + b;
             if ((rc = launch_gemv(ctx, a, int(wc.rows), launches))) return rc;
@@ -649,8 +649,8 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
                     attention_partial_floats(int(B), d.heads, nsplit, d.head_dim) * 4)))
         return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_count), B * d.kv_heads * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_val), B * ctx->sm_count * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_idx), B * ctx->sm_count * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_val), B * ctx->sm_count * 16))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_idx), B * ctx->sm_count * 16))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_count), B * 4))) return rc;
     JL_CUDA(ctx, cudaMemsetAsync(ctx->att_count, 0, B * d.kv_heads * 4, ctx->stream));
     JL_CUDA(ctx, cudaMemsetAsync(ctx->amax_count, 0, B * 4, ctx->stream));

@@ -22,15 +22,16 @@
 #include "gemv.cuh"
 
 #include <climits>
+#include <cstdlib>
 
 namespace jl {
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
-constexpr int kMaxStages = 8;
-constexpr int kHeaderBytes = 640;  // mbarriers (512) + argmax / reduction scratch (128)
+constexpr int kMaxStages = 16;
+constexpr int kHeaderBytes = 2176;  // mbarriers (16 warps x 16 stages x 8 B) + 128 B scratch
 constexpr int kUnitBytesQ4 = 36;   // 64 elements: Q4_K 144/4, Q4_0 2*18
 constexpr int kUnitBytesQ8 = 68;   // 64 elements: Q8_0 2*34
 
@@ -190,7 +191,7 @@ __host__ __device__ inline size_t x_region_bytes(int cols) {
 __device__ __forceinline__ SmemLayout carve(uint8_t *smem, int cols) {
     SmemLayout l;
     l.bars = reinterpret_cast<uint64_t *>(smem);
-    l.scratch = reinterpret_cast<float *>(smem + 512);
+    l.scratch = reinterpret_cast<float *>(smem + 2048);
     l.sx = reinterpret_cast<float *>(smem + kHeaderBytes);
     l.sumx = l.sx + cols / 32;
     l.limbs = smem + kHeaderBytes + align_up(size_t(cols) / 32 * 8, 128);
@@ -201,15 +202,28 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *smem, int cols) {
 // Quantises the activation vector (optionally RMS-normalised first) into digit planes in shared
 // memory. Layout of the planes: 16-byte cell index ((digit*4 + quarter) * nunits + unit), so that
 // the 32 lanes of a warp, working on 32 consecutive units, read consecutive cells.
+//
+// A thread handles float4 pieces; the eight lanes that hold one 32-element block agree on the
+// block maximum with three shuffles. Loads are issued eight deep before anything depends on them,
+// so the whole vector costs about one L2 round trip rather than one per block.
+__device__ __forceinline__ uint32_t pack4(int b0, int b1, int b2, int b3) {
+    return (uint32_t(b0) & 0xFFu) | ((uint32_t(b1) & 0xFFu) << 8) | ((uint32_t(b2) & 0xFFu) << 16) |
+           (uint32_t(b3) << 24);
+}
+
 __device__ void stage_activation(const GemvArgs &a, const SmemLayout &sm) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int cols = a.cols, nblk = cols / 32, nunits = cols / 64;
+    const int cols = a.cols, nunits = cols / 64, n4 = cols / 4;
+    const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
+    const float4 *w4 = reinterpret_cast<const float4 *>(a.norm_w);
+    const bool norm = a.norm_w != nullptr;
     float ss = 1.0f;
-    if (a.norm_w != nullptr) {
+    if (norm) {
         float part = 0.f;
-        for (int i = tid; i < cols; i += kThreads) {
-            const float v = a.x[i];
-            part += v * v;
+#pragma unroll 4
+        for (int i = tid; i < n4; i += kThreads) {
+            const float4 v = x4[i];
+            part += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
         part = warp_sum(part);
         if (lane == 0) sm.scratch[warp] = part;
@@ -221,30 +235,63 @@ __device__ void stage_activation(const GemvArgs &a, const SmemLayout &sm) {
         ms += a.eps;
         ss = static_cast<float>(1.0 / sqrt(static_cast<double>(ms)));
     }
-    for (int blk = warp; blk < nblk; blk += kWarps) {
-        const int i = blk * 32 + lane;
-        float v = a.x[i];
-        if (a.norm_w != nullptr) v = __fmul_rn(a.norm_w[i], __fmul_rn(ss, v));
-        const float amax = warp_max(fabsf(v));
-        const float inv = amax > 0.f ? kLimbRange / amax : 0.f;
-        int X = __float2int_rn(v * inv);
-        X = max(-1040000, min(1040000, X));
-        const int a3 = ((X + 64) & 127) - 64;
-        const int X1 = (X - a3) >> 7;
-        const int a2 = ((X1 + 64) & 127) - 64;
-        const int a1 = (X1 - a2) >> 7;
-        const int sumX = __reduce_add_sync(0xffffffffu, X);
-        if (lane == 0) {
-            const float s = amax / kLimbRange;
-            sm.sx[blk] = s;
-            sm.sumx[blk] = s * static_cast<float>(sumX);
+    constexpr int kDeep = 8;
+    const size_t plane = size_t(4) * nunits * 16;
+    for (int base = 0; base < n4; base += kThreads * kDeep) {
+        float4 v[kDeep];
+#pragma unroll
+        for (int k = 0; k < kDeep; ++k) {
+            const int i = base + k * kThreads + tid;
+            v[k] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        const int unit = i >> 6, within = i & 63, quarter = within >> 4, byte = within & 15;
-        const size_t cell = (size_t(quarter) * nunits + unit) * 16 + byte;
-        const size_t plane = size_t(4) * nunits * 16;
-        sm.limbs[cell] = static_cast<uint8_t>(a1);
-        sm.limbs[plane + cell] = static_cast<uint8_t>(a2);
-        sm.limbs[2 * plane + cell] = static_cast<uint8_t>(a3);
+        if (norm) {
+#pragma unroll
+            for (int k = 0; k < kDeep; ++k) {
+                const int i = base + k * kThreads + tid;
+                const float4 w = i < n4 ? w4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[k].x = __fmul_rn(w.x, __fmul_rn(ss, v[k].x));
+                v[k].y = __fmul_rn(w.y, __fmul_rn(ss, v[k].y));
+                v[k].z = __fmul_rn(w.z, __fmul_rn(ss, v[k].z));
+                v[k].w = __fmul_rn(w.w, __fmul_rn(ss, v[k].w));
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kDeep; ++k) {
+            const int i = base + k * kThreads + tid;  // float4 index; 8 consecutive = one block
+            float amax = fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)), fmaxf(fabsf(v[k].z), fabsf(v[k].w)));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            const float inv = amax > 0.f ? kLimbRange / amax : 0.f;
+            int X[4] = {__float2int_rn(v[k].x * inv), __float2int_rn(v[k].y * inv),
+                        __float2int_rn(v[k].z * inv), __float2int_rn(v[k].w * inv)};
+            int d1[4], d2[4], d3[4], sum = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                X[j] = max(-1040000, min(1040000, X[j]));
+                sum += X[j];
+                d3[j] = ((X[j] + 64) & 127) - 64;
+                const int X1 = (X[j] - d3[j]) >> 7;
+                d2[j] = ((X1 + 64) & 127) - 64;
+                d1[j] = (X1 - d2[j]) >> 7;
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            if (i < n4) {
+                const int e = i * 4;
+                const int unit = e >> 6, within = e & 63, quarter = within >> 4, byte = within & 15;
+                uint8_t *cell = sm.limbs + (size_t(quarter) * nunits + unit) * 16 + byte;
+                *reinterpret_cast<uint32_t *>(cell) = pack4(d1[0], d1[1], d1[2], d1[3]);
+                *reinterpret_cast<uint32_t *>(cell + plane) = pack4(d2[0], d2[1], d2[2], d2[3]);
+                *reinterpret_cast<uint32_t *>(cell + 2 * plane) = pack4(d3[0], d3[1], d3[2], d3[3]);
+                if ((i & 7) == 0) {
+                    const float s = amax / kLimbRange;
+                    sm.sx[i >> 3] = s;
+                    sm.sumx[i >> 3] = s * static_cast<float>(sum);
+                }
+            }
+        }
     }
 }
 
@@ -289,13 +336,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
     uint64_t *my_bars = sm.bars + warp * kMaxStages;
 
     // Tiles of R rows, numbered segment after segment; gate/up tiles pair the same rows.
-    int tiles_seg[3] = {0, 0, 0};
-    int total_tiles = 0;
     const int nseg_tiled = (MODE == kGemvGateUp) ? 1 : a.nseg;
-    for (int s = 0; s < nseg_tiled; ++s) {
-        tiles_seg[s] = (a.seg[s].rows + R - 1) / R;
-        total_tiles += tiles_seg[s];
-    }
+    const int t0 = (a.seg[0].rows + R - 1) / R;
+    const int t1 = nseg_tiled > 1 ? (a.seg[1].rows + R - 1) / R : 0;
+    const int t2 = nseg_tiled > 2 ? (a.seg[2].rows + R - 1) / R : 0;
+    const int total_tiles = t0 + t1 + t2;
     const int total_warps = kWarps * gridDim.x;
     const int wg = warp * gridDim.x + blockIdx.x;
     const int n_my = total_tiles > wg ? (total_tiles - wg - 1) / total_warps + 1 : 0;
@@ -303,31 +348,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
 
     auto locate = [&](int tile, int &seg, int &row0) {
         seg = 0;
-        while (seg + 1 < nseg_tiled && tile >= tiles_seg[seg]) {
-            tile -= tiles_seg[seg];
-            ++seg;
+        if (tile >= t0) {
+            tile -= t0;
+            seg = 1;
+            if (tile >= t1) {
+                tile -= t1;
+                seg = 2;
+            }
         }
         row0 = tile * R;
     };
     const uint64_t policy = policy_evict_first();
-    auto issue = [&](int it) {  // lane 0 only
-        const int s = it % stages;
-        const int tk = it / nchunks, cc = it - tk * nchunks;
-        int seg, row0;
-        locate(wg + tk * total_warps, seg, row0);
-        const int nun = min(32, nunits - cc * 32);
+    // Producer cursor (lane 0): the next item to request, advanced incrementally.
+    int p_tile = wg, p_cc = 0, p_seg = 0, p_row0 = 0, p_issued = 0;
+    locate(p_tile, p_seg, p_row0);
+    auto issue = [&](int s) {  // lane 0 only
+        const int nun = min(32, nunits - p_cc * 32);
         const uint32_t bytes = uint32_t(nun) * UB;
-        const int nrows = min(R, a.seg[seg].rows - row0);
+        const int nrows = min(R, a.seg[p_seg].rows - p_row0);
         uint8_t *stage = my_ring + size_t(s) * stage_bytes;
         uint64_t *bar = my_bars + s;
         mbar_expect_tx(bar, bytes * nrows * (MODE == kGemvGateUp ? 2 : 1));
+        const uint8_t *src = a.seg[p_seg].w + size_t(p_row0) * rowb + size_t(p_cc) * CB;
         for (int r = 0; r < nrows; ++r) {
-            bulk_g2s_hint(stage + r * CB, a.seg[seg].w + size_t(row0 + r) * rowb + size_t(cc) * CB,
-                          bytes, bar, policy);
+            bulk_g2s_hint(stage + r * CB, src + size_t(r) * rowb, bytes, bar, policy);
             if (MODE == kGemvGateUp)
                 bulk_g2s_hint(stage + (R + r) * CB,
-                              a.seg[1].w + size_t(row0 + r) * rowb + size_t(cc) * CB, bytes, bar,
+                              a.seg[1].w + size_t(p_row0 + r) * rowb + size_t(p_cc) * CB, bytes, bar,
                               policy);
+        }
+        ++p_issued;
+        if (++p_cc == nchunks) {
+            p_cc = 0;
+            p_tile += total_warps;
+            if (p_tile < total_tiles) locate(p_tile, p_seg, p_row0);
         }
     };
 
@@ -352,10 +406,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
     float best_v = -INFINITY;
     int best_i = INT_MAX;
     bool failed = false;
-    int cc = 0, tk = 0;
+    int cc = 0, tk = 0, s = 0;
+    uint32_t parity = 0;
     for (int it = 0; it < n_items; ++it) {
-        const int s = it % stages;
-        const uint32_t parity = (it / stages) & 1;
         bool ok = mbar_wait_bounded(my_bars + s, parity);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -371,9 +424,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
             for (int r = 0; r < NR; ++r) acc[r] += unit_dot<TYPE>(stage + r * CB, lane, x);
         }
         __syncwarp();
-        if (lane == 0 && it + stages < n_items) {
+        if (lane == 0 && p_issued < n_items) {
             fence_proxy_async();
-            issue(it + stages);
+            issue(s);
+        }
+        if (++s == stages) {
+            s = 0;
+            parity ^= 1u;
         }
         if (++cc == nchunks) {
             cc = 0;
@@ -413,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
     if (failed) {
         // Give copies already in flight a bounded chance to land before this CTA's shared memory
         // is released, then report; the host turns the status word into an error.
-        for (int s = 0; s < stages; ++s) mbar_wait_bounded(my_bars + s, 0, 1u << 16);
+        for (int s = 0; s < stages; ++s) mbar_wait_bounded(my_bars + s, 0, 16);
         if (lane == 0) atomicExch(a.status, kDevTimeout);
     }
 
@@ -516,17 +573,29 @@ bool gemv_plan(int type, int cols, int total_rows, int mode, int sm_count, GemvP
     if (!is_quant(type) || cols <= 0 || cols % 256 != 0 || total_rows <= 0) return false;
     const int chunk = 32 * (type == kQ8_0 ? kUnitBytesQ8 : kUnitBytesQ4);
     const size_t fixed = kHeaderBytes + x_region_bytes(cols);
-    // Half an SM's shared memory, so that under programmatic dependent launch the next kernel's
-    // CTA (already streaming its weights) fits beside this one; fall back to a whole SM for very
-    // wide inputs.
-    size_t budget = 112 * 1024;
+    // One CTA of 16 warps per SM; most of the SM's shared memory goes to the weight rings.
+    static const int env_kb = [] {
+        const char *v = getenv("JITLLM_B200_GEMV_SMEM_KB");
+        return v ? atoi(v) : 0;
+    }();
+    size_t budget = size_t(env_kb > 0 ? env_kb : 208) * 1024;
+    if (budget > 224 * 1024) budget = 224 * 1024;
     if (fixed + size_t(kWarps) * 2 * chunk > budget) budget = 224 * 1024;
     if (fixed + size_t(kWarps) * 2 * chunk > budget) return false;
-    const int grid = sm_count;
+    static const int env_mult = [] {
+        const char *v = getenv("JITLLM_B200_GEMV_GRID_MULT");
+        return v ? atoi(v) : 1;
+    }();
+    static const int env_r = [] {
+        const char *v = getenv("JITLLM_B200_GEMV_ROWS");
+        return v ? atoi(v) : 0;
+    }();
+    const int grid = sm_count * (env_mult > 0 ? env_mult : 1);
     const int warps = grid * kWarps;
     const int mult = (mode == kGemvGateUp) ? 2 : 1;
     int best_r = 1, best_s = 0;
-    const int rmax = (mode == kGemvGateUp) ? 2 : 4;
+    int rmax = (mode == kGemvGateUp) ? 2 : 4;
+    if (env_r > 0 && env_r < rmax) rmax = env_r;
     for (int r = rmax; r >= 1; r >>= 1) {
         // Taller tiles reuse the activation registers more, but leave warps idle on short matrices.
         if (r > 1 && (total_rows / mult + r - 1) / r < warps) continue;

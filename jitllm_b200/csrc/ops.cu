@@ -78,6 +78,15 @@ __device__ __forceinline__ void load_halfs(const __half *p, float (&f)[VEC]) {
 
 constexpr int kAttnThreads = 128;
 constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnMaxSplit = 32;
+constexpr int kAttnMinKeysPerSplit = 32;
+
+// Number of splits actually used for n keys: short contexts use few CTAs so that the fold at the
+// end stays small; the launch grid is sized for the maximum and surplus CTAs leave at once.
+__device__ __forceinline__ int splits_for(int n, int nsplit_max) {
+    const int want = (n + kAttnMinKeysPerSplit - 1) / kAttnMinKeysPerSplit;
+    return max(1, min(nsplit_max, want));
+}
 
 // One CTA = (split of the position range, KV head, batch row). The G query heads that share the
 // KV head are processed together so each K/V row is read once. What it computes is
@@ -87,6 +96,7 @@ constexpr int kAttnWarps = kAttnThreads / 32;
 template <int HD, int G>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
     constexpr int VEC = HD / 32;
+    constexpr int UN = 4;  // keys per warp iteration, loaded before any of them is used
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool on = a.active == nullptr || a.active[b] != 0;
@@ -94,12 +104,29 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     const int slot = on ? a.slots[b] : 0;
     pdl_wait();
     pdl_launch_dependents();
-    if (!on) return;
+    const int n = pos + 1;
+    const int nsplit = splits_for(n, a.nsplit);
+    if (!on || split >= nsplit) return;
 
     __shared__ float q_s[G][HD];
     __shared__ float red[kAttnWarps][G][HD + 2];
+    __shared__ float wgt_s[G][kAttnMaxSplit];
+    __shared__ float inv_l[G];
+    __shared__ int64_t page_base[kAttnMaxSplit * 0 + 40];
     __shared__ int is_last;
 
+    const int chunk = (n + nsplit - 1) / nsplit;
+    const int start = split * chunk;
+    const int end = min(n, start + chunk);
+    // Page bases of this CTA's key range (at most chunk/block_tokens + 2 pages).
+    const int bt = a.kv.block_tokens;
+    const int first_page = start / bt;
+    const int npages = end > start ? (end - 1) / bt - first_page + 1 : 0;
+    const int64_t block_stride = int64_t(a.kv.layers) * bt * a.kv.kv_dim;
+    for (int pg = tid; pg < npages && pg < 40; pg += kAttnThreads) {
+        const int64_t phys = a.kv.block_table[int64_t(slot) * a.kv.blocks_per_slot + first_page + pg];
+        page_base[pg] = phys * block_stride + int64_t(a.layer) * bt * a.kv.kv_dim + int64_t(kvh) * HD;
+    }
     const float *cr = a.rope_cos + size_t(pos) * (HD / 2);
     const float *ci = a.rope_sin + size_t(pos) * (HD / 2);
     for (int idx = tid; idx < G * (HD / 2); idx += kAttnThreads) {
@@ -109,10 +136,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         q_s[g][2 * i] = __fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]));
         q_s[g][2 * i + 1] = __fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]));
     }
-    const int n = pos + 1;
-    const int chunk = (n + a.nsplit - 1) / a.nsplit;
-    const int start = split * chunk;
-    const int end = min(n, start + chunk);
     if (start <= pos && pos < end) {
         // This CTA owns the new position: rotate k, round k and v to fp16, append to the page.
         const int64_t off = kv_offset(a.kv, slot, pos, a.layer) + int64_t(kvh) * HD;
@@ -142,23 +165,54 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         }
     }
     const float inv_sqrt = 1.0f / sqrtf(static_cast<float>(HD));
-    for (int t = start + warp; t < end; t += kAttnWarps) {
-        const int64_t off = kv_offset(a.kv, slot, t, a.layer) + int64_t(kvh) * HD + lane * VEC;
-        float kf[VEC], vf[VEC];
-        load_halfs<VEC>(a.kv.kpool + off, kf);
-        load_halfs<VEC>(a.kv.vpool + off, vf);
+    // Each warp takes a contiguous run of keys so that consecutive keys share a page.
+    const int per_warp = (end - start + kAttnWarps - 1) / kAttnWarps;
+    const int w0 = start + warp * per_warp;
+    const int w1 = min(end, w0 + per_warp);
+    for (int t0 = w0; t0 < w1; t0 += UN) {
+        float kf[UN][VEC], vf[UN][VEC];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int t = min(t0 + u, w1 - 1);  // the tail repeats the last key; masked below
+            const int pg = t / bt - first_page;
+            const int64_t base = (pg < 40) ? page_base[pg] : kv_offset(a.kv, slot, t, a.layer) - int64_t(t % bt) * a.kv.kv_dim + int64_t(kvh) * HD;
+            const int64_t off = base + int64_t(t % bt) * a.kv.kv_dim + lane * VEC;
+            load_halfs<VEC>(a.kv.kpool + off, kf[u]);
+            load_halfs<VEC>(a.kv.vpool + off, vf[u]);
+        }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            float s = 0.f;
+            float s[UN];
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) s += qr[g][j] * kf[j];
-            s = warp_sum(s) * inv_sqrt;
-            const float mn = fmaxf(m[g], s);
+            for (int u = 0; u < UN; ++u) {
+                float d = 0.f;
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) d += qr[g][j] * kf[u][j];
+                s[u] = d;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < UN; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+            }
+            float mn = m[g];
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                s[u] = (t0 + u < w1) ? s[u] * inv_sqrt : -INFINITY;
+                mn = fmaxf(mn, s[u]);
+            }
             const float corr = expf(m[g] - mn);
-            const float p = expf(s - mn);
-            l[g] = l[g] * corr + p;
+            float psum = 0.f;
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) acc[g][j] = acc[g][j] * corr + p * vf[j];
+            for (int j = 0; j < VEC; ++j) acc[g][j] *= corr;
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const float p = expf(s[u] - mn);  // exp(-inf) = 0 for masked keys
+                psum += p;
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) acc[g][j] += p * vf[u][j];
+            }
+            l[g] = l[g] * corr + psum;
             m[g] = mn;
         }
     }
@@ -188,7 +242,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             L += red[w][g][HD + 1] * wgt;
         }
         const int h = kvh * G + g;
-        if (a.nsplit == 1) {
+        if (nsplit == 1) {
             a.out[size_t(b) * a.dim + size_t(h) * HD + d] = val / L;
         } else {
             float *p = a.partial + ((size_t(b) * a.heads + h) * a.nsplit + split) * pstride;
@@ -199,32 +253,54 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             }
         }
     }
-    if (a.nsplit == 1) return;
+    if (nsplit == 1) return;
 
     // The last CTA of this (row, KV head) to finish folds the splits together.
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         const unsigned prev = atomicAdd(a.counters + size_t(b) * a.kv_heads + kvh, 1u);
-        is_last = (prev == unsigned(a.nsplit) - 1u);
+        is_last = (prev == unsigned(nsplit) - 1u);
     }
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // Fold weights first (one thread per (head, split)), then every output element sums its
+    // splits with the loads issued four at a time.
+    for (int idx = tid; idx < G * kAttnMaxSplit; idx += kAttnThreads) {
+        const int g = idx / kAttnMaxSplit, s = idx - g * kAttnMaxSplit;
+        const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * a.nsplit * pstride;
+        wgt_s[g][s] = s < nsplit ? __ldcg(p + s * pstride + HD) : -INFINITY;
+    }
+    __syncthreads();
+    if (tid < G) {
+        const int g = tid;
+        const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * a.nsplit * pstride;
+        float M = -INFINITY;
+        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, wgt_s[g][s]);
+        float L = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float ms = wgt_s[g][s];
+            const float w = (ms == -INFINITY) ? 0.f : expf(ms - M);
+            wgt_s[g][s] = w;
+            L += __ldcg(p + s * pstride + HD + 1) * w;
+        }
+        inv_l[g] = 1.0f / L;
+    }
+    __syncthreads();
     for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, d = idx - g * HD;
         const int h = kvh * G + g;
-        const float *p = a.partial + (size_t(b) * a.heads + h) * a.nsplit * pstride;
-        float M = -INFINITY;
-        for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, __ldcg(p + s * pstride + HD));
-        float val = 0.f, L = 0.f;
-        for (int s = 0; s < a.nsplit; ++s) {
-            const float ms = __ldcg(p + s * pstride + HD);
-            const float wgt = (ms == -INFINITY) ? 0.f : expf(ms - M);
-            val += __ldcg(p + s * pstride + d) * wgt;
-            L += __ldcg(p + s * pstride + HD + 1) * wgt;
+        const float *p = a.partial + (size_t(b) * a.heads + h) * a.nsplit * pstride + d;
+        float val = 0.f;
+        int s = 0;
+        for (; s + 4 <= nsplit; s += 4) {
+            const float v0 = __ldcg(p + (s + 0) * pstride), v1 = __ldcg(p + (s + 1) * pstride);
+            const float v2 = __ldcg(p + (s + 2) * pstride), v3 = __ldcg(p + (s + 3) * pstride);
+            val += v0 * wgt_s[g][s] + v1 * wgt_s[g][s + 1] + v2 * wgt_s[g][s + 2] + v3 * wgt_s[g][s + 3];
         }
-        a.out[size_t(b) * a.dim + size_t(h) * HD + d] = val / L;
+        for (; s < nsplit; ++s) val += __ldcg(p + s * pstride) * wgt_s[g][s];
+        a.out[size_t(b) * a.dim + size_t(h) * HD + d] = val * inv_l[g];
     }
     if (tid == 0) a.counters[size_t(b) * a.kv_heads + kvh] = 0u;
 }
