@@ -62,6 +62,7 @@ SIGNATURES = {
     "jl_stream": (_P, [_P]),
     "jl_timer_start": (_I32, [_P]),
     "jl_timer_stop": (_I32, [_P, C.POINTER(C.c_float)]),
+    "jl_debug_token_profile": (_I32, [_P, _P, _I32]),
     "jl_bench_op": (_I32, [_P, _I32, _I32, _I32]),
     "jl_get_counters": (_I32, [_P, C.POINTER(JlCounters)]),
     "jl_flush_l2": (_I32, [_P]),

@@ -81,6 +81,28 @@ __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ---- explicit shared-memory loads (32-bit shared addresses, never generic) ---------------------
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
 // ---- programmatic dependent launch ------------------------------------------------------------
 // No-ops when the kernel was launched without the programmatic-serialization attribute.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -102,6 +124,22 @@ __device__ __forceinline__ float warp_max(float v) {
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(h16)));
+}
+
+// VEC (2 or 4) consecutive binary16 values widened to binary32.
+template <int VEC>
+__device__ __forceinline__ void load_halfs(const __half *p, float (&f)[VEC]) {
+    if constexpr (VEC == 4) {
+        const uint2 u = *reinterpret_cast<const uint2 *>(p);
+        const __half2 a = *reinterpret_cast<const __half2 *>(&u.x);
+        const __half2 b = *reinterpret_cast<const __half2 *>(&u.y);
+        const float2 fa = __half22float2(a), fb = __half22float2(b);
+        f[0] = fa.x; f[1] = fa.y; f[2] = fb.x; f[3] = fb.y;
+    } else {
+        const __half2 a = *reinterpret_cast<const __half2 *>(p);
+        const float2 fa = __half22float2(a);
+        f[0] = fa.x; f[1] = fa.y;
+    }
 }
 
 }  // namespace jl

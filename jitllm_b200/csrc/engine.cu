@@ -12,6 +12,7 @@
 
 #include "gemv.cuh"
 #include "ops.cuh"
+#include "token_kernel.cuh"
 
 using namespace jl;
 
@@ -72,6 +73,13 @@ struct jl_ctx {
     int *d_status = nullptr;
     int attn_nsplit = 1;
     int32_t *d_history = nullptr, *d_step = nullptr;
+    // persistent per-token kernel (single-sequence steps)
+    bool use_token_kernel = false, tok_ok = false;
+    int tok_type = -1;
+    TokLayer *d_layers = nullptr;
+    float *tok_partial = nullptr;
+    unsigned *d_barrier = nullptr;
+    unsigned long long *d_profile = nullptr;
     size_t history_cap = 0;
     // pinned host staging: tokens | positions | slots | out | active | status
     int32_t *h_stage = nullptr;
@@ -210,6 +218,15 @@ void free_model(jl_ctx *ctx) {
     ctx->amax_val = nullptr;
     ctx->amax_idx = nullptr;
     ctx->amax_count = nullptr;
+    if (ctx->d_layers) cudaFree(ctx->d_layers);
+    ctx->d_layers = nullptr;
+    if (ctx->tok_partial) cudaFree(ctx->tok_partial);
+    if (ctx->d_barrier) cudaFree(ctx->d_barrier);
+    if (ctx->d_profile) cudaFree(ctx->d_profile);
+    ctx->d_profile = nullptr;
+    ctx->tok_partial = nullptr;
+    ctx->d_barrier = nullptr;
+    ctx->tok_ok = false;
     if (ctx->d_history) cudaFree(ctx->d_history);
     if (ctx->d_step) cudaFree(ctx->d_step);
     ctx->d_history = ctx->d_step = nullptr;
@@ -242,10 +259,106 @@ int launch_gemv(jl_ctx *ctx, GemvArgs &a, int total_rows, uint64_t *launches) {
         return fail(ctx, JL_ERR_UNSUPPORTED, "no launch plan for type %d with %d columns", a.type,
                     a.cols);
     a.status = ctx->d_status;
+    static const int dbg = [] { const char *v = getenv("JITLLM_B200_GEMV_DEBUG"); return v ? atoi(v) : 0; }();
+    a.debug = dbg;
     cudaError_t e = gemv_launch(a, plan, ctx->stream, ctx->use_pdl);
     if (e != cudaSuccess)
         return fail(ctx, JL_ERR_CUDA, "matrix-vector launch failed: %s", cudaGetErrorString(e));
     ++*launches;
+    return JL_OK;
+}
+
+// Prepares the persistent per-token kernel: layer pointer table, split scratch, barrier word.
+int build_token_ops(jl_ctx *ctx) {
+    const jl_model_desc &d = ctx->desc;
+    ctx->tok_ok = false;
+    if (!ctx->use_token_kernel) return JL_OK;
+    const int type = ctx->layer[JL_ROLE_ATTENTION_QUERY][0].type;
+    for (int l = 0; l < d.layers; ++l)
+        for (int r : {JL_ROLE_ATTENTION_QUERY, JL_ROLE_ATTENTION_OUTPUT, JL_ROLE_FFN_GATE, JL_ROLE_FFN_DOWN})
+            if (ctx->layer[r][l].type != type) return JL_OK;
+    if (wcls_of(ctx).type != type) return JL_OK;
+    if (!token_kernel_supported(type, d.head_dim, d.heads / d.kv_heads, d.dim, d.hidden, ctx->kv_dim,
+                                d.vocab, d.heads, d.kv_heads, d.layers, ctx->sm_count))
+        return JL_OK;
+    std::vector<TokLayer> table(d.layers);
+    for (int l = 0; l < d.layers; ++l) {
+        TokLayer &t = table[l];
+        t.wq = ctx->layer[JL_ROLE_ATTENTION_QUERY][l].data;
+        t.wk = ctx->layer[JL_ROLE_ATTENTION_KEY][l].data;
+        t.wv = ctx->layer[JL_ROLE_ATTENTION_VALUE][l].data;
+        t.wo = ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l].data;
+        t.w1 = ctx->layer[JL_ROLE_FFN_GATE][l].data;
+        t.w3 = ctx->layer[JL_ROLE_FFN_UP][l].data;
+        t.w2 = ctx->layer[JL_ROLE_FFN_DOWN][l].data;
+        t.attn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
+        t.ffn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
+    }
+    int rc;
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_layers), table.size() * sizeof(TokLayer))))
+        return rc;
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_layers, table.data(), table.size() * sizeof(TokLayer),
+                                 cudaMemcpyHostToDevice, ctx->stream));
+    const int max_splits = ctx->sm_count / d.kv_heads;
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->tok_partial),
+                        size_t(d.heads) * max_splits * (d.head_dim + 2) * 4)))
+        return rc;
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_barrier), 4))) return rc;
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->tok_type = type;
+    ctx->tok_ok = true;
+    return JL_OK;
+}
+
+// One single-sequence step through the persistent kernel.
+int launch_token_kernel(jl_ctx *ctx, bool with_logits, bool advance) {
+    const jl_model_desc &d = ctx->desc;
+    TokArgs a = {};
+    a.layers = ctx->d_layers;
+    a.n_layers = d.layers;
+    a.with_logits = with_logits ? 1 : 0;
+    a.dim = d.dim;
+    a.hidden = d.hidden;
+    a.kv_dim = ctx->kv_dim;
+    a.vocab = d.vocab;
+    a.eps = d.rms_eps;
+    a.emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING].data;
+    a.emb_type = ctx->global[JL_ROLE_TOKEN_EMBEDDING].type;
+    a.wcls = wcls_of(ctx).data;
+    a.out_norm = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
+    a.tokens = ctx->d_tokens;
+    a.positions = ctx->d_positions;
+    a.slots = ctx->d_slots;
+    a.out_token = ctx->d_out;
+    a.history = ctx->d_history;
+    a.step_counter = ctx->d_step;
+    a.advance = advance ? 1 : 0;
+    a.x = ctx->x;
+    a.q = ctx->q;
+    a.k = ctx->k;
+    a.v = ctx->v;
+    a.xb = ctx->xb;
+    a.hb = ctx->hb;
+    a.logits = ctx->logits;
+    a.kv = {ctx->kpool, ctx->vpool, ctx->block_table, ctx->blocks_per_slot, ctx->block_tokens, d.layers,
+            ctx->kv_dim};
+    a.rope_cos = ctx->rope_cos;
+    a.rope_sin = ctx->rope_sin;
+    a.heads = d.heads;
+    a.kv_heads = d.kv_heads;
+    a.partial = ctx->tok_partial;
+    a.max_splits = ctx->sm_count / d.kv_heads;
+    a.amax_val = ctx->amax_val;
+    a.amax_idx = ctx->amax_idx;
+    a.barrier = ctx->d_barrier;
+    a.status = ctx->d_status;
+    a.profile = ctx->d_profile;
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->d_barrier, 0, 4, ctx->stream));
+    cudaError_t e = token_kernel_launch(ctx->tok_type, d.head_dim, d.heads / d.kv_heads, a, ctx->sm_count,
+                                        ctx->stream);
+    if (e != cudaSuccess)
+        return fail(ctx, JL_ERR_CUDA, "per-token kernel launch failed: %s", cudaGetErrorString(e));
+    ctx->counters.kernel_launches += 1;
     return JL_OK;
 }
 
@@ -385,6 +498,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
 
 // Runs one step: replays the captured graph for this width, capturing it on first use.
 int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
+    if (width == 1 && ctx->tok_ok) return launch_token_kernel(ctx, with_logits, advance);
     const int key = width * 4 + (with_logits ? 1 : 0) + (advance ? 2 : 0);
     uint64_t launches = 0;
     if (!ctx->use_graph) {
@@ -458,6 +572,7 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->use_graph = env_flag("JITLLM_B200_GRAPH", true);
     ctx->use_pdl = env_flag("JITLLM_B200_PDL", true);
+    ctx->use_token_kernel = env_flag("JITLLM_B200_TOKEN_KERNEL", false);
     e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev0);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev1);
@@ -465,6 +580,7 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->tev1);
     if (e == cudaSuccess) e = gemv_configure();
     if (e == cudaSuccess) e = attention_configure();
+    if (e == cudaSuccess) e = token_kernel_configure();
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->d_status), sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
     if (e != cudaSuccess) {
@@ -660,6 +776,7 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     JL_CUDA(ctx, cudaMallocHost(reinterpret_cast<void **>(&ctx->h_stage), (5 * B + 1) * 4));
     JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     ctx->counters.workspace_bytes = ws;
+    if ((rc = build_token_ops(ctx))) return rc;
     ctx->finalized = true;
     return JL_OK;
 }
@@ -798,6 +915,12 @@ int32_t jl_decode(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32
         h_slot[b] = on ? kv_slots[b] : 0;
         h_act[b] = on ? 1 : 0;
     }
+    bool any = false;
+    for (int b = 0; b < width; ++b) any = any || h_act[b];
+    if (!any) {
+        for (int b = 0; b < width; ++b) out_tokens[b] = -1;
+        return JL_OK;
+    }
     JL_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_tokens, h_tok, width * 4, cudaMemcpyHostToDevice, ctx->stream));
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_positions, h_pos, width * 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -907,6 +1030,12 @@ int32_t jl_generate(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int
         h_slot[b] = on ? kv_slots[b] : 0;
         h_act[b] = on ? 1 : 0;
     }
+    bool any = false;
+    for (int b = 0; b < width; ++b) any = any || h_act[b];
+    if (!any) {
+        for (size_t i = 0; i < need; ++i) out_history[i] = -1;
+        return JL_OK;
+    }
     JL_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_tokens, h_tok, width * 4, cudaMemcpyHostToDevice, ctx->stream));
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_positions, h_pos, width * 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -925,6 +1054,26 @@ int32_t jl_generate(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int
     ctx->counters.h2d_bytes += width * 13;
     ctx->counters.d2h_bytes += need * 4 + 4;
     return JL_OK;
+}
+
+int32_t jl_debug_token_profile(jl_ctx *ctx, uint64_t *out, int32_t max_ops) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->finalized && ctx->tok_ok, JL_ERR_STATE, "the per-token kernel is not in use");
+    cudaSetDevice(ctx->device);
+    const int n = token_kernel_op_count(ctx->desc.layers);
+    if (!out) {  // arm: later steps record stamps
+        if (!ctx->d_profile) {
+            int rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_profile), size_t(n) * 5 * 8);
+            if (rc) return rc;
+        }
+        JL_CUDA(ctx, cudaMemsetAsync(ctx->d_profile, 0, size_t(n) * 5 * 8, ctx->stream));
+        return n;
+    }
+    JL_REQUIRE(ctx, ctx->d_profile != nullptr, JL_ERR_STATE, "profiling was not armed");
+    const int m = max_ops < n ? max_ops : n;
+    JL_CUDA(ctx, cudaMemcpyAsync(out, ctx->d_profile, size_t(m) * 5 * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return m;
 }
 
 int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters) {

@@ -31,6 +31,7 @@ struct GemvArgs {
     unsigned *argmax_count;  // zero on entry, zero again on exit
     int *out_token;
     int *status;  // device status word, see common.cuh
+    int debug;    // 0 normal; 1 = stream only (no arithmetic); 2 = arithmetic only (no copies)
 };
 
 struct GemvPlan {

@@ -8,13 +8,13 @@ namespace {
 // ---- embedding -------------------------------------------------------------------------------
 __global__ void embedding_kernel(int type, const uint8_t *table, const int32_t *tokens,
                                  const uint8_t *active, float *x, int dim) {
-    const int row = blockIdx.x;
+    const int row = blockIdx.y;
     const bool on = active == nullptr || active[row] != 0;
     pdl_wait();
     pdl_launch_dependents();
     if (!on) return;
     const int token = tokens[row];
-    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
         x[size_t(row) * dim + i] = decode_any(type, table, int64_t(token) * dim + i);
 }
 
@@ -61,25 +61,10 @@ __device__ __forceinline__ int64_t kv_offset(const KvGeom &g, int slot, int pos,
            int64_t(within) * g.kv_dim;
 }
 
-template <int VEC>
-__device__ __forceinline__ void load_halfs(const __half *p, float (&f)[VEC]) {
-    if constexpr (VEC == 4) {
-        const uint2 u = *reinterpret_cast<const uint2 *>(p);
-        const __half2 a = *reinterpret_cast<const __half2 *>(&u.x);
-        const __half2 b = *reinterpret_cast<const __half2 *>(&u.y);
-        const float2 fa = __half22float2(a), fb = __half22float2(b);
-        f[0] = fa.x; f[1] = fa.y; f[2] = fb.x; f[3] = fb.y;
-    } else {
-        const __half2 a = *reinterpret_cast<const __half2 *>(p);
-        const float2 fa = __half22float2(a);
-        f[0] = fa.x; f[1] = fa.y;
-    }
-}
-
-constexpr int kAttnThreads = 128;
+constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
 constexpr int kAttnMaxSplit = 32;
-constexpr int kAttnMinKeysPerSplit = 32;
+constexpr int kAttnMinKeysPerSplit = 64;
 
 // Number of splits actually used for n keys: short contexts use few CTAs so that the fold at the
 // end stays small; the launch grid is sized for the maximum and surplus CTAs leave at once.
@@ -288,19 +273,39 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         inv_l[g] = 1.0f / L;
     }
     __syncthreads();
-    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
-        const int g = idx / HD, d = idx - g * HD;
-        const int h = kvh * G + g;
-        const float *p = a.partial + (size_t(b) * a.heads + h) * a.nsplit * pstride + d;
-        float val = 0.f;
-        int s = 0;
-        for (; s + 4 <= nsplit; s += 4) {
-            const float v0 = __ldcg(p + (s + 0) * pstride), v1 = __ldcg(p + (s + 1) * pstride);
-            const float v2 = __ldcg(p + (s + 2) * pstride), v3 = __ldcg(p + (s + 3) * pstride);
-            val += v0 * wgt_s[g][s] + v1 * wgt_s[g][s + 1] + v2 * wgt_s[g][s + 2] + v3 * wgt_s[g][s + 3];
+    // Each thread owns G*HD/threads outputs and walks the splits eight at a time, so that all of a
+    // batch's loads are in flight together (the fold is pure L2 latency otherwise).
+    constexpr int kOuts = (G * HD + kAttnThreads - 1) / kAttnThreads;
+    float val[kOuts];
+#pragma unroll
+    for (int j = 0; j < kOuts; ++j) val[j] = 0.f;
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {
+        float ld[kOuts][8];
+#pragma unroll
+        for (int j = 0; j < kOuts; ++j) {
+            const int idx = tid + j * kAttnThreads;
+            const int g = idx / HD, d = idx - g * HD;
+            const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * a.nsplit * pstride + d;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                ld[j][u] = (idx < G * HD && s0 + u < nsplit) ? __ldcg(p + (s0 + u) * pstride) : 0.f;
         }
-        for (; s < nsplit; ++s) val += __ldcg(p + s * pstride) * wgt_s[g][s];
-        a.out[size_t(b) * a.dim + size_t(h) * HD + d] = val * inv_l[g];
+#pragma unroll
+        for (int j = 0; j < kOuts; ++j) {
+            const int idx = tid + j * kAttnThreads;
+            const int g = min(idx / HD, G - 1);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (s0 + u < nsplit) val[j] += ld[j][u] * wgt_s[g][s0 + u];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kOuts; ++j) {
+        const int idx = tid + j * kAttnThreads;
+        if (idx < G * HD) {
+            const int g = idx / HD, d = idx - g * HD;
+            a.out[size_t(b) * a.dim + size_t(kvh * G + g) * HD + d] = val[j] * inv_l[g];
+        }
     }
     if (tid == 0) a.counters[size_t(b) * a.kv_heads + kvh] = 0u;
 }
@@ -349,7 +354,7 @@ cudaError_t embedding_launch(int type, const uint8_t *table, const int32_t *toke
                              const uint8_t *active, float *x, int dim, int width,
                              cudaStream_t stream, bool programmatic) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(width);
+    cfg.gridDim = dim3((dim + 255) / 256, width);
     cfg.blockDim = dim3(256);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
