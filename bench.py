@@ -38,9 +38,14 @@ ARCHS = {
     "8b": (4096, 14336, 32, 32, 8, 128256, 4096, False),
     "1b": (2048, 8192, 16, 32, 8, 128256, 2048, True),
     "tiny": (512, 1024, 4, 8, 2, 4096, 1024, False),
+    # four layers of the 8B layer shapes with a small vocabulary: the profiling-sized case
+    "8b4": (4096, 14336, 4, 32, 8, 16384, 4096, False),
 }
 BYTES_PER_EL = {"Q4_K": 144 / 256, "Q4_0": 18 / 32, "Q8_0": 34 / 32}
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel for the 8B layer
+# shape, from the ncu capture summarised in profiles/gemv_gateup_q4k_8b_layer.md
+NCU_TRAFFIC_BYTES = {("Q4_K", 4096, 14336): 66.55e6}
 
 
 def parse_args():
@@ -56,6 +61,9 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=20261125)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-op", type=int, default=-1,
+                    help="launch one matrix-vector operator (0 qkv, 1 out, 2 gate/up, 3 down, 4 vocab) "
+                         "--steps times and exit: the small case ncu captures are taken on")
     return ap.parse_args()
 
 
@@ -213,6 +221,16 @@ def main():
     model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=B)
     t_build = time.time() - t_build
 
+    if args.profile_op >= 0:
+        model.benchOp(args.profile_op, 0, max(W, 1))
+        dev.synchronize()
+        dev.timer_start()
+        model.benchOp(args.profile_op, 0, K)
+        t_ms = dev.timer_stop()
+        print(json.dumps({"profile_op": args.profile_op, "launches": K, "us_per_launch": t_ms * 1000.0 / K,
+                          "bytes_per_launch": op_bytes(cfg, args.format, args.profile_op)}), flush=True)
+        return 0
+
     # KV pool: only the pages this run touches are mapped; the rest stay UNMAPPED (scratch block).
     bps = cfg.contextLength // 16
     total_tokens = P + W + 3 * K + 64
@@ -324,7 +342,7 @@ def main():
         "gpu_launches": int(c1["kernel_launches"] - c0["kernel_launches"]),
         "roofline": {"bound": "hbm", "kernel": "gemv_kernel<%s> %s" % (args.format, dom["kernel"]),
                      "achieved": dom["gbs"], "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": dom["frac"], "traffic": None, "bytes_per_launch": dom["bytes_per_launch"],
+                     "frac": dom["frac"], "traffic": NCU_TRAFFIC_BYTES.get((args.format, cfg.dim, cfg.hiddenDim)), "bytes_per_launch": dom["bytes_per_launch"],
                      "us_per_launch": dom["us_per_launch"]},
         "step_roofline": {"weight_bytes": weights_b, "kv_bytes": kv_b, "achieved_gbs": (weights_b + kv_b) / step_ms / 1e6,
                           "frac_of_measured_peak": (weights_b + kv_b) / step_ms / 1e6 / peak,
