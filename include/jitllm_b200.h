@@ -177,6 +177,24 @@ int32_t jl_get_counters(jl_ctx *ctx, jl_counters *out);
 /* Overwrites a 256 MiB scratch buffer (larger than L2) so that the next kernel starts cold. */
 int32_t jl_flush_l2(jl_ctx *ctx);
 
+/* ---- allocation-free operator (no counterpart in the reference: its kernels take whatever
+ * scratch the TornadoVM runtime allocates for them).
+ * y_dev[rows] = W . x (x optionally RMS-normalised with norm_w_dev / rms_eps first) and
+ * *token_dev = index of the first maximum of y, for callers that may not allocate device memory
+ * at call time (memory carved up once at start-up, a stream being captured, a host-owned pool).
+ * Every buffer is the caller's; the kernel's cross-CTA scratch is an 8.25 KiB array inside the
+ * library image (held by every GPU that loads the library, until exit), enough for 1024 CTAs.
+ * Calls no cudaMalloc / cudaFree. The first call on a device looks up the array's device address
+ * and sets kernel attributes -- make that call outside any stream capture. All calls share the
+ * array: calls whose kernels overlap on the GPU (different streams) race on it; serialise them.
+ * Shapes whose launch would need more than 1024 CTAs, or more shared memory than one SM has,
+ * are rejected with JL_ERR_UNSUPPORTED. w_dev: rows x cols in GGUF block layout, 16-byte aligned.
+ * Errors: jl_static_last_error(). */
+int32_t jl_gemv_argmax_static(int32_t ggml_type, int64_t rows, int64_t cols, const void *w_dev,
+                              const float *x_dev, const float *norm_w_dev, float rms_eps, float *y_dev,
+                              int32_t *token_dev, void *stream);
+const char *jl_static_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif
