@@ -13,6 +13,7 @@
 #include "gemv.cuh"
 #include "ops.cuh"
 #include "token_kernel.cuh"
+#include "gemm_tc.cuh"
 
 using namespace jl;
 
@@ -1243,6 +1244,24 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     JL_REQUIRE(ctx, n >= 0, JL_ERR_INVALID, "n must not be negative");
     cudaSetDevice(ctx->device);
     uint64_t launches = 0;
+    static const int gemm_min_n = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
+    if (n >= gemm_min_n) {
+        // Wide enough for the tensor cores: one tcgen05 matrix-matrix launch.
+        GemmArgs g = {};
+        g.w = w->t.data;
+        g.type = w->t.type;
+        g.rows = int(w->t.rows);
+        g.cols = int(w->t.cols);
+        g.x = x_dev;
+        g.n = n;
+        g.y = y_dev;
+        g.status = ctx->d_status;
+        cudaError_t e = gemm_tc_launch(g, ctx->stream);
+        if (e != cudaSuccess)
+            return fail(ctx, JL_ERR_CUDA, "matrix-matrix launch failed: %s", cudaGetErrorString(e));
+        ctx->counters.kernel_launches += 1;
+        return JL_OK;
+    }
     for (int b = 0; b < n; ++b) {
         GemvArgs a = {};
         a.nseg = 1;
