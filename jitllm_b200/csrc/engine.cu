@@ -73,6 +73,8 @@ struct jl_ctx {
     unsigned *amax_count = nullptr;
     int *d_status = nullptr;
     int attn_nsplit = 1;
+    int row_cap = 1;        // rows the step buffers hold: max(max_batch, prefill chunk)
+    float *hb2 = nullptr;   // second FFN buffer of the matrix-matrix path (up projection)
     int32_t *d_history = nullptr, *d_step = nullptr;
     // persistent per-token kernel (single-sequence steps)
     bool use_token_kernel = false, tok_ok = false;
@@ -205,12 +207,12 @@ void free_model(jl_ctx *ctx) {
         ctx->layer[r].clear();
     }
     void *bufs[] = {ctx->rope_cos, ctx->rope_sin, ctx->x,       ctx->q,        ctx->k,
-                    ctx->v,        ctx->xb,       ctx->hb,      ctx->logits,   ctx->d_tokens,
+                    ctx->v,        ctx->xb,       ctx->hb,      ctx->hb2,     ctx->logits,   ctx->d_tokens,
                     ctx->d_positions, ctx->d_slots, ctx->d_out, ctx->d_active, ctx->att_partial,
                     ctx->att_count, ctx->amax_val, ctx->amax_idx, ctx->amax_count};
     for (void *b : bufs)
         if (b) cudaFree(b);
-    ctx->rope_cos = ctx->rope_sin = ctx->x = ctx->q = ctx->k = ctx->v = ctx->xb = ctx->hb =
+    ctx->rope_cos = ctx->rope_sin = ctx->x = ctx->q = ctx->k = ctx->v = ctx->xb = ctx->hb = ctx->hb2 =
         ctx->logits = nullptr;
     ctx->d_tokens = ctx->d_positions = ctx->d_slots = ctx->d_out = nullptr;
     ctx->d_active = nullptr;
@@ -363,6 +365,102 @@ int launch_token_kernel(jl_ctx *ctx, bool with_logits, bool advance) {
     return JL_OK;
 }
 
+int attn_splits_for_width(const jl_ctx *ctx, int width) {
+    int n = (2 * ctx->sm_count + width * ctx->desc.kv_heads - 1) / (width * ctx->desc.kv_heads);
+    if (n > 32) n = 32;
+    if (n < 1) n = 1;
+    return n;
+}
+
+int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
+                uint64_t *launches) {
+    GemmArgs g = {};
+    g.w = w.data;
+    g.type = w.type;
+    g.rows = int(w.rows);
+    g.cols = int(w.cols);
+    g.x = x;
+    g.n = n;
+    g.y = y;
+    g.res = res;
+    g.status = ctx->d_status;
+    cudaError_t e = gemm_tc_launch(g, ctx->stream);
+    if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-matrix launch failed: %s", cudaGetErrorString(e));
+    ++*launches;
+    return JL_OK;
+}
+
+#define JL_LAUNCH(ctx, call, what)                                                            \
+    do {                                                                                      \
+        cudaError_t e_ = (call);                                                              \
+        if (e_ != cudaSuccess) return fail(ctx, JL_ERR_CUDA, what " launch failed: %s", cudaGetErrorString(e_)); \
+        ++*launches;                                                                          \
+    } while (0)
+
+// The step for n rows on the tensor-core path (chunked prompt ingestion, wide decode batches):
+// the same operator order as enqueue_step, with every projection one matrix-matrix launch and
+// the element-wise operators as row kernels. Row r uses tokens[r], positions[r], slots[r].
+int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, uint64_t *launches) {
+    const jl_model_desc &d = ctx->desc;
+    const int dim = d.dim, kv_dim = ctx->kv_dim;
+    const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
+    const KvGeom kvg = {ctx->kpool, ctx->vpool, ctx->block_table, ctx->blocks_per_slot, ctx->block_tokens,
+                        d.layers, kv_dim};
+    JL_LAUNCH(ctx, embedding_launch(emb.type, emb.data, ctx->d_tokens, ctx->d_active, ctx->x, dim, n, ctx->stream, false),
+              "embedding");
+    int rc;
+    for (int l = 0; l < d.layers; ++l) {
+        const float *attn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
+        const float *ffn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
+        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, attn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
+                  "rmsnorm");
+        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_QUERY][l], ctx->xb, n, ctx->q, nullptr, launches))) return rc;
+        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_KEY][l], ctx->xb, n, ctx->k, nullptr, launches))) return rc;
+        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_VALUE][l], ctx->xb, n, ctx->v, nullptr, launches))) return rc;
+        JL_LAUNCH(ctx, kv_append_launch(ctx->k, ctx->v, ctx->rope_cos, ctx->rope_sin, ctx->d_positions, ctx->d_slots,
+                                        ctx->d_active, kvg, l, d.head_dim, n, ctx->stream),
+                  "kv append");
+        {
+            AttnArgs a = {};
+            a.q = ctx->q;
+            a.k = ctx->k;
+            a.v = ctx->v;
+            a.out = ctx->xb;
+            a.rope_cos = ctx->rope_cos;
+            a.rope_sin = ctx->rope_sin;
+            a.positions = ctx->d_positions;
+            a.slots = ctx->d_slots;
+            a.active = ctx->d_active;
+            a.kv = kvg;
+            a.layer = l;
+            a.heads = d.heads;
+            a.kv_heads = d.kv_heads;
+            a.head_dim = d.head_dim;
+            a.dim = dim;
+            a.nsplit = attn_splits_for_width(ctx, n);
+            a.append = 0;
+            a.partial = ctx->att_partial;
+            a.counters = ctx->att_count;
+            JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, false), "attention");
+        }
+        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->x, ctx->x, launches))) return rc;
+        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, ffn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
+                  "rmsnorm");
+        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_GATE][l], ctx->xb, n, ctx->hb, nullptr, launches))) return rc;
+        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_UP][l], ctx->xb, n, ctx->hb2, nullptr, launches))) return rc;
+        JL_LAUNCH(ctx, swiglu_rows_launch(ctx->hb, ctx->hb2, d.hidden, n, ctx->stream), "swiglu");
+        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->x, ctx->x, launches))) return rc;
+    }
+    if (with_logits) {
+        const float *out_norm = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
+        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, out_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
+                  "rmsnorm");
+        if ((rc = launch_gemm(ctx, wcls_of(ctx), ctx->xb, n, ctx->logits, nullptr, launches))) return rc;
+        JL_LAUNCH(ctx, argmax_rows_launch(ctx->logits, d.vocab, n, ctx->d_active, ctx->d_out, ctx->stream), "argmax");
+    }
+    return JL_OK;
+}
+
 // Enqueues the kernels of one decode step for `width` batch rows on ctx->stream.
 // Order of operations per layer: backend/cpu/InferenceCore.java:72-141 of the reference.
 int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_t *launches) {
@@ -420,7 +518,8 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.kv_heads = d.kv_heads;
             a.head_dim = d.head_dim;
             a.dim = dim;
-            a.nsplit = ctx->attn_nsplit;
+            a.nsplit = attn_splits_for_width(ctx, width);
+            a.append = 1;
             a.partial = ctx->att_partial;
             a.counters = ctx->att_count;
             e = attention_launch(a, width, ctx->stream, ctx->use_pdl);
@@ -500,10 +599,13 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
 // Runs one step: replays the captured graph for this width, capturing it on first use.
 int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     if (width == 1 && ctx->tok_ok) return launch_token_kernel(ctx, with_logits, advance);
-    const int key = width * 4 + (with_logits ? 1 : 0) + (advance ? 2 : 0);
+    static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 16; }();
+    const bool rows_path = width >= rows_min && !advance;
+    const int key = width * 8 + (with_logits ? 1 : 0) + (advance ? 2 : 0) + (rows_path ? 4 : 0);
     uint64_t launches = 0;
     if (!ctx->use_graph) {
-        int rc = enqueue_step(ctx, width, with_logits, advance, &launches);
+        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, &launches)
+                           : enqueue_step(ctx, width, with_logits, advance, &launches);
         ctx->counters.kernel_launches += launches;
         return rc;
     }
@@ -511,7 +613,8 @@ int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     if (it == ctx->graphs.end()) {
         cudaGraph_t graph = nullptr;
         JL_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-        int rc = enqueue_step(ctx, width, with_logits, advance, &launches);
+        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, &launches)
+                           : enqueue_step(ctx, width, with_logits, advance, &launches);
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
         if (rc) {
             if (graph) cudaGraphDestroy(graph);
@@ -534,7 +637,7 @@ int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
 }
 
 int check_status(jl_ctx *ctx) {
-    int st = ctx->h_stage[5 * ctx->desc.max_batch];
+    int st = ctx->h_stage[5 * ctx->row_cap];
     if (st == kDevTimeout) {
         cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
         return fail(ctx, JL_ERR_TIMEOUT, "a kernel gave up waiting for an asynchronous copy");
@@ -582,6 +685,7 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     if (e == cudaSuccess) e = gemv_configure();
     if (e == cudaSuccess) e = attention_configure();
     if (e == cudaSuccess) e = token_kernel_configure();
+    if (e == cudaSuccess) e = gemm_tc_configure();
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->d_status), sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
     if (e != cudaSuccess) {
@@ -738,43 +842,49 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     if (ctx->finalized) return JL_OK;
     cudaSetDevice(ctx->device);
     const size_t B = d.max_batch;
+    constexpr int kPrefillChunk = 256;
+    ctx->row_cap = d.max_batch > kPrefillChunk ? d.max_batch : kPrefillChunk;
+    const size_t R = ctx->row_cap;
     int rc;
     size_t ws = 0;
     auto alloc = [&](void **p, size_t bytes) {
         ws += bytes;
         return dev_alloc(ctx, p, bytes);
     };
-    // A single-row step has (pos+1) keys to cover with ~2 CTAs per SM; wider batches already
-    // fill the grid with rows.
-    int nsplit = (2 * ctx->sm_count + int(B) * d.kv_heads - 1) / (int(B) * d.kv_heads);
-    if (nsplit > 32) nsplit = 32;
-    if (nsplit < 1) nsplit = 1;
-    ctx->attn_nsplit = nsplit;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->x), B * d.dim * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->q), B * d.dim * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->k), B * ctx->kv_dim * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->v), B * ctx->kv_dim * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->xb), B * d.dim * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb), B * d.hidden * 4))) return rc;
+    // Key-range splits per launch width: a single row has (pos+1) keys to spread over ~2 CTAs per
+    // SM; wide launches already fill the grid with rows.
+    size_t max_row_splits = 1;
+    for (int w = 1; w <= int(R); ++w) {
+        const size_t v = size_t(w) * size_t(attn_splits_for_width(ctx, w));
+        if (v > max_row_splits) max_row_splits = v;
+    }
+    ctx->attn_nsplit = attn_splits_for_width(ctx, 1);
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->x), R * d.dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->q), R * d.dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->k), R * ctx->kv_dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->v), R * ctx->kv_dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->xb), R * d.dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb), R * d.hidden * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb2), R * d.hidden * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->logits), B * d.vocab * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_tokens), B * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_positions), B * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_slots), B * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_out), B * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_active), B))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_tokens), R * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_positions), R * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_slots), R * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_out), R * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_active), R))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_partial),
-                    attention_partial_floats(int(B), d.heads, nsplit, d.head_dim) * 4)))
+                    max_row_splits * d.heads * (d.head_dim + 2) * 4)))
         return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_count), B * d.kv_heads * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_count), R * d.kv_heads * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_val), B * ctx->sm_count * 16))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_idx), B * ctx->sm_count * 16))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_count), B * 4))) return rc;
-    JL_CUDA(ctx, cudaMemsetAsync(ctx->att_count, 0, B * d.kv_heads * 4, ctx->stream));
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->att_count, 0, R * d.kv_heads * 4, ctx->stream));
     JL_CUDA(ctx, cudaMemsetAsync(ctx->amax_count, 0, B * 4, ctx->stream));
-    JL_CUDA(ctx, cudaMemsetAsync(ctx->d_active, 0, B, ctx->stream));
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->d_active, 0, R, ctx->stream));
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     ctx->h_stage = nullptr;
-    JL_CUDA(ctx, cudaMallocHost(reinterpret_cast<void **>(&ctx->h_stage), (5 * B + 1) * 4));
+    JL_CUDA(ctx, cudaMallocHost(reinterpret_cast<void **>(&ctx->h_stage), (5 * R + 1) * 4));
     JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     ctx->counters.workspace_bytes = ws;
     if ((rc = build_token_ops(ctx))) return rc;
@@ -905,7 +1015,7 @@ int32_t jl_decode(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32
     int rc = validate_rows(ctx, width, tokens, positions, kv_slots, active);
     if (rc) return rc;
     cudaSetDevice(ctx->device);
-    const size_t B = ctx->desc.max_batch;
+    const size_t B = ctx->row_cap;
     int32_t *h_tok = ctx->h_stage, *h_pos = h_tok + B, *h_slot = h_pos + B, *h_out = h_slot + B;
     uint8_t *h_act = reinterpret_cast<uint8_t *>(h_out + B);
     int32_t *h_status = ctx->h_stage + 5 * B;
@@ -952,29 +1062,52 @@ int32_t jl_prefill(jl_ctx *ctx, int32_t kv_slot, const int32_t *tokens, int32_t 
                "tokens must not be NULL, n and start_pos must not be negative");
     if (n == 0) return JL_OK;
     cudaSetDevice(ctx->device);
-    const size_t B = ctx->desc.max_batch;
+    const size_t B = ctx->row_cap;
     int32_t *h_tok = ctx->h_stage, *h_pos = h_tok + B, *h_slot = h_pos + B, *h_out = h_slot + B;
     uint8_t *h_act = reinterpret_cast<uint8_t *>(h_out + B);
     int32_t *h_status = ctx->h_stage + 5 * B;
     JL_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
-    // Token-at-a-time through the decode kernels without the vocabulary projection; the values
-    // are those of batchForwardJavaPrefill, which is the per-token layer stack row by row.
-    for (int i = 0; i < n; ++i) {
-        const int32_t one_tok = tokens[i], one_pos = start_pos + i;
+    {
+        const int32_t first = tokens[0], last_pos = start_pos + n - 1;
         const uint8_t on = 1;
-        int rc = validate_rows(ctx, 1, &one_tok, &one_pos, &kv_slot, &on);
+        int rc = validate_rows(ctx, 1, &first, &last_pos, &kv_slot, &on);
         if (rc) return rc;
-        h_tok[0] = one_tok;
-        h_pos[0] = one_pos;
-        h_slot[0] = kv_slot;
-        h_act[0] = 1;
-        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_tokens, h_tok, 4, cudaMemcpyHostToDevice, ctx->stream));
-        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_positions, h_pos, 4, cudaMemcpyHostToDevice, ctx->stream));
-        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_slots, h_slot, 4, cudaMemcpyHostToDevice, ctx->stream));
-        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_active, h_act, 1, cudaMemcpyHostToDevice, ctx->stream));
-        if ((rc = run_step(ctx, 1, false, false))) return rc;
-        // The staging words are reused by the next token's copies.
+        for (int i = 0; i < n; ++i)
+            JL_REQUIRE(ctx, tokens[i] >= 0 && tokens[i] < ctx->desc.vocab, JL_ERR_INVALID,
+                       "prompt token %d = %d outside vocabulary of %d", i, tokens[i], ctx->desc.vocab);
+    }
+    static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 16; }();
+    // Chunks of up to row_cap tokens through the tensor-core path (every projection one
+    // matrix-matrix launch, as TornadoBatchPrefillPass does per chunk,
+    // backend/tornado/TornadoBatchPrefillPass.java:104-141); a short tail goes token by token.
+    // The values are those of batchForwardJavaPrefill: the per-token layer stack, no logits.
+    int done = 0;
+    while (done < n) {
+        int chunk = n - done;
+        if (chunk > ctx->row_cap) chunk = ctx->row_cap;
+        if (chunk < rows_min) chunk = 1;
+        for (int i = 0; i < chunk; ++i) {
+            h_tok[i] = tokens[done + i];
+            h_pos[i] = start_pos + done + i;
+            h_slot[i] = kv_slot;
+            h_act[i] = 1;
+        }
+        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_tokens, h_tok, chunk * 4, cudaMemcpyHostToDevice, ctx->stream));
+        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_positions, h_pos, chunk * 4, cudaMemcpyHostToDevice, ctx->stream));
+        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_slots, h_slot, chunk * 4, cudaMemcpyHostToDevice, ctx->stream));
+        JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_active, h_act, chunk, cudaMemcpyHostToDevice, ctx->stream));
+        int rc;
+        if (chunk == 1) {
+            rc = run_step(ctx, 1, false, false);
+        } else {
+            uint64_t launches = 0;
+            rc = enqueue_rows_step(ctx, chunk, false, &launches);
+            ctx->counters.kernel_launches += launches;
+        }
+        if (rc) return rc;
+        // The staging words are reused by the next chunk's copies.
         JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        done += chunk;
     }
     JL_CUDA(ctx, cudaMemcpyAsync(h_status, ctx->d_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
     JL_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
@@ -1020,7 +1153,7 @@ int32_t jl_generate(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int
         ctx->history_cap = need;
     }
     if (!ctx->d_step && (rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_step), 4))) return rc;
-    const size_t B = ctx->desc.max_batch;
+    const size_t B = ctx->row_cap;
     int32_t *h_tok = ctx->h_stage, *h_pos = h_tok + B, *h_slot = h_pos + B, *h_out = h_slot + B;
     uint8_t *h_act = reinterpret_cast<uint8_t *>(h_out + B);
     int32_t *h_status = ctx->h_stage + 5 * B;

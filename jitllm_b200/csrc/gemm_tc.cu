@@ -313,13 +313,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmArgs
 
 template <int TYPE, int NT>
 cudaError_t launch_nt(const GemmArgs &a, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             GemmSmem<NT>::total);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
     dim3 grid((a.rows + kTileM - 1) / kTileM, (a.n + NT - 1) / NT);
     gemm_tc_kernel<TYPE, NT><<<grid, kGemmThreads, GemmSmem<NT>::total, stream>>>(a);
     return cudaGetLastError();
@@ -333,7 +326,23 @@ cudaError_t launch_type(const GemmArgs &a, cudaStream_t stream) {
     return launch_nt<TYPE, 128>(a, stream);
 }
 
+template <int TYPE>
+cudaError_t configure_type() {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<16>::total)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<32>::total)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<64>::total)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(gemm_tc_kernel<TYPE, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::total);
+}
+
 }  // namespace
+
+cudaError_t gemm_tc_configure() {
+    cudaError_t e;
+    if ((e = configure_type<kQ4_K>()) != cudaSuccess) return e;
+    if ((e = configure_type<kQ4_0>()) != cudaSuccess) return e;
+    return configure_type<kQ8_0>();
+}
 
 cudaError_t gemm_tc_launch(const GemmArgs &a, cudaStream_t stream) {
     if (a.cols <= 0 || a.cols % 256 != 0 || a.rows <= 0 || a.n <= 0) return cudaErrorInvalidValue;

@@ -16,6 +16,8 @@ struct GemmArgs {
     int *status;       // device status word
 };
 
+// Sets the shared-memory attribute of every instantiation (call once, outside stream capture).
+cudaError_t gemm_tc_configure();
 cudaError_t gemm_tc_launch(const GemmArgs &args, cudaStream_t stream);
 
 }  // namespace jl

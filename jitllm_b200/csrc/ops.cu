@@ -51,7 +51,6 @@ __global__ void advance_kernel(int32_t *tokens, int32_t *positions, const int32_
     if (b == 0) *step_counter = step + 1;
 }
 
-// ---- RoPE + KV append + paged decode attention -------------------------------------------------
 __device__ __forceinline__ int64_t kv_offset(const KvGeom &g, int slot, int pos, int layer) {
     const int blk = pos / g.block_tokens;
     const int within = pos - blk * g.block_tokens;
@@ -60,6 +59,100 @@ __device__ __forceinline__ int64_t kv_offset(const KvGeom &g, int slot, int pos,
     return phys * block_stride + int64_t(layer) * g.block_tokens * g.kv_dim +
            int64_t(within) * g.kv_dim;
 }
+
+// ---- row-wise operators for the matrix-matrix path ---------------------------------------------
+__global__ void rmsnorm_rows_kernel(const float *x, const float *w, float eps, float *out, int dim,
+                                    const uint8_t *active) {
+    const int row = blockIdx.x;
+    if (active != nullptr && active[row] == 0) return;
+    __shared__ float part[9];
+    const float *xr = x + size_t(row) * dim;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) s += xr[i] * xr[i];
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int i = 0; i < int(blockDim.x >> 5); ++i) tot += part[i];
+        float ms = tot / static_cast<float>(dim);
+        ms += eps;
+        part[8] = static_cast<float>(1.0 / sqrt(static_cast<double>(ms)));
+    }
+    __syncthreads();
+    const float ss = part[8];
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        out[size_t(row) * dim + i] = __fmul_rn(w[i], __fmul_rn(ss, xr[i]));
+}
+
+__global__ void swiglu_rows_kernel(float *g, const float *u, size_t total) {
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const float v = g[i];
+        g[i] = (v / (1.0f + expf(-v))) * u[i];
+    }
+}
+
+__global__ void kv_append_kernel(const float *k, const float *v, const float *rope_cos, const float *rope_sin,
+                                 const int32_t *positions, const int32_t *slots, const uint8_t *active,
+                                 KvGeom kv, int layer, int head_dim) {
+    const int row = blockIdx.x;
+    if (active != nullptr && active[row] == 0) return;
+    const int pos = positions[row], slot = slots[row];
+    const int64_t off = kv_offset(kv, slot, pos, layer);
+    const float *kr = k + size_t(row) * kv.kv_dim, *vr = v + size_t(row) * kv.kv_dim;
+    const int half = head_dim / 2;
+    for (int p = threadIdx.x; p < kv.kv_dim / 2; p += blockDim.x) {
+        const int i = p % half;
+        const float cr = rope_cos[size_t(pos) * half + i], ci = rope_sin[size_t(pos) * half + i];
+        const float v0 = kr[2 * p], v1 = kr[2 * p + 1];
+        kv.kpool[off + 2 * p] = __float2half_rn(__fsub_rn(__fmul_rn(v0, cr), __fmul_rn(v1, ci)));
+        kv.kpool[off + 2 * p + 1] = __float2half_rn(__fadd_rn(__fmul_rn(v0, ci), __fmul_rn(v1, cr)));
+        kv.vpool[off + 2 * p] = __float2half_rn(vr[2 * p]);
+        kv.vpool[off + 2 * p + 1] = __float2half_rn(vr[2 * p + 1]);
+    }
+}
+
+__global__ void argmax_rows_kernel(const float *logits, int vocab, const uint8_t *active, int32_t *out) {
+    const int row = blockIdx.x;
+    if (active != nullptr && active[row] == 0) return;
+    const float *lr = logits + size_t(row) * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = lr[i];
+        if (v > bv) {  // strided scan visits indices in increasing order per thread
+            bv = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = bv;
+        si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < int(blockDim.x >> 5); ++w)
+            if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) {
+                bv = sv[w];
+                bi = si[w];
+            }
+        out[row] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+// ---- RoPE + KV append + paged decode attention -------------------------------------------------
 
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
@@ -121,7 +214,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         q_s[g][2 * i] = __fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]));
         q_s[g][2 * i + 1] = __fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]));
     }
-    if (start <= pos && pos < end) {
+    if (a.append && start <= pos && pos < end) {
         // This CTA owns the new position: rotate k, round k and v to fp16, append to the page.
         const int64_t off = kv_offset(a.kv, slot, pos, a.layer) + int64_t(kvh) * HD;
         const float *kh = a.k + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
@@ -388,6 +481,33 @@ cudaError_t advance_launch(int32_t *tokens, int32_t *positions, const int32_t *s
     cfg.numAttrs = programmatic ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, advance_kernel, tokens, positions, sampled, active, history,
                               step_counter, width);
+}
+
+cudaError_t rmsnorm_rows_launch(const float *x, const float *w, float eps, float *out, int dim, int n,
+                                const uint8_t *active, cudaStream_t stream) {
+    rmsnorm_rows_kernel<<<n, 256, 0, stream>>>(x, w, eps, out, dim, active);
+    return cudaGetLastError();
+}
+
+cudaError_t swiglu_rows_launch(float *g, const float *u, int hidden, int n, cudaStream_t stream) {
+    const size_t total = size_t(hidden) * n;
+    const int grid = static_cast<int>((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
+    swiglu_rows_kernel<<<grid, 256, 0, stream>>>(g, u, total);
+    return cudaGetLastError();
+}
+
+cudaError_t kv_append_launch(const float *k, const float *v, const float *rope_cos, const float *rope_sin,
+                             const int32_t *positions, const int32_t *slots, const uint8_t *active,
+                             KvGeom kv, int layer, int head_dim, int n, cudaStream_t stream) {
+    kv_append_kernel<<<n, 256, 0, stream>>>(k, v, rope_cos, rope_sin, positions, slots, active, kv, layer,
+                                            head_dim);
+    return cudaGetLastError();
+}
+
+cudaError_t argmax_rows_launch(const float *logits, int vocab, int n, const uint8_t *active, int32_t *out,
+                               cudaStream_t stream) {
+    argmax_rows_kernel<<<n, 1024, 0, stream>>>(logits, vocab, active, out);
+    return cudaGetLastError();
 }
 
 cudaError_t fill_launch(uint32_t *buf, size_t words, uint32_t value, cudaStream_t stream) {

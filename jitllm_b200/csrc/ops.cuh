@@ -24,6 +24,7 @@ struct AttnArgs {
     KvGeom kv;
     int layer, heads, kv_heads, head_dim, dim;
     int nsplit;
+    int append;  // 1: the CTA owning the new position rotates k and appends k,v; 0: pages already hold it
     float *partial;     // scratch [width][heads][nsplit][head_dim + 2]
     unsigned *counters; // scratch [width][kv_heads], zero between launches
 };
@@ -46,6 +47,21 @@ cudaError_t dequant_launch(int type, const uint8_t *blocks, int64_t n, float *ou
 cudaError_t advance_launch(int32_t *tokens, int32_t *positions, const int32_t *sampled,
                            const uint8_t *active, int32_t *history, int32_t *step_counter, int width,
                            cudaStream_t stream, bool programmatic);
+
+// Row-wise operators for the matrix-matrix (prefill / wide batch) path.
+// out[r] = w * (rsqrt(mean(x[r]^2) + eps) * x[r])   (inference/op/CpuOperations.java:55-73)
+cudaError_t rmsnorm_rows_launch(const float *x, const float *w, float eps, float *out, int dim, int n,
+                                const uint8_t *active, cudaStream_t stream);
+// g[r] = silu(g[r]) * u[r]                          (inference/op/CpuOperations.java:255-260)
+cudaError_t swiglu_rows_launch(float *g, const float *u, int hidden, int n, cudaStream_t stream);
+// RoPE on k, then k and v rounded to fp16 into the page of (slot, position) of every row
+// (inference/op/CpuOperations.java:94-147).
+cudaError_t kv_append_launch(const float *k, const float *v, const float *rope_cos, const float *rope_sin,
+                             const int32_t *positions, const int32_t *slots, const uint8_t *active,
+                             KvGeom kv, int layer, int head_dim, int n, cudaStream_t stream);
+// out[r] = first index of the maximum of logits[r]  (inference/Logits.java:49-60)
+cudaError_t argmax_rows_launch(const float *logits, int vocab, int n, const uint8_t *active, int32_t *out,
+                               cudaStream_t stream);
 
 cudaError_t fill_launch(uint32_t *buf, size_t words, uint32_t value, cudaStream_t stream);
 

@@ -190,3 +190,51 @@ def test_device_resident_generation_equals_host_driven_steps(dev, oracle):
             assert hist[step, b] == tok, (b, step)
     with pytest.raises(ValueError, match="run past context"):
         p.executor.generate(jl.BatchSlots([True, True], first, [90, 0], [0, 1]), 10)
+
+
+@pytest.mark.parametrize("t", FORMATS)
+def test_chunked_prefill_on_the_tensor_core_path(dev, oracle, t):
+    """A 40-token prompt goes through the matrix-matrix pipeline (one chunk), then decode steps:
+    logits after the prompt must agree with the oracle fed token by token. fp16 weight rounding in
+    the tensor-core operands is the extra error source here (per-matmul bar 1e-3)."""
+    cfg = small_config(layers=2, ctx=96)
+    p = Pair(dev, oracle, cfg, t, seed=91, std=0.05)
+    prompt = [int(v) for v in np.random.default_rng(12).integers(0, cfg.vocabularySize, size=41)]
+    for pos, tok in enumerate(prompt[:-1]):
+        p.oracle_model.forward_no_logits(tok, pos)
+    p.boundary.prefill(prompt[:-1], 0)
+    for l in range(cfg.numberOfLayers):
+        for pos in (0, 17, 39):
+            ok, _ = _half_close(p.kv.readRow("k", 0, l, pos), p.oracle_model.kcache(l, pos), abs_frac=4e-3)
+            assert ok, ("k", l, pos)
+    tok = prompt[-1]
+    for pos in range(40, 48):
+        want = p.oracle_model.forward(tok, pos)
+        got = p.boundary.invoke(tok, pos)
+        assert float(np.max(np.abs(got.logits - want))) < LOGIT_BAR
+        assert rel_l2(got.logits, want) < 2e-3
+        tok = int(np.argmax(want))
+
+
+def test_wide_batch_decode_on_the_tensor_core_path(dev, oracle):
+    cfg = small_config(layers=2, ctx=64)
+    width = 16
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=93, max_batch=width, std=0.05)
+    seqs = [p.new_oracle_sequence() for _ in range(width)]
+    rng = np.random.default_rng(13)
+    positions = [0] * width
+    for step in range(6):
+        active = [not (b == 5 and step >= 3) for b in range(width)]
+        toks = [int(v) for v in rng.integers(0, cfg.vocabularySize, size=width)]
+        out, logits = p.executor.decodeStep(jl.BatchSlots(active, toks, positions, list(range(width))), wantLogits=True)
+        for b in range(width):
+            if not active[b]:
+                assert out[b] == -1
+                continue
+            want = seqs[b].forward(toks[b], positions[b])
+            assert float(np.max(np.abs(logits[b] - want))) < LOGIT_BAR
+            assert rel_l2(logits[b], want) < 2e-3
+            top2 = np.partition(want, -2)[-2:]
+            if top2[1] - top2[0] > 5e-3:
+                assert out[b] == int(np.argmax(want))
+            positions[b] += 1
