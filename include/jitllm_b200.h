@@ -177,6 +177,21 @@ int32_t jl_get_counters(jl_ctx *ctx, jl_counters *out);
 /* Overwrites a 256 MiB scratch buffer (larger than L2) so that the next kernel starts cold. */
 int32_t jl_flush_l2(jl_ctx *ctx);
 
+/* ---- tensor parallelism (the reference has none; the nearest seam is the plan's per-layer task
+ * graphs, backend/tornado/layers/LogitsQ8_0Layer.java:40-56 and docs/architecture/execution.md,
+ * which run on one device). One context per GPU, one process per context. With tp_size > 1 in
+ * jl_model_desc the host uploads this rank's shard of every matrix: rows [r*R/tp, (r+1)*R/tp) of
+ * wq, wk, wv, w1 (gate), w3 (up) and the vocabulary matrix; columns [r*C/tp, (r+1)*C/tp) of wo and
+ * w2 (down), cut on 256-column boundaries so that quantised super-blocks stay whole; norms, RoPE
+ * tables and the token embedding in full. Each step then sums the two row-parallel partial results
+ * per layer with an NCCL all-reduce on the context's stream and picks the token as the first
+ * maximum over the ranks' vocabulary shards.
+ * jl_tp_unique_id: rank 0 fills id128 (128 bytes, an ncclUniqueId) for the host to broadcast.
+ * jl_tp_init: every rank, after jl_model_create and before jl_model_finalize; collective.
+ * nccl_path: the NCCL shared library to bind at run time, or NULL for "libnccl.so.2". */
+int32_t jl_tp_unique_id(jl_ctx *ctx, const char *nccl_path, void *id128);
+int32_t jl_tp_init(jl_ctx *ctx, const char *nccl_path, const void *id128, int32_t rank, int32_t size);
+
 /* ---- allocation-free operator (no counterpart in the reference: its kernels take whatever
  * scratch the TornadoVM runtime allocates for them).
  * y_dev[rows] = W . x (x optionally RMS-normalised with norm_w_dev / rms_eps first) and

@@ -22,3 +22,4 @@ from .api import (  # noqa: F401
     synth_model_tensors,
     synth_tensor,
 )
+from .tensor_parallel import TensorParallel, local_shape, shard_tensor, torch_broadcast  # noqa: F401,E402

@@ -28,6 +28,7 @@ from typing import Dict, Optional, Sequence, Tuple
 import numpy as np
 
 from . import _lib
+from .tensor_parallel import TensorParallel, check_divisible, init_group, local_shape, shard_tensor
 
 
 class IllegalStateError(RuntimeError):
@@ -325,21 +326,26 @@ class KvStorage:
 class B200Model:
     """Device-resident weights + per-step workspace of one Llama-architecture model."""
 
-    def __init__(self, dev: Device, config: Configuration, maxBatch: int = 1):
+    def __init__(self, dev: Device, config: Configuration, maxBatch: int = 1,
+                 tp: Optional[TensorParallel] = None):
         self.dev = dev
         self.config = config
         self.maxBatch = maxBatch
+        self.tp = tp or TensorParallel()
+        check_divisible(config, self.tp.size)
         d = _lib.JlModelDesc(
             dim=config.dim, hidden=config.hiddenDim, layers=config.numberOfLayers,
             heads=config.numberOfHeads, kv_heads=config.numberOfKeyValueHeads,
             head_dim=config.headSize, vocab=config.vocabularySize, ctx_len=config.contextLength,
             rms_eps=config.rmsNormEps, tied_embeddings=1 if config.tiedEmbeddings else 0,
-            max_batch=maxBatch, tp_rank=0, tp_size=1)
+            max_batch=maxBatch, tp_rank=self.tp.rank, tp_size=self.tp.size)
         dev._check(dev._lib.jl_model_create(dev.handle, C.byref(d)))
 
     def uploadTensor(self, role: TensorRole, layer: int, ggml_type: GGMLType, data: np.ndarray) -> None:
-        rows, cols = self.config.matrix_shape(TensorRole(role))
-        data = np.ascontiguousarray(data)
+        """`data` is the whole GGUF tensor; under tensor parallelism this GPU's slice is cut here."""
+        role = TensorRole(role)
+        rows, cols = local_shape(self.config, role, self.tp.size)
+        data = np.ascontiguousarray(shard_tensor(self.config, role, ggml_type, np.ascontiguousarray(data), self.tp))
         self.dev._check(self.dev._lib.jl_upload_tensor(
             self.dev.handle, int(role), layer, int(ggml_type), rows, cols, _ptr(data), data.nbytes))
 
@@ -348,12 +354,20 @@ class B200Model:
         sin = np.ascontiguousarray(sin, dtype=np.float32)
         self.dev._check(self.dev._lib.jl_upload_rope(self.dev.handle, _ptr(cos), _ptr(sin), cos.size))
 
+    def initTensorParallel(self, broadcast) -> None:
+        """Joins the NCCL group (collective; every rank calls it between construction and finalize)."""
+        init_group(self.dev, self.tp, broadcast)
+
     def finalize(self) -> None:
         self.dev._check(self.dev._lib.jl_model_finalize(self.dev.handle))
 
+    @property
+    def localKvDim(self) -> int:
+        return self.config.kvDim // self.tp.size
+
     def createKvStorage(self, request: KvStorageRequest) -> KvStorage:
         c = self.config
-        if request.numberOfLayers != c.numberOfLayers or request.kvDim != c.kvDim:
+        if request.numberOfLayers != c.numberOfLayers or request.kvDim != self.localKvDim:
             raise ValueError("GPUL-CFG-002: KV request does not match the model's layers / kvDim")
         return KvStorage(self, request)
 
@@ -362,8 +376,9 @@ class B200Model:
 
     def debugRead(self, name: str, row: int = 0) -> np.ndarray:
         c = self.config
-        n = {"x": c.dim, "q": c.dim, "xb": c.dim, "k": c.kvDim, "v": c.kvDim,
-             "hb": c.hiddenDim, "logits": c.vocabularySize}[name]
+        t = self.tp.size
+        n = {"x": c.dim, "q": c.dim // t, "xb": c.dim, "k": c.kvDim // t, "v": c.kvDim // t,
+             "hb": c.hiddenDim // t, "logits": c.vocabularySize // t}[name]
         out = np.empty(n, dtype=np.float32)
         self.dev._check(self.dev._lib.jl_debug_read(self.dev.handle, name.encode(), row, _ptr(out), n))
         return out
@@ -519,11 +534,17 @@ def synth_model_tensors(config: Configuration, ggml_type: GGMLType, seed: int, s
 
 
 def load_model(dev: Device, config: Configuration, tensors, rope_cos: np.ndarray, rope_sin: np.ndarray,
-               maxBatch: int = 1) -> B200Model:
-    model = B200Model(dev, config, maxBatch)
+               maxBatch: int = 1, tp: Optional[TensorParallel] = None, broadcast=None) -> B200Model:
+    """`tensors` holds whole tensors; with `tp` each GPU keeps its slice and `broadcast` carries the
+    NCCL id between the ranks (see tensor_parallel.init_group)."""
+    model = B200Model(dev, config, maxBatch, tp)
     for (role, layer), (t, data) in tensors.items():
         model.uploadTensor(role, layer if role not in GLOBAL_ROLES else -1, t, data)
     model.uploadRope(rope_cos, rope_sin)
+    if model.tp.size > 1:
+        if broadcast is None:
+            raise ValueError("GPUL-CFG-002: tensor parallelism needs a broadcast channel for the NCCL id")
+        model.initTensorParallel(broadcast)
     model.finalize()
     return model
 

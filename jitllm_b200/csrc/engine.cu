@@ -2,6 +2,10 @@
 // include/jitllm_b200.h. Host-side logic only; the kernels live in gemv.cu / ops.cu.
 #include "../../include/jitllm_b200.h"
 
+#include <dlfcn.h>
+
+#include <set>
+
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -73,6 +77,15 @@ struct jl_ctx {
     unsigned *amax_count = nullptr;
     int *d_status = nullptr;
     int attn_nsplit = 1;
+    // tensor-parallel placement: local (per-GPU) extents of the sharded dimensions
+    int tp_rank = 0, tp_size = 1;
+    int l_heads = 0, l_kv_heads = 0, l_qdim = 0, l_hidden = 0, l_vocab = 0;
+    float *part = nullptr;      // row-parallel partial sums before the all-reduce, [row_cap][dim]
+    float *best = nullptr;      // local (value, index) of the arg-max and the gathered pairs
+    std::set<int> tp_warm;        // step shapes that have run once uncaptured
+    float *logits_all = nullptr;  // [rank][row][l_vocab], only when the host asks for logits
+    void *nccl_lib = nullptr;   // dlopen handle
+    void *nccl_comm = nullptr;  // ncclComm_t
     int row_cap = 1;        // rows the step buffers hold: max(max_batch, prefill chunk)
     float *hb2 = nullptr;   // second FFN buffer of the matrix-matrix path (up projection)
     int32_t *d_history = nullptr, *d_step = nullptr;
@@ -141,6 +154,48 @@ int dev_alloc(jl_ctx *ctx, void **p, size_t bytes) {
         return fail(ctx, e == cudaErrorMemoryAllocation ? JL_ERR_OOM : JL_ERR_CUDA,
                     "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
     }
+    return JL_OK;
+}
+
+
+// ---- NCCL, bound at run time (the library itself does not link against it) ---------------------
+struct NcclId {
+    char b[128];
+};
+struct NcclApi {
+    int (*GetUniqueId)(NcclId *);
+    int (*CommInitRank)(void **, int, NcclId, int);
+    int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t);
+    int (*AllGather)(const void *, void *, size_t, int, void *, cudaStream_t);
+    int (*CommDestroy)(void *);
+    const char *(*GetErrorString)(int);
+};
+NcclApi g_nccl = {};
+constexpr int kNcclFloat32 = 7, kNcclSum = 0;
+
+int nccl_bind(jl_ctx *ctx, const char *path) {
+    if (ctx->nccl_lib) return JL_OK;
+    void *h = dlopen(path && *path ? path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return fail(ctx, JL_ERR_STATE, "cannot load NCCL (%s)", dlerror());
+    g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+    g_nccl.CommInitRank = reinterpret_cast<decltype(g_nccl.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+    g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(dlsym(h, "ncclAllReduce"));
+    g_nccl.AllGather = reinterpret_cast<decltype(g_nccl.AllGather)>(dlsym(h, "ncclAllGather"));
+    g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+    g_nccl.GetErrorString = reinterpret_cast<decltype(g_nccl.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.AllGather ||
+        !g_nccl.CommDestroy || !g_nccl.GetErrorString) {
+        dlclose(h);
+        return fail(ctx, JL_ERR_STATE, "the NCCL library at '%s' lacks a required symbol", path ? path : "");
+    }
+    ctx->nccl_lib = h;
+    return JL_OK;
+}
+
+// Sum of `count` floats over the tensor-parallel group, in place, on the context's stream.
+int tp_all_reduce(jl_ctx *ctx, float *buf, size_t count) {
+    const int rc = g_nccl.AllReduce(buf, buf, count, kNcclFloat32, kNcclSum, ctx->nccl_comm, ctx->stream);
+    if (rc != 0) return fail(ctx, JL_ERR_CUDA, "ncclAllReduce failed: %s", g_nccl.GetErrorString(rc));
     return JL_OK;
 }
 
@@ -221,6 +276,11 @@ void free_model(jl_ctx *ctx) {
     ctx->amax_val = nullptr;
     ctx->amax_idx = nullptr;
     ctx->amax_count = nullptr;
+    if (ctx->part) cudaFree(ctx->part);
+    if (ctx->best) cudaFree(ctx->best);
+    if (ctx->logits_all) cudaFree(ctx->logits_all);
+    ctx->part = ctx->best = ctx->logits_all = nullptr;
+    ctx->tp_warm.clear();
     if (ctx->d_layers) cudaFree(ctx->d_layers);
     ctx->d_layers = nullptr;
     if (ctx->tok_partial) cudaFree(ctx->tok_partial);
@@ -250,9 +310,18 @@ void free_kv(jl_ctx *ctx) {
     ctx->counters.kv_bytes = 0;
 }
 
-const DevTensor &wcls_of(const jl_ctx *ctx) {
-    return ctx->global[JL_ROLE_OUTPUT].data ? ctx->global[JL_ROLE_OUTPUT]
-                                            : ctx->global[JL_ROLE_TOKEN_EMBEDDING];
+// The vocabulary projection of this GPU: output.weight, or -- tied embeddings -- this GPU's row
+// range of the (replicated) embedding table.
+DevTensor wcls_of(const jl_ctx *ctx) {
+    if (ctx->global[JL_ROLE_OUTPUT].data) return ctx->global[JL_ROLE_OUTPUT];
+    DevTensor t = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
+    if (ctx->tp_size > 1) {
+        const size_t rb = size_t(row_bytes(t.type, t.cols));
+        t.data += size_t(ctx->tp_rank) * ctx->l_vocab * rb;
+        t.rows = ctx->l_vocab;
+        t.bytes = size_t(ctx->l_vocab) * rb;
+    }
+    return t;
 }
 
 // One quantised matrix-vector launch for batch row `row`.
@@ -275,7 +344,7 @@ int launch_gemv(jl_ctx *ctx, GemvArgs &a, int total_rows, uint64_t *launches) {
 int build_token_ops(jl_ctx *ctx) {
     const jl_model_desc &d = ctx->desc;
     ctx->tok_ok = false;
-    if (!ctx->use_token_kernel) return JL_OK;
+    if (!ctx->use_token_kernel || ctx->tp_size > 1) return JL_OK;
     const int type = ctx->layer[JL_ROLE_ATTENTION_QUERY][0].type;
     for (int l = 0; l < d.layers; ++l)
         for (int r : {JL_ROLE_ATTENTION_QUERY, JL_ROLE_ATTENTION_OUTPUT, JL_ROLE_FFN_GATE, JL_ROLE_FFN_DOWN})
@@ -365,8 +434,35 @@ int launch_token_kernel(jl_ctx *ctx, bool with_logits, bool advance) {
     return JL_OK;
 }
 
+// Row-parallel epilogue under tensor parallelism: all-reduce the partial projections of `n` rows
+// and add the sum into the residual stream (one NCCL all-reduce per sublayer).
+int tp_reduce_into_x(jl_ctx *ctx, int n, uint64_t *launches) {
+    int rc = tp_all_reduce(ctx, ctx->part, size_t(n) * ctx->desc.dim);
+    if (rc) return rc;
+    cudaError_t e = add_rows_launch(ctx->x, ctx->part, size_t(n) * ctx->desc.dim, ctx->stream);
+    if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "residual add launch failed: %s", cudaGetErrorString(e));
+    ++*launches;
+    return JL_OK;
+}
+
+// Each GPU holds the arg-max of its vocabulary shard; gather (value, global index) pairs and keep
+// the best, first index on ties (inference/Logits.java:49-60).
+int tp_global_argmax(jl_ctx *ctx, int n, uint64_t *launches) {
+    float *local = ctx->best, *all = ctx->best + 2 * size_t(ctx->row_cap);
+    cudaError_t e = tp_pack_best_launch(ctx->logits, ctx->d_out, ctx->l_vocab, ctx->tp_rank * ctx->l_vocab, n,
+                                        local, ctx->stream);
+    if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "arg-max pack launch failed: %s", cudaGetErrorString(e));
+    ++*launches;
+    const int rc = g_nccl.AllGather(local, all, size_t(2) * n, kNcclFloat32, ctx->nccl_comm, ctx->stream);
+    if (rc != 0) return fail(ctx, JL_ERR_CUDA, "ncclAllGather failed: %s", g_nccl.GetErrorString(rc));
+    e = tp_pick_best_launch(all, ctx->tp_size, n, ctx->d_active, ctx->d_out, ctx->stream);
+    if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "arg-max pick launch failed: %s", cudaGetErrorString(e));
+    ++*launches;
+    return JL_OK;
+}
+
 int attn_splits_for_width(const jl_ctx *ctx, int width) {
-    int n = (2 * ctx->sm_count + width * ctx->desc.kv_heads - 1) / (width * ctx->desc.kv_heads);
+    int n = (2 * ctx->sm_count + width * ctx->l_kv_heads - 1) / (width * ctx->l_kv_heads);
     if (n > 32) n = 32;
     if (n < 1) n = 1;
     return n;
@@ -433,30 +529,41 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, uint64_t *launches) 
             a.active = ctx->d_active;
             a.kv = kvg;
             a.layer = l;
-            a.heads = d.heads;
-            a.kv_heads = d.kv_heads;
+            a.heads = ctx->l_heads;
+            a.kv_heads = ctx->l_kv_heads;
             a.head_dim = d.head_dim;
-            a.dim = dim;
+            a.dim = ctx->l_qdim;
             a.nsplit = attn_splits_for_width(ctx, n);
             a.append = 0;
             a.partial = ctx->att_partial;
             a.counters = ctx->att_count;
             JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, false), "attention");
         }
-        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->x, ctx->x, launches))) return rc;
+        if (ctx->tp_size > 1) {
+            if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->part, nullptr, launches))) return rc;
+            if ((rc = tp_reduce_into_x(ctx, n, launches))) return rc;
+        } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->x, ctx->x, launches))) {
+            return rc;
+        }
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, ffn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
                   "rmsnorm");
         if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_GATE][l], ctx->xb, n, ctx->hb, nullptr, launches))) return rc;
         if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_UP][l], ctx->xb, n, ctx->hb2, nullptr, launches))) return rc;
-        JL_LAUNCH(ctx, swiglu_rows_launch(ctx->hb, ctx->hb2, d.hidden, n, ctx->stream), "swiglu");
-        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->x, ctx->x, launches))) return rc;
+        JL_LAUNCH(ctx, swiglu_rows_launch(ctx->hb, ctx->hb2, ctx->l_hidden, n, ctx->stream), "swiglu");
+        if (ctx->tp_size > 1) {
+            if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->part, nullptr, launches))) return rc;
+            if ((rc = tp_reduce_into_x(ctx, n, launches))) return rc;
+        } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->x, ctx->x, launches))) {
+            return rc;
+        }
     }
     if (with_logits) {
         const float *out_norm = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, out_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
                   "rmsnorm");
         if ((rc = launch_gemm(ctx, wcls_of(ctx), ctx->xb, n, ctx->logits, nullptr, launches))) return rc;
-        JL_LAUNCH(ctx, argmax_rows_launch(ctx->logits, d.vocab, n, ctx->d_active, ctx->d_out, ctx->stream), "argmax");
+        JL_LAUNCH(ctx, argmax_rows_launch(ctx->logits, ctx->l_vocab, n, ctx->d_active, ctx->d_out, ctx->stream), "argmax");
+        if (ctx->tp_size > 1 && (rc = tp_global_argmax(ctx, n, launches))) return rc;
     }
     return JL_OK;
 }
@@ -465,7 +572,8 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, uint64_t *launches) 
 // Order of operations per layer: backend/cpu/InferenceCore.java:72-141 of the reference.
 int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_t *launches) {
     const jl_model_desc &d = ctx->desc;
-    const int dim = d.dim, kv_dim = ctx->kv_dim, hidden = d.hidden;
+    const int dim = d.dim, kv_dim = ctx->kv_dim, hidden = ctx->l_hidden, qdim = ctx->l_qdim;
+    const bool tp = ctx->tp_size > 1;
     const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
     cudaError_t e = embedding_launch(emb.type, emb.data, ctx->d_tokens, ctx->d_active, ctx->x, dim,
                                      width, ctx->stream, false);
@@ -488,7 +596,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
             a.nseg = 3;
-            a.seg[0] = {wq.data, ctx->q + size_t(b) * dim, nullptr, int(wq.rows)};
+            a.seg[0] = {wq.data, ctx->q + size_t(b) * qdim, nullptr, int(wq.rows)};
             a.seg[1] = {wk.data, ctx->k + size_t(b) * kv_dim, nullptr, int(wk.rows)};
             a.seg[2] = {wv.data, ctx->v + size_t(b) * kv_dim, nullptr, int(wv.rows)};
             a.cols = dim;
@@ -514,10 +622,10 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.kv = {ctx->kpool, ctx->vpool, ctx->block_table, ctx->blocks_per_slot,
                     ctx->block_tokens, d.layers, kv_dim};
             a.layer = l;
-            a.heads = d.heads;
-            a.kv_heads = d.kv_heads;
+            a.heads = ctx->l_heads;
+            a.kv_heads = ctx->l_kv_heads;
             a.head_dim = d.head_dim;
-            a.dim = dim;
+            a.dim = qdim;
             a.nsplit = attn_splits_for_width(ctx, width);
             a.append = 1;
             a.partial = ctx->att_partial;
@@ -531,14 +639,18 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             GemvArgs a = {};
             a.nseg = 1;
             float *xr = ctx->x + size_t(b) * dim;
-            a.seg[0] = {wo.data, xr, xr, int(wo.rows)};
+            if (tp)
+                a.seg[0] = {wo.data, ctx->part + size_t(b) * dim, nullptr, int(wo.rows)};
+            else
+                a.seg[0] = {wo.data, xr, xr, int(wo.rows)};
             a.cols = int(wo.cols);
             a.type = wo.type;
             a.mode = kGemvPlain;
-            a.x = ctx->xb + size_t(b) * dim;
+            a.x = ctx->xb + size_t(b) * qdim;
             a.active = ctx->d_active + b;
             if ((rc = launch_gemv(ctx, a, int(wo.rows), launches))) return rc;
         }
+        if (tp && (rc = tp_reduce_into_x(ctx, width, launches))) return rc;
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
             a.nseg = 2;
@@ -557,7 +669,10 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             GemvArgs a = {};
             a.nseg = 1;
             float *xr = ctx->x + size_t(b) * dim;
-            a.seg[0] = {w2.data, xr, xr, int(w2.rows)};
+            if (tp)
+                a.seg[0] = {w2.data, ctx->part + size_t(b) * dim, nullptr, int(w2.rows)};
+            else
+                a.seg[0] = {w2.data, xr, xr, int(w2.rows)};
             a.cols = int(w2.cols);
             a.type = w2.type;
             a.mode = kGemvPlain;
@@ -565,13 +680,14 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.active = ctx->d_active + b;
             if ((rc = launch_gemv(ctx, a, int(w2.rows), launches))) return rc;
         }
+        if (tp && (rc = tp_reduce_into_x(ctx, width, launches))) return rc;
     }
     if (with_logits) {
-        const DevTensor &wc = wcls_of(ctx);
+        const DevTensor wc = wcls_of(ctx);
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
             a.nseg = 1;
-            a.seg[0] = {wc.data, ctx->logits + size_t(b) * d.vocab, nullptr, int(wc.rows)};
+            a.seg[0] = {wc.data, ctx->logits + size_t(b) * ctx->l_vocab, nullptr, int(wc.rows)};
             a.cols = dim;
             a.type = wc.type;
             a.mode = kGemvPlain;
@@ -585,6 +701,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.out_token = ctx->d_out + b;
             if ((rc = launch_gemv(ctx, a, int(wc.rows), launches))) return rc;
         }
+        if (tp && (rc = tp_global_argmax(ctx, width, launches))) return rc;
     }
     if (advance) {
         e = advance_launch(ctx->d_tokens, ctx->d_positions, ctx->d_out, ctx->d_active, ctx->d_history,
@@ -603,7 +720,12 @@ int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     const bool rows_path = width >= rows_min && !advance;
     const int key = width * 8 + (with_logits ? 1 : 0) + (advance ? 2 : 0) + (rows_path ? 4 : 0);
     uint64_t launches = 0;
-    if (!ctx->use_graph) {
+    // Under tensor parallelism the first step of each shape runs uncaptured, so that NCCL sets up
+    // its channels and buffers outside a capture; later steps replay a graph that holds the
+    // collectives too (JITLLM_B200_TP_GRAPH=0 keeps them all uncaptured).
+    static const bool tp_graph = env_flag("JITLLM_B200_TP_GRAPH", true);
+    const bool eager = !ctx->use_graph || (ctx->tp_size > 1 && (!tp_graph || ctx->tp_warm.insert(key).second));
+    if (eager) {
         int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, &launches)
                            : enqueue_step(ctx, width, with_logits, advance, &launches);
         ctx->counters.kernel_launches += launches;
@@ -703,6 +825,8 @@ int32_t jl_destroy(jl_ctx *ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     free_model(ctx);
     free_kv(ctx);
+    if (ctx->nccl_comm) g_nccl.CommDestroy(ctx->nccl_comm);
+    ctx->nccl_comm = nullptr;
     for (void *p : ctx->user_allocs) cudaFree(p);
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
     if (ctx->d_status) cudaFree(ctx->d_status);
@@ -717,6 +841,39 @@ int32_t jl_destroy(jl_ctx *ctx) {
 }
 
 const char *jl_last_error(jl_ctx *ctx) { return ctx ? ctx->err.c_str() : g_init_error.c_str(); }
+
+int32_t jl_tp_unique_id(jl_ctx *ctx, const char *nccl_path, void *id128) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, id128 != nullptr, JL_ERR_INVALID, "id128 must not be NULL");
+    int rc = nccl_bind(ctx, nccl_path);
+    if (rc) return rc;
+    NcclId id;
+    const int nrc = g_nccl.GetUniqueId(&id);
+    if (nrc != 0) return fail(ctx, JL_ERR_CUDA, "ncclGetUniqueId failed: %s", g_nccl.GetErrorString(nrc));
+    memcpy(id128, id.b, sizeof id.b);
+    return JL_OK;
+}
+
+int32_t jl_tp_init(jl_ctx *ctx, const char *nccl_path, const void *id128, int32_t rank, int32_t size) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, id128 != nullptr, JL_ERR_INVALID, "id128 must not be NULL");
+    JL_REQUIRE(ctx, size >= 2 && rank >= 0 && rank < size, JL_ERR_INVALID,
+               "tensor-parallel rank %d of %d is not valid (size must be at least 2)", rank, size);
+    JL_REQUIRE(ctx, ctx->nccl_comm == nullptr, JL_ERR_STATE, "the tensor-parallel group is already set up");
+    JL_REQUIRE(ctx, !ctx->has_model || (ctx->tp_rank == rank && ctx->tp_size == size), JL_ERR_INVALID,
+               "rank %d of %d does not match the model description (%d of %d)", rank, size, ctx->tp_rank,
+               ctx->tp_size);
+    int rc = nccl_bind(ctx, nccl_path);
+    if (rc) return rc;
+    cudaSetDevice(ctx->device);
+    NcclId id;
+    memcpy(id.b, id128, sizeof id.b);
+    void *comm = nullptr;
+    const int nrc = g_nccl.CommInitRank(&comm, size, id, rank);
+    if (nrc != 0) return fail(ctx, JL_ERR_CUDA, "ncclCommInitRank failed: %s", g_nccl.GetErrorString(nrc));
+    ctx->nccl_comm = comm;
+    return JL_OK;
+}
 
 int32_t jl_model_create(jl_ctx *ctx, const jl_model_desc *desc) {
     if (!ctx) return JL_ERR_INVALID;
@@ -739,13 +896,31 @@ int32_t jl_model_create(jl_ctx *ctx, const jl_model_desc *desc) {
                "dim and hidden must be multiples of 256");
     JL_REQUIRE(ctx, d.max_batch >= 1 && d.max_batch <= 256, JL_ERR_INVALID,
                "max_batch must be in 1..256, got %d", d.max_batch);
-    JL_REQUIRE(ctx, d.tp_size <= 1 && d.tp_rank == 0, JL_ERR_UNSUPPORTED,
-               "tensor parallel placement %d/%d", d.tp_rank, d.tp_size);
+    const int tp = d.tp_size < 1 ? 1 : d.tp_size;
+    JL_REQUIRE(ctx, d.tp_rank >= 0 && d.tp_rank < tp, JL_ERR_INVALID, "tensor parallel rank %d outside 0..%d",
+               d.tp_rank, tp - 1);
+    JL_REQUIRE(ctx, d.heads % tp == 0 && d.kv_heads % tp == 0 && d.vocab % tp == 0 &&
+                        (d.dim / tp) % 256 == 0 && d.dim % tp == 0 && d.hidden % (tp * 256) == 0,
+               JL_ERR_UNSUPPORTED,
+               "tensor parallel degree %d must divide heads, kv_heads and vocab, and leave dim/tp and "
+               "hidden/tp multiples of 256 (column shards cut on quantisation group boundaries)",
+               tp);
+    {
+        const int lg = (d.heads / tp) / (d.kv_heads / tp);
+        JL_REQUIRE(ctx, lg == gq, JL_ERR_INVALID, "inconsistent head grouping under tensor parallelism (%d)", lg);
+    }
     cudaSetDevice(ctx->device);
     free_model(ctx);
     ctx->desc = d;
     if (ctx->desc.tp_size < 1) ctx->desc.tp_size = 1;
-    ctx->kv_dim = d.kv_heads * d.head_dim;
+    ctx->tp_size = ctx->desc.tp_size;
+    ctx->tp_rank = d.tp_rank;
+    ctx->l_heads = d.heads / ctx->tp_size;
+    ctx->l_kv_heads = d.kv_heads / ctx->tp_size;
+    ctx->l_qdim = ctx->l_heads * d.head_dim;
+    ctx->l_hidden = d.hidden / ctx->tp_size;
+    ctx->l_vocab = d.vocab / ctx->tp_size;
+    ctx->kv_dim = ctx->l_kv_heads * d.head_dim;  // local: KV pages hold this GPU's KV heads only
     for (int r = 0; r < JL_ROLE_COUNT; ++r) ctx->layer[r].assign(d.layers, DevTensor());
     ctx->has_model = true;
     return JL_OK;
@@ -767,14 +942,16 @@ int32_t jl_upload_tensor(jl_ctx *ctx, int32_t role, int32_t layer, int32_t ggml_
     bool norm = false;
     switch (role) {
         case JL_ROLE_TOKEN_EMBEDDING: er = d.vocab; ec = d.dim; break;
-        case JL_ROLE_OUTPUT: er = d.vocab; ec = d.dim; break;
-        case JL_ROLE_ATTENTION_QUERY: er = d.dim; ec = d.dim; break;
+        // Under tensor parallelism the caller uploads this GPU's shard: column-parallel matrices
+        // (Q, K, V, gate, up, output) lose rows, row-parallel ones (attention output, down) columns.
+        case JL_ROLE_OUTPUT: er = ctx->l_vocab; ec = d.dim; break;
+        case JL_ROLE_ATTENTION_QUERY: er = ctx->l_qdim; ec = d.dim; break;
         case JL_ROLE_ATTENTION_KEY:
         case JL_ROLE_ATTENTION_VALUE: er = ctx->kv_dim; ec = d.dim; break;
-        case JL_ROLE_ATTENTION_OUTPUT: er = d.dim; ec = d.dim; break;
+        case JL_ROLE_ATTENTION_OUTPUT: er = d.dim; ec = ctx->l_qdim; break;
         case JL_ROLE_FFN_GATE:
-        case JL_ROLE_FFN_UP: er = d.hidden; ec = d.dim; break;
-        case JL_ROLE_FFN_DOWN: er = d.dim; ec = d.hidden; break;
+        case JL_ROLE_FFN_UP: er = ctx->l_hidden; ec = d.dim; break;
+        case JL_ROLE_FFN_DOWN: er = d.dim; ec = ctx->l_hidden; break;
         default: er = 1; ec = d.dim; norm = true; break;
     }
     JL_REQUIRE(ctx, rows == er && cols == ec, JL_ERR_INVALID,
@@ -860,26 +1037,34 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     }
     ctx->attn_nsplit = attn_splits_for_width(ctx, 1);
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->x), R * d.dim * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->q), R * d.dim * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->q), R * ctx->l_qdim * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->k), R * ctx->kv_dim * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->v), R * ctx->kv_dim * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->xb), R * d.dim * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb), R * d.hidden * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb2), R * d.hidden * 4))) return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->logits), B * d.vocab * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb), R * ctx->l_hidden * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb2), R * ctx->l_hidden * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->logits), B * ctx->l_vocab * 4))) return rc;
+    if (ctx->tp_size > 1) {
+        JL_REQUIRE(ctx, ctx->nccl_comm != nullptr, JL_ERR_STATE, "jl_tp_init must come before jl_model_finalize");
+        if ((rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;
+        if ((rc = alloc(reinterpret_cast<void **>(&ctx->logits_all), B * d.vocab * 4))) return rc;
+        JL_CUDA(ctx, cudaMemsetAsync(ctx->part, 0, R * d.dim * 4, ctx->stream));
+        if ((rc = alloc(reinterpret_cast<void **>(&ctx->best), (2 * R + 2 * R * ctx->tp_size) * 4))) return rc;
+    }
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_tokens), R * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_positions), R * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_slots), R * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_out), R * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_active), R))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_partial),
-                    max_row_splits * d.heads * (d.head_dim + 2) * 4)))
+                    max_row_splits * ctx->l_heads * (d.head_dim + 2) * 4)))
         return rc;
-    if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_count), R * d.kv_heads * 4))) return rc;
+    if ((rc = alloc(reinterpret_cast<void **>(&ctx->att_count), R * ctx->l_kv_heads * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_val), B * ctx->sm_count * 16))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_idx), B * ctx->sm_count * 16))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->amax_count), B * 4))) return rc;
-    JL_CUDA(ctx, cudaMemsetAsync(ctx->att_count, 0, R * d.kv_heads * 4, ctx->stream));
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->att_count, 0, R * ctx->l_kv_heads * 4, ctx->stream));
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->d_out, 0, R * 4, ctx->stream));
     JL_CUDA(ctx, cudaMemsetAsync(ctx->amax_count, 0, B * 4, ctx->stream));
     JL_CUDA(ctx, cudaMemsetAsync(ctx->d_active, 0, R, ctx->stream));
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
@@ -1040,13 +1225,31 @@ int32_t jl_decode(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32
     if ((rc = run_step(ctx, width, true, false))) return rc;
     JL_CUDA(ctx, cudaMemcpyAsync(h_out, ctx->d_out, width * 4, cudaMemcpyDeviceToHost, ctx->stream));
     JL_CUDA(ctx, cudaMemcpyAsync(h_status, ctx->d_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
-    if (out_logits)
+    std::vector<float> gathered;
+    if (out_logits && ctx->tp_size > 1) {
+        // Every rank holds [row][l_vocab]; gather them as [rank][row][l_vocab] and let the host
+        // interleave them into rows of the full vocabulary after the synchronise.
+        const size_t shard = size_t(width) * ctx->l_vocab;
+        gathered.resize(shard * ctx->tp_size);
+        const int nrc = g_nccl.AllGather(ctx->logits, ctx->logits_all, shard, kNcclFloat32, ctx->nccl_comm,
+                                         ctx->stream);
+        if (nrc != 0) return fail(ctx, JL_ERR_CUDA, "ncclAllGather failed: %s", g_nccl.GetErrorString(nrc));
+        JL_CUDA(ctx, cudaMemcpyAsync(gathered.data(), ctx->logits_all, shard * ctx->tp_size * 4,
+                                     cudaMemcpyDeviceToHost, ctx->stream));
+    } else if (out_logits) {
         JL_CUDA(ctx, cudaMemcpyAsync(out_logits, ctx->logits, size_t(width) * ctx->desc.vocab * 4,
                                      cudaMemcpyDeviceToHost, ctx->stream));
+    }
     JL_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
     JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if ((rc = check_status(ctx))) return rc;
     for (int b = 0; b < width; ++b) out_tokens[b] = h_act[b] ? h_out[b] : -1;
+    if (out_logits && ctx->tp_size > 1) {
+        for (int k = 0; k < ctx->tp_size; ++k)
+            for (int b = 0; b < width; ++b)
+                memcpy(out_logits + size_t(b) * ctx->desc.vocab + size_t(k) * ctx->l_vocab,
+                       gathered.data() + (size_t(k) * width + b) * ctx->l_vocab, size_t(ctx->l_vocab) * 4);
+    }
     cudaEventElapsedTime(&ctx->counters.last_step_ms, ctx->ev0, ctx->ev1);
     ctx->counters.decode_calls++;
     ctx->counters.h2d_bytes += width * 13;
@@ -1264,7 +1467,7 @@ int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters)
             a.x = ctx->hb;
             total = int(w2.rows);
         } else {
-            const DevTensor &wc = wcls_of(ctx);
+            const DevTensor wc = wcls_of(ctx);
             a.nseg = 1;
             a.seg[0] = {wc.data, ctx->logits, nullptr, int(wc.rows)};
             a.type = wc.type;
@@ -1288,12 +1491,12 @@ int32_t jl_debug_read(jl_ctx *ctx, const char *name, int32_t row, float *out, in
     const float *src = nullptr;
     int64_t width = 0;
     if (!strcmp(name, "x")) { src = ctx->x; width = d.dim; }
-    else if (!strcmp(name, "q")) { src = ctx->q; width = d.dim; }
+    else if (!strcmp(name, "q")) { src = ctx->q; width = ctx->l_qdim; }
     else if (!strcmp(name, "k")) { src = ctx->k; width = ctx->kv_dim; }
     else if (!strcmp(name, "v")) { src = ctx->v; width = ctx->kv_dim; }
     else if (!strcmp(name, "xb")) { src = ctx->xb; width = d.dim; }
-    else if (!strcmp(name, "hb")) { src = ctx->hb; width = d.hidden; }
-    else if (!strcmp(name, "logits")) { src = ctx->logits; width = d.vocab; }
+    else if (!strcmp(name, "hb")) { src = ctx->hb; width = ctx->l_hidden; }
+    else if (!strcmp(name, "logits")) { src = ctx->logits; width = ctx->l_vocab; }
     JL_REQUIRE(ctx, src != nullptr, JL_ERR_INVALID, "unknown buffer '%s'", name);
     JL_REQUIRE(ctx, n >= 0 && n <= width, JL_ERR_INVALID, "buffer '%s' has %lld floats per row", name,
                (long long)width);

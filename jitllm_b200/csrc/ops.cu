@@ -60,6 +60,36 @@ __device__ __forceinline__ int64_t kv_offset(const KvGeom &g, int slot, int pos,
            int64_t(within) * g.kv_dim;
 }
 
+__global__ void add_rows_kernel(float *x, const float *y, size_t total) {
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) x[i] = x[i] + y[i];
+}
+
+__global__ void tp_pack_best_kernel(const float *logits, const int32_t *idx, int l_vocab, int index_offset, int n,
+                                    float *best) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n) return;
+    const int i = idx[r];
+    best[2 * r] = logits[size_t(r) * l_vocab + i];
+    best[2 * r + 1] = static_cast<float>(i + index_offset);  // vocabulary indices are exact in fp32
+}
+
+__global__ void tp_pick_best_kernel(const float *all, int ranks, int n, const uint8_t *active, int32_t *out) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n || (active != nullptr && active[r] == 0)) return;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = 0; k < ranks; ++k) {
+        const float v = all[(size_t(k) * n + r) * 2];
+        const int i = static_cast<int>(all[(size_t(k) * n + r) * 2 + 1]);
+        if (v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    out[r] = bi == 0x7fffffff ? 0 : bi;
+}
+
 // ---- row-wise operators for the matrix-matrix path ---------------------------------------------
 __global__ void rmsnorm_rows_kernel(const float *x, const float *w, float eps, float *out, int dim,
                                     const uint8_t *active) {
@@ -507,6 +537,24 @@ cudaError_t kv_append_launch(const float *k, const float *v, const float *rope_c
 cudaError_t argmax_rows_launch(const float *logits, int vocab, int n, const uint8_t *active, int32_t *out,
                                cudaStream_t stream) {
     argmax_rows_kernel<<<n, 1024, 0, stream>>>(logits, vocab, active, out);
+    return cudaGetLastError();
+}
+
+cudaError_t add_rows_launch(float *x, const float *y, size_t total, cudaStream_t stream) {
+    const int grid = static_cast<int>((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
+    add_rows_kernel<<<grid, 256, 0, stream>>>(x, y, total);
+    return cudaGetLastError();
+}
+
+cudaError_t tp_pack_best_launch(const float *logits, const int32_t *idx, int l_vocab, int index_offset, int n,
+                                float *best, cudaStream_t stream) {
+    tp_pack_best_kernel<<<(n + 127) / 128, 128, 0, stream>>>(logits, idx, l_vocab, index_offset, n, best);
+    return cudaGetLastError();
+}
+
+cudaError_t tp_pick_best_launch(const float *all, int ranks, int n, const uint8_t *active, int32_t *out,
+                                cudaStream_t stream) {
+    tp_pick_best_kernel<<<(n + 127) / 128, 128, 0, stream>>>(all, ranks, n, active, out);
     return cudaGetLastError();
 }
 

@@ -63,6 +63,15 @@ cudaError_t kv_append_launch(const float *k, const float *v, const float *rope_c
 cudaError_t argmax_rows_launch(const float *logits, int vocab, int n, const uint8_t *active, int32_t *out,
                                cudaStream_t stream);
 
+// x[i] += y[i]
+cudaError_t add_rows_launch(float *x, const float *y, size_t total, cudaStream_t stream);
+// best[r] = (logits[r][idx[r]], idx[r] + index_offset) for the n rows of this GPU's vocabulary shard.
+cudaError_t tp_pack_best_launch(const float *logits, const int32_t *idx, int l_vocab, int index_offset, int n,
+                                float *best, cudaStream_t stream);
+// out[r] = index of the best of the gathered pairs all[rank][r], lowest index on ties.
+cudaError_t tp_pick_best_launch(const float *all, int ranks, int n, const uint8_t *active, int32_t *out,
+                                cudaStream_t stream);
+
 cudaError_t fill_launch(uint32_t *buf, size_t words, uint32_t value, cudaStream_t stream);
 
 }  // namespace jl
