@@ -34,7 +34,7 @@ def _rank_main(rank, size, port, out_dir, fmt_value, width):
     try:
         cfg = _config(jl)
         fmt = jl.GGMLType(fmt_value)
-        tensors = jl.synth_model_tensors(cfg, fmt, SEED, std=0.05)
+        tensors = jl.synth_model_tensors(cfg, fmt, SEED, std=0.02)
         cr, ci = jl.precomputeFreqsCis(cfg.contextLength, cfg.headSize, cfg.ropeTheta)
         dev = jl.Device(rank)
         tp = jl.TensorParallel(rank, size)
@@ -93,7 +93,7 @@ def test_two_gpus_match_the_oracle(oracle, built, fmt_value, width):
     assert np.array_equal(got[0]["logits"], got[1]["logits"])
     assert got[0]["launches"] > 0
     cfg = _config(jl)
-    tensors = jl.synth_model_tensors(cfg, jl.GGMLType(fmt_value), SEED, std=0.05)
+    tensors = jl.synth_model_tensors(cfg, jl.GGMLType(fmt_value), SEED, std=0.02)
     prompt = got[0]["prompt"]
     for row in range(min(width, 3)):
         ref = oracle.Model(cfg, tensors)
