@@ -45,7 +45,7 @@ BYTES_PER_EL = {"Q4_K": 144 / 256, "Q4_0": 18 / 32, "Q8_0": 34 / 32}
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel for the 8B layer
 # shape, from the ncu capture summarised in profiles/gemv_gateup_q4k_8b_layer.md
-NCU_TRAFFIC_BYTES = {("Q4_K", 4096, 14336): 66.55e6}
+NCU_TRAFFIC_BYTES = {("Q4_K", 4096, 14336): 66.58e6}
 
 
 def parse_args():
@@ -61,6 +61,9 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=20261125)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
+                    help="with more than one GPU: tensor parallelism over one model (strong scaling, the default) "
+                         "or one whole model per GPU (weak scaling)")
     ap.add_argument("--profile-op", type=int, default=-1,
                     help="launch one matrix-vector operator (0 qkv, 1 out, 2 gate/up, 3 down, 4 vocab) "
                          "--steps times and exit: the small case ncu captures are taken on")
@@ -135,10 +138,12 @@ def model_bytes(cfg, fmt):
     return (per_layer * L + cfg.vocabularySize * dim) * bpe
 
 
-def op_bytes(cfg, fmt, op):
+def op_bytes(cfg, fmt, op, shards=1):
+    """Algorithmic bytes of one launch on one GPU: the weight slice once, the input vector, the output."""
     bpe = BYTES_PER_EL[fmt]
-    dim, hid, kv, V = cfg.dim, cfg.hiddenDim, cfg.kvDim, cfg.vocabularySize
-    rows, cols = {0: (dim + 2 * kv, dim), 1: (dim, dim), 2: (2 * hid, dim), 3: (dim, hid), 4: (V, dim)}[op]
+    dim, hid, kv, V = cfg.dim, cfg.hiddenDim // shards, cfg.kvDim // shards, cfg.vocabularySize // shards
+    qd = dim // shards
+    rows, cols = {0: (qd + 2 * kv, dim), 1: (dim, qd), 2: (2 * hid, dim), 3: (dim, hid), 4: (V, dim)}[op]
     out_rows = hid if op == 2 else rows
     return rows * cols * bpe + 4 * cols + 4 * out_rows
 
@@ -214,11 +219,16 @@ def main():
         if distributed:
             dist.barrier()
 
+    use_tp = distributed and args.parallel == "tp"
+    tp = jl.TensorParallel(rank, world) if use_tp else jl.TensorParallel()
+    shards = tp.size  # the matrices of one step are spread over this many GPUs
     t_build = time.time()
-    tensors = jl.synth_model_tensors(cfg, fmt, args.seed)
+    threads = max(1, (os.cpu_count() or 1) // max(1, world))
+    tensors = jl.synth_model_tensors(cfg, fmt, args.seed, threads=threads, tp=tp if use_tp else None)
     cr, ci = jl.precomputeFreqsCis(cfg.contextLength, cfg.headSize, cfg.ropeTheta)
     dev = jl.Device(local_rank)
-    model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=B)
+    model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=B, tp=tp, broadcast=jl.torch_broadcast,
+                          presharded=use_tp)
     t_build = time.time() - t_build
 
     if args.profile_op >= 0:
@@ -228,7 +238,7 @@ def main():
         model.benchOp(args.profile_op, 0, K)
         t_ms = dev.timer_stop()
         print(json.dumps({"profile_op": args.profile_op, "launches": K, "us_per_launch": t_ms * 1000.0 / K,
-                          "bytes_per_launch": op_bytes(cfg, args.format, args.profile_op)}), flush=True)
+                          "bytes_per_launch": op_bytes(cfg, args.format, args.profile_op, shards)}), flush=True)
         return 0
 
     # KV pool: only the pages this run touches are mapped; the rest stay UNMAPPED (scratch block).
@@ -237,14 +247,14 @@ def main():
     if total_tokens > cfg.contextLength:
         raise SystemExit(f"prompt + steps ({total_tokens}) exceed the context ({cfg.contextLength})")
     need = (total_tokens + 15) // 16
-    kv = model.createKvStorage(jl.KvStorageRequest(B * need, bps, B, 16, cfg.numberOfLayers, cfg.kvDim))
+    kv = model.createKvStorage(jl.KvStorageRequest(B * need, bps, B, 16, cfg.numberOfLayers, model.localKvDim))
     table = np.full(B * bps, jl.UNMAPPED, dtype=np.int32)
     for b in range(B):
         table[b * bps:b * bps + need] = np.arange(b * need, (b + 1) * need)
     kv.publishBlockTable(table)
     ex = jl.B200BatchExecutor(model)
 
-    rng = np.random.default_rng(args.seed + rank)
+    rng = np.random.default_rng(args.seed + (0 if use_tp else rank))  # one prompt for the whole group under TP
     prompts = rng.integers(0, cfg.vocabularySize, size=(B, P))
     t_prefill = time.perf_counter()
     for b in range(B):
@@ -319,30 +329,32 @@ def main():
         dev.timer_start()
         model.benchOp(op, 0, reps)
         t_ms = dev.timer_stop()
-        by = op_bytes(cfg, args.format, op)
+        by = op_bytes(cfg, args.format, op, shards)
         us = t_ms * 1000.0 / reps
         ops.append({"kernel": names[op], "bytes_per_launch": by, "us_per_launch": round(us, 3),
                     "gbs": round(by / us / 1e3, 1), "frac": round(by / us / 1e3 / peak, 4), "launches": reps})
     dom = ops[0]
 
-    weights_b = model_bytes(cfg, args.format)
-    kv_b = B * (mid_pos + 1) * cfg.numberOfLayers * cfg.kvDim * 2 * 2
+    weights_b = model_bytes(cfg, args.format) / shards  # per GPU
+    kv_b = B * (mid_pos + 1) * cfg.numberOfLayers * model.localKvDim * 2 * 2
     step_ms = ms / K
     tokens = B * K
-    replicas = world if distributed else 1
+    replicas = world if distributed and not use_tp else 1
+    parallelism = "tp%d (Megatron split, one all-reduce per sublayer: %s)" % (world, model.exchangeMode) if use_tp else \
+        ("replicas x%d" % replicas if replicas > 1 else "single GPU")
     value = tokens * replicas / (ms / 1000.0)
     line = {
         "metric": "decode tok/s", "value": value, "unit": "tok/s", "n_gpus": n_gpus, "steps": K, "warmup": max(W, 3),
         "ms_per_step": step_ms, "higher_is_better": True,
         "scaling": "weak" if replicas > 1 else "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": dict(config, parallelism="replicas x%d" % replicas if replicas > 1 else "single GPU"),
+        "data": "synthetic", "config": dict(config, parallelism=parallelism),
         "clocks": clocks,
         "e2e": {"value": tokens * replicas / (e_ms / 1000.0), "unit": "tok/s", "h2d_bytes_per_step": 13 * B,
                 "d2h_bytes_per_step": 4 * B + 4, "ms_per_step": e_ms / K},
         "gpu_launches": int(c1["kernel_launches"] - c0["kernel_launches"]),
         "roofline": {"bound": "hbm", "kernel": "gemv_kernel<%s> %s" % (args.format, dom["kernel"]),
                      "achieved": dom["gbs"], "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": dom["frac"], "traffic": NCU_TRAFFIC_BYTES.get((args.format, cfg.dim, cfg.hiddenDim)), "bytes_per_launch": dom["bytes_per_launch"],
+                     "frac": dom["frac"], "traffic": NCU_TRAFFIC_BYTES.get((args.format, cfg.dim, cfg.hiddenDim)) if shards == 1 else None, "bytes_per_launch": dom["bytes_per_launch"],
                      "us_per_launch": dom["us_per_launch"]},
         "step_roofline": {"weight_bytes": weights_b, "kv_bytes": kv_b, "achieved_gbs": (weights_b + kv_b) / step_ms / 1e6,
                           "frac_of_measured_peak": (weights_b + kv_b) / step_ms / 1e6 / peak,

@@ -191,6 +191,16 @@ int32_t jl_flush_l2(jl_ctx *ctx);
  * nccl_path: the NCCL shared library to bind at run time, or NULL for "libnccl.so.2". */
 int32_t jl_tp_unique_id(jl_ctx *ctx, const char *nccl_path, void *id128);
 int32_t jl_tp_init(jl_ctx *ctx, const char *nccl_path, const void *id128, int32_t rank, int32_t size);
+/* How the ranks exchange the small per-step messages (partial sums of up to 16 rows, the best token
+ * of each vocabulary shard) after jl_model_finalize: 0 = single GPU, 1 = NCCL collectives, 2 = one
+ * kernel per exchange over peer memory (stores into the other GPUs' inboxes through NVLink; inboxes
+ * shared by CUDA IPC between processes). Mode 2 is chosen when every rank could map every inbox;
+ * jl_tp_exchange_note says why not otherwise. JITLLM_B200_TP_PUSH=0 forces mode 1. A rank that
+ * waits longer than JITLLM_B200_TP_TIMEOUT_MS (default 5000) for a peer's message gives up and the
+ * step returns JL_ERR_TIMEOUT; the group is then out of step and must be torn down. Larger
+ * messages (prefill chunks, wide batches) always go through NCCL. */
+int32_t jl_tp_exchange_mode(jl_ctx *ctx);
+const char *jl_tp_exchange_note(jl_ctx *ctx);
 
 /* ---- allocation-free operator (no counterpart in the reference: its kernels take whatever
  * scratch the TornadoVM runtime allocates for them).

@@ -341,11 +341,15 @@ class B200Model:
             max_batch=maxBatch, tp_rank=self.tp.rank, tp_size=self.tp.size)
         dev._check(dev._lib.jl_model_create(dev.handle, C.byref(d)))
 
-    def uploadTensor(self, role: TensorRole, layer: int, ggml_type: GGMLType, data: np.ndarray) -> None:
-        """`data` is the whole GGUF tensor; under tensor parallelism this GPU's slice is cut here."""
+    def uploadTensor(self, role: TensorRole, layer: int, ggml_type: GGMLType, data: np.ndarray,
+                     presharded: bool = False) -> None:
+        """`data` is the whole GGUF tensor; under tensor parallelism this GPU's slice is cut here
+        (or, with `presharded`, `data` already is that slice)."""
         role = TensorRole(role)
         rows, cols = local_shape(self.config, role, self.tp.size)
-        data = np.ascontiguousarray(shard_tensor(self.config, role, ggml_type, np.ascontiguousarray(data), self.tp))
+        data = np.ascontiguousarray(data)
+        if not presharded:
+            data = np.ascontiguousarray(shard_tensor(self.config, role, ggml_type, data, self.tp))
         self.dev._check(self.dev._lib.jl_upload_tensor(
             self.dev.handle, int(role), layer, int(ggml_type), rows, cols, _ptr(data), data.nbytes))
 
@@ -360,6 +364,13 @@ class B200Model:
 
     def finalize(self) -> None:
         self.dev._check(self.dev._lib.jl_model_finalize(self.dev.handle))
+
+    @property
+    def exchangeMode(self) -> str:
+        """How the tensor-parallel ranks trade partial sums: 'single', 'nccl' or 'peer-memory'."""
+        mode = self.dev._lib.jl_tp_exchange_mode(self.dev.handle)
+        note = (self.dev._lib.jl_tp_exchange_note(self.dev.handle) or b"").decode()
+        return ["single", "nccl", "peer-memory"][mode] + (f" ({note})" if note else "")
 
     @property
     def localKvDim(self) -> int:
@@ -507,15 +518,22 @@ def quantize(ggml_type: GGMLType, values: np.ndarray, threads: int = 0) -> np.nd
 
 
 def synth_model_tensors(config: Configuration, ggml_type: GGMLType, seed: int, std: float = 0.02,
-                        threads: int = 0) -> Dict[Tuple[TensorRole, int], Tuple[GGMLType, np.ndarray]]:
-    """All tensors of a synthetic model: matrices N(0, std) in `ggml_type`, norm weights 1.0."""
+                        threads: int = 0, tp: Optional[TensorParallel] = None
+                        ) -> Dict[Tuple[TensorRole, int], Tuple[GGMLType, np.ndarray]]:
+    """All tensors of a synthetic model: matrices N(0, std) in `ggml_type`, norm weights 1.0.
+    With `tp`, only this GPU's slices are generated (pass them to load_model with presharded=True):
+    each slice of a split matrix draws from its own seed, so the ranks together hold one consistent
+    random model of the full shape, though not the one a single GPU would draw from `seed`."""
     out: Dict[Tuple[TensorRole, int], Tuple[GGMLType, np.ndarray]] = {}
     index = 0
+    size = tp.size if tp else 1
 
     def matrix(role: TensorRole, layer: int):
         nonlocal index
-        rows, cols = config.matrix_shape(role)
-        out[(role, layer)] = (ggml_type, synth_tensor(ggml_type, rows * cols, seed * 1000003 + index, std, threads))
+        rows, cols = local_shape(config, role, size)
+        split = (rows, cols) != config.matrix_shape(role)
+        s = seed * 1000003 + index + (7919 * 1000003 * (tp.rank + 1) if split else 0)
+        out[(role, layer)] = (ggml_type, synth_tensor(ggml_type, rows * cols, s, std, threads))
         index += 1
 
     matrix(TensorRole.TOKEN_EMBEDDING, -1)
@@ -534,12 +552,13 @@ def synth_model_tensors(config: Configuration, ggml_type: GGMLType, seed: int, s
 
 
 def load_model(dev: Device, config: Configuration, tensors, rope_cos: np.ndarray, rope_sin: np.ndarray,
-               maxBatch: int = 1, tp: Optional[TensorParallel] = None, broadcast=None) -> B200Model:
+               maxBatch: int = 1, tp: Optional[TensorParallel] = None, broadcast=None,
+               presharded: bool = False) -> B200Model:
     """`tensors` holds whole tensors; with `tp` each GPU keeps its slice and `broadcast` carries the
     NCCL id between the ranks (see tensor_parallel.init_group)."""
     model = B200Model(dev, config, maxBatch, tp)
     for (role, layer), (t, data) in tensors.items():
-        model.uploadTensor(role, layer if role not in GLOBAL_ROLES else -1, t, data)
+        model.uploadTensor(role, layer if role not in GLOBAL_ROLES else -1, t, data, presharded)
     model.uploadRope(rope_cos, rope_sin)
     if model.tp.size > 1:
         if broadcast is None:

@@ -18,6 +18,9 @@
 #include "ops.cuh"
 #include "token_kernel.cuh"
 #include "gemm_tc.cuh"
+#include "tp_exchange.cuh"
+
+#include <unistd.h>
 
 using namespace jl;
 
@@ -82,6 +85,15 @@ struct jl_ctx {
     int l_heads = 0, l_kv_heads = 0, l_qdim = 0, l_hidden = 0, l_vocab = 0;
     float *part = nullptr;      // row-parallel partial sums before the all-reduce, [row_cap][dim]
     float *best = nullptr;      // local (value, index) of the arg-max and the gathered pairs
+    // peer-memory exchange (tp_exchange.cuh): this GPU's inbox, every rank's inbox as mapped here
+    uint2 *tp_inbox = nullptr;
+    TpInboxes tp_peers = {};
+    bool tp_peer_ipc[kTpMaxRanks] = {};  // mapped with cudaIpcOpenMemHandle (to be closed)
+    unsigned *tp_ctr = nullptr;          // [0,1] reduce sequence / arrivals, [2,3] arg-max
+    bool tp_push = false;
+    size_t tp_reduce_cap = 0, tp_best_cap = 0;
+    unsigned long long tp_timeout_ns = 5000000000ull;
+    std::string tp_note;                 // why the peer-memory path is off, if it is
     std::set<int> tp_warm;        // step shapes that have run once uncaptured
     float *logits_all = nullptr;  // [rank][row][l_vocab], only when the host asks for logits
     void *nccl_lib = nullptr;   // dlopen handle
@@ -280,6 +292,16 @@ void free_model(jl_ctx *ctx) {
     if (ctx->best) cudaFree(ctx->best);
     if (ctx->logits_all) cudaFree(ctx->logits_all);
     ctx->part = ctx->best = ctx->logits_all = nullptr;
+    for (int r = 0; r < kTpMaxRanks; ++r) {
+        if (ctx->tp_peer_ipc[r] && ctx->tp_peers.of[r]) cudaIpcCloseMemHandle(ctx->tp_peers.of[r]);
+        ctx->tp_peer_ipc[r] = false;
+        ctx->tp_peers.of[r] = nullptr;
+    }
+    if (ctx->tp_inbox) cudaFree(ctx->tp_inbox);
+    if (ctx->tp_ctr) cudaFree(ctx->tp_ctr);
+    ctx->tp_inbox = nullptr;
+    ctx->tp_ctr = nullptr;
+    ctx->tp_push = false;
     ctx->tp_warm.clear();
     if (ctx->d_layers) cudaFree(ctx->d_layers);
     ctx->d_layers = nullptr;
@@ -434,10 +456,134 @@ int launch_token_kernel(jl_ctx *ctx, bool with_logits, bool advance) {
     return JL_OK;
 }
 
+
+// Sets up the peer-memory exchange: allocates this GPU's inbox, trades addresses with the other
+// ranks (an IPC handle between processes, the plain pointer inside one process) over the NCCL group
+// and maps theirs. Any rank failing turns the path off on all ranks, which then keep using NCCL.
+struct TpPeerInfo {
+    cudaIpcMemHandle_t handle;  // 64 bytes
+    unsigned long long ptr;
+    long long pid;
+    int device;
+    int ok;
+};
+static_assert(sizeof(TpPeerInfo) % 4 == 0, "gathered as 32-bit words");
+
+int tp_push_setup(jl_ctx *ctx) {
+    ctx->tp_push = false;
+    ctx->tp_note.clear();
+    if (!env_flag("JITLLM_B200_TP_PUSH", true)) {
+        ctx->tp_note = "disabled by JITLLM_B200_TP_PUSH";
+        return JL_OK;
+    }
+    if (const char *v = getenv("JITLLM_B200_TP_TIMEOUT_MS")) ctx->tp_timeout_ns = 1000000ull * strtoull(v, nullptr, 10);
+    const int tp = ctx->tp_size;
+    JL_REQUIRE(ctx, tp <= kTpMaxRanks, JL_ERR_UNSUPPORTED, "at most %d tensor-parallel ranks", kTpMaxRanks);
+    // reduce region: up to 16 rows of the residual stream; arg-max region: 2 packets per row
+    ctx->tp_reduce_cap = size_t(16) * ctx->desc.dim;
+    ctx->tp_best_cap = 2 * size_t(ctx->row_cap);
+    const size_t packets = 2 * size_t(tp) * (ctx->tp_reduce_cap + ctx->tp_best_cap);
+    int rc;
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->tp_inbox), packets * sizeof(uint2)))) return rc;
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->tp_ctr), 4 * sizeof(unsigned)))) return rc;
+    const unsigned ctr0[4] = {1u, 0u, 1u, 0u};
+    JL_CUDA(ctx, cudaMemsetAsync(ctx->tp_inbox, 0, packets * sizeof(uint2), ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->tp_ctr, ctr0, sizeof ctr0, cudaMemcpyHostToDevice, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->counters.workspace_bytes += packets * sizeof(uint2);
+
+    TpPeerInfo mine = {};
+    mine.ptr = reinterpret_cast<unsigned long long>(ctx->tp_inbox);
+    mine.pid = static_cast<long long>(getpid());
+    mine.device = ctx->device;
+    mine.ok = cudaIpcGetMemHandle(&mine.handle, ctx->tp_inbox) == cudaSuccess ? 1 : 0;
+    cudaGetLastError();
+    const size_t words = sizeof(TpPeerInfo) / 4;
+    float *d_info = nullptr;  // [1 + tp] records: own, then the gathered ones
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&d_info), (1 + tp) * sizeof(TpPeerInfo)))) return rc;
+    std::vector<TpPeerInfo> all(tp);
+    auto gather = [&]() -> int {
+        cudaError_t e = cudaMemcpyAsync(d_info, &mine, sizeof mine, cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "%s", cudaGetErrorString(e));
+        const int nrc = g_nccl.AllGather(d_info, d_info + words, words, kNcclFloat32, ctx->nccl_comm, ctx->stream);
+        if (nrc != 0) return fail(ctx, JL_ERR_CUDA, "ncclAllGather failed: %s", g_nccl.GetErrorString(nrc));
+        e = cudaMemcpyAsync(all.data(), d_info + words, tp * sizeof(TpPeerInfo), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "%s", cudaGetErrorString(e));
+        return JL_OK;
+    };
+    rc = gather();
+    // map the peers' inboxes
+    bool ok = rc == JL_OK;
+    for (int r = 0; ok && r < tp; ++r) ok = all[r].ok == 1;
+    if (rc == JL_OK && !ok) ctx->tp_note = "a rank could not export its inbox";
+    for (int r = 0; ok && r < tp; ++r) {
+        if (r == ctx->tp_rank) {
+            ctx->tp_peers.of[r] = ctx->tp_inbox;
+            continue;
+        }
+        if (all[r].pid == mine.pid) {  // same process: peer access and the pointer itself
+            int can = 0;
+            cudaDeviceCanAccessPeer(&can, ctx->device, all[r].device);
+            cudaError_t e = can ? cudaDeviceEnablePeerAccess(all[r].device, 0) : cudaErrorInvalidDevice;
+            if (e == cudaErrorPeerAccessAlreadyEnabled) e = cudaSuccess;
+            cudaGetLastError();
+            if (e != cudaSuccess) {
+                ok = false;
+                ctx->tp_note = std::string("no peer access: ") + cudaGetErrorString(e);
+                break;
+            }
+            ctx->tp_peers.of[r] = reinterpret_cast<uint2 *>(all[r].ptr);
+        } else {
+            void *p = nullptr;
+            cudaError_t e = cudaIpcOpenMemHandle(&p, all[r].handle, cudaIpcMemLazyEnablePeerAccess);
+            cudaGetLastError();
+            if (e != cudaSuccess) {
+                ok = false;
+                ctx->tp_note = std::string("cudaIpcOpenMemHandle failed: ") + cudaGetErrorString(e);
+                break;
+            }
+            ctx->tp_peers.of[r] = static_cast<uint2 *>(p);
+            ctx->tp_peer_ipc[r] = true;
+        }
+    }
+    // agree: the path is on only if every rank mapped every inbox (this also orders the zeroing
+    // of every inbox before anyone's first push)
+    if (rc == JL_OK) {
+        mine.ok = ok ? 1 : 0;
+        rc = gather();
+        for (int r = 0; rc == JL_OK && ok && r < tp; ++r) ok = all[r].ok == 1;
+    }
+    cudaFree(d_info);
+    if (rc) return rc;
+    if (!ok && ctx->tp_note.empty()) ctx->tp_note = "another rank could not map the inboxes";
+    ctx->tp_push = ok;
+    return JL_OK;
+}
+
 // Row-parallel epilogue under tensor parallelism: all-reduce the partial projections of `n` rows
 // and add the sum into the residual stream (one NCCL all-reduce per sublayer).
 int tp_reduce_into_x(jl_ctx *ctx, int n, uint64_t *launches) {
-    int rc = tp_all_reduce(ctx, ctx->part, size_t(n) * ctx->desc.dim);
+    const size_t count = size_t(n) * ctx->desc.dim;
+    if (ctx->tp_push && count <= ctx->tp_reduce_cap) {
+        TpReduceArgs a = {};
+        a.part = ctx->part;
+        a.x = ctx->x;
+        a.inbox = ctx->tp_peers;
+        a.base = 0;
+        a.cap = ctx->tp_reduce_cap;
+        a.tp = ctx->tp_size;
+        a.rank = ctx->tp_rank;
+        a.count = int(count);
+        a.ctr = ctx->tp_ctr;
+        a.status = ctx->d_status;
+        a.timeout_ns = ctx->tp_timeout_ns;
+        cudaError_t e = tp_push_reduce_launch(a, ctx->stream, ctx->use_pdl);
+        if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "peer reduce launch failed: %s", cudaGetErrorString(e));
+        ++*launches;
+        return JL_OK;
+    }
+    int rc = tp_all_reduce(ctx, ctx->part, count);
     if (rc) return rc;
     cudaError_t e = add_rows_launch(ctx->x, ctx->part, size_t(n) * ctx->desc.dim, ctx->stream);
     if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "residual add launch failed: %s", cudaGetErrorString(e));
@@ -448,6 +594,27 @@ int tp_reduce_into_x(jl_ctx *ctx, int n, uint64_t *launches) {
 // Each GPU holds the arg-max of its vocabulary shard; gather (value, global index) pairs and keep
 // the best, first index on ties (inference/Logits.java:49-60).
 int tp_global_argmax(jl_ctx *ctx, int n, uint64_t *launches) {
+    if (ctx->tp_push && 2 * size_t(n) <= ctx->tp_best_cap) {
+        TpBestArgs a = {};
+        a.logits = ctx->logits;
+        a.local = ctx->d_out;
+        a.out = ctx->d_out;
+        a.active = ctx->d_active;
+        a.inbox = ctx->tp_peers;
+        a.base = 2 * size_t(ctx->tp_size) * ctx->tp_reduce_cap;
+        a.cap = ctx->tp_best_cap;
+        a.tp = ctx->tp_size;
+        a.rank = ctx->tp_rank;
+        a.n = n;
+        a.l_vocab = ctx->l_vocab;
+        a.ctr = ctx->tp_ctr + 2;
+        a.status = ctx->d_status;
+        a.timeout_ns = ctx->tp_timeout_ns;
+        cudaError_t e = tp_push_best_launch(a, ctx->stream, ctx->use_pdl);
+        if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "peer arg-max launch failed: %s", cudaGetErrorString(e));
+        ++*launches;
+        return JL_OK;
+    }
     float *local = ctx->best, *all = ctx->best + 2 * size_t(ctx->row_cap);
     cudaError_t e = tp_pack_best_launch(ctx->logits, ctx->d_out, ctx->l_vocab, ctx->tp_rank * ctx->l_vocab, n,
                                         local, ctx->stream);
@@ -842,6 +1009,13 @@ int32_t jl_destroy(jl_ctx *ctx) {
 
 const char *jl_last_error(jl_ctx *ctx) { return ctx ? ctx->err.c_str() : g_init_error.c_str(); }
 
+int32_t jl_tp_exchange_mode(jl_ctx *ctx) {
+    if (!ctx || ctx->tp_size <= 1) return 0;
+    return ctx->tp_push ? 2 : 1;
+}
+
+const char *jl_tp_exchange_note(jl_ctx *ctx) { return ctx ? ctx->tp_note.c_str() : ""; }
+
 int32_t jl_tp_unique_id(jl_ctx *ctx, const char *nccl_path, void *id128) {
     if (!ctx) return JL_ERR_INVALID;
     JL_REQUIRE(ctx, id128 != nullptr, JL_ERR_INVALID, "id128 must not be NULL");
@@ -1049,6 +1223,7 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
         if ((rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;
         if ((rc = alloc(reinterpret_cast<void **>(&ctx->logits_all), B * d.vocab * 4))) return rc;
         JL_CUDA(ctx, cudaMemsetAsync(ctx->part, 0, R * d.dim * 4, ctx->stream));
+        if ((rc = tp_push_setup(ctx))) return rc;
         if ((rc = alloc(reinterpret_cast<void **>(&ctx->best), (2 * R + 2 * R * ctx->tp_size) * 4))) return rc;
     }
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->d_tokens), R * 4))) return rc;
@@ -1443,7 +1618,8 @@ int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters)
         } else if (op == 1) {
             const DevTensor &wo = ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l];
             a.nseg = 1;
-            a.seg[0] = {wo.data, ctx->q, nullptr, int(wo.rows)};
+            a.seg[0] = {wo.data, ctx->tp_size > 1 ? ctx->part : ctx->q, nullptr, int(wo.rows)};
+            a.cols = int(wo.cols);
             a.type = wo.type;
             a.x = ctx->xb;
             total = int(wo.rows);
@@ -1461,7 +1637,7 @@ int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters)
         } else if (op == 3) {
             const DevTensor &w2 = ctx->layer[JL_ROLE_FFN_DOWN][l];
             a.nseg = 1;
-            a.seg[0] = {w2.data, ctx->q, nullptr, int(w2.rows)};
+            a.seg[0] = {w2.data, ctx->tp_size > 1 ? ctx->part : ctx->q, nullptr, int(w2.rows)};
             a.cols = int(w2.cols);
             a.type = w2.type;
             a.x = ctx->hb;

@@ -65,7 +65,7 @@ def _rank_main(rank, size, port, out_dir, fmt_value, width):
             all_logits.append(np.array(logits).reshape(width, cfg.vocabularySize))
             tokens = np.array(out, dtype=np.int32)
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), tokens=np.stack(all_tokens), logits=np.stack(all_logits),
-                 prompt=prompt, launches=dev.counters()["kernel_launches"])
+                 prompt=prompt, launches=dev.counters()["kernel_launches"], mode=model.exchangeMode)
         dev.synchronize()
         kv.close()
         dev.close()
@@ -73,8 +73,9 @@ def _rank_main(rank, size, port, out_dir, fmt_value, width):
         dist.destroy_process_group()
 
 
-def _run(size, fmt_value, width):
+def _run(size, fmt_value, width, push=True):
     import torch.multiprocessing as mp
+    os.environ["JITLLM_B200_TP_PUSH"] = "1" if push else "0"  # inherited by the ranks
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
@@ -83,15 +84,18 @@ def _run(size, fmt_value, width):
         return [dict(np.load(os.path.join(d, f"rank{r}.npz"))) for r in range(size)]
 
 
-@pytest.mark.parametrize("fmt_value,width", [(12, 1), (8, 1), (2, 2), (12, 16)])
-def test_two_gpus_match_the_oracle(oracle, built, fmt_value, width):
+@pytest.mark.parametrize("fmt_value,width,push", [(12, 1, True), (12, 1, False), (8, 1, True), (2, 2, True),
+                                                  (12, 16, True), (12, 16, False)])
+def test_two_gpus_match_the_oracle(oracle, built, fmt_value, width, push):
     if _gpu_count() < 2:
         pytest.skip("needs two GPUs")
     import jitllm_b200 as jl
-    got = _run(2, fmt_value, width)
+    got = _run(2, fmt_value, width, push)
+    expect_mode = "peer-memory" if push else "nccl (disabled by JITLLM_B200_TP_PUSH)"
     assert np.array_equal(got[0]["tokens"], got[1]["tokens"])
     assert np.array_equal(got[0]["logits"], got[1]["logits"])
     assert got[0]["launches"] > 0
+    assert str(got[0]["mode"]) == expect_mode, str(got[0]["mode"])
     cfg = _config(jl)
     tensors = jl.synth_model_tensors(cfg, jl.GGMLType(fmt_value), SEED, std=0.02)
     prompt = got[0]["prompt"]
