@@ -33,6 +33,8 @@ struct DevTensor {
     int type = -1;
     int64_t rows = 0, cols = 0;
     size_t bytes = 0;
+    bool has_tmap = false;  // quantised with whole 256-column groups: usable by the tensor-core path
+    GemmTensorMap tmap = {};
 };
 
 struct StepGraph {
@@ -83,6 +85,10 @@ struct jl_ctx {
     // tensor-parallel placement: local (per-GPU) extents of the sharded dimensions
     int tp_rank = 0, tp_size = 1;
     int l_heads = 0, l_kv_heads = 0, l_qdim = 0, l_hidden = 0, l_vocab = 0;
+    GemmTensorMap wcls_slice_tmap = {};  // tied embeddings under tensor parallelism: this GPU's rows
+    float *gemm_scratch = nullptr;       // split-column partial tiles of the tensor-core path
+    size_t gemm_scratch_floats = 0;
+    unsigned *gemm_counters = nullptr;   // one arrival counter per output tile, zero between launches
     float *part = nullptr;      // row-parallel partial sums before the all-reduce, [row_cap][dim]
     float *best = nullptr;      // local (value, index) of the arg-max and the gathered pairs
     // peer-memory exchange (tp_exchange.cuh): this GPU's inbox, every rank's inbox as mapped here
@@ -171,6 +177,9 @@ int dev_alloc(jl_ctx *ctx, void **p, size_t bytes) {
 
 
 // ---- NCCL, bound at run time (the library itself does not link against it) ---------------------
+constexpr int kGemmCounters = 16384;
+constexpr size_t kGemmScratchFloats = size_t(16) << 20;  // 64 MiB
+
 struct NcclId {
     char b[128];
 };
@@ -253,6 +262,17 @@ int upload(jl_ctx *ctx, DevTensor *t, int type, int64_t rows, int64_t cols, cons
     t->rows = rows;
     t->cols = cols;
     t->bytes = nbytes;
+    t->has_tmap = false;
+    if (is_quant(type) && cols % 256 == 0) {
+        e = gemm_make_tensor_map(&t->tmap, p, type, rows, cols);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            *t = DevTensor();
+            return fail(ctx, JL_ERR_CUDA, "TMA descriptor for a %lld x %lld matrix failed: %s", (long long)rows,
+                        (long long)cols, cudaGetErrorString(e));
+        }
+        t->has_tmap = true;
+    }
     ctx->counters.weight_bytes += nbytes;
     ctx->counters.h2d_bytes += nbytes;
     return JL_OK;
@@ -342,6 +362,7 @@ DevTensor wcls_of(const jl_ctx *ctx) {
         t.data += size_t(ctx->tp_rank) * ctx->l_vocab * rb;
         t.rows = ctx->l_vocab;
         t.bytes = size_t(ctx->l_vocab) * rb;
+        if (t.has_tmap) t.tmap = ctx->wcls_slice_tmap;
     }
     return t;
 }
@@ -635,22 +656,39 @@ int attn_splits_for_width(const jl_ctx *ctx, int width) {
     return n;
 }
 
-int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
-                uint64_t *launches) {
+// One tensor-core launch over up to three matrices that share the input rows.
+int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, const float *const *res, int nseg,
+                     const float *x, int n, uint64_t *launches) {
     GemmArgs g = {};
-    g.w = w.data;
-    g.type = w.type;
-    g.rows = int(w.rows);
-    g.cols = int(w.cols);
+    g.nseg = nseg;
+    for (int s = 0; s < nseg; ++s) {
+        if (!w[s]->has_tmap) return fail(ctx, JL_ERR_UNSUPPORTED, "matrix-matrix product needs a quantised matrix");
+        g.seg[s] = {w[s]->data, &w[s]->tmap, y[s], res ? res[s] : nullptr, int(w[s]->rows)};
+    }
+    g.type = w[0]->type;
+    g.cols = int(w[0]->cols);
     g.x = x;
     g.n = n;
-    g.y = y;
-    g.res = res;
     g.status = ctx->d_status;
+    g.scratch = ctx->gemm_scratch;
+    g.scratch_floats = ctx->gemm_scratch_floats;
+    g.counters = ctx->gemm_counters;
+    g.counters_len = kGemmCounters;
+    g.sm_count = ctx->sm_count;
+    static const int gemm_dbg = [] { const char *v = getenv("JITLLM_B200_GEMM_DEBUG"); return v ? atoi(v) : 0; }();
+    g.debug = gemm_dbg;
     cudaError_t e = gemm_tc_launch(g, ctx->stream);
     if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-matrix launch failed: %s", cudaGetErrorString(e));
     ++*launches;
     return JL_OK;
+}
+
+int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
+                uint64_t *launches) {
+    const DevTensor *ws[1] = {&w};
+    float *ys[1] = {y};
+    const float *rs[1] = {res};
+    return launch_gemm_segs(ctx, ws, ys, rs, 1, x, n, launches);
 }
 
 #define JL_LAUNCH(ctx, call, what)                                                            \
@@ -677,9 +715,18 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, uint64_t *launches) 
         const float *ffn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, attn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
                   "rmsnorm");
-        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_QUERY][l], ctx->xb, n, ctx->q, nullptr, launches))) return rc;
-        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_KEY][l], ctx->xb, n, ctx->k, nullptr, launches))) return rc;
-        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_VALUE][l], ctx->xb, n, ctx->v, nullptr, launches))) return rc;
+        {
+            const DevTensor *ws[3] = {&ctx->layer[JL_ROLE_ATTENTION_QUERY][l], &ctx->layer[JL_ROLE_ATTENTION_KEY][l],
+                                      &ctx->layer[JL_ROLE_ATTENTION_VALUE][l]};
+            float *ys[3] = {ctx->q, ctx->k, ctx->v};
+            const bool same = ws[0]->type == ws[1]->type && ws[0]->type == ws[2]->type;
+            if (same) {
+                if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 3, ctx->xb, n, launches))) return rc;
+            } else {
+                for (int i = 0; i < 3; ++i)
+                    if ((rc = launch_gemm(ctx, *ws[i], ctx->xb, n, ys[i], nullptr, launches))) return rc;
+            }
+        }
         JL_LAUNCH(ctx, kv_append_launch(ctx->k, ctx->v, ctx->rope_cos, ctx->rope_sin, ctx->d_positions, ctx->d_slots,
                                         ctx->d_active, kvg, l, d.head_dim, n, ctx->stream),
                   "kv append");
@@ -714,8 +761,16 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, uint64_t *launches) 
         }
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, ffn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
                   "rmsnorm");
-        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_GATE][l], ctx->xb, n, ctx->hb, nullptr, launches))) return rc;
-        if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_UP][l], ctx->xb, n, ctx->hb2, nullptr, launches))) return rc;
+        {
+            const DevTensor *ws[2] = {&ctx->layer[JL_ROLE_FFN_GATE][l], &ctx->layer[JL_ROLE_FFN_UP][l]};
+            float *ys[2] = {ctx->hb, ctx->hb2};
+            if (ws[0]->type == ws[1]->type) {
+                if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 2, ctx->xb, n, launches))) return rc;
+            } else {
+                for (int i = 0; i < 2; ++i)
+                    if ((rc = launch_gemm(ctx, *ws[i], ctx->xb, n, ys[i], nullptr, launches))) return rc;
+            }
+        }
         JL_LAUNCH(ctx, swiglu_rows_launch(ctx->hb, ctx->hb2, ctx->l_hidden, n, ctx->stream), "swiglu");
         if (ctx->tp_size > 1) {
             if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->part, nullptr, launches))) return rc;
@@ -977,6 +1032,10 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     if (e == cudaSuccess) e = gemm_tc_configure();
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->d_status), sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->gemm_scratch), kGemmScratchFloats * 4);
+    if (e == cudaSuccess) ctx->gemm_scratch_floats = kGemmScratchFloats;
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->gemm_counters), kGemmCounters * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(ctx->gemm_counters, 0, kGemmCounters * sizeof(unsigned));
     if (e != cudaSuccess) {
         int rc = fail(nullptr, JL_ERR_CUDA, "context set-up failed: %s", cudaGetErrorString(e));
         jl_destroy(ctx);
@@ -997,6 +1056,8 @@ int32_t jl_destroy(jl_ctx *ctx) {
     for (void *p : ctx->user_allocs) cudaFree(p);
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+    if (ctx->gemm_counters) cudaFree(ctx->gemm_counters);
     if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
@@ -1175,6 +1236,14 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     JL_REQUIRE(ctx, d.tied_embeddings || ctx->global[JL_ROLE_OUTPUT].data, JL_ERR_STATE,
                "output.weight missing and embeddings are not tied");
     JL_REQUIRE(ctx, ctx->rope_cos != nullptr, JL_ERR_STATE, "RoPE tables missing");
+    if (ctx->tp_size > 1 && !ctx->global[JL_ROLE_OUTPUT].data) {
+        const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
+        if (emb.has_tmap) {
+            const size_t rb = size_t(row_bytes(emb.type, emb.cols));
+            JL_CUDA(ctx, gemm_make_tensor_map(&ctx->wcls_slice_tmap, emb.data + size_t(ctx->tp_rank) * ctx->l_vocab * rb,
+                                              emb.type, ctx->l_vocab, emb.cols));
+        }
+    }
     static const int per_layer_roles[] = {JL_ROLE_ATTENTION_NORM,  JL_ROLE_ATTENTION_QUERY,
                                           JL_ROLE_ATTENTION_KEY,   JL_ROLE_ATTENTION_VALUE,
                                           JL_ROLE_ATTENTION_OUTPUT, JL_ROLE_FFN_NORM,
@@ -1759,20 +1828,9 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     static const int gemm_min_n = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
     if (n >= gemm_min_n) {
         // Wide enough for the tensor cores: one tcgen05 matrix-matrix launch.
-        GemmArgs g = {};
-        g.w = w->t.data;
-        g.type = w->t.type;
-        g.rows = int(w->t.rows);
-        g.cols = int(w->t.cols);
-        g.x = x_dev;
-        g.n = n;
-        g.y = y_dev;
-        g.status = ctx->d_status;
-        cudaError_t e = gemm_tc_launch(g, ctx->stream);
-        if (e != cudaSuccess)
-            return fail(ctx, JL_ERR_CUDA, "matrix-matrix launch failed: %s", cudaGetErrorString(e));
-        ctx->counters.kernel_launches += 1;
-        return JL_OK;
+        int rc = launch_gemm(ctx, w->t, x_dev, n, y_dev, nullptr, &launches);
+        ctx->counters.kernel_launches += launches;
+        return rc;
     }
     for (int b = 0; b < n; ++b) {
         GemvArgs a = {};

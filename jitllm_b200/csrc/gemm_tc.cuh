@@ -5,15 +5,38 @@
 
 namespace jl {
 
-struct GemmArgs {
+// Opaque 128-byte TMA descriptor of one weight matrix (a CUtensorMap): rows x row-bytes as 32-bit
+// words, fetched in boxes of 128 rows x 256 columns. Built once per matrix by gemm_make_tensor_map.
+struct alignas(64) GemmTensorMap {
+    unsigned char bytes[128];
+};
+cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type, int64_t rows, int64_t cols);
+
+struct GemmSeg {
     const uint8_t *w;  // device, GGUF block layout, rows x cols
-    int type;          // kQ8_0 / kQ4_0 / kQ4_K
-    int rows, cols;    // cols a multiple of 256
-    const float *x;    // device, n x cols
-    int n;
+    const GemmTensorMap *tmap;  // host pointer, copied into the launch parameters
     float *y;          // device, n x rows
     const float *res;  // nullable: y = res + W.x (may alias y)
-    int *status;       // device status word
+    int rows;
+};
+
+// Up to three matrices that share the input (Q/K/V, gate/up) go in one launch.
+struct GemmArgs {
+    GemmSeg seg[3];
+    int nseg;
+    int type;        // kQ8_0 / kQ4_0 / kQ4_K
+    int cols;        // a multiple of 256
+    const float *x;  // device, n x cols
+    int n;
+    int *status;     // device status word
+    // Split-K workspace (nullable: then every CTA walks the whole row): partial tiles
+    // [split][n][total rows] and one arrival counter per output tile, zero between launches.
+    float *scratch;
+    size_t scratch_floats;
+    unsigned *counters;
+    int counters_len;
+    int sm_count;
+    int debug;  // timing experiments only: 1 skip weight conversion, 2 skip activation conversion, 4 skip MMA
 };
 
 // Sets the shared-memory attribute of every instantiation (call once, outside stream capture).
