@@ -53,6 +53,27 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     return false;
 }
 
+// Polling wait without the suspend hint, for waits that are expected to end within a microsecond
+// or two and sit on a kernel's critical path: test_wait never parks the thread, so the waiter
+// continues on the cycle the phase flips. Bounded like the other wait (about a second of polls).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 26)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+    }
+    return false;
+}
+
 // ---- bulk async copy global -> shared (TMA engine, 1-D, no multicast) -------------------------
 // dst and src 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes,

@@ -701,7 +701,7 @@ int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y
 // The step for n rows on the tensor-core path (chunked prompt ingestion, wide decode batches):
 // the same operator order as enqueue_step, with every projection one matrix-matrix launch and
 // the element-wise operators as row kernels. Row r uses tokens[r], positions[r], slots[r].
-int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, uint64_t *launches) {
+int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64_t *launches) {
     const jl_model_desc &d = ctx->desc;
     const int dim = d.dim, kv_dim = ctx->kv_dim;
     const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
@@ -787,6 +787,10 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, uint64_t *launches) 
         JL_LAUNCH(ctx, argmax_rows_launch(ctx->logits, ctx->l_vocab, n, ctx->d_active, ctx->d_out, ctx->stream), "argmax");
         if (ctx->tp_size > 1 && (rc = tp_global_argmax(ctx, n, launches))) return rc;
     }
+    if (advance)
+        JL_LAUNCH(ctx, advance_launch(ctx->d_tokens, ctx->d_positions, ctx->d_out, ctx->d_active, ctx->d_history,
+                                      ctx->d_step, n, ctx->stream, false),
+                  "advance");
     return JL_OK;
 }
 
@@ -938,8 +942,8 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
 // Runs one step: replays the captured graph for this width, capturing it on first use.
 int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     if (width == 1 && ctx->tok_ok) return launch_token_kernel(ctx, with_logits, advance);
-    static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 16; }();
-    const bool rows_path = width >= rows_min && !advance;
+    static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 4; }();
+    const bool rows_path = width >= rows_min;
     const int key = width * 8 + (with_logits ? 1 : 0) + (advance ? 2 : 0) + (rows_path ? 4 : 0);
     uint64_t launches = 0;
     // Under tensor parallelism the first step of each shape runs uncaptured, so that NCCL sets up
@@ -948,7 +952,7 @@ int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     static const bool tp_graph = env_flag("JITLLM_B200_TP_GRAPH", true);
     const bool eager = !ctx->use_graph || (ctx->tp_size > 1 && (!tp_graph || ctx->tp_warm.insert(key).second));
     if (eager) {
-        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, &launches)
+        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, advance, &launches)
                            : enqueue_step(ctx, width, with_logits, advance, &launches);
         ctx->counters.kernel_launches += launches;
         return rc;
@@ -957,7 +961,7 @@ int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     if (it == ctx->graphs.end()) {
         cudaGraph_t graph = nullptr;
         JL_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, &launches)
+        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, advance, &launches)
                            : enqueue_step(ctx, width, with_logits, advance, &launches);
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
         if (rc) {
@@ -1523,7 +1527,7 @@ int32_t jl_prefill(jl_ctx *ctx, int32_t kv_slot, const int32_t *tokens, int32_t 
             JL_REQUIRE(ctx, tokens[i] >= 0 && tokens[i] < ctx->desc.vocab, JL_ERR_INVALID,
                        "prompt token %d = %d outside vocabulary of %d", i, tokens[i], ctx->desc.vocab);
     }
-    static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 16; }();
+    static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 4; }();
     // Chunks of up to row_cap tokens through the tensor-core path (every projection one
     // matrix-matrix launch, as TornadoBatchPrefillPass does per chunk,
     // backend/tornado/TornadoBatchPrefillPass.java:104-141); a short tail goes token by token.
@@ -1548,7 +1552,7 @@ int32_t jl_prefill(jl_ctx *ctx, int32_t kv_slot, const int32_t *tokens, int32_t 
             rc = run_step(ctx, 1, false, false);
         } else {
             uint64_t launches = 0;
-            rc = enqueue_rows_step(ctx, chunk, false, &launches);
+            rc = enqueue_rows_step(ctx, chunk, false, false, &launches);
             ctx->counters.kernel_launches += launches;
         }
         if (rc) return rc;

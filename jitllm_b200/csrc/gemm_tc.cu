@@ -3,29 +3,33 @@
 // What it computes: FloatTensor.matmul(context, that[], out[], dim0, dim1)
 // (tensor/standard/FloatTensor.java:127-140 of the reference), n independent mat-vecs.
 //
-// Shape of the kernel. A CTA owns a 128-row x NT-token output tile over a range of columns (the
-// grid's z axis splits the columns so that small matrices still fill the GPU); the accumulator
-// lives in tensor memory (128 lanes x NT fp32 columns).
-//   * Weight bytes arrive exactly once, as they are stored: 128 threads each request their row's
-//     next 256 columns (144 or 272 bytes) with a bulk async copy (the TMA engine) into a ring of
-//     raw stages, completing on an mbarrier. Nothing waits on global-memory latency.
-//   * All 512 threads turn a raw half-stage (128 columns) into the A operand: weights dequantised
-//     element-exactly in fp32 ((d*sc)*q - dmin*m etc., as the reference's getFloat), rounded once
-//     to fp16, stored K-major with the 128-byte swizzle the tensor core expects.
-//   * B = activations split as x = hi + lo with hi, lo fp16 (22 significant bits), so the only
-//     rounding left is the fp16 rounding of the weights (rel-L2 ~3e-4 per product, inside the
-//     1e-3 bar; the reference's own tensor-core prefill feeds single fp16 operands).
-//   * One thread issues tcgen05.mma (M=128, N=NT, K=16) for hi and lo and commits to an mbarrier;
-//     the next operands are built while the tensor core works (two operand stages).
-//   * Epilogue: tcgen05.ld by all warps; with split columns the partial tile goes to a workspace
-//     and the CTA that arrives last at the tile's counter adds the partials in split order (so the
-//     result does not depend on which CTA finished first), adds the residual and writes Y.
-// Every wait is bounded; a wait that runs out sets the status word and the CTA leaves.
+// Shape of the kernel. One persistent CTA per SM. The work is the list of (128-row tile, NT-token
+// tile, 256-column raw stage) triples in that order, cut into equal contiguous ranges, one per
+// CTA, so every SM gets the same number of weight bytes whatever the matrix shape. Inside a CTA
+// three roles run concurrently and meet only at mbarriers:
+//   * warp 17, one thread: requests each raw stage (128 rows x 256 columns of quantised bytes, as
+//     stored) as one 2-D TMA box into a ring; rows past the end of the matrix arrive as zeros.
+//   * warps 0-15: turn a raw half-stage (128 columns) into the A operand -- weights rounded once
+//     to fp16 (Q4_0 / Q8_0: integer code times the block's fp16 scale in half2 arithmetic, which is
+//     exactly the fp16 rounding of the reference's fp32 product; Q4_K: (d*sc)*q - dmin*m in fp32 as
+//     the reference's getFloat, then rounded) stored K-major with the 128-byte swizzle -- and the
+//     B operand: activations split as x = hi + lo with hi, lo fp16 (22 significant bits). The only
+//     rounding left is the fp16 rounding of the weights (rel-L2 ~3e-4 per product, inside the 1e-3
+//     bar; the reference's own tensor-core prefill feeds single fp16 operands).
+//   * warp 16, one thread: issues tcgen05.mma (M=128, N=NT, K=16) for hi and lo into the tensor-
+//     memory accumulator and commits to the barriers that free the operand stage / publish the
+//     finished accumulator.
+//   Warps 0-15 also run the epilogue (tcgen05.ld). A CTA whose range covers a whole output tile
+//   writes it; where a range ends inside a tile the partial goes to a per-CTA slot and the CTA
+//   that arrives last at the tile's counter adds the partials in CTA order (the result does not
+//   depend on which CTA finished first), adds the residual and writes Y.
+// Every wait is bounded; a wait that runs out sets the status word and the CTA winds down.
 #include "gemm_tc.cuh"
 
 #include "formats.cuh"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include <cstring>
 
@@ -33,11 +37,32 @@ namespace jl {
 
 namespace {
 
-constexpr int kGemmThreads = 512;
-constexpr int kTileM = 128;    // weight rows per CTA
+// Which bounded wait the kernel uses (a build-time experiment switch).
+#ifndef JL_GEMM_SUSPENDING_WAIT
+#define GEMM_WAIT mbar_spin_bounded
+#else
+#define GEMM_WAIT mbar_wait_bounded
+#endif
+
+constexpr int kConvertWarps = 16;
+constexpr int kConvertThreads = kConvertWarps * 32;
+constexpr int kGemmThreads = kConvertThreads + 64;  // + tensor-core issue warp + copy-request warp
+constexpr int kTileM = 128;    // weight rows per tile
 constexpr int kStageK = 128;   // columns per operand stage (two 64-column swizzle atoms)
 constexpr int kRawK = 256;     // columns per raw stage (one Q4_K super-block per row)
-constexpr int kMaxSplit = 8;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Barrier among the conversion warps only, on an mbarrier so that the wait is bounded like every
+// other wait here: lane 0 of each warp arrives, everybody waits for the phase to flip.
+__device__ __forceinline__ bool convert_warps_sync(uint64_t *bar, int &phase) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+    const bool ok = GEMM_WAIT(bar, uint32_t(phase) & 1u);
+    ++phase;
+    return ok;
+}
 
 // One box of a 2-D tensor map into shared memory; x counts 32-bit words along a row (x * 4 bytes is
 // a multiple of 16 for every raw stage: 144- and 272-byte steps), y counts rows.
@@ -117,6 +142,7 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 }
 
 
+
 template <int TYPE>
 struct RawFmt {
     static constexpr int row_bytes = (TYPE == kQ8_0) ? 272 : 144;  // 256 columns of one row
@@ -124,15 +150,22 @@ struct RawFmt {
     static constexpr int stage_bytes = kTileM * row_bytes;
 };
 
+// Two bytes of v (selected by sel) as half2 {1024 + byte, 1024 + byte}: 0x64xx is 1024 + xx in fp16.
+__device__ __forceinline__ __half2 bytes_to_half2_plus1024(uint32_t v, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(v), "r"(0x64646464u), "r"(sel));
+    return *reinterpret_cast<const __half2 *>(&r);
+}
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<const uint32_t *>(&h); }
+
 // 32 consecutive weights of one row out of a raw stage in shared memory: `row_u32` is the shared
 // address of the row's 256-column slice, `unit` the 64-column unit inside it (0..3), `half` the
-// 32-column half of the unit. Element-exact in fp32, then rounded to fp16 into four 16-byte chunks.
+// 32-column half of the unit. Result: the weights rounded to fp16, as four 16-byte chunks.
 template <int TYPE>
 __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, int half, uint4 (&out)[4]) {
-    float w[32];
     if constexpr (TYPE == kQ4_K) {
         // tensor/standard/Q4_KFloatTensor.java:68-122: unit p holds sub-blocks 2p (low nibbles) and
-        // 2p+1 (high nibbles) of the same 32 bytes.
+        // 2p+1 (high nibbles) of the same 32 bytes; w = (d*sc)*q - dmin*m, every step in fp32.
         const uint4 hdr = lds128(row_u32);
         const uint4 q0 = lds128(row_u32 + 16 + unit * 32);
         const uint4 q1 = lds128(row_u32 + 32 + unit * 32);
@@ -150,86 +183,121 @@ __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, in
         const float mm = __fmul_rn(dmin, float((mw >> sh) & 0xFFu));
         const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         const int nib = half * 4;
+        float w[32];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+            const uint32_t v = (qw[i] >> nib) & 0x0F0F0F0Fu;
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const uint32_t q = (qw[i] >> (8 * b + nib)) & 0xFu;
-                w[i * 4 + b] = __fsub_rn(__fmul_rn(ds, float(q)), mm);
+                // 0x4B000000 | q is the float 2^23 + q: the integer code without a conversion unit
+                const float q = __uint_as_float(0x4B000000u | ((v >> (8 * b)) & 0xFFu)) - 8388608.0f;
+                w[i * 4 + b] = __fsub_rn(__fmul_rn(ds, q), mm);
             }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            out[c].x = pack_half2(w[8 * c + 0], w[8 * c + 1]);
+            out[c].y = pack_half2(w[8 * c + 2], w[8 * c + 3]);
+            out[c].z = pack_half2(w[8 * c + 4], w[8 * c + 5]);
+            out[c].w = pack_half2(w[8 * c + 6], w[8 * c + 7]);
         }
     } else if constexpr (TYPE == kQ4_0) {
         // tensor/standard/Q4_0FloatTensor.java:56-79: a unit is two 18-byte blocks; element i < 16
-        // is the low nibble of byte i, element i >= 16 the high nibble of byte i - 16.
+        // is the low nibble of byte i, element i >= 16 the high nibble of byte i - 16; w = (q-8)*d.
+        // (q-8) is exact in fp16 and d is fp16, so one half-precision multiply rounds exactly like
+        // the reference's fp32 product narrowed to fp16.
         const uint32_t base = row_u32 + unit * 36 + half * 16;
         uint32_t t[5];
 #pragma unroll
         for (int i = 0; i < 5; ++i) t[i] = lds32(base + 4 * i);
-        const float d = half_bits_to_float(half == 0 ? (t[0] & 0xFFFFu) : (t[0] >> 16));
+        const uint32_t dbits = half == 0 ? (t[0] & 0xFFFFu) : (t[0] >> 16);
+        const uint32_t d2u = dbits | (dbits << 16);
+        const __half2 d2 = *reinterpret_cast<const __half2 *>(&d2u);
+        const __half2 off = __float2half2_rn(1032.0f);
+        uint32_t lo[8], hi[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t q = half == 0 ? __funnelshift_r(t[i], t[i + 1], 16) : t[1 + i];
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const int byte = (q >> (8 * b)) & 0xFF;
-                w[i * 4 + b] = __fmul_rn(float((byte & 0xF) - 8), d);
-                w[16 + i * 4 + b] = __fmul_rn(float((byte >> 4) - 8), d);
-            }
+            const uint32_t l4 = q & 0x0F0F0F0Fu, h4 = (q >> 4) & 0x0F0F0F0Fu;
+            lo[2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(l4, 0x4140u), off), d2));
+            lo[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(l4, 0x4342u), off), d2));
+            hi[2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(h4, 0x4140u), off), d2));
+            hi[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(h4, 0x4342u), off), d2));
         }
+        out[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        out[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+        out[2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        out[3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
     } else {
-        // tensor/standard/Q8_0FloatTensor.java:53-61: a unit is two 34-byte blocks.
+        // tensor/standard/Q8_0FloatTensor.java:53-61: a unit is two 34-byte blocks; w = q * d, again
+        // one exact-input half-precision multiply.
         const uint32_t base = row_u32 + unit * 68 + half * 32;
         uint32_t t[9];
 #pragma unroll
         for (int i = 0; i < 9; ++i) t[i] = lds32(base + 4 * i);
-        const float d = half_bits_to_float(half == 0 ? (t[0] & 0xFFFFu) : (t[0] >> 16));
+        const uint32_t dbits = half == 0 ? (t[0] & 0xFFFFu) : (t[0] >> 16);
+        const uint32_t d2u = dbits | (dbits << 16);
+        const __half2 d2 = *reinterpret_cast<const __half2 *>(&d2u);
+        const __half2 off = __float2half2_rn(1152.0f);  // 1024 + the 128 added by the sign flip
+        uint32_t h[16];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const uint32_t q = half == 0 ? __funnelshift_r(t[i], t[i + 1], 16) : t[1 + i];
-#pragma unroll
-            for (int b = 0; b < 4; ++b) w[i * 4 + b] = __fmul_rn(float(int8_t((q >> (8 * b)) & 0xFF)), d);
+            const uint32_t q = (half == 0 ? __funnelshift_r(t[i], t[i + 1], 16) : t[1 + i]) ^ 0x80808080u;
+            h[2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(q, 0x4140u), off), d2));
+            h[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(q, 0x4342u), off), d2));
         }
-    }
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        out[c].x = pack_half2(w[8 * c + 0], w[8 * c + 1]);
-        out[c].y = pack_half2(w[8 * c + 2], w[8 * c + 3]);
-        out[c].z = pack_half2(w[8 * c + 4], w[8 * c + 5]);
-        out[c].w = pack_half2(w[8 * c + 6], w[8 * c + 7]);
+        for (int c = 0; c < 4; ++c) out[c] = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
     }
 }
 
 template <int TYPE, int NT>
 struct GemmSmem {
     static constexpr int a_sub = kTileM * 128;         // one 64-column atom of A: 16 KB
-    static constexpr int b_sub = NT * 128;             // one 64-column atom of B
+    static constexpr int b_sub = 2 * NT * 128;         // one 64-column atom of B: hi rows, then lo rows
     static constexpr int a_stage = 2 * a_sub;
-    static constexpr int b_stage = 4 * b_sub;          // hi (2 atoms) + lo (2 atoms)
+    static constexpr int b_stage = 2 * b_sub;
+    static constexpr int raw_bytes = RawFmt<TYPE>::stages * RawFmt<TYPE>::stage_bytes;
+    static constexpr int budget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/ - raw_bytes;
+    // As many operand stages as fit (2..4): the barrier round trip between conversion warps and the
+    // tensor core is hidden only when several stages are in flight.
+    static constexpr int fit = budget / (a_stage + b_stage);
+    static constexpr int stages = fit >= 4 ? 4 : (fit >= 3 ? 3 : 2);
     static constexpr int a_off = 0;
-    static constexpr int b_off = 2 * a_stage;
-    static constexpr int raw_off = b_off + 2 * b_stage;
-    static constexpr int bar_off = raw_off + RawFmt<TYPE>::stages * RawFmt<TYPE>::stage_bytes;
-    static constexpr int total = bar_off + 128 + 1024 /*alignment slack*/;
+    static constexpr int b_off = stages * a_stage;
+    static constexpr int raw_off = b_off + stages * b_stage;
+    static constexpr int bar_off = raw_off + raw_bytes;
+    static constexpr int total = bar_off + 256 + 1024;
 };
-static_assert(GemmSmem<kQ8_0, 64>::total <= 227 * 1024, "shared memory budget");
+static_assert(GemmSmem<kQ8_0, 64>::total <= 227 * 1024 && GemmSmem<kQ4_K, 64>::total <= 227 * 1024 &&
+                  GemmSmem<kQ4_K, 16>::total <= 227 * 1024 && GemmSmem<kQ8_0, 32>::total <= 227 * 1024,
+              "shared memory budget");
 
 struct TileRef {
-    int seg, row0, row_offset;  // segment, first row inside it, rows of the segments before it
+    int seg, row0;
 };
 
 __device__ __forceinline__ TileRef locate_tile(const GemmArgs &a, int tile) {
-    TileRef t = {0, 0, 0};
+    TileRef t = {0, 0};
     for (int s = 0; s < a.nseg; ++s) {
         const int tiles = (a.seg[s].rows + kTileM - 1) / kTileM;
-        if (tile < tiles) {
+        if (tile < tiles || s == a.nseg - 1) {
             t.seg = s;
             t.row0 = tile * kTileM;
             return t;
         }
         tile -= tiles;
-        t.row_offset += a.seg[s].rows;
     }
     return t;
+}
+
+// The contiguous range of the flattened work list that CTA c owns.
+__device__ __forceinline__ long long range_lo(long long total, int c, int ctas) { return total * c / ctas; }
+__device__ __forceinline__ int cta_of(long long total, long long f, int ctas) {
+    int c = int(f * ctas / total);
+    while (c + 1 < ctas && range_lo(total, c + 1, ctas) <= f) ++c;
+    while (c > 0 && range_lo(total, c, ctas) > f) --c;
+    return c;
 }
 
 template <int TYPE, int NT>
@@ -239,244 +307,333 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     extern __shared__ uint8_t smem_raw[];
     using S = GemmSmem<TYPE, NT>;
     using R = RawFmt<TYPE>;
+    constexpr int RS = R::stages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // 1024-byte aligned base: the swizzle pattern is a function of the shared address.
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t *a_free = reinterpret_cast<uint64_t *>(base + S::bar_off);  // [2]
-    uint64_t *raw_full = a_free + 2;                                      // [R::stages]
-    uint32_t *tmem_ptr = reinterpret_cast<uint32_t *>(base + S::bar_off + 64);
-    uint32_t *last_flag = tmem_ptr + 1;
-    constexpr uint32_t tmem_cols = NT < 32 ? 32 : NT;
+    constexpr int ST = S::stages;
+    uint64_t *a_free = reinterpret_cast<uint64_t *>(base + S::bar_off);  // [ST] tensor core done with operand stage
+    uint64_t *a_full = a_free + ST;                                       // [ST] operand stage written
+    uint64_t *raw_full = a_full + ST;                                     // [RS] raw bytes landed
+    uint64_t *raw_empty = raw_full + RS;                                  // [RS] raw bytes consumed
+    uint64_t *acc_full = raw_empty + RS;                                  // accumulator finished
+    uint64_t *acc_empty = acc_full + 1;                                   // accumulator read out
+    uint64_t *fix_bar = acc_empty + 1;                                    // conversion warps' own barrier
+    uint32_t *tmem_ptr = reinterpret_cast<uint32_t *>(base + S::bar_off + 192);
+    volatile uint32_t *last_flag = tmem_ptr + 1;
+    volatile uint32_t *abort_flag = tmem_ptr + 2;
+    constexpr uint32_t tmem_cols = 2 * NT;  // hi and lo partial products side by side
 
-    const TileRef tile = locate_tile(a, blockIdx.x);
-    const GemmSeg seg = a.seg[tile.seg];
-    const int tok0 = blockIdx.y * NT;
-    const int ksplit = gridDim.z, split = blockIdx.z;
-    const size_t rowb = size_t(row_bytes(TYPE, a.cols));
+    int tiles = 0;
+    for (int s = 0; s < a.nseg; ++s) tiles += (a.seg[s].rows + kTileM - 1) / kTileM;
+    const int n_tiles = (a.n + NT - 1) / NT;
     const int raw_total = a.cols / kRawK;
-    const int raw_begin = int(int64_t(raw_total) * split / ksplit);
-    const int raw_end = int(int64_t(raw_total) * (split + 1) / ksplit);
-    const int n_raw = raw_end - raw_begin;
-    const int n_a = 2 * n_raw;
+    const long long total = (long long)tiles * n_tiles * raw_total;
+    const int ctas = gridDim.x;
+    const long long lo = range_lo(total, blockIdx.x, ctas), hi = range_lo(total, blockIdx.x + 1, ctas);
 
-    if (warp == 0) tmem_alloc(tmem_ptr, tmem_cols);
+    if (warp == kConvertWarps) tmem_alloc(tmem_ptr, tmem_cols);
     if (tid == 0) {
-        mbar_init(a_free + 0, 1);
-        mbar_init(a_free + 1, 1);
-        for (int s = 0; s < R::stages; ++s) mbar_init(raw_full + s, 1);
+        for (int s = 0; s < ST; ++s) {
+            mbar_init(a_free + s, 1);
+            mbar_init(a_full + s, kConvertWarps);
+        }
+        for (int s = 0; s < RS; ++s) {
+            mbar_init(raw_full + s, 1);
+            mbar_init(raw_empty + s, kConvertWarps);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, kConvertWarps);
+        mbar_init(fix_bar, kConvertWarps);
         mbar_fence_init();
+        *last_flag = 0u;
+        *abort_flag = 0u;
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = *tmem_ptr;
-    constexpr uint32_t idesc = instr_desc_f16(NT);
 
-    // Raw producer role (one thread): a raw stage is one 2-D TMA box of 128 rows x 256 columns;
-    // rows past the end of the matrix arrive as zeros.
-    const CUtensorMap *tmap = tile.seg == 0 ? &tm0 : (tile.seg == 1 ? &tm1 : &tm2);
-    const uint64_t policy = policy_evict_first();
-    auto request_raw = [&](int i) {
-        uint64_t *bar = raw_full + (i % R::stages);
-        mbar_expect_tx(bar, R::stage_bytes);
-        tma_load_2d(base + S::raw_off + (i % R::stages) * R::stage_bytes, tmap, (raw_begin + i) * (R::row_bytes / 4),
-                    tile.row0, bar, policy);
-    };
-    if (tid == 0) {
-        fence_proxy_async();
-        for (int i = 0; i < R::stages && i < n_raw; ++i) request_raw(i);
-    }
-
-    // Operand-building role: thread t dequantises 32 columns of weight row t & 127.
-    const int a_row = tid & 127, a_q = tid >> 7;  // a_q: which 32-column quarter of the 128
-    const int a_atom = a_q >> 1, a_half = a_q & 1;
-    const bool a_valid = tile.row0 + a_row < seg.rows;
-    constexpr int kBChunks = NT * 16;  // 16-byte chunks of eight activations per operand stage
-    constexpr int kBPerThread = (kBChunks + kGemmThreads - 1) / kGemmThreads;
-    bool failed = false;
-
-    for (int it = 0; it < n_a; ++it) {
-        const int s = it & 1, j = it & 1, ri = it >> 1;
-        const int k0 = (raw_begin + ri) * kRawK + j * kStageK;
-        // Activations first: their global loads are in flight while the weights are dequantised.
-        float4 xv[kBPerThread][2];
-#pragma unroll
-        for (int u = 0; u < kBPerThread; ++u) {
-            const int ch = tid + u * kGemmThreads;
-            const int t = ch >> 4, kc = ch & 15;
-            const int tok = tok0 + t;
-            if (ch < kBChunks && tok < a.n) {
-                const float4 *src = reinterpret_cast<const float4 *>(a.x + size_t(tok) * a.cols + k0 + kc * 8);
-                xv[u][0] = __ldg(src);
-                xv[u][1] = __ldg(src + 1);
-            } else {
-                xv[u][0] = xv[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
-        bool ok = true;
-        if (j == 0) ok = mbar_wait_bounded(raw_full + (ri % R::stages), uint32_t(ri / R::stages) & 1u);
-        if (ok && it >= 2) ok = mbar_wait_bounded(a_free + s, uint32_t((it - 2) >> 1) & 1u);
-        if (ok) {
-            tc_fence_after();
-            uint8_t *a_st = base + S::a_off + s * S::a_stage;
-            uint8_t *b_st = base + S::b_off + s * S::b_stage;
-            if (!(a.debug & 1)) {
-                uint4 chunks[4];
-                const uint32_t row_u32 = smem_u32(base + S::raw_off + (ri % R::stages) * R::stage_bytes) +
-                                         uint32_t(a_row) * R::row_bytes;
-                dequant32_to_half<TYPE>(row_u32, 2 * j + a_atom, a_half, chunks);
-                uint8_t *tile_a = a_st + size_t(a_atom) * S::a_sub;
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<uint4 *>(tile_a + sw128_offset(a_row, a_half * 4 + c)) =
-                        a_valid ? chunks[c] : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int u = 0; u < kBPerThread; ++u) {
-                const int ch = tid + u * kGemmThreads;
-                if (ch < kBChunks && !(a.debug & 2)) {
-                    const int t = ch >> 4, kc = ch & 15;
-                    const int atom = kc >> 3, c = kc & 7;
-                    const float x[8] = {xv[u][0].x, xv[u][0].y, xv[u][0].z, xv[u][0].w,
-                                        xv[u][1].x, xv[u][1].y, xv[u][1].z, xv[u][1].w};
-                    float lo[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) lo[i] = x[i] - __half2float(__float2half_rn(x[i]));
-                    const uint32_t off = sw128_offset(t, c);
-                    uint8_t *bh = b_st + size_t(atom) * S::b_sub;
-                    uint8_t *bl = bh + 2 * S::b_sub;
-                    *reinterpret_cast<uint4 *>(bh + off) = make_uint4(pack_half2(x[0], x[1]), pack_half2(x[2], x[3]),
-                                                                     pack_half2(x[4], x[5]), pack_half2(x[6], x[7]));
-                    *reinterpret_cast<uint4 *>(bl + off) = make_uint4(pack_half2(lo[0], lo[1]), pack_half2(lo[2], lo[3]),
-                                                                     pack_half2(lo[4], lo[5]), pack_half2(lo[6], lo[7]));
-                }
-            }
-        }
-        // Generic-proxy writes -> visible to the tensor core's (async proxy) reads.
-        fence_proxy_async();
-        tc_fence_before();
-        if (__syncthreads_or(!ok)) {
-            failed = true;
-            break;
-        }
-        if (tid == 0) {
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(base + S::a_off + s * S::a_stage);
-            const uint32_t bh_addr = smem_u32(base + S::b_off + s * S::b_stage);
-            const uint32_t bl_addr = bh_addr + 2 * S::b_sub;
-#pragma unroll
-            for (int atom = 0; atom < 2; ++atom) {
-#pragma unroll
-                for (int k16 = 0; k16 < 4; ++k16) {
-                    const uint64_t da = smem_desc_sw128(a_addr + atom * S::a_sub + k16 * 32);
-                    const uint64_t dbh = smem_desc_sw128(bh_addr + atom * S::b_sub + k16 * 32);
-                    const uint64_t dbl = smem_desc_sw128(bl_addr + atom * S::b_sub + k16 * 32);
-                    if (a.debug & 4) continue;
-                    umma_f16(tmem_d, da, dbh, idesc, (it > 0 || atom > 0 || k16 > 0) ? 1u : 0u);
-                    umma_f16(tmem_d, da, dbl, idesc, 1u);
-                }
-            }
-            umma_commit(a_free + s);  // arrives when every MMA issued so far has completed
-        }
-        // Both halves of the raw stage have been read by every thread (they all passed the
-        // barrier above): hand it back to the copy engine.
-        if (j == 1 && tid == 0 && ri + R::stages < n_raw) {
+    if (warp == kConvertWarps + 1) {
+        // ---- copy requests -------------------------------------------------------------------
+        if (lane == 0) {
+            const uint64_t policy = policy_evict_first();
             fence_proxy_async();
-            request_raw(ri + R::stages);
+            int i = 0, cur_u = -1;
+            TileRef tr = {0, 0};
+            for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
+                const int u = int(f / raw_total), r = int(f - (long long)u * raw_total);
+                if (u != cur_u) {
+                    cur_u = u;
+                    tr = locate_tile(a, u / n_tiles);
+                }
+                const int st = i % RS;
+                if (i >= RS && !GEMM_WAIT(raw_empty + st, uint32_t(i / RS - 1) & 1u)) {
+                    *abort_flag = 1u;
+                    atomicExch(a.status, kDevTimeout);
+                    break;
+                }
+                const CUtensorMap *tmap = tr.seg == 0 ? &tm0 : (tr.seg == 1 ? &tm1 : &tm2);
+                if (a.debug & 8) {  // timing experiment: no copy at all, the stage is declared full
+                    mbar_arrive(raw_full + st);
+                    continue;
+                }
+                mbar_expect_tx(raw_full + st, R::stage_bytes);
+                tma_load_2d(base + S::raw_off + st * R::stage_bytes, tmap, r * (R::row_bytes / 4), tr.row0,
+                            raw_full + st, policy);
+            }
         }
-    }
-
-    // Wait for the last commit (covers all earlier MMAs), then read the accumulator.
-    if (!failed && n_a > 0) {
-        if (!mbar_wait_bounded(a_free + ((n_a - 1) & 1), uint32_t((n_a - 1) >> 1) & 1u)) failed = true;
-    }
-    failed = __syncthreads_or(failed);
-    tc_fence_after();
-    // TMEM lane = output row of the tile; warp w reads lanes 32*(w%4) and the 16-column group w/4.
-    const int lane_grp = warp & 3, col_grp = warp >> 2;
-    const int row = tile.row0 + lane_grp * 32 + lane;
-    size_t total_rows = 0;
-    for (int sgi = 0; sgi < a.nseg; ++sgi) total_rows += size_t(a.seg[sgi].rows);
-    const size_t grow = size_t(tile.row_offset) + row;
-    if (!failed && col_grp * 16 < NT && n_a > 0) {
-        float v[16];
-        tmem_ld16(tmem_d + (uint32_t(lane_grp * 32) << 16) + uint32_t(col_grp * 16), v);
-        if (row < seg.rows) {
+    } else if (warp == kConvertWarps) {
+        // ---- tensor-core issue ---------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_f16(2 * NT);
+            int i = 0, done = 0;
+            for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
+                const int u = int(f / raw_total);
+                const long long u_lo = (long long)u * raw_total;
+                const long long seg_begin = u_lo > lo ? u_lo : lo;
+                const long long seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
+                bool ok = true;
+                for (int j = 0; j < 2 && ok; ++j) {
+                    const int q = 2 * i + j, s = q % ST;
+                    ok = GEMM_WAIT(a_full + s, uint32_t(q / ST) & 1u);
+                    const bool first = f == seg_begin && j == 0;
+                    if (ok && first && done > 0) ok = GEMM_WAIT(acc_empty, uint32_t(done - 1) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da0 = smem_desc_sw128(smem_u32(base + S::a_off + s * S::a_stage));
+                    const uint64_t db0 = smem_desc_sw128(smem_u32(base + S::b_off + s * S::b_stage));
 #pragma unroll
-            for (int jc = 0; jc < 16; ++jc) {
-                const int tok = tok0 + col_grp * 16 + jc;
-                if (tok < a.n) {
-                    if (ksplit == 1) {
-                        float out = v[jc];
-                        if (seg.res != nullptr) out = seg.res[size_t(tok) * seg.rows + row] + out;
-                        seg.y[size_t(tok) * seg.rows + row] = out;
+                    for (int atom = 0; atom < 2; ++atom) {
+#pragma unroll
+                        for (int k16 = 0; k16 < 4; ++k16) {
+                            const uint64_t ka = uint64_t((atom * S::a_sub + k16 * 32) >> 4);
+                            const uint64_t kb = uint64_t((atom * S::b_sub + k16 * 32) >> 4);
+                            if (a.debug & 4) continue;
+                            umma_f16(tmem_d, da0 + ka, db0 + kb, idesc, (first && atom == 0 && k16 == 0) ? 0u : 1u);
+                        }
+                    }
+                    if ((a.debug & 36) == 36) mbar_arrive(a_free + s);  // timing experiment, only without MMAs
+                    else umma_commit(a_free + s);  // arrives when every MMA issued so far has completed
+                    if (f + 1 == seg_end && j == 1) {
+                        umma_commit(acc_full);
+                        ++done;
+                    }
+                }
+                if (!ok) {
+                    *abort_flag = 1u;
+                    atomicExch(a.status, kDevTimeout);
+                    break;
+                }
+            }
+        }
+    } else {
+        // ---- operand conversion and epilogue (warps 0-15) -------------------------------------
+        const int a_row = tid & 127, a_q = tid >> 7;  // a_q: which 32-column quarter of the 128
+        const int a_atom = a_q >> 1, a_half = a_q & 1;
+        constexpr int kBChunks = NT * 16;  // 16-byte chunks of eight activations per operand stage
+        constexpr int kBPerThread = (kBChunks + kConvertThreads - 1) / kConvertThreads;
+        const int lane_grp = warp & 3, col_grp = warp >> 2;  // epilogue: TMEM lanes 32*lane_grp, columns 16*col_grp
+        size_t total_rows = 0;
+        for (int sgi = 0; sgi < a.nseg; ++sgi) total_rows += size_t(a.seg[sgi].rows);
+        int i = 0, done = 0, cur_u = -1, fix_phase = 0;
+        TileRef tr = {0, 0};
+        int tok0 = 0;
+        bool a_valid = false;
+        bool ok = true;
+        for (long long f = lo; f < hi && ok && *abort_flag == 0u; ++f, ++i) {
+            const int u = int(f / raw_total), r = int(f - (long long)u * raw_total);
+            if (u != cur_u) {
+                cur_u = u;
+                tr = locate_tile(a, u / n_tiles);
+                tok0 = (u % n_tiles) * NT;
+                a_valid = tr.row0 + a_row < a.seg[tr.seg].rows;
+            }
+            const int st = i % RS;
+            ok = GEMM_WAIT(raw_full + st, uint32_t(i / RS) & 1u);
+            if (!ok) break;
+            const uint32_t row_u32 = smem_u32(base + S::raw_off + st * R::stage_bytes) + uint32_t(a_row) * R::row_bytes;
+#pragma unroll 1
+            for (int j = 0; j < 2; ++j) {
+                const int q = 2 * i + j, s = q % ST;
+                const int k0 = r * kRawK + j * kStageK;
+                // Activations first: their loads are in flight while the weights are converted.
+                float4 xv[kBPerThread][2];
+#pragma unroll
+                for (int uu = 0; uu < kBPerThread; ++uu) {
+                    const int ch = tid + uu * kConvertThreads;
+                    const int t = ch >> 4, kc = ch & 15;
+                    const int tok = tok0 + t;
+                    if (ch < kBChunks && tok < a.n) {
+                        const float4 *src = reinterpret_cast<const float4 *>(a.x + size_t(tok) * a.cols + k0 + kc * 8);
+                        xv[uu][0] = __ldg(src);
+                        xv[uu][1] = __ldg(src + 1);
                     } else {
-                        a.scratch[(size_t(split) * a.n + tok) * total_rows + grow] = v[jc];
+                        xv[uu][0] = xv[uu][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+                if (q >= ST) ok = GEMM_WAIT(a_free + s, uint32_t(q / ST - 1) & 1u);
+                if (!ok) break;
+                uint8_t *a_st = base + S::a_off + s * S::a_stage;
+                uint8_t *b_st = base + S::b_off + s * S::b_stage;
+                if (!(a.debug & 1)) {
+                    uint4 chunks[4];
+                    dequant32_to_half<TYPE>(row_u32, 2 * j + a_atom, a_half, chunks);
+                    uint8_t *tile_a = a_st + size_t(a_atom) * S::a_sub;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        *reinterpret_cast<uint4 *>(tile_a + sw128_offset(a_row, a_half * 4 + c)) =
+                            a_valid ? chunks[c] : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int uu = 0; uu < kBPerThread; ++uu) {
+                    const int ch = tid + uu * kConvertThreads;
+                    if (ch < kBChunks && !(a.debug & 2)) {
+                        const int t = ch >> 4, kc = ch & 15;
+                        const int atom = kc >> 3, c = kc & 7;
+                        const float x[8] = {xv[uu][0].x, xv[uu][0].y, xv[uu][0].z, xv[uu][0].w,
+                                            xv[uu][1].x, xv[uu][1].y, xv[uu][1].z, xv[uu][1].w};
+                        float xl[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) xl[e] = x[e] - __half2float(__float2half_rn(x[e]));
+                        const uint32_t off = sw128_offset(t, c);
+                        uint8_t *bh = b_st + size_t(atom) * S::b_sub;
+                        uint8_t *bl = bh + NT * 128;  // the lo rows follow the hi rows of the same atom
+                        *reinterpret_cast<uint4 *>(bh + off) = make_uint4(pack_half2(x[0], x[1]), pack_half2(x[2], x[3]),
+                                                                         pack_half2(x[4], x[5]), pack_half2(x[6], x[7]));
+                        *reinterpret_cast<uint4 *>(bl + off) = make_uint4(pack_half2(xl[0], xl[1]), pack_half2(xl[2], xl[3]),
+                                                                         pack_half2(xl[4], xl[5]), pack_half2(xl[6], xl[7]));
+                    }
+                }
+                // Generic-proxy writes -> visible to the tensor core's (async proxy) reads.
+                if (!(a.debug & 16)) fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(a_full + s);
+            }
+            if (!ok) break;
+            // This warp has read both halves of the raw stage: hand its share back.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(raw_empty + st);
+
+            const long long u_lo = (long long)u * raw_total;
+            const long long seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
+            if (f + 1 != seg_end) continue;
+            // ---- this CTA's share of output tile u is complete -----------------------------------
+            const long long seg_begin = u_lo > lo ? u_lo : lo;
+            const bool whole = seg_begin == u_lo && seg_end == u_lo + raw_total;
+            const GemmSeg seg = a.seg[tr.seg];
+            size_t row_offset = 0;
+            for (int sgi = 0; sgi < tr.seg; ++sgi) row_offset += size_t(a.seg[sgi].rows);
+            (void)row_offset;
+            ok = GEMM_WAIT(acc_full, uint32_t(done) & 1u);
+            if (!ok) break;
+            ++done;
+            tc_fence_after();
+            // partial slot: 0 if this CTA's range starts inside the tile, 1 if it only ends inside it
+            float *slot = a.scratch + (size_t(blockIdx.x) * 2 + (seg_begin > u_lo ? 0 : 1)) * (size_t(kTileM) * NT);
+            if (col_grp * 16 < NT) {
+                float v[16], vl[16];
+                tmem_ld16(tmem_d + (uint32_t(lane_grp * 32) << 16) + uint32_t(col_grp * 16), v);
+                tmem_ld16(tmem_d + (uint32_t(lane_grp * 32) << 16) + uint32_t(NT + col_grp * 16), vl);
+#pragma unroll
+                for (int jc = 0; jc < 16; ++jc) v[jc] += vl[jc];
+                const int rr = lane_grp * 32 + lane;
+                const int row = tr.row0 + rr;
+#pragma unroll
+                for (int jc = 0; jc < 16; ++jc) {
+                    const int t = col_grp * 16 + jc;
+                    const int tok = tok0 + t;
+                    if (whole) {
+                        if (row < seg.rows && tok < a.n) {
+                            float out = v[jc];
+                            if (seg.res != nullptr) out = seg.res[size_t(tok) * seg.rows + row] + out;
+                            seg.y[size_t(tok) * seg.rows + row] = out;
+                        }
+                    } else {
+                        slot[t * kTileM + rr] = v[jc];
                     }
                 }
             }
-        }
-    }
-    if (ksplit > 1 && !failed) {
-        // The CTA that arrives last adds the partial tiles in split order.
-        __threadfence();
-        __syncthreads();
-        unsigned *counter = a.counters + (blockIdx.y * gridDim.x + blockIdx.x);
-        if (tid == 0) {
-            const unsigned prev = atomicAdd(counter, 1u);
-            *last_flag = prev == unsigned(ksplit) - 1u ? 1u : 0u;
-        }
-        __syncthreads();
-        if (*last_flag != 0u) {
-            __threadfence();
-            const int ntok = min(NT, a.n - tok0);
-            for (int idx = tid; idx < ntok * kTileM; idx += kGemmThreads) {
-                const int t = idx >> 7, r = idx & 127;
-                const int orow = tile.row0 + r;
-                if (orow >= seg.rows) continue;
-                const int tok = tok0 + t;
-                float sum = 0.f;
-                for (int sp = 0; sp < ksplit; ++sp) {
-                    const float pv = __ldcg(a.scratch + (size_t(sp) * a.n + tok) * total_rows + tile.row_offset + orow);
-                    sum = sp == 0 ? pv : sum + pv;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty);
+            if (!whole) {
+                // The CTA that arrives last adds the partial tiles in CTA order.
+                __threadfence();
+                ok = convert_warps_sync(fix_bar, fix_phase);
+                if (!ok) break;
+                const int c_first = cta_of(total, u_lo, ctas), c_last = cta_of(total, u_lo + raw_total - 1, ctas);
+                if (tid == 0) {
+                    const unsigned prev = atomicAdd(a.counters + u, 1u);
+                    *last_flag = prev == unsigned(c_last - c_first) ? 1u : 0u;
                 }
-                if (seg.res != nullptr) sum = seg.res[size_t(tok) * seg.rows + orow] + sum;
-                seg.y[size_t(tok) * seg.rows + orow] = sum;
+                ok = convert_warps_sync(fix_bar, fix_phase);
+                if (!ok) break;
+                if (*last_flag != 0u) {
+                    __threadfence();
+                    // Four rows per item, every contributor's load issued before the first add: the
+                    // fold costs about one L2 round trip per item instead of one per contributor.
+                    const int ntok = min(NT, a.n - tok0);
+                    const int ncontrib = c_last - c_first + 1;
+                    const size_t slot_floats = size_t(kTileM) * NT;
+                    for (int item = tid; item < ntok * (kTileM / 4); item += kConvertThreads) {
+                        const int t = item >> 5, rr = (item & 31) * 4;
+                        float4 pv[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            if (k < ncontrib) {
+                                const int c = c_first + k;
+                                const int which = range_lo(total, c, ctas) > u_lo ? 0 : 1;
+                                pv[k] = __ldcg(reinterpret_cast<const float4 *>(a.scratch + (size_t(c) * 2 + which) * slot_floats +
+                                                                                t * kTileM + rr));
+                            } else {
+                                pv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        }
+                        float4 sum = pv[0];
+#pragma unroll
+                        for (int k = 1; k < 8; ++k) {
+                            if (k < ncontrib) {
+                                sum.x += pv[k].x;
+                                sum.y += pv[k].y;
+                                sum.z += pv[k].z;
+                                sum.w += pv[k].w;
+                            }
+                        }
+                        for (int c = c_first + 8; c <= c_last; ++c) {  // more than eight contributors: rare
+                            const int which = range_lo(total, c, ctas) > u_lo ? 0 : 1;
+                            const float4 more = __ldcg(reinterpret_cast<const float4 *>(
+                                a.scratch + (size_t(c) * 2 + which) * slot_floats + t * kTileM + rr));
+                            sum.x += more.x;
+                            sum.y += more.y;
+                            sum.z += more.z;
+                            sum.w += more.w;
+                        }
+                        const int tok = tok0 + t;
+                        const float s4[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int orow = tr.row0 + rr + e;
+                            if (orow < seg.rows) {
+                                float out = s4[e];
+                                if (seg.res != nullptr) out = seg.res[size_t(tok) * seg.rows + orow] + out;
+                                seg.y[size_t(tok) * seg.rows + orow] = out;
+                            }
+                        }
+                    }
+                    if (tid == 0) a.counters[u] = 0u;
+                }
+                ok = convert_warps_sync(fix_bar, fix_phase);  // last_flag is reused by the next partial tile
             }
-            if (tid == 0) *counter = 0u;
+        }
+        if (!ok && lane == 0) {
+            *abort_flag = 1u;
+            atomicExch(a.status, kDevTimeout);
         }
     }
-    if (failed && tid == 0) atomicExch(a.status, kDevTimeout);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_d, tmem_cols);
-}
-
-// Column splits: enough CTAs to fill the GPU's last wave, at least two raw stages per CTA, and
-// no more than the workspace holds.
-int choose_split(const GemmArgs &a, int tiles, int n_tiles, int nt) {
-    if (a.scratch == nullptr || a.counters == nullptr || tiles * n_tiles > a.counters_len) return 1;
-    const int sms = a.sm_count > 0 ? a.sm_count : 148;
-    const int raw_total = a.cols / kRawK;
-    size_t total_rows = 0;
-    for (int s = 0; s < a.nseg; ++s) total_rows += size_t(a.seg[s].rows);
-    const int work = tiles * n_tiles;
-    if (work >= 4 * sms) return 1;
-    int best = 1;
-    double best_eff = 0.0;
-    for (int ks = 1; ks <= kMaxSplit; ++ks) {
-        if (raw_total / ks < 2) break;
-        if (size_t(ks) * a.n * total_rows > a.scratch_floats && ks > 1) break;
-        const double waves = double(work) * ks / sms;
-        const double eff = waves / double((long long)(waves + 0.999999));
-        // a later (larger) split must be clearly better to be worth its workspace traffic
-        if (eff > best_eff * 1.08) {
-            best_eff = eff;
-            best = ks;
-        }
-    }
-    (void)nt;
-    return best;
+    if (warp == kConvertWarps) tmem_dealloc(tmem_d, tmem_cols);
 }
 
 template <int TYPE, int NT>
@@ -484,14 +641,17 @@ cudaError_t launch_nt(const GemmArgs &a, cudaStream_t stream) {
     int tiles = 0;
     for (int s = 0; s < a.nseg; ++s) tiles += (a.seg[s].rows + kTileM - 1) / kTileM;
     const int n_tiles = (a.n + NT - 1) / NT;
-    const int ks = choose_split(a, tiles, n_tiles, NT);
-    dim3 grid(tiles, n_tiles, ks);
+    const long long total = (long long)tiles * n_tiles * (a.cols / kRawK);
+    const int sms = a.sm_count > 0 ? a.sm_count : 148;
+    long long ctas = total / 2 < sms ? total / 2 : sms;  // at least two raw stages per CTA
+    if (ctas < 1) ctas = 1;
+    if (a.scratch == nullptr || a.counters == nullptr || tiles * n_tiles > a.counters_len ||
+        size_t(ctas) * 2 * kTileM * NT > a.scratch_floats)
+        return cudaErrorInvalidValue;
     CUtensorMap maps[3];
-    for (int s = 0; s < 3; ++s) {
-        const GemmTensorMap *m = a.seg[s < a.nseg ? s : 0].tmap;
-        memcpy(&maps[s], m->bytes, sizeof(CUtensorMap));
-    }
-    gemm_tc_kernel<TYPE, NT><<<grid, kGemmThreads, GemmSmem<TYPE, NT>::total, stream>>>(a, maps[0], maps[1], maps[2]);
+    for (int s = 0; s < 3; ++s) memcpy(&maps[s], a.seg[s < a.nseg ? s : 0].tmap->bytes, sizeof(CUtensorMap));
+    gemm_tc_kernel<TYPE, NT><<<dim3(unsigned(ctas)), kGemmThreads, GemmSmem<TYPE, NT>::total, stream>>>(a, maps[0], maps[1],
+                                                                                                     maps[2]);
     return cudaGetLastError();
 }
 
@@ -557,15 +717,36 @@ cudaError_t gemm_tc_configure() {
 
 cudaError_t gemm_tc_launch(const GemmArgs &a, cudaStream_t stream) {
     if (a.cols <= 0 || a.cols % 256 != 0 || a.n <= 0 || a.nseg < 1 || a.nseg > 3) return cudaErrorInvalidValue;
-    for (int s = 0; s < a.nseg; ++s)
+    int tiles = 0;
+    for (int s = 0; s < a.nseg; ++s) {
         if (a.seg[s].rows <= 0 || a.seg[s].w == nullptr || a.seg[s].y == nullptr || a.seg[s].tmap == nullptr)
             return cudaErrorInvalidValue;
-    switch (a.type) {
-        case kQ4_K: return launch_type<kQ4_K>(a, stream);
-        case kQ4_0: return launch_type<kQ4_0>(a, stream);
-        case kQ8_0: return launch_type<kQ8_0>(a, stream);
-        default: return cudaErrorInvalidValue;
+        tiles += (a.seg[s].rows + kTileM - 1) / kTileM;
     }
+    // One arrival counter per output tile: very tall products go in token slabs that fit the counters.
+    int slab = a.n;
+    if (a.counters_len > 0 && tiles <= a.counters_len) {
+        const int max_tiles_n = a.counters_len / tiles;
+        if ((a.n + 63) / 64 > max_tiles_n) slab = max_tiles_n * 64;
+    }
+    for (int t0 = 0; t0 < a.n; t0 += slab) {
+        GemmArgs part = a;
+        part.n = a.n - t0 < slab ? a.n - t0 : slab;
+        part.x = a.x + size_t(t0) * a.cols;
+        for (int s = 0; s < a.nseg; ++s) {
+            part.seg[s].y = a.seg[s].y + size_t(t0) * a.seg[s].rows;
+            if (a.seg[s].res != nullptr) part.seg[s].res = a.seg[s].res + size_t(t0) * a.seg[s].rows;
+        }
+        cudaError_t e;
+        switch (a.type) {
+            case kQ4_K: e = launch_type<kQ4_K>(part, stream); break;
+            case kQ4_0: e = launch_type<kQ4_0>(part, stream); break;
+            case kQ8_0: e = launch_type<kQ8_0>(part, stream); break;
+            default: return cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 }  // namespace jl

@@ -11,6 +11,7 @@ from tests.util import Pair, rel_l2, small_config
 pytestmark = pytest.mark.gpu
 FORMATS = [GGMLType.Q8_0, GGMLType.Q4_0, GGMLType.Q4_K]
 LOGIT_BAR = 1e-2
+TENSOR_CORE_LOGIT_EXPECT = 6e-3  # batches of four or more rows: binary16 weight rounding on top
 LOGIT_EXPECT = 2e-3  # binary16 K/V rounding flips (one ulp, ~1% of elements) perturb logits at the 1e-4 level
 
 
@@ -111,8 +112,13 @@ def test_batched_decode_matches_independent_sequences(dev, oracle):
                 assert out[b] == -1
                 continue
             want = seqs[b].forward(toks[b], positions[b])
-            assert float(np.max(np.abs(logits[b] - want))) < LOGIT_EXPECT
-            assert out[b] == int(np.argmax(want))
+            # width 4 runs on the tensor-core path: weights rounded once to binary16 (rel-L2 ~3e-4
+            # per product), so the logits sit inside the 1e-2 bar but above the mat-vec path's level
+            err = float(np.max(np.abs(logits[b] - want)))
+            assert err < LOGIT_BAR and err < TENSOR_CORE_LOGIT_EXPECT, (step, b, err)
+            top2 = np.sort(want)[-2:]
+            if top2[1] - top2[0] > 2 * TENSOR_CORE_LOGIT_EXPECT:
+                assert out[b] == int(np.argmax(want))
             positions[b] += 1
     assert p.executor.maxBatchSize() == width
 
