@@ -183,23 +183,21 @@ __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, in
         const float mm = __fmul_rn(dmin, float((mw >> sh) & 0xFFu));
         const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         const int nib = half * 4;
-        float w[32];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t v = (qw[i] >> nib) & 0x0F0F0F0Fu;
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                // 0x4B000000 | q is the float 2^23 + q: the integer code without a conversion unit
-                const float q = __uint_as_float(0x4B000000u | ((v >> (8 * b)) & 0xFFu)) - 8388608.0f;
-                w[i * 4 + b] = __fsub_rn(__fmul_rn(ds, q), mm);
-            }
-        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            out[c].x = pack_half2(w[8 * c + 0], w[8 * c + 1]);
-            out[c].y = pack_half2(w[8 * c + 2], w[8 * c + 3]);
-            out[c].z = pack_half2(w[8 * c + 4], w[8 * c + 5]);
-            out[c].w = pack_half2(w[8 * c + 6], w[8 * c + 7]);
+            float w[8];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint32_t v = (qw[2 * c + i] >> nib) & 0x0F0F0F0Fu;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    // 0x4B000000 | q is the float 2^23 + q: the integer code without a conversion unit
+                    const float q = __uint_as_float(0x4B000000u | ((v >> (8 * b)) & 0xFFu)) - 8388608.0f;
+                    w[i * 4 + b] = __fsub_rn(__fmul_rn(ds, q), mm);
+                }
+            }
+            out[c] = make_uint4(pack_half2(w[0], w[1]), pack_half2(w[2], w[3]), pack_half2(w[4], w[5]),
+                                pack_half2(w[6], w[7]));
         }
     } else if constexpr (TYPE == kQ4_0) {
         // tensor/standard/Q4_0FloatTensor.java:56-79: a unit is two 18-byte blocks; element i < 16
@@ -298,6 +296,62 @@ __device__ __forceinline__ int cta_of(long long total, long long f, int ctas) {
     while (c + 1 < ctas && range_lo(total, c + 1, ctas) <= f) ++c;
     while (c > 0 && range_lo(total, c, ctas) > f) --c;
     return c;
+}
+
+// Adds the partial tiles of one output tile in CTA order and writes the result. Kept out of line so
+// that its registers (every contributor's load is issued before the first add: the fold costs about
+// one L2 round trip per item instead of one per contributor) do not weigh on the conversion loop.
+template <int NT>
+__device__ __noinline__ void fold_partials(const GemmArgs &a, const GemmSeg &seg, int row0, int tok0, long long u_lo,
+                                           long long total, int ctas, int c_first, int c_last, int tid) {
+    const int ntok = min(NT, a.n - tok0);
+    const int ncontrib = c_last - c_first + 1;
+    const size_t slot_floats = size_t(kTileM) * NT;
+    for (int item = tid; item < ntok * (kTileM / 4); item += kConvertThreads) {
+        const int t = item >> 5, rr = (item & 31) * 4;
+        float4 pv[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (k < ncontrib) {
+                const int c = c_first + k;
+                const int which = range_lo(total, c, ctas) > u_lo ? 0 : 1;
+                pv[k] = __ldcg(reinterpret_cast<const float4 *>(a.scratch + (size_t(c) * 2 + which) * slot_floats +
+                                                                t * kTileM + rr));
+            } else {
+                pv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        float4 sum = pv[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) {
+            if (k < ncontrib) {
+                sum.x += pv[k].x;
+                sum.y += pv[k].y;
+                sum.z += pv[k].z;
+                sum.w += pv[k].w;
+            }
+        }
+        for (int c = c_first + 8; c <= c_last; ++c) {  // more than eight contributors: rare
+            const int which = range_lo(total, c, ctas) > u_lo ? 0 : 1;
+            const float4 more = __ldcg(reinterpret_cast<const float4 *>(a.scratch + (size_t(c) * 2 + which) * slot_floats +
+                                                                        t * kTileM + rr));
+            sum.x += more.x;
+            sum.y += more.y;
+            sum.z += more.z;
+            sum.w += more.w;
+        }
+        const int tok = tok0 + t;
+        const float s4[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int orow = row0 + rr + e;
+            if (orow < seg.rows) {
+                float out = s4[e];
+                if (seg.res != nullptr) out = seg.res[size_t(tok) * seg.rows + orow] + out;
+                seg.y[size_t(tok) * seg.rows + orow] = out;
+            }
+        }
+    }
 }
 
 template <int TYPE, int NT>
@@ -558,12 +612,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty);
             if (!whole) {
-                // The CTA that arrives last adds the partial tiles in CTA order.
-                __threadfence();
+                // The CTA that arrives last adds the partial tiles in CTA order. The barrier orders
+                // every thread's partial stores before thread 0's fence, which is cumulative.
                 ok = convert_warps_sync(fix_bar, fix_phase);
                 if (!ok) break;
                 const int c_first = cta_of(total, u_lo, ctas), c_last = cta_of(total, u_lo + raw_total - 1, ctas);
                 if (tid == 0) {
+                    __threadfence();
                     const unsigned prev = atomicAdd(a.counters + u, 1u);
                     *last_flag = prev == unsigned(c_last - c_first) ? 1u : 0u;
                 }
@@ -571,56 +626,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (!ok) break;
                 if (*last_flag != 0u) {
                     __threadfence();
-                    // Four rows per item, every contributor's load issued before the first add: the
-                    // fold costs about one L2 round trip per item instead of one per contributor.
-                    const int ntok = min(NT, a.n - tok0);
-                    const int ncontrib = c_last - c_first + 1;
-                    const size_t slot_floats = size_t(kTileM) * NT;
-                    for (int item = tid; item < ntok * (kTileM / 4); item += kConvertThreads) {
-                        const int t = item >> 5, rr = (item & 31) * 4;
-                        float4 pv[8];
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            if (k < ncontrib) {
-                                const int c = c_first + k;
-                                const int which = range_lo(total, c, ctas) > u_lo ? 0 : 1;
-                                pv[k] = __ldcg(reinterpret_cast<const float4 *>(a.scratch + (size_t(c) * 2 + which) * slot_floats +
-                                                                                t * kTileM + rr));
-                            } else {
-                                pv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-                        }
-                        float4 sum = pv[0];
-#pragma unroll
-                        for (int k = 1; k < 8; ++k) {
-                            if (k < ncontrib) {
-                                sum.x += pv[k].x;
-                                sum.y += pv[k].y;
-                                sum.z += pv[k].z;
-                                sum.w += pv[k].w;
-                            }
-                        }
-                        for (int c = c_first + 8; c <= c_last; ++c) {  // more than eight contributors: rare
-                            const int which = range_lo(total, c, ctas) > u_lo ? 0 : 1;
-                            const float4 more = __ldcg(reinterpret_cast<const float4 *>(
-                                a.scratch + (size_t(c) * 2 + which) * slot_floats + t * kTileM + rr));
-                            sum.x += more.x;
-                            sum.y += more.y;
-                            sum.z += more.z;
-                            sum.w += more.w;
-                        }
-                        const int tok = tok0 + t;
-                        const float s4[4] = {sum.x, sum.y, sum.z, sum.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int orow = tr.row0 + rr + e;
-                            if (orow < seg.rows) {
-                                float out = s4[e];
-                                if (seg.res != nullptr) out = seg.res[size_t(tok) * seg.rows + orow] + out;
-                                seg.y[size_t(tok) * seg.rows + orow] = out;
-                            }
-                        }
-                    }
+                    fold_partials<NT>(a, seg, tr.row0, tok0, u_lo, total, ctas, c_first, c_last, tid);
                     if (tid == 0) a.counters[u] = 0u;
                 }
                 ok = convert_warps_sync(fix_bar, fix_phase);  // last_flag is reused by the next partial tile
@@ -645,6 +651,15 @@ cudaError_t launch_nt(const GemmArgs &a, cudaStream_t stream) {
     const int sms = a.sm_count > 0 ? a.sm_count : 148;
     long long ctas = total / 2 < sms ? total / 2 : sms;  // at least two raw stages per CTA
     if (ctas < 1) ctas = 1;
+    // Fewer output tiles than SMs: a whole number of CTAs per tile, so that each CTA's range lies
+    // inside one tile and it takes part in one partial-tile fold instead of two.
+    const long long units = (long long)tiles * n_tiles;
+    if (units < ctas && ctas / units >= 1) {
+        long long per = ctas / units;
+        const int raw_total = a.cols / kRawK;
+        if (per > raw_total / 2) per = raw_total / 2 > 0 ? raw_total / 2 : 1;
+        ctas = units * per;
+    }
     if (a.scratch == nullptr || a.counters == nullptr || tiles * n_tiles > a.counters_len ||
         size_t(ctas) * 2 * kTileM * NT > a.scratch_floats)
         return cudaErrorInvalidValue;
