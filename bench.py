@@ -61,6 +61,8 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=20261125)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true",
+                    help="standalone quantised mat-vec / mat-mat sweep (formats x shapes x N): one JSON line per case")
     ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
                     help="with more than one GPU: tensor parallelism over one model (strong scaling, the default) "
                          "or one whole model per GPU (weak scaling)")
@@ -148,6 +150,45 @@ def op_bytes(cfg, fmt, op, shards=1):
     return rows * cols * bpe + 4 * cols + 4 * out_rows
 
 
+def run_sweep(jl, args):
+    """Formats {Q8_0, Q4_0, Q4_K} x shapes x N through jl_gemv_dev with device-resident operands. Each
+    case cycles over enough copies of the matrix to exceed L2 (126 MB), so every launch reads HBM."""
+    import numpy as np
+    dev = jl.Device(0)
+    peak, peak_kind = measured_peak()
+    shapes = ((4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096))
+    for fmt_name in ("Q8_0", "Q4_0", "Q4_K"):
+        t = jl.GGMLType[fmt_name]
+        for rows, cols in shapes:
+            w = jl.synth_tensor(t, rows * cols, seed=args.seed + rows + cols)
+            wbytes = rows * cols * BYTES_PER_EL[fmt_name]
+            copies = int(min(32, max(1, -(-300e6 // wbytes))))
+            mats = [dev.upload_matrix(t, w, rows, cols) for _ in range(copies)]
+            for n in (1, 8, 32, 512, 2048):
+                x = np.random.default_rng(args.seed + n).standard_normal((n, cols)).astype(np.float32)
+                xd, yd = dev.alloc(x.nbytes), dev.alloc(n * rows * 4)
+                dev.h2d(xd, x)
+                for m in mats:
+                    m.matmul_dev(xd, n, yd)
+                reps = max(1, min(8, 64 // copies)) if n <= 32 else 1
+                dev.synchronize()
+                dev.timer_start()
+                for _ in range(reps):
+                    for m in mats:
+                        m.matmul_dev(xd, n, yd)
+                us = dev.timer_stop() * 1000.0 / (reps * copies)
+                by = wbytes + 4 * cols * n + 4 * rows * n
+                print(json.dumps({"sweep": fmt_name, "rows": rows, "cols": cols, "n": n, "us": round(us, 2),
+                                  "bytes": by, "gbs": round(by / us / 1e3, 1), "hbm_frac": round(by / us / 1e3 / peak, 4),
+                                  "tflops": round(2.0 * rows * cols * n / us / 1e6, 2), "peak_kind": peak_kind,
+                                  "kernel": "gemv" if n < 8 else "gemm_tc"}), flush=True)
+                dev.free(xd)
+                dev.free(yd)
+            for m in mats:
+                m.close()
+    return 0
+
+
 def cpu_decode_rate(cfg, tensors, budget_s, max_steps, seed):
     """tokens/s of the oracle's forwardJava on this host, decode steps from position 0."""
     from oracle import binding as oracle
@@ -176,6 +217,9 @@ def main():
     n_gpus = args.gpus
 
     import jitllm_b200 as jl
+
+    if args.sweep:
+        return run_sweep(jl, args) if rank == 0 else 0
 
     dims = ARCHS[args.arch]
     cfg = jl.Configuration(dim=dims[0], hiddenDim=dims[1], numberOfLayers=dims[2], numberOfHeads=dims[3],

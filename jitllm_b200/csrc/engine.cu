@@ -85,6 +85,11 @@ struct jl_ctx {
     // tensor-parallel placement: local (per-GPU) extents of the sharded dimensions
     int tp_rank = 0, tp_size = 1;
     int l_heads = 0, l_kv_heads = 0, l_qdim = 0, l_hidden = 0, l_vocab = 0;
+    // activations of the tensor-core path, pre-split into binary16 hi / lo rows, and their TMA
+    // descriptors per token-tile size (16, 32, 64): [0] xb as rows of dim, [1] xb as rows of the
+    // local query width, [2] hb as rows of the local hidden width
+    void *xb16 = nullptr, *hb16 = nullptr;
+    GemmTensorMap xmaps[3][3] = {};
     GemmTensorMap wcls_slice_tmap = {};  // tied embeddings under tensor parallelism: this GPU's rows
     float *gemm_scratch = nullptr;       // split-column partial tiles of the tensor-core path
     size_t gemm_scratch_floats = 0;
@@ -308,6 +313,9 @@ void free_model(jl_ctx *ctx) {
     ctx->amax_val = nullptr;
     ctx->amax_idx = nullptr;
     ctx->amax_count = nullptr;
+    if (ctx->xb16) cudaFree(ctx->xb16);
+    if (ctx->hb16) cudaFree(ctx->hb16);
+    ctx->xb16 = ctx->hb16 = nullptr;
     if (ctx->part) cudaFree(ctx->part);
     if (ctx->best) cudaFree(ctx->best);
     if (ctx->logits_all) cudaFree(ctx->logits_all);
@@ -657,9 +665,23 @@ int attn_splits_for_width(const jl_ctx *ctx, int width) {
 }
 
 // One tensor-core launch over up to three matrices that share the input rows.
+// in_kind: which pre-split activation buffer x is mirrored in (0 xb by dim, 1 xb by the local query
+// width, 2 hb by the local hidden width), or -1 to let the kernel convert x itself.
 int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, const float *const *res, int nseg,
-                     const float *x, int n, uint64_t *launches) {
+                     const float *x, int n, uint64_t *launches, int in_kind = -1, bool presplit = false) {
     GemmArgs g = {};
+    if (in_kind >= 0 && ctx->xb16 != nullptr && n <= ctx->row_cap) {
+        if (!presplit) {  // otherwise the producing kernel already wrote the hi / lo rows
+            const int cols = int(w[0]->cols);
+            char *buf = static_cast<char *>(in_kind == 2 ? ctx->hb16 : ctx->xb16);
+            cudaError_t e = split_rows_launch(x, size_t(n) * cols, buf, buf + size_t(ctx->row_cap) * cols * 2, ctx->stream);
+            if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "activation split launch failed: %s", cudaGetErrorString(e));
+            ++*launches;
+        }
+        const int nt = gemm_token_tile(n);
+        g.xmap = &ctx->xmaps[in_kind][nt == 16 ? 0 : (nt == 32 ? 1 : 2)];
+        g.x_lo_row = ctx->row_cap;
+    }
     g.nseg = nseg;
     for (int s = 0; s < nseg; ++s) {
         if (!w[s]->has_tmap) return fail(ctx, JL_ERR_UNSUPPORTED, "matrix-matrix product needs a quantised matrix");
@@ -684,11 +706,11 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
 }
 
 int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
-                uint64_t *launches) {
+                uint64_t *launches, int in_kind = -1, bool presplit = false) {
     const DevTensor *ws[1] = {&w};
     float *ys[1] = {y};
     const float *rs[1] = {res};
-    return launch_gemm_segs(ctx, ws, ys, rs, 1, x, n, launches);
+    return launch_gemm_segs(ctx, ws, ys, rs, 1, x, n, launches, in_kind, presplit);
 }
 
 #define JL_LAUNCH(ctx, call, what)                                                            \
@@ -713,7 +735,8 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
     for (int l = 0; l < d.layers; ++l) {
         const float *attn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
         const float *ffn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
-        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, attn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
+        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, attn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream, ctx->xb16,
+                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2),
                   "rmsnorm");
         {
             const DevTensor *ws[3] = {&ctx->layer[JL_ROLE_ATTENTION_QUERY][l], &ctx->layer[JL_ROLE_ATTENTION_KEY][l],
@@ -721,7 +744,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             float *ys[3] = {ctx->q, ctx->k, ctx->v};
             const bool same = ws[0]->type == ws[1]->type && ws[0]->type == ws[2]->type;
             if (same) {
-                if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 3, ctx->xb, n, launches))) return rc;
+                if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 3, ctx->xb, n, launches, 0, true))) return rc;
             } else {
                 for (int i = 0; i < 3; ++i)
                     if ((rc = launch_gemm(ctx, *ws[i], ctx->xb, n, ys[i], nullptr, launches))) return rc;
@@ -754,36 +777,40 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, false), "attention");
         }
         if (ctx->tp_size > 1) {
-            if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->part, nullptr, launches))) return rc;
+            if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->part, nullptr, launches, 1))) return rc;
             if ((rc = tp_reduce_into_x(ctx, n, launches))) return rc;
-        } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->x, ctx->x, launches))) {
+        } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->x, ctx->x, launches, 1))) {
             return rc;
         }
-        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, ffn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
+        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, ffn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream, ctx->xb16,
+                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2),
                   "rmsnorm");
         {
             const DevTensor *ws[2] = {&ctx->layer[JL_ROLE_FFN_GATE][l], &ctx->layer[JL_ROLE_FFN_UP][l]};
             float *ys[2] = {ctx->hb, ctx->hb2};
             if (ws[0]->type == ws[1]->type) {
-                if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 2, ctx->xb, n, launches))) return rc;
+                if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 2, ctx->xb, n, launches, 0, true))) return rc;
             } else {
                 for (int i = 0; i < 2; ++i)
                     if ((rc = launch_gemm(ctx, *ws[i], ctx->xb, n, ys[i], nullptr, launches))) return rc;
             }
         }
-        JL_LAUNCH(ctx, swiglu_rows_launch(ctx->hb, ctx->hb2, ctx->l_hidden, n, ctx->stream), "swiglu");
+        JL_LAUNCH(ctx, swiglu_rows_launch(ctx->hb, ctx->hb2, ctx->l_hidden, n, ctx->stream, ctx->hb16,
+                                          static_cast<char *>(ctx->hb16) + size_t(ctx->row_cap) * ctx->l_hidden * 2),
+                  "swiglu");
         if (ctx->tp_size > 1) {
-            if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->part, nullptr, launches))) return rc;
+            if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->part, nullptr, launches, 2, true))) return rc;
             if ((rc = tp_reduce_into_x(ctx, n, launches))) return rc;
-        } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->x, ctx->x, launches))) {
+        } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->x, ctx->x, launches, 2, true))) {
             return rc;
         }
     }
     if (with_logits) {
         const float *out_norm = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
-        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, out_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream),
+        JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, out_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream, ctx->xb16,
+                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2),
                   "rmsnorm");
-        if ((rc = launch_gemm(ctx, wcls_of(ctx), ctx->xb, n, ctx->logits, nullptr, launches))) return rc;
+        if ((rc = launch_gemm(ctx, wcls_of(ctx), ctx->xb, n, ctx->logits, nullptr, launches, 0, true))) return rc;
         JL_LAUNCH(ctx, argmax_rows_launch(ctx->logits, ctx->l_vocab, n, ctx->d_active, ctx->d_out, ctx->stream), "argmax");
         if (ctx->tp_size > 1 && (rc = tp_global_argmax(ctx, n, launches))) return rc;
     }
@@ -1291,6 +1318,18 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb), R * ctx->l_hidden * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb2), R * ctx->l_hidden * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->logits), B * ctx->l_vocab * 4))) return rc;
+    {
+        const size_t widest = size_t(d.dim) > size_t(ctx->l_hidden) ? size_t(d.dim) : size_t(ctx->l_hidden);
+        (void)widest;
+        if ((rc = alloc(&ctx->xb16, 2 * R * d.dim * 2))) return rc;
+        if ((rc = alloc(&ctx->hb16, 2 * R * ctx->l_hidden * 2))) return rc;
+        const int nts[3] = {16, 32, 64};
+        for (int i = 0; i < 3; ++i) {
+            JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[0][i], ctx->xb16, R, d.dim, nts[i]));
+            JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[1][i], ctx->xb16, R, ctx->l_qdim, nts[i]));
+            JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[2][i], ctx->hb16, R, ctx->l_hidden, nts[i]));
+        }
+    }
     if (ctx->tp_size > 1) {
         JL_REQUIRE(ctx, ctx->nccl_comm != nullptr, JL_ERR_STATE, "jl_tp_init must come before jl_model_finalize");
         if ((rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;

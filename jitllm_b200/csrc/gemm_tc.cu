@@ -46,7 +46,7 @@ namespace {
 
 constexpr int kConvertWarps = 16;
 constexpr int kConvertThreads = kConvertWarps * 32;
-constexpr int kGemmThreads = kConvertThreads + 64;  // + tensor-core issue warp + copy-request warp
+constexpr int kGemmThreads = kConvertThreads + 96;  // + tensor-core issue warp + two copy-request warps
 constexpr int kTileM = 128;    // weight rows per tile
 constexpr int kStageK = 128;   // columns per operand stage (two 64-column swizzle atoms)
 constexpr int kRawK = 256;     // columns per raw stage (one Q4_K super-block per row)
@@ -75,6 +75,13 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_2d_plain(void *dst_smem, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
                  "r"(ncols)
@@ -99,6 +106,26 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// Same with the A operand in tensor memory: lane = row, one 32-bit column = two consecutive K
+// elements (even K in the low half); eight columns per K = 16 step.
+__device__ __forceinline__ void umma_f16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -249,27 +276,32 @@ __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, in
     }
 }
 
+// Tensor-memory columns: the accumulator (hi and lo partial products side by side, 2*NT <= 128
+// columns) and, from column 128 on, the A operand stages of 64 columns (128 K elements) each.
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemAStage0 = 128;
+constexpr uint32_t kTmemAStageCols = kStageK / 2;
+
 template <int TYPE, int NT>
 struct GemmSmem {
-    static constexpr int a_sub = kTileM * 128;         // one 64-column atom of A: 16 KB
     static constexpr int b_sub = 2 * NT * 128;         // one 64-column atom of B: hi rows, then lo rows
-    static constexpr int a_stage = 2 * a_sub;
     static constexpr int b_stage = 2 * b_sub;
     static constexpr int raw_bytes = RawFmt<TYPE>::stages * RawFmt<TYPE>::stage_bytes;
     static constexpr int budget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/ - raw_bytes;
-    // As many operand stages as fit (2..4): the barrier round trip between conversion warps and the
-    // tensor core is hidden only when several stages are in flight.
-    static constexpr int fit = budget / (a_stage + b_stage);
-    static constexpr int stages = fit >= 4 ? 4 : (fit >= 3 ? 3 : 2);
-    static constexpr int a_off = 0;
-    static constexpr int b_off = stages * a_stage;
-    static constexpr int raw_off = b_off + stages * b_stage;
+    // Operand stages: the A half lives in tensor memory (six stages fit beside the accumulator), the
+    // B half in shared memory. Several stages must be in flight to hide the round trip
+    // conversion -> MMA -> commit -> stage free again.
+    static constexpr int fit = budget / b_stage;
+    static constexpr int stages = fit >= 6 ? 6 : fit;
+    static constexpr int b_off = 0;
+    static constexpr int raw_off = stages * b_stage;
     static constexpr int bar_off = raw_off + raw_bytes;
     static constexpr int total = bar_off + 256 + 1024;
 };
 static_assert(GemmSmem<kQ8_0, 64>::total <= 227 * 1024 && GemmSmem<kQ4_K, 64>::total <= 227 * 1024 &&
                   GemmSmem<kQ4_K, 16>::total <= 227 * 1024 && GemmSmem<kQ8_0, 32>::total <= 227 * 1024,
               "shared memory budget");
+static_assert(GemmSmem<kQ8_0, 64>::stages >= 3, "pipeline depth");
 
 struct TileRef {
     int seg, row0;
@@ -357,7 +389,7 @@ __device__ __noinline__ void fold_partials(const GemmArgs &a, const GemmSeg &seg
 template <int TYPE, int NT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1,
-                   const __grid_constant__ CUtensorMap tm2) {
+                   const __grid_constant__ CUtensorMap tm2, const __grid_constant__ CUtensorMap tmx) {
     extern __shared__ uint8_t smem_raw[];
     using S = GemmSmem<TYPE, NT>;
     using R = RawFmt<TYPE>;
@@ -376,7 +408,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint32_t *tmem_ptr = reinterpret_cast<uint32_t *>(base + S::bar_off + 192);
     volatile uint32_t *last_flag = tmem_ptr + 1;
     volatile uint32_t *abort_flag = tmem_ptr + 2;
-    constexpr uint32_t tmem_cols = 2 * NT;  // hi and lo partial products side by side
+    constexpr uint32_t tmem_cols = kTmemCols;
 
     int tiles = 0;
     for (int s = 0; s < a.nseg; ++s) tiles += (a.seg[s].rows + kTileM - 1) / kTileM;
@@ -390,7 +422,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (tid == 0) {
         for (int s = 0; s < ST; ++s) {
             mbar_init(a_free + s, 1);
-            mbar_init(a_full + s, kConvertWarps);
+            mbar_init(a_full + s, kConvertWarps + (a.xmap != nullptr ? 1 : 0));
         }
         for (int s = 0; s < RS; ++s) {
             mbar_init(raw_full + s, 1);
@@ -415,8 +447,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             fence_proxy_async();
             int i = 0, cur_u = -1;
             TileRef tr = {0, 0};
+            int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
             for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
-                const int u = int(f / raw_total), r = int(f - (long long)u * raw_total);
+                if (++r == raw_total) {
+                    r = 0;
+                    ++u;
+                }
                 if (u != cur_u) {
                     cur_u = u;
                     tr = locate_tile(a, u / n_tiles);
@@ -437,13 +473,50 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                             raw_full + st, policy);
             }
         }
+    } else if (warp == kConvertWarps + 2) {
+        // ---- activation tiles by TMA (pre-split binary16 hi / lo rows), one request set per operand stage
+        if (lane == 0 && a.xmap != nullptr) {
+            int i = 0;
+            int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
+            for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
+                if (++r == raw_total) {
+                    r = 0;
+                    ++u;
+                }
+                const int tok0 = (u % n_tiles) * NT;
+                bool ok = true;
+                for (int j = 0; j < 2 && ok; ++j) {
+                    const int q = 2 * i + j, s = q % ST;
+                    if (q >= ST) ok = GEMM_WAIT(a_free + s, uint32_t(q / ST - 1) & 1u);
+                    if (!ok) break;
+                    uint8_t *b_st = base + S::b_off + s * S::b_stage;
+                    const int k0 = r * kRawK + j * kStageK;
+                    mbar_expect_tx(a_full + s, S::b_stage);
+#pragma unroll
+                    for (int atom = 0; atom < 2; ++atom) {
+                        tma_load_2d_plain(b_st + atom * S::b_sub, &tmx, k0 + atom * 64, tok0, a_full + s);
+                        tma_load_2d_plain(b_st + atom * S::b_sub + NT * 128, &tmx, k0 + atom * 64, a.x_lo_row + tok0,
+                                          a_full + s);
+                    }
+                }
+                if (!ok) {
+                    *abort_flag = 1u;
+                    atomicExch(a.status, kDevTimeout);
+                    break;
+                }
+            }
+        }
     } else if (warp == kConvertWarps) {
         // ---- tensor-core issue ---------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_f16(2 * NT);
             int i = 0, done = 0;
+            int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
             for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
-                const int u = int(f / raw_total);
+                if (++r == raw_total) {
+                    r = 0;
+                    ++u;
+                }
                 const long long u_lo = (long long)u * raw_total;
                 const long long seg_begin = u_lo > lo ? u_lo : lo;
                 const long long seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
@@ -455,16 +528,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     if (ok && first && done > 0) ok = GEMM_WAIT(acc_empty, uint32_t(done - 1) & 1u);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t da0 = smem_desc_sw128(smem_u32(base + S::a_off + s * S::a_stage));
+                    const uint32_t ta0 = tmem_d + kTmemAStage0 + uint32_t(s) * kTmemAStageCols;
                     const uint64_t db0 = smem_desc_sw128(smem_u32(base + S::b_off + s * S::b_stage));
 #pragma unroll
                     for (int atom = 0; atom < 2; ++atom) {
 #pragma unroll
                         for (int k16 = 0; k16 < 4; ++k16) {
-                            const uint64_t ka = uint64_t((atom * S::a_sub + k16 * 32) >> 4);
+                            const uint32_t ka = uint32_t(atom * 4 + k16) * 8u;  // eight columns per K = 16
                             const uint64_t kb = uint64_t((atom * S::b_sub + k16 * 32) >> 4);
                             if (a.debug & 4) continue;
-                            umma_f16(tmem_d, da0 + ka, db0 + kb, idesc, (first && atom == 0 && k16 == 0) ? 0u : 1u);
+                            umma_f16_tmem_a(tmem_d, ta0 + ka, db0 + kb, idesc, (first && atom == 0 && k16 == 0) ? 0u : 1u);
                         }
                     }
                     if ((a.debug & 36) == 36) mbar_arrive(a_free + s);  // timing experiment, only without MMAs
@@ -495,8 +568,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int tok0 = 0;
         bool a_valid = false;
         bool ok = true;
+        int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
         for (long long f = lo; f < hi && ok && *abort_flag == 0u; ++f, ++i) {
-            const int u = int(f / raw_total), r = int(f - (long long)u * raw_total);
+            if (++r == raw_total) {
+                r = 0;
+                ++u;
+            }
             if (u != cur_u) {
                 cur_u = u;
                 tr = locate_tile(a, u / n_tiles);
@@ -518,7 +595,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const int ch = tid + uu * kConvertThreads;
                     const int t = ch >> 4, kc = ch & 15;
                     const int tok = tok0 + t;
-                    if (ch < kBChunks && tok < a.n) {
+                    if (ch < kBChunks && tok < a.n && a.xmap == nullptr) {
                         const float4 *src = reinterpret_cast<const float4 *>(a.x + size_t(tok) * a.cols + k0 + kc * 8);
                         xv[uu][0] = __ldg(src);
                         xv[uu][1] = __ldg(src + 1);
@@ -528,21 +605,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 }
                 if (q >= ST) ok = GEMM_WAIT(a_free + s, uint32_t(q / ST - 1) & 1u);
                 if (!ok) break;
-                uint8_t *a_st = base + S::a_off + s * S::a_stage;
                 uint8_t *b_st = base + S::b_off + s * S::b_stage;
                 if (!(a.debug & 1)) {
+                    tc_fence_after();  // the stage's previous MMAs are complete (a_free): order the store after them
                     uint4 chunks[4];
                     dequant32_to_half<TYPE>(row_u32, 2 * j + a_atom, a_half, chunks);
-                    uint8_t *tile_a = a_st + size_t(a_atom) * S::a_sub;
+                    uint32_t cols16[16];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        *reinterpret_cast<uint4 *>(tile_a + sw128_offset(a_row, a_half * 4 + c)) =
-                            a_valid ? chunks[c] : make_uint4(0, 0, 0, 0);
+                    for (int c = 0; c < 4; ++c) {
+                        cols16[4 * c + 0] = a_valid ? chunks[c].x : 0u;
+                        cols16[4 * c + 1] = a_valid ? chunks[c].y : 0u;
+                        cols16[4 * c + 2] = a_valid ? chunks[c].z : 0u;
+                        cols16[4 * c + 3] = a_valid ? chunks[c].w : 0u;
+                    }
+                    // this thread's row is TMEM lane a_row (its warp may touch lanes 32 * (warp % 4) ..);
+                    // its 32 weights are columns a_q * 16 .. + 15 of the stage
+                    tmem_st16(tmem_d + (uint32_t(a_row & ~31) << 16) + kTmemAStage0 + uint32_t(s) * kTmemAStageCols +
+                                  uint32_t(a_q) * 16u,
+                              cols16);
+                    tc_fence_before();
                 }
 #pragma unroll
                 for (int uu = 0; uu < kBPerThread; ++uu) {
                     const int ch = tid + uu * kConvertThreads;
-                    if (ch < kBChunks && !(a.debug & 2)) {
+                    if (ch < kBChunks && !(a.debug & 2) && a.xmap == nullptr) {
                         const int t = ch >> 4, kc = ch & 15;
                         const int atom = kc >> 3, c = kc & 7;
                         const float x[8] = {xv[uu][0].x, xv[uu][0].y, xv[uu][0].z, xv[uu][0].w,
@@ -663,10 +749,11 @@ cudaError_t launch_nt(const GemmArgs &a, cudaStream_t stream) {
     if (a.scratch == nullptr || a.counters == nullptr || tiles * n_tiles > a.counters_len ||
         size_t(ctas) * 2 * kTileM * NT > a.scratch_floats)
         return cudaErrorInvalidValue;
-    CUtensorMap maps[3];
+    CUtensorMap maps[4];
     for (int s = 0; s < 3; ++s) memcpy(&maps[s], a.seg[s < a.nseg ? s : 0].tmap->bytes, sizeof(CUtensorMap));
+    memcpy(&maps[3], (a.xmap != nullptr ? a.xmap : a.seg[0].tmap)->bytes, sizeof(CUtensorMap));
     gemm_tc_kernel<TYPE, NT><<<dim3(unsigned(ctas)), kGemmThreads, GemmSmem<TYPE, NT>::total, stream>>>(a, maps[0], maps[1],
-                                                                                                     maps[2]);
+                                                                                                     maps[2], maps[3]);
     return cudaGetLastError();
 }
 
@@ -723,6 +810,33 @@ cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type
     return cudaSuccess;
 }
 
+int gemm_token_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : 64); }
+
+cudaError_t gemm_make_activation_map(GemmTensorMap *out, const void *x16_dev, int64_t row_cap, int64_t cols, int nt) {
+    if (!out || !x16_dev || row_cap <= 0 || cols <= 0 || cols % 64 != 0 || (nt != 16 && nt != 32 && nt != 64))
+        return cudaErrorInvalidValue;
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess) return e;
+    if (q != cudaDriverEntryPointSuccess || fn == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t gdim[2] = {cuuint64_t(cols), cuuint64_t(2 * row_cap)};
+    const cuuint64_t gstride[1] = {cuuint64_t(cols) * 2};
+    const cuuint32_t box[2] = {64, cuuint32_t(nt)};  // 64 binary16 = one 128-byte swizzle row
+    const cuuint32_t estride[2] = {1, 1};
+    CUtensorMap map;
+    const CUresult r = reinterpret_cast<EncodeFn>(fn)(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x16_dev),
+                                                      gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    memcpy(out->bytes, &map, sizeof map);
+    return cudaSuccess;
+}
+
 cudaError_t gemm_tc_configure() {
     cudaError_t e;
     if ((e = configure_type<kQ4_K>()) != cudaSuccess) return e;
@@ -744,6 +858,7 @@ cudaError_t gemm_tc_launch(const GemmArgs &a, cudaStream_t stream) {
         const int max_tiles_n = a.counters_len / tiles;
         if ((a.n + 63) / 64 > max_tiles_n) slab = max_tiles_n * 64;
     }
+    if (a.xmap != nullptr && slab < a.n) return cudaErrorInvalidValue;  // pre-split activations: one slab only
     for (int t0 = 0; t0 < a.n; t0 += slab) {
         GemmArgs part = a;
         part.n = a.n - t0 < slab ? a.n - t0 : slab;

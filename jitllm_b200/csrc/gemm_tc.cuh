@@ -11,6 +11,10 @@ struct alignas(64) GemmTensorMap {
     unsigned char bytes[128];
 };
 cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type, int64_t rows, int64_t cols);
+// TMA descriptor of a pre-split activation buffer: binary16 [2 * row_cap][cols] (the hi rows, then
+// the lo rows), fetched in swizzled boxes of nt rows x 64 columns; nt is 16, 32 or 64.
+cudaError_t gemm_make_activation_map(GemmTensorMap *out, const void *x16_dev, int64_t row_cap, int64_t cols, int nt);
+int gemm_token_tile(int n);  // the nt the kernel will use for n rows
 
 struct GemmSeg {
     const uint8_t *w;  // device, GGUF block layout, rows x cols
@@ -26,7 +30,9 @@ struct GemmArgs {
     int nseg;
     int type;        // kQ8_0 / kQ4_0 / kQ4_K
     int cols;        // a multiple of 256
-    const float *x;  // device, n x cols
+    const float *x;  // device, n x cols (used when xmap is NULL: converted inside the kernel)
+    const GemmTensorMap *xmap;  // host pointer or NULL: pre-split activations for this launch's token tile
+    int x_lo_row;    // first row of the lo half in that buffer (its row_cap)
     int n;
     int *status;     // device status word
     // Split-K workspace (nullable: then every CTA walks the whole row): partial tiles

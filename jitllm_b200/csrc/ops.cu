@@ -1,6 +1,8 @@
 // Per-layer kernels around the matrix products (see ops.cuh).
 #include "ops.cuh"
 
+#include <cuda_fp16.h>
+
 namespace jl {
 
 namespace {
@@ -65,6 +67,18 @@ __global__ void add_rows_kernel(float *x, const float *y, size_t total) {
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) x[i] = x[i] + y[i];
 }
 
+__global__ void split_rows_kernel(const float4 *x, size_t total4, uint2 *hi, uint2 *lo) {
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total4; i += stride) {
+        const float4 v = x[i];
+        const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+        const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
+        const __half2 l0 = __floats2half2_rn(v.x - b0.x, v.y - b0.y), l1 = __floats2half2_rn(v.z - b1.x, v.w - b1.y);
+        hi[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+        lo[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
+    }
+}
+
 __global__ void tp_pack_best_kernel(const float *logits, const int32_t *idx, int l_vocab, int index_offset, int n,
                                     float *best) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -91,35 +105,84 @@ __global__ void tp_pick_best_kernel(const float *all, int ranks, int n, const ui
 }
 
 // ---- row-wise operators for the matrix-matrix path ---------------------------------------------
-__global__ void rmsnorm_rows_kernel(const float *x, const float *w, float eps, float *out, int dim,
-                                    const uint8_t *active) {
+// One CTA per row. The row is read once, as float4 batches held in registers (all loads issued
+// before the first use: one L2 round trip, not one per element), and the same registers feed the
+// output pass. Optionally also writes the row as binary16 hi / lo parts (x = hi + lo), the
+// activation format of the tensor-core path.
+constexpr int kNormThreads = 256;
+constexpr int kNormBatch = 8;  // float4 per thread per batch: rows up to 8192 in one batch
+
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const float *x, const float *w, float eps, float *out,
+                                                                    int dim, const uint8_t *active, uint2 *hi, uint2 *lo) {
     const int row = blockIdx.x;
     if (active != nullptr && active[row] == 0) return;
     __shared__ float part[9];
-    const float *xr = x + size_t(row) * dim;
+    const int n4 = dim / 4;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + size_t(row) * dim);
+    const float4 *w4 = reinterpret_cast<const float4 *>(w);
+    float4 v[kNormBatch];
+#pragma unroll
+    for (int k = 0; k < kNormBatch; ++k) {
+        const int i = k * kNormThreads + threadIdx.x;
+        v[k] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float s = 0.f;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) s += xr[i] * xr[i];
+#pragma unroll
+    for (int k = 0; k < kNormBatch; ++k) s += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    for (int i = kNormBatch * kNormThreads + threadIdx.x; i < n4; i += kNormThreads) {
+        const float4 u = xr[i];
+        s += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+    }
     s = warp_sum(s);
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
     __syncthreads();
     if (threadIdx.x == 0) {
         float tot = 0.f;
-        for (int i = 0; i < int(blockDim.x >> 5); ++i) tot += part[i];
+        for (int i = 0; i < kNormThreads / 32; ++i) tot += part[i];
         float ms = tot / static_cast<float>(dim);
         ms += eps;
         part[8] = static_cast<float>(1.0 / sqrt(static_cast<double>(ms)));
     }
     __syncthreads();
     const float ss = part[8];
-    for (int i = threadIdx.x; i < dim; i += blockDim.x)
-        out[size_t(row) * dim + i] = __fmul_rn(w[i], __fmul_rn(ss, xr[i]));
+    float4 *o4 = reinterpret_cast<float4 *>(out + size_t(row) * dim);
+    uint2 *hr = hi != nullptr ? hi + size_t(row) * n4 : nullptr;
+    uint2 *lr = lo != nullptr ? lo + size_t(row) * n4 : nullptr;
+    auto emit = [&](int i, float4 u) {
+        const float4 g = w4[i];
+        float4 r;
+        r.x = __fmul_rn(g.x, __fmul_rn(ss, u.x));
+        r.y = __fmul_rn(g.y, __fmul_rn(ss, u.y));
+        r.z = __fmul_rn(g.z, __fmul_rn(ss, u.z));
+        r.w = __fmul_rn(g.w, __fmul_rn(ss, u.w));
+        o4[i] = r;
+        if (hr != nullptr) {
+            const __half2 h0 = __floats2half2_rn(r.x, r.y), h1 = __floats2half2_rn(r.z, r.w);
+            const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
+            const __half2 l0 = __floats2half2_rn(r.x - b0.x, r.y - b0.y), l1 = __floats2half2_rn(r.z - b1.x, r.w - b1.y);
+            hr[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+            lr[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
+        }
+    };
+#pragma unroll
+    for (int k = 0; k < kNormBatch; ++k) {
+        const int i = k * kNormThreads + threadIdx.x;
+        if (i < n4) emit(i, v[k]);
+    }
+    for (int i = kNormBatch * kNormThreads + threadIdx.x; i < n4; i += kNormThreads) emit(i, xr[i]);
 }
 
-__global__ void swiglu_rows_kernel(float *g, const float *u, size_t total) {
+__global__ void swiglu_rows_kernel(float *g, const float *u, size_t total, __half *hi, __half *lo) {
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const float v = g[i];
-        g[i] = (v / (1.0f + expf(-v))) * u[i];
+        const float r = (v / (1.0f + expf(-v))) * u[i];
+        g[i] = r;
+        if (hi != nullptr) {
+            const __half h = __float2half_rn(r);
+            hi[i] = h;
+            lo[i] = __float2half_rn(r - __half2float(h));
+        }
     }
 }
 
@@ -514,15 +577,16 @@ cudaError_t advance_launch(int32_t *tokens, int32_t *positions, const int32_t *s
 }
 
 cudaError_t rmsnorm_rows_launch(const float *x, const float *w, float eps, float *out, int dim, int n,
-                                const uint8_t *active, cudaStream_t stream) {
-    rmsnorm_rows_kernel<<<n, 256, 0, stream>>>(x, w, eps, out, dim, active);
+                                const uint8_t *active, cudaStream_t stream, void *hi, void *lo) {
+    rmsnorm_rows_kernel<<<n, kNormThreads, 0, stream>>>(x, w, eps, out, dim, active, static_cast<uint2 *>(hi),
+                                                        static_cast<uint2 *>(lo));
     return cudaGetLastError();
 }
 
-cudaError_t swiglu_rows_launch(float *g, const float *u, int hidden, int n, cudaStream_t stream) {
+cudaError_t swiglu_rows_launch(float *g, const float *u, int hidden, int n, cudaStream_t stream, void *hi, void *lo) {
     const size_t total = size_t(hidden) * n;
     const int grid = static_cast<int>((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
-    swiglu_rows_kernel<<<grid, 256, 0, stream>>>(g, u, total);
+    swiglu_rows_kernel<<<grid, 256, 0, stream>>>(g, u, total, static_cast<__half *>(hi), static_cast<__half *>(lo));
     return cudaGetLastError();
 }
 
@@ -543,6 +607,14 @@ cudaError_t argmax_rows_launch(const float *logits, int vocab, int n, const uint
 cudaError_t add_rows_launch(float *x, const float *y, size_t total, cudaStream_t stream) {
     const int grid = static_cast<int>((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
     add_rows_kernel<<<grid, 256, 0, stream>>>(x, y, total);
+    return cudaGetLastError();
+}
+
+cudaError_t split_rows_launch(const float *x, size_t total, void *hi, void *lo, cudaStream_t stream) {
+    const size_t total4 = total / 4;  // row lengths are multiples of 256
+    const int grid = static_cast<int>((total4 + 255) / 256 < 148 * 8 ? (total4 + 255) / 256 : 148 * 8);
+    split_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4 *>(x), total4, static_cast<uint2 *>(hi),
+                                                static_cast<uint2 *>(lo));
     return cudaGetLastError();
 }
 
