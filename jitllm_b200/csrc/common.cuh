@@ -73,6 +73,15 @@ __device__ __forceinline__ bool mbar_spin_bounded(uint64_t *bar, uint32_t parity
     }
     return false;
 }
+// Polling with a short sleep between polls: a waiting warp stays off the issue ports (a spinning warp
+// takes slots from the warps that share its scheduler) and still notices the flip within ~50 ns.
+__device__ __forceinline__ bool mbar_poll_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 24)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        __nanosleep(40);
+    }
+    return false;
+}
 
 // ---- bulk async copy global -> shared (TMA engine, 1-D, no multicast) -------------------------
 // dst and src 16-byte aligned, bytes a multiple of 16.

@@ -89,7 +89,7 @@ struct jl_ctx {
     // descriptors per token-tile size (16, 32, 64): [0] xb as rows of dim, [1] xb as rows of the
     // local query width, [2] hb as rows of the local hidden width
     void *xb16 = nullptr, *hb16 = nullptr;
-    GemmTensorMap xmaps[3][3] = {};
+    GemmTensorMap xmaps[3][4] = {};
     GemmTensorMap wcls_slice_tmap = {};  // tied embeddings under tensor parallelism: this GPU's rows
     float *gemm_scratch = nullptr;       // split-column partial tiles of the tensor-core path
     size_t gemm_scratch_floats = 0;
@@ -679,7 +679,7 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
             ++*launches;
         }
         const int nt = gemm_token_tile(n);
-        g.xmap = &ctx->xmaps[in_kind][nt == 16 ? 0 : (nt == 32 ? 1 : 2)];
+        g.xmap = &ctx->xmaps[in_kind][nt == 16 ? 0 : (nt == 32 ? 1 : (nt == 64 ? 2 : 3))];
         g.x_lo_row = ctx->row_cap;
     }
     g.nseg = nseg;
@@ -1323,8 +1323,8 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
         (void)widest;
         if ((rc = alloc(&ctx->xb16, 2 * R * d.dim * 2))) return rc;
         if ((rc = alloc(&ctx->hb16, 2 * R * ctx->l_hidden * 2))) return rc;
-        const int nts[3] = {16, 32, 64};
-        for (int i = 0; i < 3; ++i) {
+        const int nts[4] = {16, 32, 64, 128};
+        for (int i = 0; i < 4; ++i) {
             JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[0][i], ctx->xb16, R, d.dim, nts[i]));
             JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[1][i], ctx->xb16, R, ctx->l_qdim, nts[i]));
             JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[2][i], ctx->hb16, R, ctx->l_hidden, nts[i]));

@@ -39,7 +39,7 @@ namespace {
 
 // Which bounded wait the kernel uses (a build-time experiment switch).
 #ifndef JL_GEMM_SUSPENDING_WAIT
-#define GEMM_WAIT mbar_spin_bounded
+#define GEMM_WAIT mbar_poll_bounded
 #else
 #define GEMM_WAIT mbar_wait_bounded
 #endif
@@ -276,11 +276,15 @@ __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, in
     }
 }
 
-// Tensor-memory columns: the accumulator (hi and lo partial products side by side, 2*NT <= 128
-// columns) and, from column 128 on, the A operand stages of 64 columns (128 K elements) each.
+// Tensor-memory columns: the accumulator (hi and lo partial products side by side, 2*NT columns)
+// and behind it the A operand stages of 64 columns (128 K elements) each.
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemAStage0 = 128;
 constexpr uint32_t kTmemAStageCols = kStageK / 2;
+template <int NT>
+struct TmemPlan {
+    static constexpr uint32_t a_stage0 = NT <= 64 ? 128 : 256;
+    static constexpr int a_stages = int((kTmemCols - a_stage0) / kTmemAStageCols);  // 6, or 4 for NT = 128
+};
 
 template <int TYPE, int NT>
 struct GemmSmem {
@@ -292,7 +296,7 @@ struct GemmSmem {
     // B half in shared memory. Several stages must be in flight to hide the round trip
     // conversion -> MMA -> commit -> stage free again.
     static constexpr int fit = budget / b_stage;
-    static constexpr int stages = fit >= 6 ? 6 : fit;
+    static constexpr int stages = fit >= TmemPlan<NT>::a_stages ? TmemPlan<NT>::a_stages : fit;
     static constexpr int b_off = 0;
     static constexpr int raw_off = stages * b_stage;
     static constexpr int bar_off = raw_off + raw_bytes;
@@ -301,7 +305,9 @@ struct GemmSmem {
 static_assert(GemmSmem<kQ8_0, 64>::total <= 227 * 1024 && GemmSmem<kQ4_K, 64>::total <= 227 * 1024 &&
                   GemmSmem<kQ4_K, 16>::total <= 227 * 1024 && GemmSmem<kQ8_0, 32>::total <= 227 * 1024,
               "shared memory budget");
-static_assert(GemmSmem<kQ8_0, 64>::stages >= 3, "pipeline depth");
+static_assert(GemmSmem<kQ8_0, 64>::stages >= 3 && GemmSmem<kQ8_0, 128>::stages >= 2 &&
+                  GemmSmem<kQ8_0, 128>::total <= 227 * 1024 && GemmSmem<kQ4_K, 128>::total <= 227 * 1024,
+              "pipeline depth");
 
 struct TileRef {
     int seg, row0;
@@ -528,7 +534,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     if (ok && first && done > 0) ok = GEMM_WAIT(acc_empty, uint32_t(done - 1) & 1u);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t ta0 = tmem_d + kTmemAStage0 + uint32_t(s) * kTmemAStageCols;
+                    const uint32_t ta0 = tmem_d + TmemPlan<NT>::a_stage0 + uint32_t(s) * kTmemAStageCols;
                     const uint64_t db0 = smem_desc_sw128(smem_u32(base + S::b_off + s * S::b_stage));
 #pragma unroll
                     for (int atom = 0; atom < 2; ++atom) {
@@ -559,7 +565,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int a_row = tid & 127, a_q = tid >> 7;  // a_q: which 32-column quarter of the 128
         const int a_atom = a_q >> 1, a_half = a_q & 1;
         constexpr int kBChunks = NT * 16;  // 16-byte chunks of eight activations per operand stage
-        constexpr int kBPerThread = (kBChunks + kConvertThreads - 1) / kConvertThreads;
+        // converting activations inside the kernel (no pre-split buffer) is kept for tiles up to 64 tokens
+        constexpr int kBPerThread = NT <= 64 ? (kBChunks + kConvertThreads - 1) / kConvertThreads : 0;
         const int lane_grp = warp & 3, col_grp = warp >> 2;  // epilogue: TMEM lanes 32*lane_grp, columns 16*col_grp
         size_t total_rows = 0;
         for (int sgi = 0; sgi < a.nseg; ++sgi) total_rows += size_t(a.seg[sgi].rows);
@@ -589,7 +596,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const int q = 2 * i + j, s = q % ST;
                 const int k0 = r * kRawK + j * kStageK;
                 // Activations first: their loads are in flight while the weights are converted.
-                float4 xv[kBPerThread][2];
+                float4 xv[kBPerThread > 0 ? kBPerThread : 1][2];
 #pragma unroll
                 for (int uu = 0; uu < kBPerThread; ++uu) {
                     const int ch = tid + uu * kConvertThreads;
@@ -620,7 +627,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     }
                     // this thread's row is TMEM lane a_row (its warp may touch lanes 32 * (warp % 4) ..);
                     // its 32 weights are columns a_q * 16 .. + 15 of the stage
-                    tmem_st16(tmem_d + (uint32_t(a_row & ~31) << 16) + kTmemAStage0 + uint32_t(s) * kTmemAStageCols +
+                    tmem_st16(tmem_d + (uint32_t(a_row & ~31) << 16) + TmemPlan<NT>::a_stage0 + uint32_t(s) * kTmemAStageCols +
                                   uint32_t(a_q) * 16u,
                               cols16);
                     tc_fence_before();
@@ -671,17 +678,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tc_fence_after();
             // partial slot: 0 if this CTA's range starts inside the tile, 1 if it only ends inside it
             float *slot = a.scratch + (size_t(blockIdx.x) * 2 + (seg_begin > u_lo ? 0 : 1)) * (size_t(kTileM) * NT);
-            if (col_grp * 16 < NT) {
+#pragma unroll
+            for (int cg = col_grp; cg * 16 < NT; cg += 4) {
                 float v[16], vl[16];
-                tmem_ld16(tmem_d + (uint32_t(lane_grp * 32) << 16) + uint32_t(col_grp * 16), v);
-                tmem_ld16(tmem_d + (uint32_t(lane_grp * 32) << 16) + uint32_t(NT + col_grp * 16), vl);
+                tmem_ld16(tmem_d + (uint32_t(lane_grp * 32) << 16) + uint32_t(cg * 16), v);
+                tmem_ld16(tmem_d + (uint32_t(lane_grp * 32) << 16) + uint32_t(NT + cg * 16), vl);
 #pragma unroll
                 for (int jc = 0; jc < 16; ++jc) v[jc] += vl[jc];
                 const int rr = lane_grp * 32 + lane;
                 const int row = tr.row0 + rr;
 #pragma unroll
                 for (int jc = 0; jc < 16; ++jc) {
-                    const int t = col_grp * 16 + jc;
+                    const int t = cg * 16 + jc;
                     const int tok = tok0 + t;
                     if (whole) {
                         if (row < seg.rows && tok < a.n) {
@@ -761,7 +769,8 @@ template <int TYPE>
 cudaError_t launch_type(const GemmArgs &a, cudaStream_t stream) {
     if (a.n <= 16) return launch_nt<TYPE, 16>(a, stream);
     if (a.n <= 32) return launch_nt<TYPE, 32>(a, stream);
-    return launch_nt<TYPE, 64>(a, stream);
+    if (a.n <= 64 || a.xmap == nullptr) return launch_nt<TYPE, 64>(a, stream);
+    return launch_nt<TYPE, 128>(a, stream);
 }
 
 template <int TYPE, int NT>
@@ -775,7 +784,8 @@ cudaError_t configure_type() {
     cudaError_t e;
     if ((e = configure_nt<TYPE, 16>()) != cudaSuccess) return e;
     if ((e = configure_nt<TYPE, 32>()) != cudaSuccess) return e;
-    return configure_nt<TYPE, 64>();
+    if ((e = configure_nt<TYPE, 64>()) != cudaSuccess) return e;
+    return configure_nt<TYPE, 128>();
 }
 
 }  // namespace
@@ -810,10 +820,10 @@ cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type
     return cudaSuccess;
 }
 
-int gemm_token_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : 64); }
+int gemm_token_tile(int n) { return n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : 128)); }  // with pre-split activations
 
 cudaError_t gemm_make_activation_map(GemmTensorMap *out, const void *x16_dev, int64_t row_cap, int64_t cols, int nt) {
-    if (!out || !x16_dev || row_cap <= 0 || cols <= 0 || cols % 64 != 0 || (nt != 16 && nt != 32 && nt != 64))
+    if (!out || !x16_dev || row_cap <= 0 || cols <= 0 || cols % 64 != 0 || (nt != 16 && nt != 32 && nt != 64 && nt != 128))
         return cudaErrorInvalidValue;
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -856,7 +866,7 @@ cudaError_t gemm_tc_launch(const GemmArgs &a, cudaStream_t stream) {
     int slab = a.n;
     if (a.counters_len > 0 && tiles <= a.counters_len) {
         const int max_tiles_n = a.counters_len / tiles;
-        if ((a.n + 63) / 64 > max_tiles_n) slab = max_tiles_n * 64;
+        if ((a.n + 127) / 128 > max_tiles_n) slab = max_tiles_n * 128;
     }
     if (a.xmap != nullptr && slab < a.n) return cudaErrorInvalidValue;  // pre-split activations: one slab only
     for (int t0 = 0; t0 < a.n; t0 += slab) {

@@ -12,7 +12,7 @@ struct alignas(64) GemmTensorMap {
 };
 cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type, int64_t rows, int64_t cols);
 // TMA descriptor of a pre-split activation buffer: binary16 [2 * row_cap][cols] (the hi rows, then
-// the lo rows), fetched in swizzled boxes of nt rows x 64 columns; nt is 16, 32 or 64.
+// the lo rows), fetched in swizzled boxes of nt rows x 64 columns; nt is 16, 32, 64 or 128.
 cudaError_t gemm_make_activation_map(GemmTensorMap *out, const void *x16_dev, int64_t row_cap, int64_t cols, int nt);
 int gemm_token_tile(int n);  // the nt the kernel will use for n rows
 
