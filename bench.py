@@ -38,6 +38,8 @@ ARCHS = {
     "8b": (4096, 14336, 32, 32, 8, 128256, 4096, False),
     "1b": (2048, 8192, 16, 32, 8, 128256, 2048, True),
     "tiny": (512, 1024, 4, 8, 2, 4096, 1024, False),
+    # Llama-3-70B architecture: the tensor-parallel configuration (B=16, 1024-token prompts)
+    "70b": (8192, 28672, 80, 64, 8, 128256, 4096, False),
     # four layers of the 8B layer shapes with a small vocabulary: the profiling-sized case
     "8b4": (4096, 14336, 4, 32, 8, 16384, 4096, False),
 }

@@ -200,6 +200,10 @@ int32_t jl_tp_init(jl_ctx *ctx, const char *nccl_path, const void *id128, int32_
  * step returns JL_ERR_TIMEOUT; the group is then out of step and must be torn down. Larger
  * messages (prefill chunks, wide batches) always go through NCCL. */
 int32_t jl_tp_exchange_mode(jl_ctx *ctx);
+/* Self-test of the bounded wait (no counterpart in the reference): runs one two-rank peer exchange in
+ * which the second rank is a local buffer that nobody writes, with the given patience (1..2000 ms).
+ * The kernel gives up, the call returns JL_ERR_TIMEOUT, and the context stays usable. */
+int32_t jl_debug_peer_wait_timeout(jl_ctx *ctx, int32_t timeout_ms);
 const char *jl_tp_exchange_note(jl_ctx *ctx);
 
 /* ---- allocation-free operator (no counterpart in the reference: its kernels take whatever

@@ -69,6 +69,7 @@ SIGNATURES = {
     "jl_tp_unique_id": (_I32, [_P, C.c_char_p, _P]),
     "jl_tp_init": (_I32, [_P, C.c_char_p, _P, _I32, _I32]),
     "jl_tp_exchange_mode": (_I32, [_P]),
+    "jl_debug_peer_wait_timeout": (_I32, [_P, _I32]),
     "jl_tp_exchange_note": (C.c_char_p, [_P]),
     "jl_gemv_argmax_static": (_I32, [_I32, _I64, _I64, _P, _P, _P, C.c_float, _P, _P, _P]),
     "jl_static_last_error": (C.c_char_p, []),

@@ -225,6 +225,11 @@ class Device:
         self._check(self._lib.jl_timer_stop(self.handle, C.byref(ms)))
         return ms.value
 
+    def peer_wait_self_test(self, timeout_ms: int = 50) -> None:
+        """Runs a peer exchange whose partner never answers; raises DeviceTimeoutError when the bounded
+        wait gives up (the expected outcome) and leaves the context usable."""
+        self._check(self._lib.jl_debug_peer_wait_timeout(self.handle, int(timeout_ms)))
+
     def flush_l2(self) -> None:
         self._check(self._lib.jl_flush_l2(self.handle))
 

@@ -2015,4 +2015,46 @@ int32_t jl_flush_l2(jl_ctx *ctx) {
     return JL_OK;
 }
 
+int32_t jl_debug_peer_wait_timeout(jl_ctx *ctx, int32_t timeout_ms) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, timeout_ms >= 1 && timeout_ms <= 2000, JL_ERR_INVALID, "timeout_ms must be 1..2000");
+    cudaSetDevice(ctx->device);
+    // A two-rank exchange in which this GPU is rank 0 and "rank 1" is a local buffer nobody writes:
+    // the kernel pushes, waits for packets that never come, gives up after timeout_ms and says so.
+    constexpr int kCount = 256;
+    const size_t cap = kCount;
+    const size_t inbox_packets = 2 * 2 * cap;  // [slot][source rank][cap]
+    char *buf = nullptr;
+    const size_t bytes = 2 * inbox_packets * sizeof(uint2) + 2 * kCount * sizeof(float) + 4 * sizeof(unsigned);
+    int rc = dev_alloc(ctx, reinterpret_cast<void **>(&buf), bytes);
+    if (rc) return rc;
+    cudaError_t e = cudaMemsetAsync(buf, 0, bytes, ctx->stream);
+    TpReduceArgs a = {};
+    a.inbox.of[0] = reinterpret_cast<uint2 *>(buf);
+    a.inbox.of[1] = reinterpret_cast<uint2 *>(buf) + inbox_packets;
+    a.part = reinterpret_cast<float *>(buf + 2 * inbox_packets * sizeof(uint2));
+    a.x = const_cast<float *>(a.part) + kCount;
+    a.ctr = reinterpret_cast<unsigned *>(a.x + kCount);
+    a.base = 0;
+    a.cap = cap;
+    a.tp = 2;
+    a.rank = 0;
+    a.count = kCount;
+    a.status = ctx->d_status;
+    a.timeout_ns = 1000000ull * unsigned(timeout_ms);
+    const unsigned ctr0[4] = {1u, 0u, 0u, 0u};
+    if (e == cudaSuccess) e = cudaMemcpyAsync(a.ctr, ctr0, sizeof ctr0, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = tp_push_reduce_launch(a, ctx->stream, false);
+    int status = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&status, ctx->d_status, sizeof status, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(buf);
+    if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "peer wait self-test failed: %s", cudaGetErrorString(e));
+    ctx->counters.kernel_launches += 1;
+    if (status == kDevTimeout) return fail(ctx, JL_ERR_TIMEOUT, "a peer did not answer within %d ms", timeout_ms);
+    return JL_OK;
+}
+
 }  // extern "C"

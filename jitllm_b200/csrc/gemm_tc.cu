@@ -11,8 +11,8 @@
 //     stored) as one 2-D TMA box into a ring; rows past the end of the matrix arrive as zeros.
 //   * warps 0-15: turn a raw half-stage (128 columns) into the A operand -- weights rounded once
 //     to fp16 (Q4_0 / Q8_0: integer code times the block's fp16 scale in half2 arithmetic, which is
-//     exactly the fp16 rounding of the reference's fp32 product; Q4_K: (d*sc)*q - dmin*m in fp32 as
-//     the reference's getFloat, then rounded) stored K-major with the 128-byte swizzle -- and the
+//     exactly the fp16 rounding of the reference's fp32 product; Q4_K: (d*sc)*q - dmin*m in fp32
+//     with the last two steps fused, then rounded) stored K-major with the 128-byte swizzle -- and the
 //     B operand: activations split as x = hi + lo with hi, lo fp16 (22 significant bits). The only
 //     rounding left is the fp16 rounding of the weights (rel-L2 ~3e-4 per product, inside the 1e-3
 //     bar; the reference's own tensor-core prefill feeds single fp16 operands).
@@ -192,7 +192,7 @@ template <int TYPE>
 __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, int half, uint4 (&out)[4]) {
     if constexpr (TYPE == kQ4_K) {
         // tensor/standard/Q4_KFloatTensor.java:68-122: unit p holds sub-blocks 2p (low nibbles) and
-        // 2p+1 (high nibbles) of the same 32 bytes; w = (d*sc)*q - dmin*m, every step in fp32.
+        // 2p+1 (high nibbles) of the same 32 bytes; w = (d*sc)*q - dmin*m in fp32.
         const uint4 hdr = lds128(row_u32);
         const uint4 q0 = lds128(row_u32 + 16 + unit * 32);
         const uint4 q1 = lds128(row_u32 + 32 + unit * 32);
@@ -216,12 +216,17 @@ __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, in
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const uint32_t v = (qw[2 * c + i] >> nib) & 0x0F0F0F0Fu;
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    // 0x4B000000 | q is the float 2^23 + q: the integer code without a conversion unit
-                    const float q = __uint_as_float(0x4B000000u | ((v >> (8 * b)) & 0xFFu)) - 8388608.0f;
-                    w[i * 4 + b] = __fsub_rn(__fmul_rn(ds, q), mm);
-                }
+                // One byte permute builds the float 2^23 + q (0x4B0000qq): the integer code without a
+                // conversion unit. The product and the subtraction are fused: the operand is rounded
+                // to binary16 right after, and a fused and an unfused fp32 result round alike there.
+                const float q0 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440)) - 8388608.0f;
+                const float q1 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7441)) - 8388608.0f;
+                const float q2 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7442)) - 8388608.0f;
+                const float q3 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7443)) - 8388608.0f;
+                w[i * 4 + 0] = __fmaf_rn(ds, q0, -mm);
+                w[i * 4 + 1] = __fmaf_rn(ds, q1, -mm);
+                w[i * 4 + 2] = __fmaf_rn(ds, q2, -mm);
+                w[i * 4 + 3] = __fmaf_rn(ds, q3, -mm);
             }
             out[c] = make_uint4(pack_half2(w[0], w[1]), pack_half2(w[2], w[3]), pack_half2(w[4], w[5]),
                                 pack_half2(w[6], w[7]));

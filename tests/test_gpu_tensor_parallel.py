@@ -121,3 +121,20 @@ def test_four_gpus_match_two(oracle, built):
         pytest.skip("needs four GPUs")
     a, b = _run(4, 12, 1), _run(2, 12, 1)
     assert np.max(np.abs(a[0]["logits"][0] - b[0]["logits"][0])) <= 1e-3
+
+
+def test_a_peer_that_never_answers_times_out_and_the_context_survives(dev):
+    """Failure detection without a fault: the wait of the peer exchange is bounded; with a partner that
+    never writes, the kernel returns a status and the call raises -- nothing hangs, nothing traps."""
+    import time
+    import jitllm_b200 as jl
+    t0 = time.time()
+    with pytest.raises(jl.DeviceTimeoutError, match="did not answer"):
+        dev.peer_wait_self_test(50)
+    assert time.time() - t0 < 5.0
+    # the context still works: a bit-exact dequantisation afterwards
+    raw = jl.synth_tensor(jl.GGMLType.Q8_0, 1024, seed=3)
+    out = dev.dequantize(jl.GGMLType.Q8_0, raw, 1024)
+    assert out.shape == (1024,) and np.isfinite(out).all()
+    with pytest.raises(ValueError):
+        dev.peer_wait_self_test(0)
