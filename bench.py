@@ -63,6 +63,9 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=20261125)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-matmul", default="",
+                    help="ROWSxCOLSxN: launch the standalone product on three copies of one matrix --steps times and "
+                         "exit: the small case ncu captures of the tensor-core kernel are taken on")
     ap.add_argument("--sweep", action="store_true",
                     help="standalone quantised mat-vec / mat-mat sweep (formats x shapes x N): one JSON line per case")
     ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
@@ -222,6 +225,30 @@ def main():
 
     if args.sweep:
         return run_sweep(jl, args) if rank == 0 else 0
+    if args.profile_matmul:
+        if rank != 0:
+            return 0
+        rows, cols, n = (int(v) for v in args.profile_matmul.lower().split("x"))
+        t = jl.GGMLType[args.format]
+        dev = jl.Device(0)
+        w = jl.synth_tensor(t, rows * cols, seed=args.seed)
+        mats = [dev.upload_matrix(t, w, rows, cols) for _ in range(3)]
+        x = np.random.default_rng(args.seed).standard_normal((n, cols)).astype(np.float32)
+        xd, yd = dev.alloc(x.nbytes), dev.alloc(n * rows * 4)
+        dev.h2d(xd, x)
+        for _ in range(max(args.warmup, 1)):
+            for m in mats:
+                m.matmul_dev(xd, n, yd)
+        dev.synchronize()
+        dev.timer_start()
+        for _ in range(args.steps):
+            for m in mats:
+                m.matmul_dev(xd, n, yd)
+        us = dev.timer_stop() * 1000.0 / (3 * args.steps)
+        by = rows * cols * BYTES_PER_EL[args.format] + 4 * cols * n + 4 * rows * n
+        print(json.dumps({"profile_matmul": args.profile_matmul, "format": args.format, "launches": 3 * args.steps,
+                          "us_per_launch": us, "bytes_per_launch": by, "flops_per_launch": 2.0 * rows * cols * n}), flush=True)
+        return 0
 
     dims = ARCHS[args.arch]
     cfg = jl.Configuration(dim=dims[0], hiddenDim=dims[1], numberOfLayers=dims[2], numberOfHeads=dims[3],

@@ -871,7 +871,8 @@ cudaError_t gemm_tc_launch(const GemmArgs &a, cudaStream_t stream) {
     int slab = a.n;
     if (a.counters_len > 0 && tiles <= a.counters_len) {
         const int max_tiles_n = a.counters_len / tiles;
-        if ((a.n + 127) / 128 > max_tiles_n) slab = max_tiles_n * 128;
+        const int widest = a.xmap != nullptr ? 128 : 64;  // the token tile launch_type will pick for a tall product
+        if ((a.n + widest - 1) / widest > max_tiles_n) slab = max_tiles_n * widest;
     }
     if (a.xmap != nullptr && slab < a.n) return cudaErrorInvalidValue;  // pre-split activations: one slab only
     for (int t0 = 0; t0 < a.n; t0 += slab) {

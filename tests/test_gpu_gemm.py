@@ -59,3 +59,16 @@ def test_wide_activations_do_not_overflow_fp16(dev, oracle):
     x = (np.random.default_rng(6).standard_normal((n, cols)) * 300.0).astype(np.float32)
     got, want = dev.matmul(t, w, rows, cols, x), oracle.matmul(t, w, x, rows, cols)
     assert rel_l2(got, want) < EXPECT
+
+
+def test_tall_product_goes_in_token_slabs(dev, oracle):
+    """More output tiles than arrival counters (1002 row tiles x 18 token tiles): the launch is cut into
+    token slabs; sampled rows against the oracle and two slabs' boundary rows included."""
+    rows, cols, n, t = 128256, 256, 1100, GGMLType.Q4_0
+    w = jl.synth_tensor(t, rows * cols, seed=23)
+    x = np.random.default_rng(7).standard_normal((n, cols)).astype(np.float32)
+    got = dev.matmul(t, w, rows, cols, x)
+    assert got.shape == (n, rows)
+    sample = [0, 63, 64, 1023, 1024, 1025, 1099]
+    want = oracle.matmul(t, w, x[sample], rows, cols)
+    assert rel_l2(got[sample], want) < EXPECT
