@@ -107,6 +107,18 @@ __device__ __forceinline__ void bulk_g2s_hint(void *dst_smem, const void *src_gm
         "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
+// Same, with the shared-memory addresses already in their 32-bit form (no conversion per copy).
+__device__ __forceinline__ void bulk_g2s_hint_u32(uint32_t dst_smem, const void *src_gmem, uint32_t bytes,
+                                                  uint32_t bar_smem, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;" ::"r"(dst_smem),
+        "l"(src_gmem), "r"(bytes), "r"(bar_smem), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_u32(uint32_t bar_smem, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_smem), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -573,8 +573,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // converting activations inside the kernel (no pre-split buffer) is kept for tiles up to 64 tokens
         constexpr int kBPerThread = NT <= 64 ? (kBChunks + kConvertThreads - 1) / kConvertThreads : 0;
         const int lane_grp = warp & 3, col_grp = warp >> 2;  // epilogue: TMEM lanes 32*lane_grp, columns 16*col_grp
-        size_t total_rows = 0;
-        for (int sgi = 0; sgi < a.nseg; ++sgi) total_rows += size_t(a.seg[sgi].rows);
         int i = 0, done = 0, cur_u = -1, fix_phase = 0;
         TileRef tr = {0, 0};
         int tok0 = 0;
@@ -674,9 +672,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const long long seg_begin = u_lo > lo ? u_lo : lo;
             const bool whole = seg_begin == u_lo && seg_end == u_lo + raw_total;
             const GemmSeg seg = a.seg[tr.seg];
-            size_t row_offset = 0;
-            for (int sgi = 0; sgi < tr.seg; ++sgi) row_offset += size_t(a.seg[sgi].rows);
-            (void)row_offset;
             ok = GEMM_WAIT(acc_full, uint32_t(done) & 1u);
             if (!ok) break;
             ++done;

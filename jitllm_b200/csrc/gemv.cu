@@ -103,29 +103,41 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         row0 = tile * R;
     };
     const uint64_t policy = policy_evict_first();
-    // Producer cursor (lane 0): the next item to request, advanced incrementally.
-    int p_tile = wg, p_cc = 0, p_seg = 0, p_row0 = 0, p_issued = 0;
-    locate(p_tile, p_seg, p_row0);
+    // Producer cursor (lane 0): the next item to request, advanced incrementally; source pointers
+    // move by one chunk per item and are recomputed only when the cursor enters a new tile.
+    int p_tile = wg, p_cc = 0, p_seg = 0, p_row0 = 0, p_issued = 0, p_rows = 0;
+    const uint8_t *p_src0 = nullptr, *p_src1 = nullptr;
+    auto enter_tile = [&]() {
+        locate(p_tile, p_seg, p_row0);
+        p_rows = min(R, a.seg[p_seg].rows - p_row0);
+        p_src0 = a.seg[p_seg].w + size_t(p_row0) * rowb;
+        if (MODE == kGemvGateUp) p_src1 = a.seg[1].w + size_t(p_row0) * rowb;
+    };
+    if (n_items > 0) enter_tile();
+    const uint32_t bars_u32 = smem_u32(my_bars);
+    const uint32_t last_bytes = uint32_t(nunits - (nchunks - 1) * 32) * UB;
     auto issue = [&](int s) {  // lane 0 only
-        const int nun = min(32, nunits - p_cc * 32);
-        const uint32_t bytes = uint32_t(nun) * UB;
-        const int nrows = min(R, a.seg[p_seg].rows - p_row0);
-        uint8_t *stage = my_ring + size_t(s) * stage_bytes;
-        uint64_t *bar = my_bars + s;
-        mbar_expect_tx(bar, bytes * nrows * (MODE == kGemvGateUp ? 2 : 1));
-        const uint8_t *src = a.seg[p_seg].w + size_t(p_row0) * rowb + size_t(p_cc) * CB;
-        for (int r = 0; r < nrows; ++r) {
-            bulk_g2s_hint(stage + r * CB, src + size_t(r) * rowb, bytes, bar, policy);
-            if (MODE == kGemvGateUp)
-                bulk_g2s_hint(stage + (R + r) * CB,
-                              a.seg[1].w + size_t(p_row0 + r) * rowb + size_t(p_cc) * CB, bytes, bar,
-                              policy);
+        const uint32_t bytes = p_cc == nchunks - 1 ? last_bytes : uint32_t(CB);
+        const uint32_t stage = ring_u32 + uint32_t(s) * stage_bytes;
+        const uint32_t bar = bars_u32 + uint32_t(s) * 8u;
+        mbar_expect_tx_u32(bar, bytes * p_rows * (MODE == kGemvGateUp ? 2 : 1));
+        const uint8_t *src0 = p_src0, *src1 = p_src1;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (r < p_rows) {
+                bulk_g2s_hint_u32(stage + r * CB, src0, bytes, bar, policy);
+                if (MODE == kGemvGateUp) bulk_g2s_hint_u32(stage + (R + r) * CB, src1, bytes, bar, policy);
+                src0 += rowb;
+                if (MODE == kGemvGateUp) src1 += rowb;
+            }
         }
         ++p_issued;
+        p_src0 += CB;
+        if (MODE == kGemvGateUp) p_src1 += CB;
         if (++p_cc == nchunks) {
             p_cc = 0;
             p_tile += total_warps;
-            if (p_tile < total_tiles) locate(p_tile, p_seg, p_row0);
+            if (p_tile < total_tiles) enter_tile();
         }
     };
 
