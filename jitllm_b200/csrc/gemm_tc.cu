@@ -397,7 +397,7 @@ __device__ __noinline__ void fold_partials(const GemmArgs &a, const GemmSeg &seg
     }
 }
 
-template <int TYPE, int NT>
+template <int TYPE, int NT, bool XT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1,
                    const __grid_constant__ CUtensorMap tm2, const __grid_constant__ CUtensorMap tmx) {
@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (tid == 0) {
         for (int s = 0; s < ST; ++s) {
             mbar_init(a_free + s, 1);
-            mbar_init(a_full + s, kConvertWarps + (a.xmap != nullptr ? 1 : 0));
+            mbar_init(a_full + s, kConvertWarps + (XT ? 1 : 0));
         }
         for (int s = 0; s < RS; ++s) {
             mbar_init(raw_full + s, 1);
@@ -486,7 +486,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
     } else if (warp == kConvertWarps + 2) {
         // ---- activation tiles by TMA (pre-split binary16 hi / lo rows), one request set per operand stage
-        if (lane == 0 && a.xmap != nullptr) {
+        if (lane == 0 && XT) {
             int i = 0;
             int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
             for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
@@ -571,7 +571,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int a_atom = a_q >> 1, a_half = a_q & 1;
         constexpr int kBChunks = NT * 16;  // 16-byte chunks of eight activations per operand stage
         // converting activations inside the kernel (no pre-split buffer) is kept for tiles up to 64 tokens
-        constexpr int kBPerThread = NT <= 64 ? (kBChunks + kConvertThreads - 1) / kConvertThreads : 0;
+        constexpr int kBPerThread = (!XT && NT <= 64) ? (kBChunks + kConvertThreads - 1) / kConvertThreads : 0;
         const int lane_grp = warp & 3, col_grp = warp >> 2;  // epilogue: TMEM lanes 32*lane_grp, columns 16*col_grp
         int i = 0, done = 0, cur_u = -1, fix_phase = 0;
         TileRef tr = {0, 0};
@@ -605,7 +605,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const int ch = tid + uu * kConvertThreads;
                     const int t = ch >> 4, kc = ch & 15;
                     const int tok = tok0 + t;
-                    if (ch < kBChunks && tok < a.n && a.xmap == nullptr) {
+                    if (ch < kBChunks && tok < a.n) {
                         const float4 *src = reinterpret_cast<const float4 *>(a.x + size_t(tok) * a.cols + k0 + kc * 8);
                         xv[uu][0] = __ldg(src);
                         xv[uu][1] = __ldg(src + 1);
@@ -620,14 +620,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     tc_fence_after();  // the stage's previous MMAs are complete (a_free): order the store after them
                     uint4 chunks[4];
                     dequant32_to_half<TYPE>(row_u32, 2 * j + a_atom, a_half, chunks);
-                    uint32_t cols16[16];
+                    if (!a_valid) {  // rows past the end of the matrix (bottom tile only)
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        cols16[4 * c + 0] = a_valid ? chunks[c].x : 0u;
-                        cols16[4 * c + 1] = a_valid ? chunks[c].y : 0u;
-                        cols16[4 * c + 2] = a_valid ? chunks[c].z : 0u;
-                        cols16[4 * c + 3] = a_valid ? chunks[c].w : 0u;
+                        for (int c = 0; c < 4; ++c) chunks[c] = make_uint4(0u, 0u, 0u, 0u);
                     }
+                    const uint32_t cols16[16] = {chunks[0].x, chunks[0].y, chunks[0].z, chunks[0].w,
+                                                 chunks[1].x, chunks[1].y, chunks[1].z, chunks[1].w,
+                                                 chunks[2].x, chunks[2].y, chunks[2].z, chunks[2].w,
+                                                 chunks[3].x, chunks[3].y, chunks[3].z, chunks[3].w};
                     // this thread's row is TMEM lane a_row (its warp may touch lanes 32 * (warp % 4) ..);
                     // its 32 weights are columns a_q * 16 .. + 15 of the stage
                     tmem_st16(tmem_d + (uint32_t(a_row & ~31) << 16) + TmemPlan<NT>::a_stage0 + uint32_t(s) * kTmemAStageCols +
@@ -638,7 +638,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                 for (int uu = 0; uu < kBPerThread; ++uu) {
                     const int ch = tid + uu * kConvertThreads;
-                    if (ch < kBChunks && !(a.debug & 2) && a.xmap == nullptr) {
+                    if (ch < kBChunks && !(a.debug & 2)) {
                         const int t = ch >> 4, kc = ch & 15;
                         const int atom = kc >> 3, c = kc & 7;
                         const float x[8] = {xv[uu][0].x, xv[uu][0].y, xv[uu][0].z, xv[uu][0].w,
@@ -760,8 +760,12 @@ cudaError_t launch_nt(const GemmArgs &a, cudaStream_t stream) {
     CUtensorMap maps[4];
     for (int s = 0; s < 3; ++s) memcpy(&maps[s], a.seg[s < a.nseg ? s : 0].tmap->bytes, sizeof(CUtensorMap));
     memcpy(&maps[3], (a.xmap != nullptr ? a.xmap : a.seg[0].tmap)->bytes, sizeof(CUtensorMap));
-    gemm_tc_kernel<TYPE, NT><<<dim3(unsigned(ctas)), kGemmThreads, GemmSmem<TYPE, NT>::total, stream>>>(a, maps[0], maps[1],
-                                                                                                     maps[2], maps[3]);
+    if (a.xmap != nullptr)
+        gemm_tc_kernel<TYPE, NT, true><<<dim3(unsigned(ctas)), kGemmThreads, GemmSmem<TYPE, NT>::total, stream>>>(
+            a, maps[0], maps[1], maps[2], maps[3]);
+    else
+        gemm_tc_kernel<TYPE, NT, false><<<dim3(unsigned(ctas)), kGemmThreads, GemmSmem<TYPE, NT>::total, stream>>>(
+            a, maps[0], maps[1], maps[2], maps[3]);
     return cudaGetLastError();
 }
 
@@ -775,7 +779,10 @@ cudaError_t launch_type(const GemmArgs &a, cudaStream_t stream) {
 
 template <int TYPE, int NT>
 cudaError_t configure_nt() {
-    return cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmSmem<TYPE, NT>::total);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(gemm_tc_kernel<TYPE, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 GemmSmem<TYPE, NT>::total);
 }
 
