@@ -655,8 +655,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                                                                          pack_half2(xl[4], xl[5]), pack_half2(xl[6], xl[7]));
                     }
                 }
-                // Generic-proxy writes -> visible to the tensor core's (async proxy) reads.
-                if (!(a.debug & 16)) fence_proxy_async();
+                // Generic-proxy writes to shared memory (the B operand, when converted here) must be
+                // visible to the tensor core's async-proxy reads; the A operand went to tensor memory.
+                if (!XT) fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(a_full + s);
             }
