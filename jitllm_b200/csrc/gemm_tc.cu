@@ -281,6 +281,57 @@ __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, in
     }
 }
 
+// 64 consecutive weights of one row (one unit: for Q4_K the two sub-blocks that share 32 bytes of
+// nibbles) as 32 tensor-memory columns: `first` = the first 32 weights, `second` = the next 32.
+template <int TYPE>
+__device__ __forceinline__ void dequant64_to_half(uint32_t row_u32, int unit, uint32_t (&first)[16], uint32_t (&second)[16]) {
+    if constexpr (TYPE == kQ4_K) {
+        const uint4 hdr = lds128(row_u32);
+        const uint4 q0 = lds128(row_u32 + 16 + unit * 32);
+        const uint4 q1 = lds128(row_u32 + 32 + unit * 32);
+        const float d = half_bits_to_float(hdr.x & 0xFFFFu), dmin = half_bits_to_float(hdr.x >> 16);
+        uint32_t scw, mw;
+        if (unit < 2) {
+            scw = hdr.y & 0x3F3F3F3Fu;
+            mw = hdr.z & 0x3F3F3F3Fu;
+        } else {
+            scw = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+            mw = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+        }
+        const int sh = (unit & 1) * 16;
+        const float ds0 = __fmul_rn(d, float((scw >> sh) & 0xFFu)), ds1 = __fmul_rn(d, float((scw >> (sh + 8)) & 0xFFu));
+        const float mm0 = __fmul_rn(dmin, float((mw >> sh) & 0xFFu)), mm1 = __fmul_rn(dmin, float((mw >> (sh + 8)) & 0xFFu));
+        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t vl = qw[i] & 0x0F0F0F0Fu, vh = (qw[i] >> 4) & 0x0F0F0F0Fu;
+            // 0x4B0000qq is the float 2^23 + q (one byte permute); multiply and subtract are fused,
+            // the result is rounded to binary16 right after.
+            const float a0 = __uint_as_float(__byte_perm(vl, 0x4B000000u, 0x7440)) - 8388608.0f;
+            const float a1 = __uint_as_float(__byte_perm(vl, 0x4B000000u, 0x7441)) - 8388608.0f;
+            const float a2 = __uint_as_float(__byte_perm(vl, 0x4B000000u, 0x7442)) - 8388608.0f;
+            const float a3 = __uint_as_float(__byte_perm(vl, 0x4B000000u, 0x7443)) - 8388608.0f;
+            const float b0 = __uint_as_float(__byte_perm(vh, 0x4B000000u, 0x7440)) - 8388608.0f;
+            const float b1 = __uint_as_float(__byte_perm(vh, 0x4B000000u, 0x7441)) - 8388608.0f;
+            const float b2 = __uint_as_float(__byte_perm(vh, 0x4B000000u, 0x7442)) - 8388608.0f;
+            const float b3 = __uint_as_float(__byte_perm(vh, 0x4B000000u, 0x7443)) - 8388608.0f;
+            first[2 * i] = pack_half2(__fmaf_rn(ds0, a0, -mm0), __fmaf_rn(ds0, a1, -mm0));
+            first[2 * i + 1] = pack_half2(__fmaf_rn(ds0, a2, -mm0), __fmaf_rn(ds0, a3, -mm0));
+            second[2 * i] = pack_half2(__fmaf_rn(ds1, b0, -mm1), __fmaf_rn(ds1, b1, -mm1));
+            second[2 * i + 1] = pack_half2(__fmaf_rn(ds1, b2, -mm1), __fmaf_rn(ds1, b3, -mm1));
+        }
+    } else {
+        uint4 c0[4], c1[4];
+        dequant32_to_half<TYPE>(row_u32, unit, 0, c0);
+        dequant32_to_half<TYPE>(row_u32, unit, 1, c1);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            first[4 * c] = c0[c].x; first[4 * c + 1] = c0[c].y; first[4 * c + 2] = c0[c].z; first[4 * c + 3] = c0[c].w;
+            second[4 * c] = c1[c].x; second[4 * c + 1] = c1[c].y; second[4 * c + 2] = c1[c].z; second[4 * c + 3] = c1[c].w;
+        }
+    }
+}
+
 // Tensor-memory columns: the accumulator (hi and lo partial products side by side, 2*NT columns)
 // and behind it the A operand stages of 64 columns (128 K elements) each.
 constexpr uint32_t kTmemCols = 512;
@@ -433,7 +484,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (tid == 0) {
         for (int s = 0; s < ST; ++s) {
             mbar_init(a_free + s, 1);
-            mbar_init(a_full + s, kConvertWarps + (XT ? 1 : 0));
+            mbar_init(a_full + s, kConvertWarps / 2 + (XT ? 1 : 0));  // one group of eight warps per stage
         }
         for (int s = 0; s < RS; ++s) {
             mbar_init(raw_full + s, 1);
@@ -567,11 +618,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
     } else {
         // ---- operand conversion and epilogue (warps 0-15) -------------------------------------
-        const int a_row = tid & 127, a_q = tid >> 7;  // a_q: which 32-column quarter of the 128
-        const int a_atom = a_q >> 1, a_half = a_q & 1;
+        // Two groups of eight warps take alternate operand stages (group 0 the first 128 columns of
+        // every raw stage, group 1 the second): a thread converts a whole 64-column unit of its row,
+        // so block headers, scale unpacking and barrier traffic are paid once per 64 weights.
+        constexpr int kGroupThreads = kConvertThreads / 2;
+        const int grp = warp >> 3, g_tid = tid & (kGroupThreads - 1);
+        const int a_row = g_tid & 127, a_unit = g_tid >> 7;  // a_unit: which 64-column unit of the 128
         constexpr int kBChunks = NT * 16;  // 16-byte chunks of eight activations per operand stage
         // converting activations inside the kernel (no pre-split buffer) is kept for tiles up to 64 tokens
-        constexpr int kBPerThread = (!XT && NT <= 64) ? (kBChunks + kConvertThreads - 1) / kConvertThreads : 0;
+        constexpr int kBPerThread = (!XT && NT <= 64) ? (kBChunks + kGroupThreads - 1) / kGroupThreads : 0;
         const int lane_grp = warp & 3, col_grp = warp >> 2;  // epilogue: TMEM lanes 32*lane_grp, columns 16*col_grp
         int i = 0, done = 0, cur_u = -1, fix_phase = 0;
         TileRef tr = {0, 0};
@@ -594,15 +649,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             ok = GEMM_WAIT(raw_full + st, uint32_t(i / RS) & 1u);
             if (!ok) break;
             const uint32_t row_u32 = smem_u32(base + S::raw_off + st * R::stage_bytes) + uint32_t(a_row) * R::row_bytes;
-#pragma unroll 1
-            for (int j = 0; j < 2; ++j) {
+            {
+                const int j = grp;
                 const int q = 2 * i + j, s = q % ST;
                 const int k0 = r * kRawK + j * kStageK;
                 // Activations first: their loads are in flight while the weights are converted.
                 float4 xv[kBPerThread > 0 ? kBPerThread : 1][2];
 #pragma unroll
                 for (int uu = 0; uu < kBPerThread; ++uu) {
-                    const int ch = tid + uu * kConvertThreads;
+                    const int ch = g_tid + uu * kGroupThreads;
                     const int t = ch >> 4, kc = ch & 15;
                     const int tok = tok0 + t;
                     if (ch < kBChunks && tok < a.n) {
@@ -614,30 +669,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     }
                 }
                 if (q >= ST) ok = GEMM_WAIT(a_free + s, uint32_t(q / ST - 1) & 1u);
-                if (!ok) break;
+                if (ok) {
                 uint8_t *b_st = base + S::b_off + s * S::b_stage;
                 if (!(a.debug & 1)) {
                     tc_fence_after();  // the stage's previous MMAs are complete (a_free): order the store after them
-                    uint4 chunks[4];
-                    dequant32_to_half<TYPE>(row_u32, 2 * j + a_atom, a_half, chunks);
+                    uint32_t first[16], second[16];
+                    dequant64_to_half<TYPE>(row_u32, 2 * j + a_unit, first, second);
                     if (!a_valid) {  // rows past the end of the matrix (bottom tile only)
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) chunks[c] = make_uint4(0u, 0u, 0u, 0u);
+                        for (int c = 0; c < 16; ++c) first[c] = second[c] = 0u;
                     }
-                    const uint32_t cols16[16] = {chunks[0].x, chunks[0].y, chunks[0].z, chunks[0].w,
-                                                 chunks[1].x, chunks[1].y, chunks[1].z, chunks[1].w,
-                                                 chunks[2].x, chunks[2].y, chunks[2].z, chunks[2].w,
-                                                 chunks[3].x, chunks[3].y, chunks[3].z, chunks[3].w};
                     // this thread's row is TMEM lane a_row (its warp may touch lanes 32 * (warp % 4) ..);
-                    // its 32 weights are columns a_q * 16 .. + 15 of the stage
-                    tmem_st16(tmem_d + (uint32_t(a_row & ~31) << 16) + TmemPlan<NT>::a_stage0 + uint32_t(s) * kTmemAStageCols +
-                                  uint32_t(a_q) * 16u,
-                              cols16);
+                    // its 64 weights are columns a_unit * 32 .. + 31 of the stage
+                    const uint32_t col0 = tmem_d + (uint32_t(a_row & ~31) << 16) + TmemPlan<NT>::a_stage0 +
+                                          uint32_t(s) * kTmemAStageCols + uint32_t(a_unit) * 32u;
+                    tmem_st16(col0, first);
+                    tmem_st16(col0 + 16u, second);
                     tc_fence_before();
                 }
 #pragma unroll
                 for (int uu = 0; uu < kBPerThread; ++uu) {
-                    const int ch = tid + uu * kConvertThreads;
+                    const int ch = g_tid + uu * kGroupThreads;
                     if (ch < kBChunks && !(a.debug & 2)) {
                         const int t = ch >> 4, kc = ch & 15;
                         const int atom = kc >> 3, c = kc & 7;
@@ -660,6 +712,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (!XT) fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(a_full + s);
+                }
             }
             if (!ok) break;
             // This warp has read both halves of the raw stage: hand its share back.
