@@ -206,6 +206,23 @@ int32_t jl_tp_exchange_mode(jl_ctx *ctx);
 int32_t jl_debug_peer_wait_timeout(jl_ctx *ctx, int32_t timeout_ms);
 const char *jl_tp_exchange_note(jl_ctx *ctx);
 
+/* ---- native GGUF reader (replaces the Java-side parse and per-tensor Panama copies:
+ * format/GGUF.java:60-110,123-165, model/loader/LlamaModelLoader.java:49-67,125-188,
+ * model/loader/ModelLoader.java:246-290). jl_gguf_open maps the file and parses header, metadata and
+ * tensor infos; jl_gguf_describe fills the model description from the llama.* keys (max_batch 1,
+ * single GPU: adjust before use) and the RoPE base; jl_gguf_upload does jl_model_create, uploads
+ * every tensor from the mapping (under tensor parallelism only this rank's slice, cut as described
+ * at jl_tp_init) and the RoPE tables (rope_cos / rope_sin, or computed with the reference's formula
+ * when NULL); the caller then calls jl_tp_init (tensor parallel) and jl_model_finalize. Errors:
+ * jl_gguf_last_error(). Tokenizer metadata is skipped, not interpreted. */
+typedef struct jl_gguf jl_gguf;
+int32_t jl_gguf_open(const char *path, jl_gguf **out);
+int32_t jl_gguf_describe(const jl_gguf *g, jl_model_desc *desc, float *rope_theta, int64_t *n_tensors);
+int32_t jl_gguf_upload(jl_ctx *ctx, const jl_gguf *g, int32_t max_batch, int32_t tp_rank, int32_t tp_size,
+                       const float *rope_cos, const float *rope_sin, int64_t rope_n);
+void jl_gguf_close(jl_gguf *g);
+const char *jl_gguf_last_error(void);
+
 /* ---- allocation-free operator (no counterpart in the reference: its kernels take whatever
  * scratch the TornadoVM runtime allocates for them).
  * y_dev[rows] = W . x (x optionally RMS-normalised with norm_w_dev / rms_eps first) and

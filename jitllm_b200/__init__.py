@@ -23,3 +23,4 @@ from .api import (  # noqa: F401
     synth_tensor,
 )
 from .tensor_parallel import TensorParallel, local_shape, shard_tensor, torch_broadcast  # noqa: F401,E402
+from .gguf import GgufFile, load_model_gguf, write_gguf  # noqa: F401,E402

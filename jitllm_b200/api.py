@@ -346,6 +346,14 @@ class B200Model:
             max_batch=maxBatch, tp_rank=self.tp.rank, tp_size=self.tp.size)
         dev._check(dev._lib.jl_model_create(dev.handle, C.byref(d)))
 
+    @classmethod
+    def adopt(cls, dev: Device, config: Configuration, maxBatch: int = 1,
+              tp: Optional[TensorParallel] = None) -> "B200Model":
+        """Wraps a model the library has already created on `dev` (the native GGUF reader does that)."""
+        self = cls.__new__(cls)
+        self.dev, self.config, self.maxBatch, self.tp = dev, config, maxBatch, tp or TensorParallel()
+        return self
+
     def uploadTensor(self, role: TensorRole, layer: int, ggml_type: GGMLType, data: np.ndarray,
                      presharded: bool = False) -> None:
         """`data` is the whole GGUF tensor; under tensor parallelism this GPU's slice is cut here
