@@ -25,7 +25,7 @@ def _config(jl):
                             vocabularySize=2048, contextLength=128)
 
 
-def _rank_main(rank, size, port, out_dir, fmt_value, width):
+def _rank_main(rank, size, port, out_dir, fmt_value, width, via_gguf=False):
     import torch
     import torch.distributed as dist
     import jitllm_b200 as jl
@@ -38,7 +38,13 @@ def _rank_main(rank, size, port, out_dir, fmt_value, width):
         cr, ci = jl.precomputeFreqsCis(cfg.contextLength, cfg.headSize, cfg.ropeTheta)
         dev = jl.Device(rank)
         tp = jl.TensorParallel(rank, size)
-        model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=width, tp=tp, broadcast=jl.torch_broadcast)
+        if via_gguf:  # the native reader cuts this rank's slices out of the file mapping
+            path = os.path.join(out_dir, f"model{rank}.gguf")
+            jl.write_gguf(path, cfg, tensors)
+            model = jl.load_model_gguf(dev, path, maxBatch=width, tp=tp, broadcast=jl.torch_broadcast,
+                                       rope_cos=cr, rope_sin=ci)
+        else:
+            model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=width, tp=tp, broadcast=jl.torch_broadcast)
         bps = cfg.contextLength // 16
         kv = model.createKvStorage(jl.KvStorageRequest(width * bps, bps, width, 16, cfg.numberOfLayers,
                                                        model.localKvDim))
@@ -73,14 +79,14 @@ def _rank_main(rank, size, port, out_dir, fmt_value, width):
         dist.destroy_process_group()
 
 
-def _run(size, fmt_value, width, push=True):
+def _run(size, fmt_value, width, push=True, via_gguf=False):
     import torch.multiprocessing as mp
     os.environ["JITLLM_B200_TP_PUSH"] = "1" if push else "0"  # inherited by the ranks
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(_rank_main, args=(size, port, d, fmt_value, width), nprocs=size, join=True)
+        mp.spawn(_rank_main, args=(size, port, d, fmt_value, width, via_gguf), nprocs=size, join=True)
         return [dict(np.load(os.path.join(d, f"rank{r}.npz"))) for r in range(size)]
 
 
@@ -114,6 +120,14 @@ def test_two_gpus_match_the_oracle(oracle, built, fmt_value, width, push):
             token = int(got[0]["tokens"][s, row])
             if token != int(np.argmax(want)):
                 break  # near-tie resolved the other way: the sequences part here
+
+
+def test_shards_cut_by_the_native_gguf_reader_match_the_host_cutter(oracle, built):
+    if _gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    a, b = _run(2, 12, 1, via_gguf=True), _run(2, 12, 1)
+    assert np.array_equal(a[0]["tokens"], b[0]["tokens"])
+    assert np.array_equal(a[0]["logits"], b[0]["logits"])  # same slices, same kernels: same bits
 
 
 def test_four_gpus_match_two(oracle, built):
