@@ -1319,8 +1319,6 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->hb2), R * ctx->l_hidden * 4))) return rc;
     if ((rc = alloc(reinterpret_cast<void **>(&ctx->logits), B * ctx->l_vocab * 4))) return rc;
     {
-        const size_t widest = size_t(d.dim) > size_t(ctx->l_hidden) ? size_t(d.dim) : size_t(ctx->l_hidden);
-        (void)widest;
         if ((rc = alloc(&ctx->xb16, 2 * R * d.dim * 2))) return rc;
         if ((rc = alloc(&ctx->hb16, 2 * R * ctx->l_hidden * 2))) return rc;
         const int nts[4] = {16, 32, 64, 128};

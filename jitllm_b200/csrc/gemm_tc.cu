@@ -5,20 +5,26 @@
 //
 // Shape of the kernel. One persistent CTA per SM. The work is the list of (128-row tile, NT-token
 // tile, 256-column raw stage) triples in that order, cut into equal contiguous ranges, one per
-// CTA, so every SM gets the same number of weight bytes whatever the matrix shape. Inside a CTA
-// three roles run concurrently and meet only at mbarriers:
+// CTA, so every SM gets the same number of weight bytes whatever the matrix shape (with fewer tiles
+// than SMs the ranges are aligned to tiles). Inside a CTA four roles run concurrently and meet only
+// at mbarriers:
 //   * warp 17, one thread: requests each raw stage (128 rows x 256 columns of quantised bytes, as
 //     stored) as one 2-D TMA box into a ring; rows past the end of the matrix arrive as zeros.
-//   * warps 0-15: turn a raw half-stage (128 columns) into the A operand -- weights rounded once
-//     to fp16 (Q4_0 / Q8_0: integer code times the block's fp16 scale in half2 arithmetic, which is
+//   * warp 18, one thread: requests the B operand of every stage, NT rows of the activations' hi part
+//     and NT rows of their lo part (x = hi + lo, both fp16: 22 significant bits; written by the
+//     kernels that produce the activations) as swizzled TMA boxes, stacked along N so that one MMA
+//     covers both. Entry points without such a buffer convert fp32 activations in warps 0-15.
+//   * warps 0-15: turn raw half-stages (128 columns) into the A operand -- weights rounded once to
+//     fp16 (Q4_0 / Q8_0: integer code times the block's fp16 scale in half2 arithmetic, which is
 //     exactly the fp16 rounding of the reference's fp32 product; Q4_K: (d*sc)*q - dmin*m in fp32
-//     with the last two steps fused, then rounded) stored K-major with the 128-byte swizzle -- and the
-//     B operand: activations split as x = hi + lo with hi, lo fp16 (22 significant bits). The only
-//     rounding left is the fp16 rounding of the weights (rel-L2 ~3e-4 per product, inside the 1e-3
-//     bar; the reference's own tensor-core prefill feeds single fp16 operands).
-//   * warp 16, one thread: issues tcgen05.mma (M=128, N=NT, K=16) for hi and lo into the tensor-
-//     memory accumulator and commits to the barriers that free the operand stage / publish the
-//     finished accumulator.
+//     with the last two steps fused, then rounded) -- and store it into tensor memory with
+//     tcgen05.st (lane = weight row, 64 columns per stage). Two groups of eight warps take alternate
+//     stages, one 64-column unit per thread. The only rounding left is the fp16 rounding of the
+//     weights (rel-L2 ~3e-4 per product, inside the 1e-3 bar; the reference's own tensor-core
+//     prefill feeds single fp16 operands).
+//   * warp 16, one thread: issues tcgen05.mma (M=128, N=2*NT, K=16; A from tensor memory, B from
+//     shared memory) into the tensor-memory accumulator and commits to the barriers that free the
+//     operand stage / publish the finished accumulator.
 //   Warps 0-15 also run the epilogue (tcgen05.ld). A CTA whose range covers a whole output tile
 //   writes it; where a range ends inside a tile the partial goes to a per-CTA slot and the CTA
 //   that arrives last at the tile's counter adds the partials in CTA order (the result does not
@@ -97,18 +103,8 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]; fp16 operands, fp32 accumulate.
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same with the A operand in tensor memory: lane = row, one 32-bit column = two consecutive K
-// elements (even K in the low half); eight columns per K = 16 step.
+// D[tmem] (+)= A * B; fp16 operands, fp32 accumulate, A in tensor memory: lane = row, one 32-bit column =
+// two consecutive K elements (even K in the low half), eight columns per K = 16 step; B in shared memory.
 __device__ __forceinline__ void umma_f16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                                 uint32_t accumulate) {
     asm volatile(
