@@ -66,6 +66,9 @@ def parse_args():
     ap.add_argument("--profile-matmul", default="",
                     help="ROWSxCOLSxN: launch the standalone product on three copies of one matrix --steps times and "
                          "exit: the small case ncu captures of the tensor-core kernel are taken on")
+    ap.add_argument("--also-batch", type=int, default=32,
+                    help="after the B=1 measurement on one GPU, also time this many sequences decoded together "
+                         "(the metric names B=1 and B=32) and report it under \"batched\"; 0 skips it")
     ap.add_argument("--sweep", action="store_true",
                     help="standalone quantised mat-vec / mat-mat sweep (formats x shapes x N): one JSON line per case")
     ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
@@ -192,6 +195,38 @@ def run_sweep(jl, args):
             for m in mats:
                 m.close()
     return 0
+
+
+def batched_leg(jl, dev, kv, cfg, tensors, cr, ci, args):
+    """The same model with `--also-batch` sequences decoded together (tensor-core path): prompts of the
+    same length, token feedback on the device, CUDA events around the timed steps."""
+    import numpy as np
+    Bn, P, K = args.also_batch, args.prompt, max(8, min(args.steps, 64))
+    kv.close()
+    model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=Bn)  # replaces the B=1 model on this context
+    bps = cfg.contextLength // 16
+    need = (P + K + 3 + 64 + 15) // 16
+    store = model.createKvStorage(jl.KvStorageRequest(Bn * need, bps, Bn, 16, cfg.numberOfLayers, cfg.kvDim))
+    table = np.full(Bn * bps, jl.UNMAPPED, dtype=np.int32)
+    for b in range(Bn):
+        table[b * bps:b * bps + need] = np.arange(b * need, (b + 1) * need)
+    store.publishBlockTable(table)
+    ex = jl.B200BatchExecutor(model)
+    prompts = np.random.default_rng(args.seed + 1).integers(0, cfg.vocabularySize, size=(Bn, P))
+    for b in range(Bn):
+        jl.B200InvocationBoundary(model, kvSlot=b, copyLogits=False).prefill(prompts[b, :P - 1], 0)
+    slots, active = list(range(Bn)), [True] * Bn
+    hist = ex.generate(jl.BatchSlots(active, [int(t) for t in prompts[:, P - 1]], [P - 1] * Bn, slots), 3)
+    dev.synchronize()
+    dev.timer_start()
+    ex.generate(jl.BatchSlots(active, [int(t) for t in hist[-1]], [P + 2] * Bn, slots), K)
+    ms = dev.timer_stop()
+    weights_b = model_bytes(cfg, args.format)
+    kv_b = Bn * (P + 2 + K // 2) * cfg.numberOfLayers * cfg.kvDim * 2 * 2
+    peak, _ = measured_peak()
+    store.close()
+    return {"batch": Bn, "value": Bn * K / (ms / 1000.0), "unit": "tok/s", "steps": K, "ms_per_step": ms / K,
+            "frac_of_measured_hbm_peak": (weights_b + kv_b) / (ms / K) / 1e6 / peak, "kernel": "gemm_tc_kernel (tcgen05)"}
 
 
 def cpu_decode_rate(cfg, tensors, budget_s, max_steps, seed):
@@ -435,6 +470,8 @@ def main():
         "kernels": ops,
         "setup": {"synth_and_upload_s": round(t_build, 1), "prefill_tok_s": round(B * (P - 1) / t_prefill, 1)},
     }
+    if rank == 0 and n_gpus == 1 and B == 1 and args.also_batch > 1 and args.arch in ("8b", "8b4", "tiny", "1b"):
+        line["batched"] = batched_leg(jl, dev, kv, cfg, tensors, cr, ci, args)
     if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
         rate, cores, done, dt = cpu_decode_rate(cfg, tensors, args.cpu_seconds, 64, args.seed)
         line["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": cores, "kind": "port",
