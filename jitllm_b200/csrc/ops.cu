@@ -172,16 +172,23 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const float 
     for (int i = kNormBatch * kNormThreads + threadIdx.x; i < n4; i += kNormThreads) emit(i, xr[i]);
 }
 
-__global__ void swiglu_rows_kernel(float *g, const float *u, size_t total, __half *hi, __half *lo) {
+// Four elements per thread per step (row lengths are multiples of 256, so float4 never straddles).
+__global__ void swiglu_rows_kernel(float4 *g, const float4 *u, size_t total4, uint2 *hi, uint2 *lo) {
     const size_t stride = size_t(gridDim.x) * blockDim.x;
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const float v = g[i];
-        const float r = (v / (1.0f + expf(-v))) * u[i];
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total4; i += stride) {
+        const float4 v = g[i], w = u[i];
+        float4 r;
+        r.x = (v.x / (1.0f + expf(-v.x))) * w.x;
+        r.y = (v.y / (1.0f + expf(-v.y))) * w.y;
+        r.z = (v.z / (1.0f + expf(-v.z))) * w.z;
+        r.w = (v.w / (1.0f + expf(-v.w))) * w.w;
         g[i] = r;
         if (hi != nullptr) {
-            const __half h = __float2half_rn(r);
-            hi[i] = h;
-            lo[i] = __float2half_rn(r - __half2float(h));
+            const __half2 h0 = __floats2half2_rn(r.x, r.y), h1 = __floats2half2_rn(r.z, r.w);
+            const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
+            const __half2 l0 = __floats2half2_rn(r.x - b0.x, r.y - b0.y), l1 = __floats2half2_rn(r.z - b1.x, r.w - b1.y);
+            hi[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+            lo[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
         }
     }
 }
@@ -584,9 +591,10 @@ cudaError_t rmsnorm_rows_launch(const float *x, const float *w, float eps, float
 }
 
 cudaError_t swiglu_rows_launch(float *g, const float *u, int hidden, int n, cudaStream_t stream, void *hi, void *lo) {
-    const size_t total = size_t(hidden) * n;
-    const int grid = static_cast<int>((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
-    swiglu_rows_kernel<<<grid, 256, 0, stream>>>(g, u, total, static_cast<__half *>(hi), static_cast<__half *>(lo));
+    const size_t total4 = size_t(hidden) * n / 4;
+    const int grid = static_cast<int>((total4 + 255) / 256 < 148 * 8 ? (total4 + 255) / 256 : 148 * 8);
+    swiglu_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<float4 *>(g), reinterpret_cast<const float4 *>(u), total4,
+                                                 static_cast<uint2 *>(hi), static_cast<uint2 *>(lo));
     return cudaGetLastError();
 }
 
