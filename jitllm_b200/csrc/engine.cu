@@ -723,7 +723,9 @@ int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y
 // The step for n rows on the tensor-core path (chunked prompt ingestion, wide decode batches):
 // the same operator order as enqueue_step, with every projection one matrix-matrix launch and
 // the element-wise operators as row kernels. Row r uses tokens[r], positions[r], slots[r].
-int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64_t *launches) {
+// own_sequences: every row is a different sequence (a decode batch), so the attention kernel can
+// rotate and append each row's K/V itself; rows of one prompt chunk need all appends done first.
+int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64_t *launches, bool own_sequences) {
     const jl_model_desc &d = ctx->desc;
     const int dim = d.dim, kv_dim = ctx->kv_dim;
     const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
@@ -750,9 +752,10 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
                     if ((rc = launch_gemm(ctx, *ws[i], ctx->xb, n, ys[i], nullptr, launches))) return rc;
             }
         }
-        JL_LAUNCH(ctx, kv_append_launch(ctx->k, ctx->v, ctx->rope_cos, ctx->rope_sin, ctx->d_positions, ctx->d_slots,
-                                        ctx->d_active, kvg, l, d.head_dim, n, ctx->stream),
-                  "kv append");
+        if (!own_sequences)
+            JL_LAUNCH(ctx, kv_append_launch(ctx->k, ctx->v, ctx->rope_cos, ctx->rope_sin, ctx->d_positions, ctx->d_slots,
+                                            ctx->d_active, kvg, l, d.head_dim, n, ctx->stream),
+                      "kv append");
         {
             AttnArgs a = {};
             a.q = ctx->q;
@@ -771,7 +774,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             a.head_dim = d.head_dim;
             a.dim = ctx->l_qdim;
             a.nsplit = attn_splits_for_width(ctx, n);
-            a.append = 0;
+            a.append = own_sequences ? 1 : 0;
             a.partial = ctx->att_partial;
             a.counters = ctx->att_count;
             JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, false), "attention");
@@ -979,7 +982,7 @@ int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     static const bool tp_graph = env_flag("JITLLM_B200_TP_GRAPH", true);
     const bool eager = !ctx->use_graph || (ctx->tp_size > 1 && (!tp_graph || ctx->tp_warm.insert(key).second));
     if (eager) {
-        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, advance, &launches)
+        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, advance, &launches, true)
                            : enqueue_step(ctx, width, with_logits, advance, &launches);
         ctx->counters.kernel_launches += launches;
         return rc;
@@ -988,7 +991,7 @@ int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     if (it == ctx->graphs.end()) {
         cudaGraph_t graph = nullptr;
         JL_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, advance, &launches)
+        int rc = rows_path ? enqueue_rows_step(ctx, width, with_logits, advance, &launches, true)
                            : enqueue_step(ctx, width, with_logits, advance, &launches);
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
         if (rc) {
@@ -1589,7 +1592,7 @@ int32_t jl_prefill(jl_ctx *ctx, int32_t kv_slot, const int32_t *tokens, int32_t 
             rc = run_step(ctx, 1, false, false);
         } else {
             uint64_t launches = 0;
-            rc = enqueue_rows_step(ctx, chunk, false, false, &launches);
+            rc = enqueue_rows_step(ctx, chunk, false, false, &launches, false);
             ctx->counters.kernel_launches += launches;
         }
         if (rc) return rc;
