@@ -167,12 +167,15 @@ int32_t jl_timer_stop(jl_ctx *ctx, float *elapsed_ms);
  * output projection, 2 = RMSNorm+gate/up+SwiGLU, 3 = down projection, 4 = RMSNorm+vocabulary.
  * The measuring counterpart of backend/tornado/bench/SyntheticKernelBench.java:87-161. */
 int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters);
-/* Per-operator phase timing of the persistent single-sequence kernel (no counterpart in the
- * reference; its closest relative is the TornadoVM profiler seam, backend/tornado/
- * TornadoMetricsReporter.java:52-64). Call with out == NULL to arm (returns the operator count);
- * after the next step call with a buffer of 5 * max_ops words to read CTA 0's nanosecond stamps:
- * start, activation staged, items consumed, results written, barrier passed. */
-int32_t jl_debug_token_profile(jl_ctx *ctx, uint64_t *out, int32_t max_ops);
+/* Launch timeline of the kernels this context enqueues (no counterpart in the reference; its
+ * closest relative is the TornadoVM profiler seam, backend/tornado/TornadoMetricsReporter.java:52-64).
+ * Only the trace build of the library (compiled with -DJL_TRACE) records anything; the default build
+ * returns JL_ERR_UNSUPPORTED. Call with out == NULL to arm and clear the buffer (returns its capacity
+ * in records); after some steps call with room for 8 * max_records words: every launch leaves one
+ * record written by its first CTA -- kernel id, then nanosecond stamps (entry, grid dependency
+ * resolved, inputs staged, main loop done, exit) and two kernel-specific words. Returns the number
+ * of records copied. */
+int32_t jl_debug_trace(jl_ctx *ctx, uint64_t *out, int32_t max_records);
 int32_t jl_get_counters(jl_ctx *ctx, jl_counters *out);
 /* Overwrites a 256 MiB scratch buffer (larger than L2) so that the next kernel starts cold. */
 int32_t jl_flush_l2(jl_ctx *ctx);

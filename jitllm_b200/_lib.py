@@ -6,7 +6,10 @@ import ctypes as C
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "lib" / "libjitllm_b200.so"
+import os
+
+# JITLLM_B200_TRACE=1 selects the build with launch-timeline stamps (python -m jitllm_b200.build --trace).
+LIB_PATH = PKG / "lib" / ("libjitllm_b200_trace.so" if os.environ.get("JITLLM_B200_TRACE") == "1" else "libjitllm_b200.so")
 SYNTH_PATH = PKG / "lib" / "libjl_synth.so"
 
 
@@ -62,7 +65,7 @@ SIGNATURES = {
     "jl_stream": (_P, [_P]),
     "jl_timer_start": (_I32, [_P]),
     "jl_timer_stop": (_I32, [_P, C.POINTER(C.c_float)]),
-    "jl_debug_token_profile": (_I32, [_P, _P, _I32]),
+    "jl_debug_trace": (_I32, [_P, _P, _I32]),
     "jl_bench_op": (_I32, [_P, _I32, _I32, _I32]),
     "jl_get_counters": (_I32, [_P, C.POINTER(JlCounters)]),
     "jl_flush_l2": (_I32, [_P]),

@@ -20,12 +20,11 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib"
 
-CUDA_SOURCES = ["gemv.cu", "token_kernel.cu", "ops.cu", "engine.cu", "static_entry.cu", "gemm_tc.cu", "tp_exchange.cu", "gguf_loader.cu"]
+CUDA_SOURCES = ["gemv.cu", "ops.cu", "engine.cu", "static_entry.cu", "gemm_tc.cu", "tp_exchange.cu", "gguf_loader.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
-    "-shared",
 ]
 HOST_CC = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
 HOST_CFLAGS = ["-O2", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared", "-std=c11", "-Wall"]
@@ -57,18 +56,31 @@ def _run(cmd: list[str], verbose: bool) -> None:
         sys.stderr.write(proc.stderr)
 
 
-def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
+def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = False, trace: bool = False) -> Path:
+    """Compiles every .cu file to its own object (in parallel) and links the shared library.
+
+    trace=True builds ``libjitllm_b200_trace.so`` with -DJL_TRACE: the same kernels plus nanosecond
+    stamps that ``jl_debug_trace`` reads back; the default library carries none of that code."""
     LIB.mkdir(exist_ok=True)
-    target = LIB / "libjitllm_b200.so"
-    deps = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [
-        PKG.parent / "include" / "jitllm_b200.h"
-    ]
-    if force or _stale(target, deps):
-        cmd = [_nvcc(), *NVCC_FLAGS]
-        if ptxas_info:
-            cmd += ["-Xptxas", "-v"]
-        cmd += ["-o", str(target), *[str(CSRC / s) for s in CUDA_SOURCES]]
-        _run(cmd, verbose or ptxas_info)
+    objdir = PKG / "build" / ("trace" if trace else "release")
+    objdir.mkdir(parents=True, exist_ok=True)
+    target = LIB / ("libjitllm_b200_trace.so" if trace else "libjitllm_b200.so")
+    headers = sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "jitllm_b200.h", Path(__file__)]
+    flags = list(NVCC_FLAGS) + (["-DJL_TRACE"] if trace else [])
+    if ptxas_info:
+        flags += ["-Xptxas", "-v"]
+    jobs = []
+    for src in CUDA_SOURCES:
+        obj = objdir / (src[:-3] + ".o")
+        if force or ptxas_info or _stale(obj, [CSRC / src, *headers]):
+            jobs.append([_nvcc(), *flags, "-c", "-o", str(obj), str(CSRC / src)])
+    if jobs:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
+            list(pool.map(lambda c: _run(c, verbose or ptxas_info), jobs))
+    objs = [objdir / (s[:-3] + ".o") for s in CUDA_SOURCES]
+    if jobs or _stale(target, objs):
+        _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", str(target), *[str(o) for o in objs]], verbose)
     return target
 
 
@@ -87,6 +99,9 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv, verbose=True)
     if "--ptxas" in sys.argv:
         build_cuda(force=True, ptxas_info=True)
+    elif "--trace" in sys.argv:
+        build_cuda(force="--force" in sys.argv, verbose=True, trace=True)
+    else:
+        build_all(force="--force" in sys.argv, verbose=True)

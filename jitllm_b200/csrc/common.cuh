@@ -152,6 +152,65 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// ---- launch-timeline stamps (trace build only) ---------------------------------------------------
+// With -DJL_TRACE the first CTA of every launch claims a record in a device buffer and stamps it
+// with %globaltimer at a few points; without it these are empty inline functions, so the default
+// library carries no tracing code at all. Each translation unit has its own copy of the buffer
+// pointer, bound from the host by JL_TRACE_DEFINE_BIND's function.
+constexpr int kTraceWords = 8;  // kernel id, five stamps, two free words
+enum : int { kTraceGemv = 1, kTraceAttn = 2, kTraceEmbed = 3, kTraceAdvance = 4, kTraceGemm = 5, kTraceRows = 6,
+             kTraceExchange = 7 };
+#ifdef JL_TRACE
+static __device__ unsigned long long *g_trace_buf;
+static __device__ unsigned g_trace_cap;
+static __device__ int g_trace_mode;  // experiment switches of the trace build (0 = none)
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Thread 0 of CTA (0,0,0) claims the next record; every other thread gets -1.
+__device__ __forceinline__ int trace_begin(int kernel_id) {
+    if (threadIdx.x != 0 || blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0 || g_trace_buf == nullptr) return -1;
+    const unsigned slot = static_cast<unsigned>(atomicAdd(g_trace_buf, 1ull));
+    if (slot >= g_trace_cap) return -1;
+    unsigned long long *r = g_trace_buf + kTraceWords * (1 + size_t(slot));
+    r[0] = static_cast<unsigned long long>(kernel_id);
+    r[1] = trace_now();
+    return static_cast<int>(slot);
+}
+__device__ __forceinline__ void trace_mark(int slot, int word) {
+    if (slot >= 0) g_trace_buf[kTraceWords * (1 + size_t(slot)) + word] = trace_now();
+}
+__device__ __forceinline__ void trace_word(int slot, int word, unsigned long long v) {
+    if (slot >= 0) g_trace_buf[kTraceWords * (1 + size_t(slot)) + word] = v;
+}
+// Every CTA calls this from one thread when it is done: word 1 of the header keeps the latest exit
+// of any CTA so far, which the next kernel reads once its grid dependency is resolved.
+__device__ __forceinline__ void trace_cta_exit() {
+    if (g_trace_buf != nullptr) atomicMax(g_trace_buf + 1, trace_now());
+}
+__device__ __forceinline__ unsigned long long trace_latest_exit() {
+    return g_trace_buf != nullptr ? __ldcg(g_trace_buf + 1) : 0ull;
+}
+#define JL_TRACE_DEFINE_BIND(fn)                                                              \
+    cudaError_t fn(unsigned long long *buf, unsigned cap, int mode) {                        \
+        cudaError_t e_ = cudaMemcpyToSymbol(g_trace_buf, &buf, sizeof buf);                   \
+        if (e_ == cudaSuccess) e_ = cudaMemcpyToSymbol(g_trace_mode, &mode, sizeof mode);     \
+        return e_ != cudaSuccess ? e_ : cudaMemcpyToSymbol(g_trace_cap, &cap, sizeof cap);    \
+    }
+#define JL_TRACE_MODE(bit) ((g_trace_mode & (bit)) != 0)
+#else
+__device__ __forceinline__ int trace_begin(int) { return -1; }
+__device__ __forceinline__ void trace_mark(int, int) {}
+__device__ __forceinline__ void trace_word(int, int, unsigned long long) {}
+__device__ __forceinline__ void trace_cta_exit() {}
+__device__ __forceinline__ unsigned long long trace_latest_exit() { return 0ull; }
+#define JL_TRACE_DEFINE_BIND(fn) \
+    cudaError_t fn(unsigned long long *, unsigned, int) { return cudaSuccess; }
+#define JL_TRACE_MODE(bit) false
+#endif
+
 // ---- arithmetic helpers -----------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -16,7 +16,6 @@
 
 #include "gemv.cuh"
 #include "ops.cuh"
-#include "token_kernel.cuh"
 #include "gemm_tc.cuh"
 #include "tp_exchange.cuh"
 
@@ -112,14 +111,8 @@ struct jl_ctx {
     int row_cap = 1;        // rows the step buffers hold: max(max_batch, prefill chunk)
     float *hb2 = nullptr;   // second FFN buffer of the matrix-matrix path (up projection)
     int32_t *d_history = nullptr, *d_step = nullptr;
-    // persistent per-token kernel (single-sequence steps)
-    bool use_token_kernel = false, tok_ok = false;
-    int tok_type = -1;
-    TokLayer *d_layers = nullptr;
-    float *tok_partial = nullptr;
-    unsigned *d_barrier = nullptr;
-    unsigned long long *d_profile = nullptr;
     size_t history_cap = 0;
+    unsigned long long *d_trace = nullptr;  // launch-timeline records (trace build only)
     // pinned host staging: tokens | positions | slots | out | active | status
     int32_t *h_stage = nullptr;
 
@@ -331,15 +324,6 @@ void free_model(jl_ctx *ctx) {
     ctx->tp_ctr = nullptr;
     ctx->tp_push = false;
     ctx->tp_warm.clear();
-    if (ctx->d_layers) cudaFree(ctx->d_layers);
-    ctx->d_layers = nullptr;
-    if (ctx->tok_partial) cudaFree(ctx->tok_partial);
-    if (ctx->d_barrier) cudaFree(ctx->d_barrier);
-    if (ctx->d_profile) cudaFree(ctx->d_profile);
-    ctx->d_profile = nullptr;
-    ctx->tok_partial = nullptr;
-    ctx->d_barrier = nullptr;
-    ctx->tok_ok = false;
     if (ctx->d_history) cudaFree(ctx->d_history);
     if (ctx->d_step) cudaFree(ctx->d_step);
     ctx->d_history = ctx->d_step = nullptr;
@@ -382,109 +366,12 @@ int launch_gemv(jl_ctx *ctx, GemvArgs &a, int total_rows, uint64_t *launches) {
         return fail(ctx, JL_ERR_UNSUPPORTED, "no launch plan for type %d with %d columns", a.type,
                     a.cols);
     a.status = ctx->d_status;
-    static const int dbg = [] { const char *v = getenv("JITLLM_B200_GEMV_DEBUG"); return v ? atoi(v) : 0; }();
-    a.debug = dbg;
     cudaError_t e = gemv_launch(a, plan, ctx->stream, ctx->use_pdl);
     if (e != cudaSuccess)
         return fail(ctx, JL_ERR_CUDA, "matrix-vector launch failed: %s", cudaGetErrorString(e));
     ++*launches;
     return JL_OK;
 }
-
-// Prepares the persistent per-token kernel: layer pointer table, split scratch, barrier word.
-int build_token_ops(jl_ctx *ctx) {
-    const jl_model_desc &d = ctx->desc;
-    ctx->tok_ok = false;
-    if (!ctx->use_token_kernel || ctx->tp_size > 1) return JL_OK;
-    const int type = ctx->layer[JL_ROLE_ATTENTION_QUERY][0].type;
-    for (int l = 0; l < d.layers; ++l)
-        for (int r : {JL_ROLE_ATTENTION_QUERY, JL_ROLE_ATTENTION_OUTPUT, JL_ROLE_FFN_GATE, JL_ROLE_FFN_DOWN})
-            if (ctx->layer[r][l].type != type) return JL_OK;
-    if (wcls_of(ctx).type != type) return JL_OK;
-    if (!token_kernel_supported(type, d.head_dim, d.heads / d.kv_heads, d.dim, d.hidden, ctx->kv_dim,
-                                d.vocab, d.heads, d.kv_heads, d.layers, ctx->sm_count))
-        return JL_OK;
-    std::vector<TokLayer> table(d.layers);
-    for (int l = 0; l < d.layers; ++l) {
-        TokLayer &t = table[l];
-        t.wq = ctx->layer[JL_ROLE_ATTENTION_QUERY][l].data;
-        t.wk = ctx->layer[JL_ROLE_ATTENTION_KEY][l].data;
-        t.wv = ctx->layer[JL_ROLE_ATTENTION_VALUE][l].data;
-        t.wo = ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l].data;
-        t.w1 = ctx->layer[JL_ROLE_FFN_GATE][l].data;
-        t.w3 = ctx->layer[JL_ROLE_FFN_UP][l].data;
-        t.w2 = ctx->layer[JL_ROLE_FFN_DOWN][l].data;
-        t.attn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
-        t.ffn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
-    }
-    int rc;
-    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_layers), table.size() * sizeof(TokLayer))))
-        return rc;
-    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_layers, table.data(), table.size() * sizeof(TokLayer),
-                                 cudaMemcpyHostToDevice, ctx->stream));
-    const int max_splits = ctx->sm_count / d.kv_heads;
-    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->tok_partial),
-                        size_t(d.heads) * max_splits * (d.head_dim + 2) * 4)))
-        return rc;
-    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_barrier), 4))) return rc;
-    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    ctx->tok_type = type;
-    ctx->tok_ok = true;
-    return JL_OK;
-}
-
-// One single-sequence step through the persistent kernel.
-int launch_token_kernel(jl_ctx *ctx, bool with_logits, bool advance) {
-    const jl_model_desc &d = ctx->desc;
-    TokArgs a = {};
-    a.layers = ctx->d_layers;
-    a.n_layers = d.layers;
-    a.with_logits = with_logits ? 1 : 0;
-    a.dim = d.dim;
-    a.hidden = d.hidden;
-    a.kv_dim = ctx->kv_dim;
-    a.vocab = d.vocab;
-    a.eps = d.rms_eps;
-    a.emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING].data;
-    a.emb_type = ctx->global[JL_ROLE_TOKEN_EMBEDDING].type;
-    a.wcls = wcls_of(ctx).data;
-    a.out_norm = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
-    a.tokens = ctx->d_tokens;
-    a.positions = ctx->d_positions;
-    a.slots = ctx->d_slots;
-    a.out_token = ctx->d_out;
-    a.history = ctx->d_history;
-    a.step_counter = ctx->d_step;
-    a.advance = advance ? 1 : 0;
-    a.x = ctx->x;
-    a.q = ctx->q;
-    a.k = ctx->k;
-    a.v = ctx->v;
-    a.xb = ctx->xb;
-    a.hb = ctx->hb;
-    a.logits = ctx->logits;
-    a.kv = {ctx->kpool, ctx->vpool, ctx->block_table, ctx->blocks_per_slot, ctx->block_tokens, d.layers,
-            ctx->kv_dim};
-    a.rope_cos = ctx->rope_cos;
-    a.rope_sin = ctx->rope_sin;
-    a.heads = d.heads;
-    a.kv_heads = d.kv_heads;
-    a.partial = ctx->tok_partial;
-    a.max_splits = ctx->sm_count / d.kv_heads;
-    a.amax_val = ctx->amax_val;
-    a.amax_idx = ctx->amax_idx;
-    a.barrier = ctx->d_barrier;
-    a.status = ctx->d_status;
-    a.profile = ctx->d_profile;
-    JL_CUDA(ctx, cudaMemsetAsync(ctx->d_barrier, 0, 4, ctx->stream));
-    cudaError_t e = token_kernel_launch(ctx->tok_type, d.head_dim, d.heads / d.kv_heads, a, ctx->sm_count,
-                                        ctx->stream);
-    if (e != cudaSuccess)
-        return fail(ctx, JL_ERR_CUDA, "per-token kernel launch failed: %s", cudaGetErrorString(e));
-    ctx->counters.kernel_launches += 1;
-    return JL_OK;
-}
-
 
 // Sets up the peer-memory exchange: allocates this GPU's inbox, trades addresses with the other
 // ranks (an IPC handle between processes, the plain pointer inside one process) over the NCCL group
@@ -971,7 +858,6 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
 
 // Runs one step: replays the captured graph for this width, capturing it on first use.
 int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
-    if (width == 1 && ctx->tok_ok) return launch_token_kernel(ctx, with_logits, advance);
     static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 4; }();
     const bool rows_path = width >= rows_min;
     const int key = width * 8 + (with_logits ? 1 : 0) + (advance ? 2 : 0) + (rows_path ? 4 : 0);
@@ -1054,7 +940,6 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->use_graph = env_flag("JITLLM_B200_GRAPH", true);
     ctx->use_pdl = env_flag("JITLLM_B200_PDL", true);
-    ctx->use_token_kernel = env_flag("JITLLM_B200_TOKEN_KERNEL", false);
     e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev0);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev1);
@@ -1062,7 +947,6 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->tev1);
     if (e == cudaSuccess) e = gemv_configure();
     if (e == cudaSuccess) e = attention_configure();
-    if (e == cudaSuccess) e = token_kernel_configure();
     if (e == cudaSuccess) e = gemm_tc_configure();
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->d_status), sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
@@ -1360,7 +1244,6 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     JL_CUDA(ctx, cudaMallocHost(reinterpret_cast<void **>(&ctx->h_stage), (5 * R + 1) * 4));
     JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     ctx->counters.workspace_bytes = ws;
-    if ((rc = build_token_ops(ctx))) return rc;
     ctx->finalized = true;
     return JL_OK;
 }
@@ -1681,24 +1564,38 @@ int32_t jl_generate(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int
     return JL_OK;
 }
 
-int32_t jl_debug_token_profile(jl_ctx *ctx, uint64_t *out, int32_t max_ops) {
+int32_t jl_debug_trace(jl_ctx *ctx, uint64_t *out, int32_t max_records) {
     if (!ctx) return JL_ERR_INVALID;
-    JL_REQUIRE(ctx, ctx->finalized && ctx->tok_ok, JL_ERR_STATE, "the per-token kernel is not in use");
+#ifndef JL_TRACE
+    (void)out;
+    (void)max_records;
+    return fail(ctx, JL_ERR_UNSUPPORTED, "this build of the library records no launch timeline (build with --trace)");
+#else
+    constexpr unsigned kCap = 16384;
     cudaSetDevice(ctx->device);
-    const int n = token_kernel_op_count(ctx->desc.layers);
-    if (!out) {  // arm: later steps record stamps
-        if (!ctx->d_profile) {
-            int rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_profile), size_t(n) * 5 * 8);
+    if (!out) {  // arm: later launches record stamps
+        if (!ctx->d_trace) {
+            int rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_trace), size_t(kCap + 1) * kTraceWords * 8);
             if (rc) return rc;
+            ctx->user_allocs.push_back(ctx->d_trace);  // released with the context
+            const char *mv = getenv("JITLLM_B200_TRACE_MODE");
+            const int mode = mv ? atoi(mv) : 0;
+            JL_CUDA(ctx, gemv_trace_bind(ctx->d_trace, kCap, mode));
+            JL_CUDA(ctx, ops_trace_bind(ctx->d_trace, kCap, mode));
         }
-        JL_CUDA(ctx, cudaMemsetAsync(ctx->d_profile, 0, size_t(n) * 5 * 8, ctx->stream));
-        return n;
+        JL_CUDA(ctx, cudaMemsetAsync(ctx->d_trace, 0, size_t(kCap + 1) * kTraceWords * 8, ctx->stream));
+        JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        return int32_t(kCap);
     }
-    JL_REQUIRE(ctx, ctx->d_profile != nullptr, JL_ERR_STATE, "profiling was not armed");
-    const int m = max_ops < n ? max_ops : n;
-    JL_CUDA(ctx, cudaMemcpyAsync(out, ctx->d_profile, size_t(m) * 5 * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_REQUIRE(ctx, ctx->d_trace != nullptr, JL_ERR_STATE, "the trace was not armed");
+    unsigned long long n = 0;
     JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return m;
+    JL_CUDA(ctx, cudaMemcpy(&n, ctx->d_trace, 8, cudaMemcpyDeviceToHost));
+    if (n > kCap) n = kCap;
+    if (n > (unsigned long long)max_records) n = max_records;
+    JL_CUDA(ctx, cudaMemcpy(out, ctx->d_trace + kTraceWords, size_t(n) * kTraceWords * 8, cudaMemcpyDeviceToHost));
+    return int32_t(n);
+#endif
 }
 
 int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters) {

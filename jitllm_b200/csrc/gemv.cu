@@ -6,19 +6,23 @@
 // gate/up pair (:255-260) or the greedy argmax (inference/Logits.java:49-60) folded in.
 //
 // How: the kernel is HBM-bound, so the design goal is "every weight byte crosses HBM once, in
-// large aligned bursts, with few issue slots spent per weight":
-//   * weights: each warp owns a ring of shared-memory stages that one lane fills with 1-D bulk
-//     async copies (cp.async.bulk, the TMA engine) completing on an mbarrier; a stage holds the
-//     same 2048-column chunk of R consecutive rows. No registers are tied up by loads in flight.
-//   * activations: quantised once per CTA into three signed 7-bit digits per element
-//     (x ~ s_blk * (a1*2^14 + a2*2^7 + a3), error <= 2^-21 of the block maximum, i.e. at the
-//     level of fp32 rounding itself) so that the inner product of 4 weights is 3 dp4a
-//     instructions on the packed integer weights instead of 4 unpack + 4 convert + 4 FMA.
-//     Integer sums are exact; block results are scaled and accumulated in fp32.
-//   * a lane works on a 64-element unit (a Q4_K nibble pair of sub-blocks, or two Q4_0 / Q8_0
-//     blocks) and keeps its activation digits in registers across the R rows of the tile.
-//   * the kernel prefetches its first stages before griddepcontrol.wait, so under programmatic
-//     dependent launch the weight stream of kernel N+1 starts while kernel N drains.
+// large aligned bursts, with few issue slots spent per weight, and as little fixed time per launch
+// as possible":
+//   * one CTA per SM: 16 consumer warps and one producer warp. The producer warp does nothing but
+//     issue 1-D bulk async copies (cp.async.bulk, the TMA engine) of weight rows into per-warp
+//     rings of shared-memory stages, completing on mbarriers; consumers hand stages back through a
+//     second set of mbarriers. The producer starts before the grid dependency is resolved, so under
+//     programmatic dependent launch the weight stream runs while the previous kernel drains.
+//   * activations: quantised once per CTA into two signed 8-bit digits per element with one scale
+//     per 32 elements (16-bit fixed point per block), so the inner product of 4 weights is
+//     2 dp4a instructions on the packed integer weights. Integer sums are exact; block results are
+//     scaled and accumulated in fp32.
+//   * a consumer warp owns one 2048-column chunk of the activation (a lane: 64 elements, in
+//     registers for the whole launch) and walks the rows of its group; the warps that hold the
+//     other chunks of the same rows leave their partial sums in shared memory and one thread per
+//     row adds them in chunk order, applies the RMS factor, residual, SwiGLU or arg-max and stores.
+//     Every sum has a fixed order: results do not vary from run to run.
+//   * a CTA's rows are one contiguous range, so its output is written in one coalesced burst.
 #include "gemv_core.cuh"
 
 #include <climits>
@@ -26,220 +30,376 @@
 
 namespace jl {
 
+JL_TRACE_DEFINE_BIND(gemv_trace_bind)
+
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = kThreads / 32;
-constexpr int kMaxStages = 16;
-constexpr int kHeaderBytes = 2176;  // mbarriers (16 warps x 16 stages x 8 B) + 128 B scratch
-struct SmemLayout {
-    uint64_t *bars;
-    float *scratch;  // 32 floats
-    float *sx, *sumx;
-    uint8_t *limbs;
-    uint8_t *ring;
-};
+constexpr int kThreads = kGemvThreads;
+constexpr int kWarps = kGemvConsumerWarps;
+constexpr int kConsumers = kWarps * 32;
+constexpr int kBarBytes = 2 * kWarps * kGemvMaxStages * 8;  // full + empty barriers
+constexpr int kScratchFloats = 64;                          // RMS partials, RMS factor, arg-max fold
+constexpr int kHeaderBytes = kBarBytes + kScratchFloats * 4;
+constexpr int kPartialFloatsMax = 4096;
+constexpr int kBarConsumers = 1;
 
-__device__ __forceinline__ SmemLayout carve(uint8_t *smem, int cols) {
-    SmemLayout l;
-    l.bars = reinterpret_cast<uint64_t *>(smem);
-    l.scratch = reinterpret_cast<float *>(smem + 2048);
-    l.sx = reinterpret_cast<float *>(smem + kHeaderBytes);
-    l.sumx = l.sx + cols / 32;
-    l.limbs = smem + kHeaderBytes + align_up(size_t(cols) / 32 * 8, 128);
-    l.ring = smem + kHeaderBytes + x_region_bytes(cols);
-    return l;
+__device__ __forceinline__ void mbar_arrive_u32(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test_wait_u32(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_u32(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 16)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
 }
 
-__device__ void stage_activation(const GemvArgs &a, const SmemLayout &sm) {
-    stage_activation_core<kThreads>(a.x, a.norm_w, a.eps, a.cols, sm.scratch, sm.sx, sm.sumx,
-                                    smem_u32(sm.limbs));
+// Which matrix and row a job of a plain launch is: jobs number the rows of the segments one
+// after another.
+__device__ __forceinline__ void locate(const GemvArgs &a, int job, int &seg, int &row) {
+    seg = 0;
+    row = job;
+    if (row >= a.seg[0].rows) {
+        row -= a.seg[0].rows;
+        seg = 1;
+        if (a.nseg > 2 && row >= a.seg[1].rows) {
+            row -= a.seg[1].rows;
+            seg = 2;
+        }
+    }
 }
 
-template <int TYPE, int R, int MODE>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, const int stages) {
+// One step of a group's walk over its jobs [0, nj): the rows the next stage holds. They are
+// consecutive rows of one matrix (one contiguous piece of memory, one bulk copy), at most S of
+// them, and never straddle the end of a matrix or of a phase. The producer and the consumers of a
+// group call this with the same arguments and so agree on every stage.
+template <int MODE, int S>
+__device__ __forceinline__ int stage_rows_at(const GemvArgs &a, int first_job, int k, int nj, int PJ, int &seg,
+                                             int &row) {
+    int n = min(S, nj - k);
+    n = min(n, (k / PJ + 1) * PJ - k);
+    if (MODE == kGemvGateUp) {
+        seg = 0;
+        row = first_job + k;
+    } else {
+        locate(a, first_job + k, seg, row);
+        n = min(n, a.seg[seg].rows - row);
+    }
+    return n;
+}
+
+template <int TYPE, int MODE>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, const GemvPlan pl) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int NR = (MODE == kGemvGateUp) ? 2 * R : R;
     constexpr int CB = Fmt<TYPE>::chunk_bytes;
     constexpr int UB = Fmt<TYPE>::unit_bytes;
+    constexpr int S = Fmt<TYPE>::streams;               // rows per stage
+    constexpr int SPJ = (MODE == kGemvGateUp) ? 2 : 1;  // row streams per job
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nunits = a.cols / 64;
-    const int nchunks = (nunits + 31) / 32;
-    const size_t rowb = size_t(a.cols) / 64 * UB;
+    const int trace = trace_begin(kTraceGemv);
     if (a.active != nullptr && *a.active == 0) {
         // Still wait: a grid that finished without waiting would let its successor run ahead of
         // the grid before this one.
         pdl_wait();
         return;
     }
-    const SmemLayout sm = carve(smem, a.cols);
-    const int stage_bytes = NR * CB;
-    uint8_t *my_ring = sm.ring + size_t(warp) * stages * stage_bytes;
-    uint64_t *my_bars = sm.bars + warp * kMaxStages;
-    const uint32_t ring_u32 = smem_u32(my_ring);
-    const uint32_t limbs_u32 = smem_u32(sm.limbs), sx_u32 = smem_u32(sm.sx), sumx_u32 = smem_u32(sm.sumx);
+    const int nunits = a.cols / 64;
+    const int nchunks = pl.nchunks, G = pl.groups, D = pl.stages, PJ = pl.phase_jobs;
+    const uint32_t rowb = uint32_t(nunits) * UB;
+    const uint32_t stage_bytes = S * rowb;
+    const int total_jobs = (MODE == kGemvGateUp) ? a.seg[0].rows
+                                                 : a.seg[0].rows + (a.nseg > 1 ? a.seg[1].rows : 0) +
+                                                       (a.nseg > 2 ? a.seg[2].rows : 0);
+    const int job0 = gemv_split(total_jobs, blockIdx.x, gridDim.x);
+    const int njobs = gemv_split(total_jobs, blockIdx.x + 1, gridDim.x) - job0;
 
-    // Tiles of R rows, numbered segment after segment; gate/up tiles pair the same rows.
-    const int nseg_tiled = (MODE == kGemvGateUp) ? 1 : a.nseg;
-    const int t0 = (a.seg[0].rows + R - 1) / R;
-    const int t1 = nseg_tiled > 1 ? (a.seg[1].rows + R - 1) / R : 0;
-    const int t2 = nseg_tiled > 2 ? (a.seg[2].rows + R - 1) / R : 0;
-    const int total_tiles = t0 + t1 + t2;
-    const int total_warps = kWarps * gridDim.x;
-    const int wg = warp * gridDim.x + blockIdx.x;
-    const int n_my = total_tiles > wg ? (total_tiles - wg - 1) / total_warps + 1 : 0;
-    const int n_items = n_my * nchunks;
+    const uint32_t full_u32 = smem_u32(smem);  // [group][stage], then the same for "empty"
+    const uint32_t empty_u32 = full_u32 + kWarps * kGemvMaxStages * 8;
+    float *scratch = reinterpret_cast<float *>(smem + kBarBytes);
+    float *sx = reinterpret_cast<float *>(smem + pl.off_x);
+    float *sumx = sx + a.cols / 32;
+    const uint32_t planes_u32 = smem_u32(smem + pl.off_x) + uint32_t(align_up(size_t(a.cols) / 32 * 8, 128));
+    float *partial = reinterpret_cast<float *>(smem + pl.off_partial);
+    const uint32_t ring_u32 = smem_u32(smem + pl.off_ring);
 
-    auto locate = [&](int tile, int &seg, int &row0) {
-        seg = 0;
-        if (tile >= t0) {
-            tile -= t0;
-            seg = 1;
-            if (tile >= t1) {
-                tile -= t1;
-                seg = 2;
-            }
+    if (tid == 0) {
+        for (int i = 0; i < G * D; ++i) {
+            const int g = i / D, s = i - g * D;
+            mbar_init(reinterpret_cast<uint64_t *>(smem) + g * kGemvMaxStages + s, 1);
+            mbar_init(reinterpret_cast<uint64_t *>(smem) + (kWarps + g) * kGemvMaxStages + s, nchunks);
         }
-        row0 = tile * R;
-    };
-    const uint64_t policy = policy_evict_first();
-    // Producer cursor (lane 0): the next item to request, advanced incrementally; source pointers
-    // move by one chunk per item and are recomputed only when the cursor enters a new tile.
-    int p_tile = wg, p_cc = 0, p_seg = 0, p_row0 = 0, p_issued = 0, p_rows = 0;
-    const uint8_t *p_src0 = nullptr, *p_src1 = nullptr;
-    auto enter_tile = [&]() {
-        locate(p_tile, p_seg, p_row0);
-        p_rows = min(R, a.seg[p_seg].rows - p_row0);
-        p_src0 = a.seg[p_seg].w + size_t(p_row0) * rowb;
-        if (MODE == kGemvGateUp) p_src1 = a.seg[1].w + size_t(p_row0) * rowb;
-    };
-    if (n_items > 0) enter_tile();
-    const uint32_t bars_u32 = smem_u32(my_bars);
-    const uint32_t last_bytes = uint32_t(nunits - (nchunks - 1) * 32) * UB;
-    auto issue = [&](int s) {  // lane 0 only
-        const uint32_t bytes = p_cc == nchunks - 1 ? last_bytes : uint32_t(CB);
-        const uint32_t stage = ring_u32 + uint32_t(s) * stage_bytes;
-        const uint32_t bar = bars_u32 + uint32_t(s) * 8u;
-        mbar_expect_tx_u32(bar, bytes * p_rows * (MODE == kGemvGateUp ? 2 : 1));
-        const uint8_t *src0 = p_src0, *src1 = p_src1;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            if (r < p_rows) {
-                bulk_g2s_hint_u32(stage + r * CB, src0, bytes, bar, policy);
-                if (MODE == kGemvGateUp) bulk_g2s_hint_u32(stage + (R + r) * CB, src1, bytes, bar, policy);
-                src0 += rowb;
-                if (MODE == kGemvGateUp) src1 += rowb;
-            }
-        }
-        ++p_issued;
-        p_src0 += CB;
-        if (MODE == kGemvGateUp) p_src1 += CB;
-        if (++p_cc == nchunks) {
-            p_cc = 0;
-            p_tile += total_warps;
-            if (p_tile < total_tiles) enter_tile();
-        }
-    };
-
-    if (lane == 0) {
-        for (int s = 0; s < stages; ++s) mbar_init(my_bars + s, 1);
         mbar_fence_init();
         fence_proxy_async();
-        const int first = a.debug == 2 ? 0 : min(stages, n_items);
-        for (int it = 0; it < first; ++it) issue(it);
     }
-    __syncwarp();
-
-    // Everything above touches only weights, which no earlier kernel writes.
-    pdl_wait();
-    stage_activation(a, sm);
     __syncthreads();
+    // The next kernel of the chain may be scheduled as soon as SMs free up; whatever it does before
+    // its own griddepcontrol.wait touches weights only.
     pdl_launch_dependents();
 
-    float acc[NR];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+    if (warp == kWarps) {
+        // ---------------------------------------------------------------- producer warp
+        // Lane g feeds the ring of group g: one bulk copy per stage, the stage's rows being one
+        // contiguous piece of the matrix. Nothing here reads what an earlier kernel wrote.
+        if (njobs == 0) return;
+        const int g = lane;
+        int gs = 0, nj = 0;
+        if (g < G) {
+            gs = gemv_split(njobs, g, G);
+            nj = gemv_split(njobs, g + 1, G) - gs;
+        }
+        const uint32_t my_full = full_u32 + uint32_t(g) * kGemvMaxStages * 8;
+        const uint32_t my_empty = empty_u32 + uint32_t(g) * kGemvMaxStages * 8;
+        const uint32_t my_ring = ring_u32 + uint32_t(g) * D * stage_bytes;
+        const uint64_t policy = policy_evict_first();
+        int k = 0, which = 0, slot = 0, use = 0;
+        uint32_t idle = 0;
+        bool failed = false;
+        while (true) {
+            const bool want = k < nj;
+            if (!__any_sync(0xffffffffu, want)) break;
+            bool can = false;
+            if (want) can = use == 0 || mbar_test_wait_u32(my_empty + slot * 8, uint32_t(use - 1) & 1u);
+            if (can) {
+                int seg, row;
+                const int n = stage_rows_at<MODE, S>(a, job0 + gs, k, nj, PJ, seg, row);
+                const uint8_t *src = a.seg[MODE == kGemvGateUp ? which : seg].w + size_t(row) * rowb;
+                fence_proxy_async();
+                mbar_expect_tx_u32(my_full + slot * 8, uint32_t(n) * rowb);
+                bulk_g2s_hint_u32(my_ring + slot * stage_bytes, src, uint32_t(n) * rowb, my_full + slot * 8, policy);
+                if (SPJ == 2) {
+                    which ^= 1;
+                    if (which == 0) k += n;
+                } else {
+                    k += n;
+                }
+                if (++slot == D) {
+                    slot = 0;
+                    ++use;
+                }
+            }
+            if (__any_sync(0xffffffffu, can)) {
+                idle = 0;
+            } else {
+                // Every ring is full: stay off the issue ports for a moment. Bounded (about two
+                // seconds) so that a consumer that never hands a stage back cannot hang the GPU.
+                if (++idle > (1u << 24)) {
+                    failed = true;
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        if (failed && lane == 0) atomicExch(a.status, kDevTimeout);
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumer warps
+    const bool norm = a.norm_w != nullptr;
+    const int n4 = a.cols / 4;
     float best_v = -INFINITY;
     int best_i = INT_MAX;
     bool failed = false;
-    int cc = 0, tk = 0, s = 0;
-    uint32_t parity = 0;
-    for (int it = 0; it < n_items; ++it) {
-        bool ok = a.debug == 2 ? true : mbar_wait_bounded(my_bars + s, parity);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-            failed = true;
-            break;
-        }
-        const uint32_t stage = ring_u32 + uint32_t(s) * stage_bytes;
-        const int unit = cc * 32 + lane;
-        if (unit < nunits && a.debug != 1) {
-            UnitX x;
-            load_unit_x(limbs_u32, sx_u32, sumx_u32, nunits, unit, x);
+    if (njobs > 0) {
+        float4 wpre[kStageDeep];
+        if (norm) {
 #pragma unroll
-            for (int r = 0; r < NR; ++r) acc[r] += unit_dot<TYPE>(stage + r * CB, lane, x);
+            for (int k = 0; k < kStageDeep; ++k) {
+                const int i = k * kConsumers + tid;
+                wpre[k] = i < n4 ? reinterpret_cast<const float4 *>(a.norm_w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
-        __syncwarp();
-        if (lane == 0 && p_issued < n_items && a.debug != 2) {
-            fence_proxy_async();
-            issue(s);
+        pdl_wait();
+        trace_mark(trace, 2);
+        trace_word(trace, 6, trace_latest_exit());
+        float ssq = stage_activation_core<kConsumers>(a.x, a.norm_w, wpre, a.cols, tid, sx, sumx, planes_u32);
+        if (norm) {
+            ssq = warp_sum(ssq);
+            if (lane == 0) scratch[warp] = ssq;
         }
-        if (++s == stages) {
-            s = 0;
-            parity ^= 1u;
-        }
-        if (++cc == nchunks) {
-            cc = 0;
-            int seg, row0;
-            locate(wg + tk * total_warps, seg, row0);
-            ++tk;
-            const int nrows = min(R, a.seg[seg].rows - row0);
+        named_bar_sync(kBarConsumers, kConsumers);
+        if (norm && tid == 0) {
+            // One thread does the double-precision reciprocal square root (the reference narrows
+            // 1.0 / Math.sqrt(ss) once); it is needed only when the rows are finished.
+            float tot = 0.f;
 #pragma unroll
-            for (int r = 0; r < NR; ++r) acc[r] = warp_sum(acc[r]);
-            if (MODE == kGemvGateUp) {
+            for (int w = 0; w < kWarps; ++w) tot += scratch[w];
+            float ms = tot / static_cast<float>(a.cols);
+            ms += a.eps;
+            scratch[kWarps] = static_cast<float>(1.0 / sqrt(static_cast<double>(ms)));
+        }
+        trace_mark(trace, 3);
+
+        const int c = warp % nchunks, g = warp / nchunks;
+        int gs = 0, nj = 0;
+        if (g < G) {
+            gs = gemv_split(njobs, g, G);
+            nj = gemv_split(njobs, g + 1, G) - gs;
+        }
+        const int unit = c * 32 + lane;
+        const bool lane_on = unit < nunits;
+        UnitX x;
+        if (nj > 0 && lane_on) {
+            load_unit_x(planes_u32, smem_u32(sx), smem_u32(sumx), nunits, unit, x);
+        } else {
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    if (r < nrows && lane == r) {
-                        const float g = acc[r], u = acc[R + r];
-                        const float silu = g / (1.0f + expf(-g));
-                        a.seg[0].y[row0 + r] = silu * u;
+            for (int m = 0; m < kDigits; ++m)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x.a[m][i] = x.b[m][i] = 0;
+            x.sa = x.sb = x.ma = x.mb = 0.f;
+        }
+        const uint32_t my_full = full_u32 + uint32_t(g) * kGemvMaxStages * 8;
+        const uint32_t my_empty = empty_u32 + uint32_t(g) * kGemvMaxStages * 8;
+        const uint32_t my_ring = ring_u32 + uint32_t(g) * D * stage_bytes + uint32_t(c) * CB;
+        const int slots = G * PJ * SPJ;  // partial sums per chunk
+        const int nphases = ((njobs + G - 1) / G + PJ - 1) / PJ;
+        int slot = 0;
+        uint32_t parity = 0;
+#ifdef JL_TRACE
+        long long t_wait = 0;
+        const long long t_loop0 = clock64();
+#endif
+        for (int ph = 0; ph < nphases; ++ph) {
+            const int k_end = min(nj, (ph + 1) * PJ);
+            int k = ph * PJ;
+            while (k < k_end) {
+                int seg, row;
+                const int n = stage_rows_at<MODE, S>(a, job0 + gs, k, nj, PJ, seg, row);
+#pragma unroll
+                for (int which = 0; which < SPJ; ++which) {
+                    if (!failed) {
+#ifdef JL_TRACE
+                        const long long t_w0 = clock64();
+#endif
+                        bool ok;
+                        if (JL_TRACE_MODE(2)) {
+                            ok = false;
+                            for (uint32_t sp = 0; sp < (1u << 26) && !ok; ++sp) ok = mbar_test_wait_u32(my_full + slot * 8, parity);
+                        } else {
+                            ok = mbar_wait_bounded_u32(my_full + slot * 8, parity);
+                        }
+                        ok = __all_sync(0xffffffffu, ok);
+                        failed = !ok;
+#ifdef JL_TRACE
+                        t_wait += clock64() - t_w0;
+#endif
+                    }
+                    if (failed) continue;  // keep walking so that every barrier below is still reached
+                    const uint32_t stage = my_ring + slot * stage_bytes;
+                    float acc[S];
+#pragma unroll
+                    for (int i = 0; i < S; ++i)
+                        acc[i] = (lane_on && i < n && !JL_TRACE_MODE(1)) ? unit_dot<TYPE>(stage + i * rowb, lane, x) : 0.f;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_u32(my_empty + slot * 8);
+                    if (++slot == D) {
+                        slot = 0;
+                        parity ^= 1u;
+                    }
+                    float *dst = partial + size_t(c) * slots + (g * PJ + (k - ph * PJ)) * SPJ + which;
+                    if constexpr (S == 2) {
+                        // Both rows reduced together: lanes 0-15 end up with row 0, lanes 16-31 with row 1.
+                        const bool up = (lane & 16) != 0;
+                        float keep = up ? acc[1] : acc[0];
+                        const float send = up ? acc[0] : acc[1];
+                        keep += __shfl_xor_sync(0xffffffffu, send, 16);
+#pragma unroll
+                        for (int o = 8; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+                        if ((lane & 15) == 0 && (lane >> 4) < n) dst[(lane >> 4) * SPJ] = keep;
+                    } else {
+                        const float tot = warp_sum(acc[0]);
+                        if (lane == 0) dst[0] = tot;
                     }
                 }
-            } else {
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    if (r < nrows) {
-                        float v = acc[r];
-                        if (a.seg[seg].res != nullptr) v = a.seg[seg].res[row0 + r] + v;
-                        if (lane == r) a.seg[seg].y[row0 + r] = v;
-                        if (v > best_v || (v == best_v && row0 + r < best_i)) {
-                            best_v = v;
-                            best_i = row0 + r;
-                        }
+                k += n;
+            }
+#ifdef JL_TRACE
+            if (ph == 0)
+                trace_word(trace, 7, (static_cast<unsigned long long>(t_wait) << 32) |
+                                         static_cast<unsigned long long>((clock64() - t_loop0) & 0xffffffffll));
+#endif
+            named_bar_sync(kBarConsumers, kConsumers);
+            // One thread per job: add the chunks in order, finish, store.
+            const float rms = norm ? scratch[kWarps] : 1.0f;
+            for (int idx = tid; idx < G * PJ; idx += kConsumers) {
+                const int eg = idx / PJ, jl = idx - eg * PJ;
+                const int egs = gemv_split(njobs, eg, G), ege = gemv_split(njobs, eg + 1, G);
+                const int lj = egs + ph * PJ + jl;  // job within this CTA
+                if (lj >= ege) continue;
+                const float *pp = partial + size_t(idx) * SPJ;
+                if (MODE == kGemvGateUp) {
+                    float gt = 0.f, ut = 0.f;
+                    for (int cc = 0; cc < nchunks; ++cc) {
+                        gt += pp[size_t(cc) * slots];
+                        ut += pp[size_t(cc) * slots + 1];
+                    }
+                    gt *= rms;
+                    ut *= rms;
+                    const float silu = gt / (1.0f + expf(-gt));
+                    a.seg[0].y[job0 + lj] = silu * ut;
+                } else {
+                    float v = 0.f;
+                    for (int cc = 0; cc < nchunks; ++cc) v += pp[size_t(cc) * slots];
+                    v *= rms;
+                    int seg, row;
+                    locate(a, job0 + lj, seg, row);
+                    if (a.seg[seg].res != nullptr) v = a.seg[seg].res[row] + v;
+                    a.seg[seg].y[row] = v;
+                    if (v > best_v || (v == best_v && row < best_i)) {
+                        best_v = v;
+                        best_i = row;
                     }
                 }
             }
-#pragma unroll
-            for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+            if (ph + 1 < nphases) named_bar_sync(kBarConsumers, kConsumers);  // partials are reused
         }
-    }
-    if (failed) {
-        // Give copies already in flight a bounded chance to land before this CTA's shared memory
-        // is released, then report; the host turns the status word into an error.
-        for (int s = 0; s < stages; ++s) mbar_wait_bounded(my_bars + s, 0, 16);
-        if (lane == 0) atomicExch(a.status, kDevTimeout);
+        trace_mark(trace, 4);
+        if (failed) {
+            // Give copies already in flight a bounded chance to land before this CTA's shared memory
+            // is released, then report; the host turns the status word into an error.
+            if (g < G)
+                for (int s = 0; s < D; ++s) mbar_wait_bounded_u32(my_full + s * 8, 0, 16);
+            if (lane == 0) atomicExch(a.status, kDevTimeout);
+        }
+    } else {
+        pdl_wait();
     }
 
     if (a.argmax_val != nullptr) {
-        // Block-level then grid-level reduction of (value, first index).
-        __syncthreads();
-        float *bv = sm.scratch;
-        int *bi = reinterpret_cast<int *>(sm.scratch + kWarps);
+        // Warp, block, then grid reduction of (value, first index).
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best_v || (ov == best_v && oi < best_i)) {
+                best_v = ov;
+                best_i = oi;
+            }
+        }
+        float *bv = scratch + 32;
+        int *bi = reinterpret_cast<int *>(scratch + 48);
         if (lane == 0) {
             bv[warp] = best_v;
             bi[warp] = best_i;
         }
-        __syncthreads();
+        named_bar_sync(kBarConsumers, kConsumers);
         if (tid == 0) {
             float v = bv[0];
             int i = bi[0];
@@ -270,17 +430,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
             }
         }
     }
+    trace_mark(trace, 5);
+    if (tid == 0) trace_cta_exit();
 }
 
-template <int TYPE, int R, int MODE>
+template <int TYPE, int MODE>
 cudaError_t configure_one() {
-    return cudaFuncSetAttribute(gemv_kernel<TYPE, R, MODE>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    return cudaFuncSetAttribute(gemv_kernel<TYPE, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
-template <int TYPE, int R, int MODE>
-cudaError_t launch_one(const GemvArgs &args, const GemvPlan &plan, cudaStream_t stream,
-                       bool programmatic) {
+template <int TYPE, int MODE>
+cudaError_t launch_one(const GemvArgs &args, const GemvPlan &plan, cudaStream_t stream, bool programmatic) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(plan.grid);
     cfg.blockDim = dim3(kThreads);
@@ -291,90 +451,52 @@ cudaError_t launch_one(const GemvArgs &args, const GemvPlan &plan, cudaStream_t 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_kernel<TYPE, R, MODE>, args, plan.stages);
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<TYPE, MODE>, args, plan);
 }
 
-template <int TYPE, int MODE>
-cudaError_t launch_r(const GemvArgs &a, const GemvPlan &p, cudaStream_t s, bool pdl) {
-    switch (p.rows_per_tile) {
-        case 4: return launch_one<TYPE, 4, MODE>(a, p, s, pdl);
-        case 2: return launch_one<TYPE, 2, MODE>(a, p, s, pdl);
-        default: return launch_one<TYPE, 1, MODE>(a, p, s, pdl);
-    }
-}
 template <int TYPE>
 cudaError_t launch_mode(const GemvArgs &a, const GemvPlan &p, cudaStream_t s, bool pdl) {
-    if (a.mode == kGemvGateUp) {
-        // Gate/up tiles hold twice the rows; height 4 is not instantiated for them.
-        if (p.rows_per_tile == 2) return launch_one<TYPE, 2, kGemvGateUp>(a, p, s, pdl);
-        return launch_one<TYPE, 1, kGemvGateUp>(a, p, s, pdl);
-    }
-    return launch_r<TYPE, kGemvPlain>(a, p, s, pdl);
+    if (a.mode == kGemvGateUp) return launch_one<TYPE, kGemvGateUp>(a, p, s, pdl);
+    return launch_one<TYPE, kGemvPlain>(a, p, s, pdl);
 }
 
 template <int TYPE>
 cudaError_t configure_type() {
     cudaError_t e;
-    if ((e = configure_one<TYPE, 1, kGemvPlain>()) != cudaSuccess) return e;
-    if ((e = configure_one<TYPE, 2, kGemvPlain>()) != cudaSuccess) return e;
-    if ((e = configure_one<TYPE, 4, kGemvPlain>()) != cudaSuccess) return e;
-    if ((e = configure_one<TYPE, 1, kGemvGateUp>()) != cudaSuccess) return e;
-    if ((e = configure_one<TYPE, 2, kGemvGateUp>()) != cudaSuccess) return e;
-    return cudaSuccess;
+    if ((e = configure_one<TYPE, kGemvPlain>()) != cudaSuccess) return e;
+    return configure_one<TYPE, kGemvGateUp>();
 }
 
 }  // namespace
 
 bool gemv_plan(int type, int cols, int total_rows, int mode, int sm_count, GemvPlan *out) {
-    if (!is_quant(type) || cols <= 0 || cols % 256 != 0 || total_rows <= 0) return false;
-    const int chunk = 32 * (type == kQ8_0 ? kUnitBytesQ8 : kUnitBytesQ4);
-    const size_t fixed = kHeaderBytes + x_region_bytes(cols);
-    // One CTA of 16 warps per SM; most of the SM's shared memory goes to the weight rings.
-    static const int env_kb = [] {
-        const char *v = getenv("JITLLM_B200_GEMV_SMEM_KB");
-        return v ? atoi(v) : 0;
-    }();
-    size_t budget = size_t(env_kb > 0 ? env_kb : 208) * 1024;
-    if (budget > 224 * 1024) budget = 224 * 1024;
-    if (fixed + size_t(kWarps) * 2 * chunk > budget) budget = 224 * 1024;
-    if (fixed + size_t(kWarps) * 2 * chunk > budget) return false;
-    static const int env_mult = [] {
-        const char *v = getenv("JITLLM_B200_GEMV_GRID_MULT");
-        return v ? atoi(v) : 1;
-    }();
-    static const int env_r = [] {
-        const char *v = getenv("JITLLM_B200_GEMV_ROWS");
-        return v ? atoi(v) : 0;
-    }();
-    const int grid = sm_count * (env_mult > 0 ? env_mult : 1);
-    const int warps = grid * kWarps;
-    const int mult = (mode == kGemvGateUp) ? 2 : 1;
-    int best_r = 1, best_s = 0;
-    int rmax = (mode == kGemvGateUp) ? 2 : 4;
-    if (env_r > 0 && env_r < rmax) rmax = env_r;
-    for (int r = rmax; r >= 1; r >>= 1) {
-        // Taller tiles reuse the activation registers more, but leave warps idle on short matrices.
-        if (r > 1 && (total_rows / mult + r - 1) / r < warps) continue;
-        const size_t stage = size_t(r) * mult * chunk;
-        int s = static_cast<int>((budget - fixed) / (size_t(kWarps) * stage));
-        if (s > kMaxStages) s = kMaxStages;
-        if (s >= 2) {
-            best_r = r;
-            best_s = s;
-            break;
-        }
-    }
-    if (best_s < 2) {
-        const size_t stage = size_t(mult) * chunk;
-        best_r = 1;
-        best_s = static_cast<int>((budget - fixed) / (size_t(kWarps) * stage));
-        if (best_s > kMaxStages) best_s = kMaxStages;
-        if (best_s < 2) return false;
-    }
-    out->rows_per_tile = best_r;
-    out->stages = best_s;
-    out->grid = grid;
-    out->smem_bytes = fixed + size_t(kWarps) * best_s * best_r * mult * chunk;
+    if (!is_quant(type) || cols <= 0 || cols % 256 != 0 || cols > kGemvMaxCols || total_rows <= 0) return false;
+    const size_t rowb = size_t(row_bytes(type, cols));
+    const size_t stage = gemv_rows_per_stage(type) * rowb;
+    const int spj = mode == kGemvGateUp ? 2 : 1;
+    const int jobs = total_rows / spj;
+    GemvPlan p = {};
+    p.grid = sm_count;
+    p.nchunks = (cols + kGemvChunkCols - 1) / kGemvChunkCols;
+    p.groups = kGemvConsumerWarps / p.nchunks;
+    // Jobs per group between two epilogues: all of a CTA's rows when their partial sums fit (they do
+    // for every decode shape), otherwise as many as fit, in several phases.
+    const int per_cta = (jobs + p.grid - 1) / p.grid;
+    const int per_group = (per_cta + p.groups - 1) / p.groups;
+    int pj = kPartialFloatsMax / (p.nchunks * p.groups * spj);
+    if (pj < 1) return false;
+    if (per_group < pj) pj = per_group;
+    p.phase_jobs = pj;
+    p.off_x = kHeaderBytes;
+    p.off_partial = p.off_x + int(x_region_bytes(cols));
+    p.off_ring = int(align_up(size_t(p.off_partial) + size_t(p.nchunks) * p.groups * pj * spj * 4, 128));
+    const size_t budget = 227 * 1024;
+    if (size_t(p.off_ring) + size_t(p.groups) * 2 * stage > budget) return false;
+    int s = int((budget - p.off_ring) / (size_t(p.groups) * stage));
+    if (s > kGemvMaxStages) s = kGemvMaxStages;
+    p.stages = s;
+    p.smem_bytes = size_t(p.off_ring) + size_t(p.groups) * s * stage;
+    *out = p;
     return true;
 }
 
@@ -382,12 +504,10 @@ cudaError_t gemv_configure() {
     cudaError_t e;
     if ((e = configure_type<kQ4_K>()) != cudaSuccess) return e;
     if ((e = configure_type<kQ4_0>()) != cudaSuccess) return e;
-    if ((e = configure_type<kQ8_0>()) != cudaSuccess) return e;
-    return cudaSuccess;
+    return configure_type<kQ8_0>();
 }
 
-cudaError_t gemv_launch(const GemvArgs &args, const GemvPlan &plan, cudaStream_t stream,
-                        bool programmatic) {
+cudaError_t gemv_launch(const GemvArgs &args, const GemvPlan &plan, cudaStream_t stream, bool programmatic) {
     switch (args.type) {
         case kQ4_K: return launch_mode<kQ4_K>(args, plan, stream, programmatic);
         case kQ4_0: return launch_mode<kQ4_0>(args, plan, stream, programmatic);

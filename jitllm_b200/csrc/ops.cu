@@ -5,6 +5,8 @@
 
 namespace jl {
 
+JL_TRACE_DEFINE_BIND(ops_trace_bind)
+
 namespace {
 
 // ---- embedding -------------------------------------------------------------------------------
@@ -277,11 +279,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     constexpr int UN = 4;  // keys per warp iteration, loaded before any of them is used
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int trace = trace_begin(kTraceAttn);
     const bool on = a.active == nullptr || a.active[b] != 0;
-    const int pos = on ? a.positions[b] : 0;
-    const int slot = on ? a.slots[b] : 0;
     pdl_wait();
     pdl_launch_dependents();
+    trace_mark(trace, 2);
+    const int pos = on ? a.positions[b] : 0;
+    const int slot = on ? a.slots[b] : 0;
     const int n = pos + 1;
     const int nsplit = splits_for(n, a.nsplit);
     if (!on || split >= nsplit) return;

@@ -77,6 +77,8 @@ cudaError_t tp_pack_best_launch(const float *logits, const int32_t *idx, int l_v
 cudaError_t tp_pick_best_launch(const float *all, int ranks, int n, const uint8_t *active, int32_t *out,
                                 cudaStream_t stream);
 
+cudaError_t ops_trace_bind(unsigned long long *buf, unsigned cap, int mode);
+
 cudaError_t fill_launch(uint32_t *buf, size_t words, uint32_t value, cudaStream_t stream);
 
 }  // namespace jl
