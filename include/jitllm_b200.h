@@ -236,12 +236,19 @@ const char *jl_gguf_last_error(void);
  * Calls no cudaMalloc / cudaFree. The first call on a device looks up the array's device address
  * and sets kernel attributes -- make that call outside any stream capture. All calls share the
  * array: calls whose kernels overlap on the GPU (different streams) race on it; serialise them.
- * Shapes whose launch would need more than 1024 CTAs, or more shared memory than one SM has,
- * are rejected with JL_ERR_UNSUPPORTED. w_dev: rows x cols in GGUF block layout, 16-byte aligned.
- * Errors: jl_static_last_error(). */
+ * Shapes whose launch would need more than 1024 CTAs, more than 32768 columns, or more shared
+ * memory than one SM has, are rejected with JL_ERR_UNSUPPORTED. w_dev: rows x cols in GGUF block
+ * layout. w_dev, x_dev and norm_w_dev must be 16-byte aligned, y_dev and token_dev 4-byte aligned;
+ * anything else is refused with JL_ERR_INVALID before a kernel is launched.
+ * Errors: jl_static_last_error(). The call returns as soon as the kernel is enqueued, so a wait
+ * that ran out inside the kernel (every device-side wait is bounded) cannot show in its return
+ * value: jl_static_status(stream) synchronises the stream, reads the status word of the latest
+ * call on the current device from the static array (a 4-byte copy, no allocation) and returns
+ * JL_ERR_TIMEOUT if that kernel gave up, in which case y_dev and token_dev hold nothing valid. */
 int32_t jl_gemv_argmax_static(int32_t ggml_type, int64_t rows, int64_t cols, const void *w_dev,
                               const float *x_dev, const float *norm_w_dev, float rms_eps, float *y_dev,
                               int32_t *token_dev, void *stream);
+int32_t jl_static_status(void *stream);
 const char *jl_static_last_error(void);
 
 #ifdef __cplusplus

@@ -76,6 +76,7 @@ SIGNATURES = {
     "jl_tp_exchange_note": (C.c_char_p, [_P]),
     "jl_gemv_argmax_static": (_I32, [_I32, _I64, _I64, _P, _P, _P, C.c_float, _P, _P, _P]),
     "jl_static_last_error": (C.c_char_p, []),
+    "jl_static_status": (_I32, [_P]),
     "jl_gguf_open": (_I32, [C.c_char_p, C.POINTER(_P)]),
     "jl_gguf_describe": (_I32, [_P, C.POINTER(JlModelDesc), C.POINTER(C.c_float), C.POINTER(C.c_int64)]),
     "jl_gguf_upload": (_I32, [_P, _P, _I32, _I32, _I32, _P, _P, C.c_int64]),

@@ -193,6 +193,14 @@ __device__ __forceinline__ void trace_cta_exit() {
 __device__ __forceinline__ unsigned long long trace_latest_exit() {
     return g_trace_buf != nullptr ? __ldcg(g_trace_buf + 1) : 0ull;
 }
+// Per-CTA cells behind the records (kTraceCtaWords words for each of the first 1024 CTAs of the
+// latest launch that writes them): how evenly the CTAs of one launch finish.
+constexpr int kTraceCtaWords = 4;
+constexpr int kTraceCtaMax = 160, kTraceClasses = 6;  // cells: [class of launch][CTA][word]
+__device__ __forceinline__ void trace_cta_word(int cls, int word, unsigned long long v) {
+    if (g_trace_buf != nullptr && blockIdx.x < kTraceCtaMax && cls < kTraceClasses)
+        g_trace_buf[kTraceWords * (1 + size_t(g_trace_cap)) + (size_t(cls) * kTraceCtaMax + blockIdx.x) * kTraceCtaWords + word] = v;
+}
 #define JL_TRACE_DEFINE_BIND(fn)                                                              \
     cudaError_t fn(unsigned long long *buf, unsigned cap, int mode) {                        \
         cudaError_t e_ = cudaMemcpyToSymbol(g_trace_buf, &buf, sizeof buf);                   \
@@ -206,6 +214,7 @@ __device__ __forceinline__ void trace_mark(int, int) {}
 __device__ __forceinline__ void trace_word(int, int, unsigned long long) {}
 __device__ __forceinline__ void trace_cta_exit() {}
 __device__ __forceinline__ unsigned long long trace_latest_exit() { return 0ull; }
+__device__ __forceinline__ void trace_cta_word(int, int, unsigned long long) {}
 #define JL_TRACE_DEFINE_BIND(fn) \
     cudaError_t fn(unsigned long long *, unsigned, int) { return cudaSuccess; }
 #define JL_TRACE_MODE(bit) false

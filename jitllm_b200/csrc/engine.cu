@@ -545,10 +545,7 @@ int tp_global_argmax(jl_ctx *ctx, int n, uint64_t *launches) {
 }
 
 int attn_splits_for_width(const jl_ctx *ctx, int width) {
-    int n = (2 * ctx->sm_count + width * ctx->l_kv_heads - 1) / (width * ctx->l_kv_heads);
-    if (n > 32) n = 32;
-    if (n < 1) n = 1;
-    return n;
+    return attention_splits(ctx->sm_count, width, ctx->l_kv_heads);
 }
 
 // One tensor-core launch over up to three matrices that share the input rows.
@@ -1575,7 +1572,7 @@ int32_t jl_debug_trace(jl_ctx *ctx, uint64_t *out, int32_t max_records) {
     cudaSetDevice(ctx->device);
     if (!out) {  // arm: later launches record stamps
         if (!ctx->d_trace) {
-            int rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_trace), size_t(kCap + 1) * kTraceWords * 8);
+            int rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_trace), (size_t(kCap + 1) * kTraceWords + kTraceClasses * kTraceCtaMax * kTraceCtaWords) * 8);
             if (rc) return rc;
             ctx->user_allocs.push_back(ctx->d_trace);  // released with the context
             const char *mv = getenv("JITLLM_B200_TRACE_MODE");
@@ -1583,7 +1580,7 @@ int32_t jl_debug_trace(jl_ctx *ctx, uint64_t *out, int32_t max_records) {
             JL_CUDA(ctx, gemv_trace_bind(ctx->d_trace, kCap, mode));
             JL_CUDA(ctx, ops_trace_bind(ctx->d_trace, kCap, mode));
         }
-        JL_CUDA(ctx, cudaMemsetAsync(ctx->d_trace, 0, size_t(kCap + 1) * kTraceWords * 8, ctx->stream));
+        JL_CUDA(ctx, cudaMemsetAsync(ctx->d_trace, 0, (size_t(kCap + 1) * kTraceWords + kTraceClasses * kTraceCtaMax * kTraceCtaWords) * 8, ctx->stream));
         JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         return int32_t(kCap);
     }
@@ -1593,6 +1590,10 @@ int32_t jl_debug_trace(jl_ctx *ctx, uint64_t *out, int32_t max_records) {
     JL_CUDA(ctx, cudaMemcpy(&n, ctx->d_trace, 8, cudaMemcpyDeviceToHost));
     if (n > kCap) n = kCap;
     if (n > (unsigned long long)max_records) n = max_records;
+    if (max_records < 0) {  // the per-CTA cells of the latest launch instead of the records
+        JL_CUDA(ctx, cudaMemcpy(out, ctx->d_trace + size_t(kCap + 1) * kTraceWords, kTraceClasses * kTraceCtaMax * kTraceCtaWords * 8, cudaMemcpyDeviceToHost));
+        return kTraceClasses * kTraceCtaMax;
+    }
     JL_CUDA(ctx, cudaMemcpy(out, ctx->d_trace + kTraceWords, size_t(n) * kTraceWords * 8, cudaMemcpyDeviceToHost));
     return int32_t(n);
 #endif
@@ -1764,6 +1765,10 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     if (!ctx) return JL_ERR_INVALID;
     JL_REQUIRE(ctx, w && x_dev && y_dev, JL_ERR_INVALID, "NULL argument");
     JL_REQUIRE(ctx, n >= 0, JL_ERR_INVALID, "n must not be negative");
+    // The kernels read activation rows with 16-byte loads (rows are a multiple of 256 floats long, so
+    // every row of an aligned buffer is aligned); a pointer that breaks that would fault on the device.
+    JL_REQUIRE(ctx, reinterpret_cast<uintptr_t>(x_dev) % 16 == 0 && reinterpret_cast<uintptr_t>(y_dev) % 16 == 0,
+               JL_ERR_INVALID, "x_dev and y_dev must be 16-byte aligned");
     cudaSetDevice(ctx->device);
     uint64_t launches = 0;
     static const int gemm_min_n = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();

@@ -37,11 +37,12 @@ namespace {
 constexpr int kThreads = kGemvThreads;
 constexpr int kWarps = kGemvConsumerWarps;
 constexpr int kConsumers = kWarps * 32;
-constexpr int kBarBytes = 2 * kWarps * kGemvMaxStages * 8;  // full + empty barriers
+constexpr int kBarBytes = 2 * kWarps * kGemvMaxStages * 8 + 128;  // full + empty barriers, then the RMS barrier
 constexpr int kScratchFloats = 64;                          // RMS partials, RMS factor, arg-max fold
 constexpr int kHeaderBytes = kBarBytes + kScratchFloats * 4;
 constexpr int kPartialFloatsMax = 4096;
-constexpr int kBarConsumers = 1;
+constexpr int kBarStaged = 1;     // consumers + producer warp: the activation is staged
+constexpr int kBarConsumers = 2;  // consumers only: a phase's partial sums are complete / consumed
 
 __device__ __forceinline__ void mbar_arrive_u32(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
 
     const uint32_t full_u32 = smem_u32(smem);  // [group][stage], then the same for "empty"
     const uint32_t empty_u32 = full_u32 + kWarps * kGemvMaxStages * 8;
+    const uint32_t rms_bar_u32 = full_u32 + 2 * kWarps * kGemvMaxStages * 8;
     float *scratch = reinterpret_cast<float *>(smem + kBarBytes);
     float *sx = reinterpret_cast<float *>(smem + pl.off_x);
     float *sumx = sx + a.cols / 32;
@@ -146,6 +148,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
             mbar_init(reinterpret_cast<uint64_t *>(smem) + g * kGemvMaxStages + s, 1);
             mbar_init(reinterpret_cast<uint64_t *>(smem) + (kWarps + g) * kGemvMaxStages + s, nchunks);
         }
+        mbar_init(reinterpret_cast<uint64_t *>(smem) + 2 * kWarps * kGemvMaxStages, 1);
         mbar_fence_init();
         fence_proxy_async();
     }
@@ -171,8 +174,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         const uint64_t policy = policy_evict_first();
         int k = 0, which = 0, slot = 0, use = 0;
         uint32_t idle = 0;
-        bool failed = false;
+        bool failed = false, joined = false;
         while (true) {
+            if (!joined && (idle > 0 || !__any_sync(0xffffffffu, k < nj))) {
+                // Every ring is full (or all copies are out): nothing to do until the consumers, which
+                // are staging the activation, start to hand stages back. Meet them at their barrier
+                // and take the one serial piece of the RMSNorm off their hands: the reference
+                // narrows 1.0 / Math.sqrt(ss) from double once.
+                joined = true;
+                named_bar_sync(kBarStaged, kThreads);
+                if (a.norm_w != nullptr && lane == 0) {
+                    float tot = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kWarps; ++w) tot += scratch[w];
+                    float ms = tot / static_cast<float>(a.cols);
+                    ms += a.eps;
+                    scratch[kWarps] = static_cast<float>(1.0 / sqrt(static_cast<double>(ms)));
+                    mbar_arrive_u32(rms_bar_u32);  // release: the consumers wait on it before they read
+                }
+                __syncwarp();
+            }
             const bool want = k < nj;
             if (!__any_sync(0xffffffffu, want)) break;
             bool can = false;
@@ -229,23 +250,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         pdl_wait();
         trace_mark(trace, 2);
         trace_word(trace, 6, trace_latest_exit());
+#ifdef JL_TRACE
+        // class of this launch for the per-CTA cells: 0 QKV, 1 output projection, 2 gate/up, 3 down, 4 vocabulary
+        const int tcls = MODE == kGemvGateUp ? 2 : (a.argmax_val != nullptr ? 4 : (a.nseg == 3 ? 0 : (a.cols > 8192 ? 3 : 1)));
+        if (tid == 0) trace_cta_word(tcls, 3, trace_now());
+#endif
         float ssq = stage_activation_core<kConsumers>(a.x, a.norm_w, wpre, a.cols, tid, sx, sumx, planes_u32);
         if (norm) {
             ssq = warp_sum(ssq);
             if (lane == 0) scratch[warp] = ssq;
         }
-        named_bar_sync(kBarConsumers, kConsumers);
-        if (norm && tid == 0) {
-            // One thread does the double-precision reciprocal square root (the reference narrows
-            // 1.0 / Math.sqrt(ss) once); it is needed only when the rows are finished.
-            float tot = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) tot += scratch[w];
-            float ms = tot / static_cast<float>(a.cols);
-            ms += a.eps;
-            scratch[kWarps] = static_cast<float>(1.0 / sqrt(static_cast<double>(ms)));
-        }
+        named_bar_sync(kBarStaged, kThreads);  // the producer warp joins: it computes the RMS factor
         trace_mark(trace, 3);
+#ifdef JL_TRACE
+        if (tid == 0) {
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            trace_cta_word(tcls, 0, trace_now());
+            trace_cta_word(tcls, 2, smid);
+        }
+#endif
 
         const int c = warp % nchunks, g = warp / nchunks;
         int gs = 0, nj = 0;
@@ -270,6 +294,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         const uint32_t my_ring = ring_u32 + uint32_t(g) * D * stage_bytes + uint32_t(c) * CB;
         const int slots = G * PJ * SPJ;  // partial sums per chunk
         const int nphases = ((njobs + G - 1) / G + PJ - 1) / PJ;
+        // The residual this thread will add in the (only) epilogue, fetched now so that its trip to
+        // L2 is over by then.
+        float res_pre = 0.f;
+        if (MODE == kGemvPlain && nphases == 1 && tid < G * PJ) {
+            const int eg = tid / PJ, jl = tid - eg * PJ;
+            const int lj = gemv_split(njobs, eg, G) + jl;
+            if (lj < gemv_split(njobs, eg + 1, G)) {
+                int seg, row;
+                locate(a, job0 + lj, seg, row);
+                if (a.seg[seg].res != nullptr) res_pre = __ldcg(a.seg[seg].res + row);
+            }
+        }
         int slot = 0;
         uint32_t parity = 0;
 #ifdef JL_TRACE
@@ -337,6 +373,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
 #endif
             named_bar_sync(kBarConsumers, kConsumers);
             // One thread per job: add the chunks in order, finish, store.
+            if (norm && ph == 0 && !mbar_wait_bounded_u32(rms_bar_u32, 0)) failed = true;
             const float rms = norm ? scratch[kWarps] : 1.0f;
             for (int idx = tid; idx < G * PJ; idx += kConsumers) {
                 const int eg = idx / PJ, jl = idx - eg * PJ;
@@ -360,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
                     v *= rms;
                     int seg, row;
                     locate(a, job0 + lj, seg, row);
-                    if (a.seg[seg].res != nullptr) v = a.seg[seg].res[row] + v;
+                    if (a.seg[seg].res != nullptr) v = (nphases == 1 ? res_pre : a.seg[seg].res[row]) + v;
                     a.seg[seg].y[row] = v;
                     if (v > best_v || (v == best_v && row < best_i)) {
                         best_v = v;
@@ -371,6 +408,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
             if (ph + 1 < nphases) named_bar_sync(kBarConsumers, kConsumers);  // partials are reused
         }
         trace_mark(trace, 4);
+#ifdef JL_TRACE
+        if (tid == 0) trace_cta_word(tcls, 1, trace_now());
+#endif
         if (failed) {
             // Give copies already in flight a bounded chance to land before this CTA's shared memory
             // is released, then report; the host turns the status word into an error.

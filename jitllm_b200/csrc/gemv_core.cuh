@@ -172,7 +172,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 // float4 pieces; the eight lanes that hold one 32-element block agree on the block maximum with
 // three shuffles. wpre: the first KD float4 of norm_w for this thread, loaded by the caller before
 // it waited for the producing kernel (weights are never written by a kernel).
-constexpr int kStageDeep = 4;
+constexpr int kStageDeep = 8;
 template <int NTHREADS>
 __device__ __forceinline__ float stage_activation_core(const float *x, const float *norm_w, const float4 *wpre,
                                                        int cols, int tid, float *sx_p, float *sumx_p,

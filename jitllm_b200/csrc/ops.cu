@@ -256,178 +256,357 @@ __global__ void argmax_rows_kernel(const float *logits, int vocab, const uint8_t
 
 // ---- RoPE + KV append + paged decode attention -------------------------------------------------
 
-constexpr int kAttnThreads = 256;
-constexpr int kAttnWarps = kAttnThreads / 32;
-constexpr int kAttnMaxSplit = 32;
-constexpr int kAttnMinKeysPerSplit = 64;
+// Sixteen warps per CTA (eight when the G query heads of a KV head hold more state per thread than
+// 512 threads leave registers for). A warp takes eight keys per iteration: four lanes share a key for the
+// q.k products (each lane a quarter of the head dimension), while for the p.v sums every lane owns
+// head_dim / 32 output dimensions of all eight keys.
+template <int HD, int G>
+struct AttnShape {
+    static constexpr int threads = (G * HD > 512) ? 256 : 512;
+    static constexpr int warps = threads / 32;
+    static constexpr int keys = 8;
+    static constexpr int dk = HD / 4;       // dimensions of a key one lane multiplies
+    static constexpr int qpad = dk + 4;     // quarter stride of q in shared memory: no bank conflicts
+};
+constexpr int kAttnMaxCluster = 8;      // CTAs of one cluster share a (row, KV head) and fold through shared memory
+constexpr int kAttnMaxFold = 8;         // clusters per (row, KV head) at most: their fold goes through global memory
+constexpr int kAttnKeysPerCluster = 1024;  // short contexts use one cluster, so nothing crosses global memory
+constexpr int kAttnPages = 264;         // page bases kept in shared memory (4096 keys of 16-token pages, and margin)
 
-// Number of splits actually used for n keys: short contexts use few CTAs so that the fold at the
-// end stays small; the launch grid is sized for the maximum and surplus CTAs leave at once.
-__device__ __forceinline__ int splits_for(int n, int nsplit_max) {
-    const int want = (n + kAttnMinKeysPerSplit - 1) / kAttnMinKeysPerSplit;
-    return max(1, min(nsplit_max, want));
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Clusters actually used for n keys: short contexts use one, so that the fold stays on chip; the
+// launch grid is sized for the maximum and surplus clusters leave at once.
+__device__ __forceinline__ int clusters_for(int n, int ncl_max) {
+    return max(1, min(ncl_max, (n + kAttnKeysPerCluster - 1) / kAttnKeysPerCluster));
 }
 
-// One CTA = (split of the position range, KV head, batch row). The G query heads that share the
-// KV head are processed together so each K/V row is read once. What it computes is
-// CpuOperations.rope + appendKeyValue + attention (inference/op/CpuOperations.java:94-204) with
-// the softmax evaluated online; K and V are rounded to binary16 on append exactly as
-// ArrayHalfFloatTensor.setFloat does (tensor/standard/ArrayHalfFloatTensor.java:33-40).
+__device__ __forceinline__ void st_cluster_f32(float *local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 template <int HD, int G>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
+struct AttnSmem {
+    float q[G][4][AttnShape<HD, G>::qpad];
+    float red[AttnShape<HD, G>::warps][G][HD + 2];
+    float part[kAttnMaxCluster][G][HD + 2];  // in the cluster's first CTA: every CTA's result
+    float wgt[G][kAttnMaxFold];
+    float inv_l[G];
+    long long page_base[kAttnPages];
+    int is_last;
+};
+
+// One CTA = (split of the position range, KV head, batch row); `csize` consecutive splits form a
+// thread-block cluster. The G query heads that share the KV head are processed together so each
+// K/V row is read once. What it computes is CpuOperations.rope + appendKeyValue + attention
+// (inference/op/CpuOperations.java:94-204) with the softmax evaluated online; K and V are rounded
+// to binary16 on append exactly as ArrayHalfFloatTensor.setFloat does
+// (tensor/standard/ArrayHalfFloatTensor.java:33-40).
+//
+// Decode launches (a.append != 0: every row is its own sequence and position pos is the only key
+// this step adds) read everything that no kernel of this step writes -- position, slot, block
+// table, RoPE row and the first batch of old K/V rows -- before waiting for the kernel that
+// produces q, k and v, so that memory latency overlaps that kernel's tail. The new key never
+// comes back from the pool: the warp that appends it uses the rounded values it just wrote.
+// positions[] and slots[] are written by the host before the step or by advance_kernel, and the
+// kernel that follows advance_kernel releases its dependents only after it has itself waited, so
+// no kernel of a step starts before advance_kernel has completed.
+//
+// Folding: the warps of a CTA fold in its shared memory; the CTAs of a cluster store their results
+// into the shared memory of the cluster's first CTA, which folds them; only when a context is long
+// enough to use several clusters do their results meet in global memory, where the last cluster
+// to arrive folds them.
+template <int HD, int G>
+__global__ void __launch_bounds__(AttnShape<HD, G>::threads) attn_decode_kernel(const AttnArgs a, const int csize) {
     constexpr int VEC = HD / 32;
-    constexpr int UN = 4;  // keys per warp iteration, loaded before any of them is used
+    constexpr int UN = AttnShape<HD, G>::keys;
+    constexpr int kAttnThreads = AttnShape<HD, G>::threads, kAttnWarps = AttnShape<HD, G>::warps;
+    extern __shared__ __align__(16) uint8_t attn_smem_raw[];
+    AttnSmem<HD, G> &sm = *reinterpret_cast<AttnSmem<HD, G> *>(attn_smem_raw);
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int trace = trace_begin(kTraceAttn);
-    const bool on = a.active == nullptr || a.active[b] != 0;
-    pdl_wait();
     pdl_launch_dependents();
-    trace_mark(trace, 2);
-    const int pos = on ? a.positions[b] : 0;
-    const int slot = on ? a.slots[b] : 0;
-    const int n = pos + 1;
-    const int nsplit = splits_for(n, a.nsplit);
-    if (!on || split >= nsplit) return;
+    const bool on = a.active == nullptr || a.active[b] != 0;
+    const bool dec = a.append != 0;
+    int pos = 0, slot = 0;
+    if (on && dec) {
+        pos = a.positions[b];
+        slot = a.slots[b];
+    }
+    if (!dec) {
+        pdl_wait();
+        if (on) {
+            pos = a.positions[b];
+            slot = a.slots[b];
+        }
+    }
+    const int n_old = dec ? pos : pos + 1;  // keys that come from the pool
+    const int ncl_max = a.nsplit / csize;
+    const int ncl = clusters_for(max(n_old, 1), ncl_max);
+    const int cl = split / csize;
+    if (!on || cl >= ncl) {  // whole clusters leave; still in step with the chain of launches
+        if (dec) pdl_wait();
+        return;
+    }
+    const int nsplit = ncl * csize;
+    const uint32_t crank = csize > 1 ? cluster_rank() : 0u;
+    // First half of a cluster barrier whose second half sits just before the stores into the first
+    // CTA's shared memory: that CTA must have started before anybody writes there.
+    if (csize > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
-    __shared__ float q_s[G][HD];
-    __shared__ float red[kAttnWarps][G][HD + 2];
-    __shared__ float wgt_s[G][kAttnMaxSplit];
-    __shared__ float inv_l[G];
-    __shared__ int64_t page_base[kAttnMaxSplit * 0 + 40];
-    __shared__ int is_last;
-
-    const int chunk = (n + nsplit - 1) / nsplit;
-    const int start = split * chunk;
-    const int end = min(n, start + chunk);
-    // Page bases of this CTA's key range (at most chunk/block_tokens + 2 pages).
+    const int chunk = (n_old + nsplit - 1) / nsplit;
+    const int start = min(n_old, split * chunk);
+    const int end = min(n_old, start + chunk);
+    // Page bases of this CTA's key range.
     const int bt = a.kv.block_tokens;
     const int first_page = start / bt;
     const int npages = end > start ? (end - 1) / bt - first_page + 1 : 0;
     const int64_t block_stride = int64_t(a.kv.layers) * bt * a.kv.kv_dim;
-    for (int pg = tid; pg < npages && pg < 40; pg += kAttnThreads) {
+    for (int pg = tid; pg < npages && pg < kAttnPages; pg += kAttnThreads) {
         const int64_t phys = a.kv.block_table[int64_t(slot) * a.kv.blocks_per_slot + first_page + pg];
-        page_base[pg] = phys * block_stride + int64_t(a.layer) * bt * a.kv.kv_dim + int64_t(kvh) * HD;
+        sm.page_base[pg] = phys * block_stride + int64_t(a.layer) * bt * a.kv.kv_dim + int64_t(kvh) * HD;
     }
+    __syncthreads();
+    // Each warp takes a contiguous run of keys so that consecutive keys share a page. The new key
+    // of a decode launch goes to the last warp of the first CTA, behind that warp's old keys.
+    constexpr int DK = AttnShape<HD, G>::dk;
+    const int per_warp = (end - start + kAttnWarps - 1) / kAttnWarps;
+    const int w0 = min(end, start + warp * per_warp);
+    const int w1 = min(end, w0 + per_warp);
+    const int extra = (dec && split == 0 && warp == kAttnWarps - 1) ? 1 : 0;
+    const int ku = lane >> 2, qd = lane & 3;  // this lane's key of the batch and quarter of its dimensions
+    auto key_base = [&](int t) -> int64_t {
+        const int pg = t / bt - first_page;
+        const int64_t base = (pg < kAttnPages) ? int64_t(sm.page_base[pg])
+                                               : kv_offset(a.kv, slot, t, a.layer) - int64_t(t % bt) * a.kv.kv_dim + int64_t(kvh) * HD;
+        return base + int64_t(t % bt) * a.kv.kv_dim;
+    };
+    uint4 kq[DK / 8];    // this lane's quarter of its key, as stored (binary16)
+    uint32_t vq[UN][VEC / 2];  // this lane's output dimensions of the batch's eight values
+    auto load_batch = [&](int t0) {
+        if (t0 + ku < w1) {
+            const uint4 *kp = reinterpret_cast<const uint4 *>(a.kv.kpool + key_base(t0 + ku) + qd * DK);
+#pragma unroll
+            for (int i = 0; i < DK / 8; ++i) kq[i] = kp[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < DK / 8; ++i) kq[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            if (t0 + u < w1) {
+                const uint32_t *vp = reinterpret_cast<const uint32_t *>(a.kv.vpool + key_base(t0 + u) + lane * VEC);
+#pragma unroll
+                for (int j = 0; j < VEC / 2; ++j) vq[u][j] = vp[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < VEC / 2; ++j) vq[u][j] = 0u;
+            }
+        }
+    };
     const float *cr = a.rope_cos + size_t(pos) * (HD / 2);
     const float *ci = a.rope_sin + size_t(pos) * (HD / 2);
+    if (dec) {
+        load_batch(w0);
+        pdl_wait();
+    }
+    trace_mark(trace, 2);
+    trace_word(trace, 6, trace_latest_exit());
     for (int idx = tid; idx < G * (HD / 2); idx += kAttnThreads) {
         const int g = idx / (HD / 2), i = idx - g * (HD / 2);
         const float *qh = a.q + size_t(b) * a.dim + size_t(kvh * G + g) * HD;
         const float v0 = qh[2 * i], v1 = qh[2 * i + 1];
-        q_s[g][2 * i] = __fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]));
-        q_s[g][2 * i + 1] = __fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]));
-    }
-    if (a.append && start <= pos && pos < end) {
-        // This CTA owns the new position: rotate k, round k and v to fp16, append to the page.
-        const int64_t off = kv_offset(a.kv, slot, pos, a.layer) + int64_t(kvh) * HD;
-        const float *kh = a.k + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
-        const float *vh = a.v + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
-        for (int i = tid; i < HD / 2; i += kAttnThreads) {
-            const float v0 = kh[2 * i], v1 = kh[2 * i + 1];
-            const float r0 = __fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]));
-            const float r1 = __fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]));
-            a.kv.kpool[off + 2 * i] = __float2half_rn(r0);
-            a.kv.kpool[off + 2 * i + 1] = __float2half_rn(r1);
-            a.kv.vpool[off + 2 * i] = __float2half_rn(vh[2 * i]);
-            a.kv.vpool[off + 2 * i + 1] = __float2half_rn(vh[2 * i + 1]);
-        }
+        const int d0 = 2 * i;
+        sm.q[g][d0 / DK][d0 % DK] = __fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]));
+        sm.q[g][d0 / DK][d0 % DK + 1] = __fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]));
     }
     __syncthreads();
+    trace_mark(trace, 3);
 
-    float m[G], l[G], acc[G][VEC], qr[G][VEC];
+    float m[G], l[G], acc[G][VEC];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m[g] = -INFINITY;
         l[g] = 0.f;
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-            acc[g][j] = 0.f;
-            qr[g][j] = q_s[g][lane * VEC + j];
-        }
+        for (int j = 0; j < VEC; ++j) acc[g][j] = 0.f;
     }
     const float inv_sqrt = 1.0f / sqrtf(static_cast<float>(HD));
-    // Each warp takes a contiguous run of keys so that consecutive keys share a page.
-    const int per_warp = (end - start + kAttnWarps - 1) / kAttnWarps;
-    const int w0 = start + warp * per_warp;
-    const int w1 = min(end, w0 + per_warp);
-    for (int t0 = w0; t0 < w1; t0 += UN) {
-        float kf[UN][VEC], vf[UN][VEC];
+    const int w1x = w1 + extra;
+    for (int t0 = w0; t0 < w1x; t0 += UN) {
+        if (!(dec && t0 == w0)) load_batch(t0);
+        if (extra && w1 - t0 < UN && w1 >= t0) {
+            // The new key sits in this batch: rotate k, round k and v to fp16 as the append does,
+            // keep the rounded values for this step and write them to the page.
+            const int64_t off = kv_offset(a.kv, slot, pos, a.layer) + int64_t(kvh) * HD;
+            if (ku == w1 - t0) {
+                const float *kh = a.k + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD + qd * DK;
+                uint32_t packed[DK / 2];
 #pragma unroll
-        for (int u = 0; u < UN; ++u) {
-            const int t = min(t0 + u, w1 - 1);  // the tail repeats the last key; masked below
-            const int pg = t / bt - first_page;
-            const int64_t base = (pg < 40) ? page_base[pg] : kv_offset(a.kv, slot, t, a.layer) - int64_t(t % bt) * a.kv.kv_dim + int64_t(kvh) * HD;
-            const int64_t off = base + int64_t(t % bt) * a.kv.kv_dim + lane * VEC;
-            load_halfs<VEC>(a.kv.kpool + off, kf[u]);
-            load_halfs<VEC>(a.kv.vpool + off, vf[u]);
+                for (int j = 0; j < DK / 2; ++j) {
+                    const float v0 = kh[2 * j], v1 = kh[2 * j + 1];
+                    const float c = cr[qd * (DK / 2) + j], sn = ci[qd * (DK / 2) + j];
+                    const __half2 h = __halves2half2(__float2half_rn(__fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, sn))),
+                                                     __float2half_rn(__fadd_rn(__fmul_rn(v0, sn), __fmul_rn(v1, c))));
+                    packed[j] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+#pragma unroll
+                for (int i = 0; i < DK / 8; ++i) {
+                    kq[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    reinterpret_cast<uint4 *>(a.kv.kpool + off + qd * DK)[i] = kq[i];
+                }
+            }
+            const float *vh = a.v + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD + lane * VEC;
+            uint32_t vnew[VEC / 2];
+#pragma unroll
+            for (int j = 0; j < VEC / 2; ++j) {
+                const __half2 h = __halves2half2(__float2half_rn(vh[2 * j]), __float2half_rn(vh[2 * j + 1]));
+                vnew[j] = *reinterpret_cast<const uint32_t *>(&h);
+                reinterpret_cast<uint32_t *>(a.kv.vpool + off + lane * VEC)[j] = vnew[j];
+            }
+#pragma unroll
+            for (int u = 0; u < UN; ++u)
+                if (t0 + u == w1) {
+#pragma unroll
+                    for (int j = 0; j < VEC / 2; ++j) vq[u][j] = vnew[j];
+                }
         }
+        // q.k: this lane's quarter of its key against the same quarter of every query head.
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DK / 8; ++i) {
+            const uint32_t w[4] = {kq[i].x, kq[i].y, kq[i].z, kq[i].w};
+            float kf[8];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[h]));
+                kf[2 * h] = f.x;
+                kf[2 * h + 1] = f.y;
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float4 qa = *reinterpret_cast<const float4 *>(&sm.q[g][qd][8 * i]);
+                const float4 qb = *reinterpret_cast<const float4 *>(&sm.q[g][qd][8 * i + 4]);
+                s[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] + qb.y * kf[5] +
+                        qb.z * kf[6] + qb.w * kf[7];
+            }
+        }
+        const bool valid = t0 + ku < w1x;
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            float s[UN];
-#pragma unroll
-            for (int u = 0; u < UN; ++u) {
-                float d = 0.f;
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) d += qr[g][j] * kf[u][j];
-                s[u] = d;
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-                for (int u = 0; u < UN; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
-            }
-            float mn = m[g];
-#pragma unroll
-            for (int u = 0; u < UN; ++u) {
-                s[u] = (t0 + u < w1) ? s[u] * inv_sqrt : -INFINITY;
-                mn = fmaxf(mn, s[u]);
-            }
+            float sg = s[g];
+            sg += __shfl_xor_sync(0xffffffffu, sg, 1);
+            sg += __shfl_xor_sync(0xffffffffu, sg, 2);
+            sg = valid ? sg * inv_sqrt : -INFINITY;
+            float mn = sg;
+            mn = fmaxf(mn, __shfl_xor_sync(0xffffffffu, mn, 4));
+            mn = fmaxf(mn, __shfl_xor_sync(0xffffffffu, mn, 8));
+            mn = fmaxf(mn, __shfl_xor_sync(0xffffffffu, mn, 16));
+            mn = fmaxf(mn, m[g]);  // finite: the batch has at least one valid key
             const float corr = expf(m[g] - mn);
-            float psum = 0.f;
+            const float p = expf(sg - mn);  // exp(-inf) = 0 for masked keys
+            float psum = p;
+            psum += __shfl_xor_sync(0xffffffffu, psum, 4);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 8);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 16);
+            l[g] = l[g] * corr + psum;
+            m[g] = mn;
 #pragma unroll
             for (int j = 0; j < VEC; ++j) acc[g][j] *= corr;
 #pragma unroll
             for (int u = 0; u < UN; ++u) {
-                const float p = expf(s[u] - mn);  // exp(-inf) = 0 for masked keys
-                psum += p;
+                const float pu = __shfl_sync(0xffffffffu, p, 4 * u);
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) acc[g][j] += p * vf[u][j];
+                for (int j = 0; j < VEC / 2; ++j) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&vq[u][j]));
+                    acc[g][2 * j] += pu * f.x;
+                    acc[g][2 * j + 1] += pu * f.y;
+                }
             }
-            l[g] = l[g] * corr + psum;
-            m[g] = mn;
         }
     }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) red[warp][g][lane * VEC + j] = acc[g][j];
+        for (int j = 0; j < VEC; ++j) sm.red[warp][g][lane * VEC + j] = acc[g][j];
         if (lane == 0) {
-            red[warp][g][HD] = m[g];
-            red[warp][g][HD + 1] = l[g];
+            sm.red[warp][g][HD] = m[g];
+            sm.red[warp][g][HD + 1] = l[g];
         }
     }
     __syncthreads();
+    trace_mark(trace, 4);
 
+    // Fold the warps of this CTA (a warp without keys has m = -inf, l = 0 and weighs nothing) and
+    // hand the result to the cluster's first CTA.
+    if (csize > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, d = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, sm.red[w][g][HD]);
+        float val = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float mw = sm.red[w][g][HD];
+            const float wgt = (mw == -INFINITY) ? 0.f : expf(mw - M);
+            val += sm.red[w][g][d] * wgt;
+            L += sm.red[w][g][HD + 1] * wgt;
+        }
+        if (crank == 0) {
+            sm.part[0][g][d] = val;
+            if (d == 0) {
+                sm.part[0][g][HD] = M;
+                sm.part[0][g][HD + 1] = L;
+            }
+        } else {
+            st_cluster_f32(&sm.part[crank][g][d], 0, val);
+            if (d == 0) {
+                st_cluster_f32(&sm.part[crank][g][HD], 0, M);
+                st_cluster_f32(&sm.part[crank][g][HD + 1], 0, L);
+            }
+        }
+    }
+    if (csize > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        if (crank != 0) {
+            if (tid == 0) trace_cta_exit();
+            return;  // the stores above are ordered before the arrival; nobody reads this CTA's memory
+        }
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    } else {
+        __syncthreads();
+    }
     const size_t pstride = size_t(HD + 2);
     for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, d = idx - g * HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, red[w][g][HD]);
+        for (int r = 0; r < kAttnMaxCluster; ++r)
+            if (r < csize) M = fmaxf(M, sm.part[r][g][HD]);
         float val = 0.f, L = 0.f;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) {
-            const float mw = red[w][g][HD];
-            const float wgt = (mw == -INFINITY) ? 0.f : expf(mw - M);
-            val += red[w][g][d] * wgt;
-            L += red[w][g][HD + 1] * wgt;
+        for (int r = 0; r < kAttnMaxCluster; ++r) {
+            if (r < csize) {
+                const float mr = sm.part[r][g][HD];
+                const float wgt = (mr == -INFINITY) ? 0.f : expf(mr - M);
+                val += sm.part[r][g][d] * wgt;
+                L += sm.part[r][g][HD + 1] * wgt;
+            }
         }
         const int h = kvh * G + g;
-        if (nsplit == 1) {
+        if (ncl == 1) {
             a.out[size_t(b) * a.dim + size_t(h) * HD + d] = val / L;
         } else {
-            float *p = a.partial + ((size_t(b) * a.heads + h) * a.nsplit + split) * pstride;
+            float *p = a.partial + ((size_t(b) * a.heads + h) * ncl_max + cl) * pstride;
             p[d] = val;
             if (d == 0) {
                 p[HD] = M;
@@ -435,91 +614,92 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             }
         }
     }
-    if (nsplit == 1) return;
+    if (ncl == 1) {
+        trace_mark(trace, 5);
+        if (tid == 0) trace_cta_exit();
+        return;
+    }
 
-    // The last CTA of this (row, KV head) to finish folds the splits together.
+    // Several clusters: the last of them to finish folds their results.
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         const unsigned prev = atomicAdd(a.counters + size_t(b) * a.kv_heads + kvh, 1u);
-        is_last = (prev == unsigned(nsplit) - 1u);
+        sm.is_last = (prev == unsigned(ncl) - 1u);
     }
     __syncthreads();
-    if (!is_last) return;
+    if (!sm.is_last) return;
     __threadfence();
-    // Fold weights first (one thread per (head, split)), then every output element sums its
-    // splits with the loads issued four at a time.
-    for (int idx = tid; idx < G * kAttnMaxSplit; idx += kAttnThreads) {
-        const int g = idx / kAttnMaxSplit, s = idx - g * kAttnMaxSplit;
-        const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * a.nsplit * pstride;
-        wgt_s[g][s] = s < nsplit ? __ldcg(p + s * pstride + HD) : -INFINITY;
+    for (int idx = tid; idx < G * kAttnMaxFold; idx += kAttnThreads) {
+        const int g = idx / kAttnMaxFold, s = idx - g * kAttnMaxFold;
+        const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * ncl_max * pstride;
+        sm.wgt[g][s] = s < ncl ? __ldcg(p + s * pstride + HD) : -INFINITY;
     }
     __syncthreads();
     if (tid < G) {
         const int g = tid;
-        const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * a.nsplit * pstride;
+        const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * ncl_max * pstride;
         float M = -INFINITY;
-        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, wgt_s[g][s]);
+        for (int s = 0; s < ncl; ++s) M = fmaxf(M, sm.wgt[g][s]);
         float L = 0.f;
-        for (int s = 0; s < nsplit; ++s) {
-            const float ms = wgt_s[g][s];
-            const float w = (ms == -INFINITY) ? 0.f : expf(ms - M);
-            wgt_s[g][s] = w;
+        for (int s = 0; s < ncl; ++s) {
+            const float msv = sm.wgt[g][s];
+            const float w = (msv == -INFINITY) ? 0.f : expf(msv - M);
+            sm.wgt[g][s] = w;
             L += __ldcg(p + s * pstride + HD + 1) * w;
         }
-        inv_l[g] = 1.0f / L;
+        sm.inv_l[g] = 1.0f / L;
     }
     __syncthreads();
-    // Each thread owns G*HD/threads outputs and walks the splits eight at a time, so that all of a
-    // batch's loads are in flight together (the fold is pure L2 latency otherwise).
-    constexpr int kOuts = (G * HD + kAttnThreads - 1) / kAttnThreads;
-    float val[kOuts];
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, d = idx - g * HD;
+        const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * ncl_max * pstride + d;
+        float ld[kAttnMaxFold];
 #pragma unroll
-    for (int j = 0; j < kOuts; ++j) val[j] = 0.f;
-    for (int s0 = 0; s0 < nsplit; s0 += 8) {
-        float ld[kOuts][8];
+        for (int u = 0; u < kAttnMaxFold; ++u) ld[u] = u < ncl ? __ldcg(p + u * pstride) : 0.f;
+        float val = 0.f;
 #pragma unroll
-        for (int j = 0; j < kOuts; ++j) {
-            const int idx = tid + j * kAttnThreads;
-            const int g = idx / HD, d = idx - g * HD;
-            const float *p = a.partial + (size_t(b) * a.heads + kvh * G + g) * a.nsplit * pstride + d;
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                ld[j][u] = (idx < G * HD && s0 + u < nsplit) ? __ldcg(p + (s0 + u) * pstride) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < kOuts; ++j) {
-            const int idx = tid + j * kAttnThreads;
-            const int g = min(idx / HD, G - 1);
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (s0 + u < nsplit) val[j] += ld[j][u] * wgt_s[g][s0 + u];
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < kOuts; ++j) {
-        const int idx = tid + j * kAttnThreads;
-        if (idx < G * HD) {
-            const int g = idx / HD, d = idx - g * HD;
-            a.out[size_t(b) * a.dim + size_t(kvh * G + g) * HD + d] = val[j] * inv_l[g];
-        }
+        for (int u = 0; u < kAttnMaxFold; ++u)
+            if (u < ncl) val += ld[u] * sm.wgt[g][u];
+        a.out[size_t(b) * a.dim + size_t(kvh * G + g) * HD + d] = val * sm.inv_l[g];
     }
     if (tid == 0) a.counters[size_t(b) * a.kv_heads + kvh] = 0u;
 }
 
+// nsplit = cluster size * clusters per (row, KV head); the cluster size is the largest power of two
+// up to 8 that divides it.
+int attention_cluster_size(int nsplit) {
+    int c = 1;
+    while (c < kAttnMaxCluster && nsplit % (2 * c) == 0) c *= 2;
+    return c;
+}
+
 template <int HD, int G>
 cudaError_t attn_launch_t(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
+    const int csize = attention_cluster_size(a.nsplit);
+    if (a.nsplit / csize > kAttnMaxFold || (G * HD) % csize != 0) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.nsplit, a.kv_heads, width);
-    cfg.blockDim = dim3(kAttnThreads);
-    cfg.dynamicSmemBytes = 0;
+    cfg.blockDim = dim3(AttnShape<HD, G>::threads);
+    cfg.dynamicSmemBytes = sizeof(AttnSmem<HD, G>);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (programmatic) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (csize > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = csize;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = programmatic ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, G>, a);
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, G>, a, csize);
 }
 
 template <int HD>
@@ -535,10 +715,41 @@ cudaError_t attn_launch_hd(const AttnArgs &a, int width, cudaStream_t s, bool pd
 
 }  // namespace
 
-cudaError_t attention_configure() { return cudaSuccess; }
+namespace {
+template <int HD, int G>
+cudaError_t attn_configure_t() {
+    return cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                int(sizeof(AttnSmem<HD, G>)));
+}
+template <int HD>
+cudaError_t attn_configure_hd() {
+    cudaError_t e;
+    if ((e = attn_configure_t<HD, 1>()) != cudaSuccess) return e;
+    if ((e = attn_configure_t<HD, 2>()) != cudaSuccess) return e;
+    if ((e = attn_configure_t<HD, 4>()) != cudaSuccess) return e;
+    return attn_configure_t<HD, 8>();
+}
+}  // namespace
+
+cudaError_t attention_configure() {
+    const cudaError_t e = attn_configure_hd<128>();
+    return e != cudaSuccess ? e : attn_configure_hd<64>();
+}
 
 size_t attention_partial_floats(int width, int heads, int nsplit, int head_dim) {
     return size_t(width) * heads * nsplit * (head_dim + 2);
+}
+
+int attention_splits(int sm_count, int width, int kv_heads) {
+    // About two CTAs per SM over the whole launch: first a cluster of up to 8 per (row, KV head),
+    // then up to kAttnMaxFold clusters.
+    const int per = (2 * sm_count) / (width * kv_heads);
+    int c = 1;
+    while (c < kAttnMaxCluster && 2 * c <= per) c *= 2;
+    int ncl = per / c;
+    if (ncl < 1) ncl = 1;
+    if (ncl > 4) ncl = 4;
+    return c * ncl;
 }
 
 cudaError_t attention_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {

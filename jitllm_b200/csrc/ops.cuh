@@ -23,7 +23,7 @@ struct AttnArgs {
     const uint8_t *active;
     KvGeom kv;
     int layer, heads, kv_heads, head_dim, dim;
-    int nsplit;
+    int nsplit;  // from attention_splits()
     int append;  // 1: the CTA owning the new position rotates k and appends k,v; 0: pages already hold it
     float *partial;     // scratch [width][heads][nsplit][head_dim + 2]
     unsigned *counters; // scratch [width][kv_heads], zero between launches
@@ -32,6 +32,8 @@ struct AttnArgs {
 cudaError_t attention_configure();
 cudaError_t attention_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic);
 size_t attention_partial_floats(int width, int heads, int nsplit, int head_dim);
+// Key-range splits per (row, KV head) for a launch of `width` rows: cluster size times clusters.
+int attention_splits(int sm_count, int width, int kv_heads);
 
 // x[row] = getFloat of embedding row tokens[row] (inference/op/CpuOperations.java:30-32).
 cudaError_t embedding_launch(int type, const uint8_t *table, const int32_t *tokens,

@@ -54,10 +54,19 @@ int32_t jl_gemv_argmax_static(int32_t ggml_type, int64_t rows, int64_t cols, con
     if (rows <= 0 || rows > INT32_MAX || cols <= 0 || cols % 256 != 0 || cols > INT32_MAX)
         return static_fail(JL_ERR_INVALID, "GPUL-CFG-002: %s",
                            "rows must be in 1..2^31-1 and cols a positive multiple of 256");
+    // The kernel fetches weights with 16-byte bulk copies and the vectors with 16-byte loads; a
+    // pointer that breaks that would fault on the device, so it is refused here, before any launch.
+    if (reinterpret_cast<uintptr_t>(w_dev) % 16 != 0 || reinterpret_cast<uintptr_t>(x_dev) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(norm_w_dev) % 16 != 0)
+        return static_fail(JL_ERR_INVALID, "GPUL-CFG-002: %s", "w_dev, x_dev and norm_w_dev must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(y_dev) % 4 != 0 || reinterpret_cast<uintptr_t>(token_dev) % 4 != 0)
+        return static_fail(JL_ERR_INVALID, "GPUL-CFG-002: %s", "y_dev and token_dev must be 4-byte aligned");
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
-    if (e != cudaSuccess || device < 0 || device >= kMaxDevices)
+    if (e != cudaSuccess || device < 0)
         return static_fail(JL_ERR_CUDA, "CUDA: no current device (%s)", cudaGetErrorString(e));
+    if (device >= kMaxDevices)
+        return static_fail(JL_ERR_UNSUPPORTED, "GPUL-CFG-002: unsupported: %s", "device ordinal beyond 63");
     unsigned char *scratch = nullptr;
     {
         // Set-up, once per device, with that device current: the array's name is only a host-side
@@ -111,6 +120,29 @@ int32_t jl_gemv_argmax_static(int32_t ggml_type, int64_t rows, int64_t cols, con
     e = gemv_launch(a, plan, s, false);
     if (e != cudaSuccess)
         return static_fail(JL_ERR_CUDA, "CUDA: launch failed: %s", cudaGetErrorString(e));
+    return JL_OK;
+}
+
+int32_t jl_static_status(void *stream) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= kMaxDevices)
+        return static_fail(JL_ERR_CUDA, "CUDA: no current device (%s)", cudaGetErrorString(e));
+    unsigned char *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        scratch = g_scratch_addr[device];
+    }
+    if (scratch == nullptr)
+        return static_fail(JL_ERR_STATE, "GPUL-CFG-002: %s", "jl_gemv_argmax_static has not run on this device");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int status = 0;
+    e = cudaMemcpyAsync(&status, scratch + size_t(kStaticMaxCtas) * 8 + 128, sizeof status, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return static_fail(JL_ERR_CUDA, "CUDA: %s", cudaGetErrorString(e));
+    if (status == kDevTimeout)
+        return static_fail(JL_ERR_TIMEOUT, "GPUL-RUN-001: %s",
+                           "the kernel gave up waiting for an asynchronous copy; y_dev and token_dev are not valid");
     return JL_OK;
 }
 

@@ -103,6 +103,15 @@ def get_float(t: int, blocks: np.ndarray, index: int) -> float:
     return float(lib().orc_get_float(int(t), _p(blocks), index))
 
 
+def rmsnorm(x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+    """CpuOperations.rmsNorm (inference/op/CpuOperations.java:55-73) of one vector."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    weight = np.ascontiguousarray(weight, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().orc_rmsnorm(_p(out), _p(x), _p(weight), int(x.size), C.c_float(eps))
+    return out
+
+
 def matmul(t: int, w: np.ndarray, x: np.ndarray, rows: int, cols: int) -> np.ndarray:
     w = np.ascontiguousarray(w, dtype=np.uint8)
     x = np.ascontiguousarray(x, dtype=np.float32)
