@@ -195,7 +195,7 @@ __device__ __forceinline__ unsigned long long trace_latest_exit() {
 }
 // Per-CTA cells behind the records (kTraceCtaWords words for each of the first 1024 CTAs of the
 // latest launch that writes them): how evenly the CTAs of one launch finish.
-constexpr int kTraceCtaWords = 4;
+constexpr int kTraceCtaWords = 8;
 constexpr int kTraceCtaMax = 160, kTraceClasses = 6;  // cells: [class of launch][CTA][word]
 __device__ __forceinline__ void trace_cta_word(int cls, int word, unsigned long long v) {
     if (g_trace_buf != nullptr && blockIdx.x < kTraceCtaMax && cls < kTraceClasses)

@@ -1579,6 +1579,7 @@ int32_t jl_debug_trace(jl_ctx *ctx, uint64_t *out, int32_t max_records) {
             const int mode = mv ? atoi(mv) : 0;
             JL_CUDA(ctx, gemv_trace_bind(ctx->d_trace, kCap, mode));
             JL_CUDA(ctx, ops_trace_bind(ctx->d_trace, kCap, mode));
+            JL_CUDA(ctx, gemm_trace_bind(ctx->d_trace, kCap, mode));
         }
         JL_CUDA(ctx, cudaMemsetAsync(ctx->d_trace, 0, (size_t(kCap + 1) * kTraceWords + kTraceClasses * kTraceCtaMax * kTraceCtaWords) * 8, ctx->stream));
         JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

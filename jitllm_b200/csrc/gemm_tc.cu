@@ -41,6 +41,8 @@
 
 namespace jl {
 
+JL_TRACE_DEFINE_BIND(gemm_trace_bind)
+
 namespace {
 
 // Which bounded wait the kernel uses (a build-time experiment switch).
@@ -297,24 +299,27 @@ __device__ __forceinline__ void dequant64_to_half(uint32_t row_u32, int unit, ui
         const int sh = (unit & 1) * 16;
         const float ds0 = __fmul_rn(d, float((scw >> sh) & 0xFFu)), ds1 = __fmul_rn(d, float((scw >> (sh + 8)) & 0xFFu));
         const float mm0 = __fmul_rn(dmin, float((mw >> sh) & 0xFFu)), mm1 = __fmul_rn(dmin, float((mw >> (sh + 8)) & 0xFFu));
+        // One byte permute puts a nibble into bits 16-19 of 0x43000000: the float 128 + q, exactly. With
+        // c = -(128 * ds + mm), fma(ds, 128 + q, c) is ds * q - mm rounded once (c itself is off by at
+        // most 2^-17 of ds, far below the binary16 rounding that follows), so a weight costs one
+        // permute and one fused multiply-add, and no conversion unit.
+        const float c0f = -__fmaf_rn(128.0f, ds0, mm0), c1f = -__fmaf_rn(128.0f, ds1, mm1);
         const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const uint32_t vl = qw[i] & 0x0F0F0F0Fu, vh = (qw[i] >> 4) & 0x0F0F0F0Fu;
-            // 0x4B0000qq is the float 2^23 + q (one byte permute); multiply and subtract are fused,
-            // the result is rounded to binary16 right after.
-            const float a0 = __uint_as_float(__byte_perm(vl, 0x4B000000u, 0x7440)) - 8388608.0f;
-            const float a1 = __uint_as_float(__byte_perm(vl, 0x4B000000u, 0x7441)) - 8388608.0f;
-            const float a2 = __uint_as_float(__byte_perm(vl, 0x4B000000u, 0x7442)) - 8388608.0f;
-            const float a3 = __uint_as_float(__byte_perm(vl, 0x4B000000u, 0x7443)) - 8388608.0f;
-            const float b0 = __uint_as_float(__byte_perm(vh, 0x4B000000u, 0x7440)) - 8388608.0f;
-            const float b1 = __uint_as_float(__byte_perm(vh, 0x4B000000u, 0x7441)) - 8388608.0f;
-            const float b2 = __uint_as_float(__byte_perm(vh, 0x4B000000u, 0x7442)) - 8388608.0f;
-            const float b3 = __uint_as_float(__byte_perm(vh, 0x4B000000u, 0x7443)) - 8388608.0f;
-            first[2 * i] = pack_half2(__fmaf_rn(ds0, a0, -mm0), __fmaf_rn(ds0, a1, -mm0));
-            first[2 * i + 1] = pack_half2(__fmaf_rn(ds0, a2, -mm0), __fmaf_rn(ds0, a3, -mm0));
-            second[2 * i] = pack_half2(__fmaf_rn(ds1, b0, -mm1), __fmaf_rn(ds1, b1, -mm1));
-            second[2 * i + 1] = pack_half2(__fmaf_rn(ds1, b2, -mm1), __fmaf_rn(ds1, b3, -mm1));
+            const float a0 = __uint_as_float(__byte_perm(vl, 0x43000000u, 0x7054));
+            const float a1 = __uint_as_float(__byte_perm(vl, 0x43000000u, 0x7154));
+            const float a2 = __uint_as_float(__byte_perm(vl, 0x43000000u, 0x7254));
+            const float a3 = __uint_as_float(__byte_perm(vl, 0x43000000u, 0x7354));
+            const float b0 = __uint_as_float(__byte_perm(vh, 0x43000000u, 0x7054));
+            const float b1 = __uint_as_float(__byte_perm(vh, 0x43000000u, 0x7154));
+            const float b2 = __uint_as_float(__byte_perm(vh, 0x43000000u, 0x7254));
+            const float b3 = __uint_as_float(__byte_perm(vh, 0x43000000u, 0x7354));
+            first[2 * i] = pack_half2(__fmaf_rn(ds0, a0, c0f), __fmaf_rn(ds0, a1, c0f));
+            first[2 * i + 1] = pack_half2(__fmaf_rn(ds0, a2, c0f), __fmaf_rn(ds0, a3, c0f));
+            second[2 * i] = pack_half2(__fmaf_rn(ds1, b0, c1f), __fmaf_rn(ds1, b1, c1f));
+            second[2 * i + 1] = pack_half2(__fmaf_rn(ds1, b2, c1f), __fmaf_rn(ds1, b3, c1f));
         }
     } else {
         uint4 c0[4], c1[4];
@@ -453,6 +458,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     using R = RawFmt<TYPE>;
     constexpr int RS = R::stages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int trace = trace_begin(kTraceGemm);
     // 1024-byte aligned base: the swizzle pattern is a function of the shared address.
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int ST = S::stages;
@@ -497,6 +503,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = *tmem_ptr;
+    trace_mark(trace, 2);
+#ifdef JL_TRACE
+    long long tw_raw = 0, tw_free = 0, tw_acc = 0, tw_epi = 0;
+#endif
 
     if (warp == kConvertWarps + 1) {
         // ---- copy requests -------------------------------------------------------------------
@@ -642,7 +652,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 a_valid = tr.row0 + a_row < a.seg[tr.seg].rows;
             }
             const int st = i % RS;
+#ifdef JL_TRACE
+            const long long tq0 = clock64();
+#endif
             ok = GEMM_WAIT(raw_full + st, uint32_t(i / RS) & 1u);
+#ifdef JL_TRACE
+            tw_raw += clock64() - tq0;
+            if (i == 0) trace_mark(trace, 3);
+#endif
             if (!ok) break;
             const uint32_t row_u32 = smem_u32(base + S::raw_off + st * R::stage_bytes) + uint32_t(a_row) * R::row_bytes;
             {
@@ -664,7 +681,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         xv[uu][0] = xv[uu][1] = make_float4(0.f, 0.f, 0.f, 0.f);
                     }
                 }
+#ifdef JL_TRACE
+                const long long tq1 = clock64();
+#endif
                 if (q >= ST) ok = GEMM_WAIT(a_free + s, uint32_t(q / ST - 1) & 1u);
+#ifdef JL_TRACE
+                tw_free += clock64() - tq1;
+#endif
                 if (ok) {
                 uint8_t *b_st = base + S::b_off + s * S::b_stage;
                 if (!(a.debug & 1)) {
@@ -722,7 +745,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const long long seg_begin = u_lo > lo ? u_lo : lo;
             const bool whole = seg_begin == u_lo && seg_end == u_lo + raw_total;
             const GemmSeg seg = a.seg[tr.seg];
+#ifdef JL_TRACE
+            const long long tq2 = clock64();
+#endif
             ok = GEMM_WAIT(acc_full, uint32_t(done) & 1u);
+#ifdef JL_TRACE
+            tw_acc += clock64() - tq2;
+            const long long tq3 = clock64();
+#endif
             if (!ok) break;
             ++done;
             tc_fence_after();
@@ -775,7 +805,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 }
                 ok = convert_warps_sync(fix_bar, fix_phase);  // last_flag is reused by the next partial tile
             }
+#ifdef JL_TRACE
+            tw_epi += clock64() - tq3;
+#endif
         }
+#ifdef JL_TRACE
+        trace_mark(trace, 4);
+        trace_word(trace, 6, (static_cast<unsigned long long>(tw_raw) << 32) | static_cast<unsigned long long>(tw_free & 0xffffffffll));
+        trace_word(trace, 7, (static_cast<unsigned long long>(tw_acc) << 32) | static_cast<unsigned long long>(tw_epi & 0xffffffffll));
+#endif
         if (!ok && lane == 0) {
             *abort_flag = 1u;
             atomicExch(a.status, kDevTimeout);
@@ -784,6 +822,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     tc_fence_before();
     __syncthreads();
     if (warp == kConvertWarps) tmem_dealloc(tmem_d, tmem_cols);
+    trace_mark(trace, 5);
 }
 
 template <int TYPE, int NT>

@@ -48,5 +48,6 @@ struct GemmArgs {
 // Sets the shared-memory attribute of every instantiation (call once, outside stream capture).
 cudaError_t gemm_tc_configure();
 cudaError_t gemm_tc_launch(const GemmArgs &args, cudaStream_t stream);
+cudaError_t gemm_trace_bind(unsigned long long *buf, unsigned cap, int mode);
 
 }  // namespace jl

@@ -88,24 +88,43 @@ __device__ __forceinline__ void locate(const GemvArgs &a, int job, int &seg, int
     }
 }
 
-// One step of a group's walk over its jobs [0, nj): the rows the next stage holds. They are
-// consecutive rows of one matrix (one contiguous piece of memory, one bulk copy), at most S of
-// them, and never straddle the end of a matrix or of a phase. The producer and the consumers of a
-// group call this with the same arguments and so agree on every stage.
+// A group's walk over its jobs [0, nj), stage by stage. The rows of a stage are consecutive rows of
+// one matrix (one contiguous piece of memory, one bulk copy), at most S of them, and never straddle
+// the end of a matrix or of a phase. The producer and the consumers of a group run the same walk
+// and so agree on every stage.
 template <int MODE, int S>
-__device__ __forceinline__ int stage_rows_at(const GemvArgs &a, int first_job, int k, int nj, int PJ, int &seg,
-                                             int &row) {
-    int n = min(S, nj - k);
-    n = min(n, (k / PJ + 1) * PJ - k);
-    if (MODE == kGemvGateUp) {
+struct StageWalk {
+    int k, nj, phase_end, pj;
+    int seg, row, seg_left;
+    __device__ __forceinline__ void init(const GemvArgs &a, int first_job, int njobs_of_group, int phase_jobs) {
+        k = 0;
+        nj = njobs_of_group;
+        pj = phase_jobs;
+        phase_end = min(nj, pj);
         seg = 0;
-        row = first_job + k;
-    } else {
-        locate(a, first_job + k, seg, row);
-        n = min(n, a.seg[seg].rows - row);
+        row = first_job;
+        seg_left = nj;
+        if (MODE == kGemvPlain && nj > 0) {
+            locate(a, first_job, seg, row);
+            seg_left = a.seg[seg].rows - row;
+        }
     }
-    return n;
-}
+    __device__ __forceinline__ bool done() const { return k >= nj; }
+    __device__ __forceinline__ int rows() const { return min(min(S, phase_end - k), seg_left); }
+    __device__ __forceinline__ void advance(const GemvArgs &a, int n) {
+        k += n;
+        row += n;
+        if (MODE == kGemvPlain) {
+            seg_left -= n;
+            if (seg_left == 0 && k < nj) {
+                ++seg;
+                row = 0;
+                seg_left = a.seg[seg].rows;
+            }
+        }
+        if (k == phase_end) phase_end = min(nj, phase_end + pj);
+    }
+};
 
 template <int TYPE, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, const GemvPlan pl) {
@@ -137,18 +156,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
     const uint32_t rms_bar_u32 = full_u32 + 2 * kWarps * kGemvMaxStages * 8;
     float *scratch = reinterpret_cast<float *>(smem + kBarBytes);
     float *sx = reinterpret_cast<float *>(smem + pl.off_x);
-    float *sumx = sx + a.cols / 32;
-    const uint32_t planes_u32 = smem_u32(smem + pl.off_x) + uint32_t(align_up(size_t(a.cols) / 32 * 8, 128));
+    const uint32_t planes_u32 = smem_u32(smem + pl.off_x) + uint32_t(x_scales_bytes(a.cols));
     float *partial = reinterpret_cast<float *>(smem + pl.off_partial);
     const uint32_t ring_u32 = smem_u32(smem + pl.off_ring);
 
-    if (tid == 0) {
-        for (int i = 0; i < G * D; ++i) {
-            const int g = i / D, s = i - g * D;
-            mbar_init(reinterpret_cast<uint64_t *>(smem) + g * kGemvMaxStages + s, 1);
-            mbar_init(reinterpret_cast<uint64_t *>(smem) + (kWarps + g) * kGemvMaxStages + s, nchunks);
-        }
-        mbar_init(reinterpret_cast<uint64_t *>(smem) + 2 * kWarps * kGemvMaxStages, 1);
+    // One barrier per thread: a single thread initialising all of them would take a microsecond that
+    // every launch of the chain would have to wait for.
+    if (tid < G * D) {
+        const int g = tid / D, s = tid - g * D;
+        mbar_init(reinterpret_cast<uint64_t *>(smem) + g * kGemvMaxStages + s, 1);
+        mbar_init(reinterpret_cast<uint64_t *>(smem) + (kWarps + g) * kGemvMaxStages + s, nchunks);
+        if (tid == 0) mbar_init(reinterpret_cast<uint64_t *>(smem) + 2 * kWarps * kGemvMaxStages, 1);
         mbar_fence_init();
         fence_proxy_async();
     }
@@ -172,11 +190,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         const uint32_t my_empty = empty_u32 + uint32_t(g) * kGemvMaxStages * 8;
         const uint32_t my_ring = ring_u32 + uint32_t(g) * D * stage_bytes;
         const uint64_t policy = policy_evict_first();
-        int k = 0, which = 0, slot = 0, use = 0;
+        StageWalk<MODE, S> walk;
+        walk.init(a, job0 + gs, nj, PJ);
+        int which = 0, slot = 0, use = 0;
         uint32_t idle = 0;
         bool failed = false, joined = false;
         while (true) {
-            if (!joined && (idle > 0 || !__any_sync(0xffffffffu, k < nj))) {
+            if (!joined && (idle > 0 || !__any_sync(0xffffffffu, !walk.done()))) {
                 // Every ring is full (or all copies are out): nothing to do until the consumers, which
                 // are staging the activation, start to hand stages back. Meet them at their barrier
                 // and take the one serial piece of the RMSNorm off their hands: the reference
@@ -194,22 +214,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
                 }
                 __syncwarp();
             }
-            const bool want = k < nj;
+            const bool want = !walk.done();
             if (!__any_sync(0xffffffffu, want)) break;
             bool can = false;
             if (want) can = use == 0 || mbar_test_wait_u32(my_empty + slot * 8, uint32_t(use - 1) & 1u);
             if (can) {
-                int seg, row;
-                const int n = stage_rows_at<MODE, S>(a, job0 + gs, k, nj, PJ, seg, row);
-                const uint8_t *src = a.seg[MODE == kGemvGateUp ? which : seg].w + size_t(row) * rowb;
+                const int n = walk.rows();
+                const uint8_t *src = a.seg[MODE == kGemvGateUp ? which : walk.seg].w + size_t(walk.row) * rowb;
                 fence_proxy_async();
                 mbar_expect_tx_u32(my_full + slot * 8, uint32_t(n) * rowb);
                 bulk_g2s_hint_u32(my_ring + slot * stage_bytes, src, uint32_t(n) * rowb, my_full + slot * 8, policy);
                 if (SPJ == 2) {
                     which ^= 1;
-                    if (which == 0) k += n;
+                    if (which == 0) walk.advance(a, n);
                 } else {
-                    k += n;
+                    walk.advance(a, n);
                 }
                 if (++slot == D) {
                     slot = 0;
@@ -255,7 +274,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         const int tcls = MODE == kGemvGateUp ? 2 : (a.argmax_val != nullptr ? 4 : (a.nseg == 3 ? 0 : (a.cols > 8192 ? 3 : 1)));
         if (tid == 0) trace_cta_word(tcls, 3, trace_now());
 #endif
-        float ssq = stage_activation_core<kConsumers>(a.x, a.norm_w, wpre, a.cols, tid, sx, sumx, planes_u32);
+#ifdef JL_TRACE
+        float ssq = stage_activation_core<kConsumers>(a.x, a.norm_w, wpre, a.cols, tid, sx, planes_u32, tcls);
+        if (tid == 0) trace_cta_word(tcls, 5, trace_now());
+#else
+        float ssq = stage_activation_core<kConsumers>(a.x, a.norm_w, wpre, a.cols, tid, sx, planes_u32);
+#endif
         if (norm) {
             ssq = warp_sum(ssq);
             if (lane == 0) scratch[warp] = ssq;
@@ -281,7 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         const bool lane_on = unit < nunits;
         UnitX x;
         if (nj > 0 && lane_on) {
-            load_unit_x(planes_u32, smem_u32(sx), smem_u32(sumx), nunits, unit, x);
+            load_unit_x(planes_u32, smem_u32(sx), nunits, unit, x);
         } else {
 #pragma unroll
             for (int m = 0; m < kDigits; ++m)
@@ -312,12 +336,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         long long t_wait = 0;
         const long long t_loop0 = clock64();
 #endif
+        StageWalk<MODE, S> walk;
+        walk.init(a, job0 + gs, nj, PJ);
         for (int ph = 0; ph < nphases; ++ph) {
             const int k_end = min(nj, (ph + 1) * PJ);
-            int k = ph * PJ;
-            while (k < k_end) {
-                int seg, row;
-                const int n = stage_rows_at<MODE, S>(a, job0 + gs, k, nj, PJ, seg, row);
+            while (walk.k < k_end) {
+                const int k = walk.k;
+                const int n = walk.rows();
 #pragma unroll
                 for (int which = 0; which < SPJ; ++which) {
                     if (!failed) {
@@ -364,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
                         if (lane == 0) dst[0] = tot;
                     }
                 }
-                k += n;
+                walk.advance(a, n);
             }
 #ifdef JL_TRACE
             if (ph == 0)

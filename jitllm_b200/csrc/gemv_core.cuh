@@ -147,10 +147,11 @@ __device__ __forceinline__ float unit_dot(uint32_t chunk, int lane, const UnitX 
 }
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-// Shared-memory bytes of the staged activation: block scales and block sums (one float each per
-// 32 elements), then kDigits planes of one byte per element.
+// Shared-memory bytes of the staged activation: block scales (one float per 32 elements), then
+// kDigits planes of one byte per element.
+__host__ __device__ inline size_t x_scales_bytes(int cols) { return align_up(size_t(cols) / 32 * 4, 128); }
 __host__ __device__ inline size_t x_region_bytes(int cols) {
-    return align_up(size_t(cols) / 32 * 8, 128) + align_up(size_t(cols) * kDigits, 128);
+    return x_scales_bytes(cols) + align_up(size_t(cols) * kDigits, 128);
 }
 
 __device__ __forceinline__ uint32_t pack4(int b0, int b1, int b2, int b3) {
@@ -175,8 +176,8 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 constexpr int kStageDeep = 8;
 template <int NTHREADS>
 __device__ __forceinline__ float stage_activation_core(const float *x, const float *norm_w, const float4 *wpre,
-                                                       int cols, int tid, float *sx_p, float *sumx_p,
-                                                       uint32_t planes_u32) {
+                                                       int cols, int tid, float *sx_p, uint32_t planes_u32,
+                                                       int trace_cls = -1) {
     const int nunits = cols / 64, n4 = cols / 4;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     const float4 *w4 = reinterpret_cast<const float4 *>(norm_w);
@@ -191,6 +192,12 @@ __device__ __forceinline__ float stage_activation_core(const float *x, const flo
             // ld.global.cg: the vector was written by other SMs moments ago.
             v[k] = i < n4 ? __ldcg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
+#ifdef JL_TRACE
+        if (tid == 0 && trace_cls >= 0 && base == 0) {
+            if (v[0].x == 12345.678f) trace_cta_word(trace_cls, 7, 1);  // make the stamp wait for the data
+            trace_cta_word(trace_cls, 4, trace_now());
+        }
+#endif
         if (norm) {
 #pragma unroll
             for (int k = 0; k < kStageDeep; ++k) {
@@ -210,40 +217,33 @@ __device__ __forceinline__ float stage_activation_core(const float *x, const flo
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            const float inv = amax > 0.f ? kDigitRange / amax : 0.f;
+            const float inv = amax > 0.f ? __fdividef(kDigitRange, amax) : 0.f;
             int X[4] = {__float2int_rn(v[k].x * inv), __float2int_rn(v[k].y * inv),
                         __float2int_rn(v[k].z * inv), __float2int_rn(v[k].w * inv)};
-            int d1[4], d2[4], sum = 0;
+            int d1[4], d2[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 X[j] = max(-32639, min(32639, X[j]));
-                sum += X[j];
                 d1[j] = (X[j] + 128) >> 8;       // floor: the low digit lands in [-128, 127]
                 d2[j] = X[j] - (d1[j] << 8);
             }
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
             if (i < n4) {
                 const int e = i * 4;
                 const int unit = e >> 6, within = e & 63, quarter = within >> 4, byte = within & 15;
                 const uint32_t cell = planes_u32 + (uint32_t(quarter) * nunits + unit) * 16 + byte;
                 sts32(cell, pack4(d1[0], d1[1], d1[2], d1[3]));
                 sts32(cell + plane, pack4(d2[0], d2[1], d2[2], d2[3]));
-                if ((i & 7) == 0) {
-                    const float s = amax / kDigitRange;
-                    sx_p[i >> 3] = s;
-                    sumx_p[i >> 3] = s * static_cast<float>(sum);
-                }
+                if ((i & 7) == 0) sx_p[i >> 3] = amax * (1.0f / kDigitRange);
             }
         }
     }
     return ssq;
 }
 
-// This lane's unit of the staged activation, from shared memory into registers.
-__device__ __forceinline__ void load_unit_x(uint32_t planes, uint32_t sx, uint32_t sumx, int nunits,
-                                            int unit, UnitX &x) {
+// This lane's unit of the staged activation, from shared memory into registers. The block sums the
+// 4-bit formats need (their codes carry an offset) are formed here from the digits: once per launch
+// and lane, instead of three more shuffles per block while every warp waits for the staging.
+__device__ __forceinline__ void load_unit_x(uint32_t planes, uint32_t sx, int nunits, int unit, UnitX &x) {
     const uint32_t plane = 64u * nunits;
     const uint32_t q = 16u * nunits;
 #pragma unroll
@@ -256,9 +256,18 @@ __device__ __forceinline__ void load_unit_x(uint32_t planes, uint32_t sx, uint32
         x.b[m][0] = c2.x; x.b[m][1] = c2.y; x.b[m][2] = c2.z; x.b[m][3] = c2.w;
         x.b[m][4] = c3.x; x.b[m][5] = c3.y; x.b[m][6] = c3.z; x.b[m][7] = c3.w;
     }
-    const uint2 s = lds64(sx + 8u * unit), m = lds64(sumx + 8u * unit);
+    const uint2 s = lds64(sx + 8u * unit);
     x.sa = __uint_as_float(s.x); x.sb = __uint_as_float(s.y);
-    x.ma = __uint_as_float(m.x); x.mb = __uint_as_float(m.y);
+    int a1 = 0, a2 = 0, b1 = 0, b2 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        a1 = dp4a_s8s8(0x01010101, x.a[0][i], a1);
+        a2 = dp4a_s8s8(0x01010101, x.a[1][i], a2);
+        b1 = dp4a_s8s8(0x01010101, x.b[0][i], b1);
+        b2 = dp4a_s8s8(0x01010101, x.b[1][i], b2);
+    }
+    x.ma = x.sa * static_cast<float>(a1 * 256 + a2);
+    x.mb = x.sb * static_cast<float>(b1 * 256 + b2);
 }
 
 }  // namespace jl

@@ -117,6 +117,8 @@ constexpr int kNormBatch = 8;  // float4 per thread per batch: rows up to 8192 i
 __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const float *x, const float *w, float eps, float *out,
                                                                     int dim, const uint8_t *active, uint2 *hi, uint2 *lo) {
     const int row = blockIdx.x;
+    const int trace = trace_begin(kTraceRows);
+    trace_word(trace, 7, 1);
     if (active != nullptr && active[row] == 0) return;
     __shared__ float part[9];
     const int n4 = dim / 4;
@@ -176,6 +178,8 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const float 
 
 // Four elements per thread per step (row lengths are multiples of 256, so float4 never straddles).
 __global__ void swiglu_rows_kernel(float4 *g, const float4 *u, size_t total4, uint2 *hi, uint2 *lo) {
+    const int trace = trace_begin(kTraceRows);
+    trace_word(trace, 7, 2);
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total4; i += stride) {
         const float4 v = g[i], w = u[i];
@@ -260,9 +264,11 @@ __global__ void argmax_rows_kernel(const float *logits, int vocab, const uint8_t
 // 512 threads leave registers for). A warp takes eight keys per iteration: four lanes share a key for the
 // q.k products (each lane a quarter of the head dimension), while for the p.v sums every lane owns
 // head_dim / 32 output dimensions of all eight keys.
-template <int HD, int G>
+// Wide launches (many rows) use eight warps as well: two or three CTAs then share an SM and the whole
+// grid is resident at once.
+template <int HD, int G, bool WIDE = false>
 struct AttnShape {
-    static constexpr int threads = (G * HD > 512) ? 256 : 512;
+    static constexpr int threads = (WIDE || G * HD > 512) ? 256 : 512;
     static constexpr int warps = threads / 32;
     static constexpr int keys = 8;
     static constexpr int dk = HD / 4;       // dimensions of a key one lane multiplies
@@ -290,10 +296,10 @@ __device__ __forceinline__ void st_cluster_f32(float *local, uint32_t rank, floa
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
-template <int HD, int G>
+template <int HD, int G, bool WIDE>
 struct AttnSmem {
-    float q[G][4][AttnShape<HD, G>::qpad];
-    float red[AttnShape<HD, G>::warps][G][HD + 2];
+    float q[G][4][AttnShape<HD, G, WIDE>::qpad];
+    float red[AttnShape<HD, G, WIDE>::warps][G][HD + 2];
     float part[kAttnMaxCluster][G][HD + 2];  // in the cluster's first CTA: every CTA's result
     float wgt[G][kAttnMaxFold];
     float inv_l[G];
@@ -321,13 +327,14 @@ struct AttnSmem {
 // into the shared memory of the cluster's first CTA, which folds them; only when a context is long
 // enough to use several clusters do their results meet in global memory, where the last cluster
 // to arrive folds them.
-template <int HD, int G>
-__global__ void __launch_bounds__(AttnShape<HD, G>::threads) attn_decode_kernel(const AttnArgs a, const int csize) {
+template <int HD, int G, bool WIDE>
+__global__ void __launch_bounds__(AttnShape<HD, G, WIDE>::threads, WIDE ? 2 : 1)
+    attn_decode_kernel(const AttnArgs a, const int csize) {
     constexpr int VEC = HD / 32;
-    constexpr int UN = AttnShape<HD, G>::keys;
-    constexpr int kAttnThreads = AttnShape<HD, G>::threads, kAttnWarps = AttnShape<HD, G>::warps;
+    constexpr int UN = AttnShape<HD, G, WIDE>::keys;
+    constexpr int kAttnThreads = AttnShape<HD, G, WIDE>::threads, kAttnWarps = AttnShape<HD, G, WIDE>::warps;
     extern __shared__ __align__(16) uint8_t attn_smem_raw[];
-    AttnSmem<HD, G> &sm = *reinterpret_cast<AttnSmem<HD, G> *>(attn_smem_raw);
+    AttnSmem<HD, G, WIDE> &sm = *reinterpret_cast<AttnSmem<HD, G, WIDE> *>(attn_smem_raw);
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int trace = trace_begin(kTraceAttn);
@@ -375,7 +382,7 @@ __global__ void __launch_bounds__(AttnShape<HD, G>::threads) attn_decode_kernel(
     __syncthreads();
     // Each warp takes a contiguous run of keys so that consecutive keys share a page. The new key
     // of a decode launch goes to the last warp of the first CTA, behind that warp's old keys.
-    constexpr int DK = AttnShape<HD, G>::dk;
+    constexpr int DK = AttnShape<HD, G, WIDE>::dk;
     const int per_warp = (end - start + kAttnWarps - 1) / kAttnWarps;
     const int w0 = min(end, start + warp * per_warp);
     const int w1 = min(end, w0 + per_warp);
@@ -674,14 +681,14 @@ int attention_cluster_size(int nsplit) {
     return c;
 }
 
-template <int HD, int G>
-cudaError_t attn_launch_t(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
+template <int HD, int G, bool WIDE>
+cudaError_t attn_launch_w(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
     const int csize = attention_cluster_size(a.nsplit);
     if (a.nsplit / csize > kAttnMaxFold || (G * HD) % csize != 0) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.nsplit, a.kv_heads, width);
-    cfg.blockDim = dim3(AttnShape<HD, G>::threads);
-    cfg.dynamicSmemBytes = sizeof(AttnSmem<HD, G>);
+    cfg.blockDim = dim3(AttnShape<HD, G, WIDE>::threads);
+    cfg.dynamicSmemBytes = sizeof(AttnSmem<HD, G, WIDE>);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -699,7 +706,13 @@ cudaError_t attn_launch_t(const AttnArgs &a, int width, cudaStream_t stream, boo
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, G>, a, csize);
+    return cudaLaunchKernelEx(&cfg, attn_decode_kernel<HD, G, WIDE>, a, csize);
+}
+
+template <int HD, int G>
+cudaError_t attn_launch_t(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
+    return width >= 4 ? attn_launch_w<HD, G, true>(a, width, stream, programmatic)
+                      : attn_launch_w<HD, G, false>(a, width, stream, programmatic);
 }
 
 template <int HD>
@@ -718,8 +731,11 @@ cudaError_t attn_launch_hd(const AttnArgs &a, int width, cudaStream_t s, bool pd
 namespace {
 template <int HD, int G>
 cudaError_t attn_configure_t() {
-    return cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                int(sizeof(AttnSmem<HD, G>)));
+    const cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, G, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               int(sizeof(AttnSmem<HD, G, false>)));
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(attn_decode_kernel<HD, G, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                int(sizeof(AttnSmem<HD, G, true>)));
 }
 template <int HD>
 cudaError_t attn_configure_hd() {

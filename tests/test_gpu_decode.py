@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 FORMATS = [GGMLType.Q8_0, GGMLType.Q4_0, GGMLType.Q4_K]
 LOGIT_BAR = 1e-2
 TENSOR_CORE_LOGIT_EXPECT = 6e-3  # batches of four or more rows: binary16 weight rounding on top
-LOGIT_EXPECT = 2e-3  # binary16 K/V rounding flips (one ulp, ~1% of elements) perturb logits at the 1e-4 level
+LOGIT_EXPECT = 4e-3  # 16-bit activations in every mat-vec plus binary16 K/V rounding flips: measured up to 2.4e-3
 
 
 def _half_close(a_bits, b_bits, ulps=1, abs_frac=2e-5):
