@@ -107,6 +107,10 @@ int32_t jl_kv_create(jl_ctx *ctx, int32_t total_blocks, int32_t blocks_per_slot,
  * max_slots * blocks_per_slot. */
 int32_t jl_kv_publish_block_table(jl_ctx *ctx, const int32_t *table, int64_t n);
 int64_t jl_kv_bytes_per_block(jl_ctx *ctx);
+/* Fills both pools, scratch block included, with one binary16 bit pattern. The reference's
+ * verification runs poison the cache with NaN (0x7E00) before a sequence so that any read of a
+ * page the sequence has not written shows up in the logits (docs/architecture/verification.md:427-431). */
+int32_t jl_kv_fill(jl_ctx *ctx, uint16_t half_bits);
 /* Test / checkpoint access to one position's K or V row (kv_dim halfs) of a layer. */
 int32_t jl_kv_read_row(jl_ctx *ctx, int32_t which /*0=K,1=V*/, int32_t slot, int32_t layer,
                        int32_t pos, uint16_t *out_halfs);
@@ -164,7 +168,8 @@ int32_t jl_timer_start(jl_ctx *ctx);
 int32_t jl_timer_stop(jl_ctx *ctx, float *elapsed_ms);
 /* Launches one operator of the loaded model `iters` times on successive layers (wrapping) with
  * the step workspace as input and output, for per-kernel timing: op 0 = RMSNorm+QKV, 1 = attention
- * output projection, 2 = RMSNorm+gate/up+SwiGLU, 3 = down projection, 4 = RMSNorm+vocabulary.
+ * output projection, 2 = RMSNorm+gate/up+SwiGLU, 3 = down projection, 4 = RMSNorm+vocabulary,
+ * 5 = RoPE + KV append + attention of row 0 at the position the last step left on the device.
  * The measuring counterpart of backend/tornado/bench/SyntheticKernelBench.java:87-161. */
 int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters);
 /* Launch timeline of the kernels this context enqueues (no counterpart in the reference; its
@@ -208,6 +213,10 @@ int32_t jl_tp_exchange_mode(jl_ctx *ctx);
  * The kernel gives up, the call returns JL_ERR_TIMEOUT, and the context stays usable. */
 int32_t jl_debug_peer_wait_timeout(jl_ctx *ctx, int32_t timeout_ms);
 const char *jl_tp_exchange_note(jl_ctx *ctx);
+/* The peer exchange's sequence counter after `seq` (host-side mirror of the device rule, for tests; no
+ * counterpart in the reference): consecutive exchanges use inbox slots of opposite parity, also
+ * across the wrap of the 32-bit counter, and 0 ("never written") is never produced. Needs no GPU. */
+uint32_t jl_debug_tp_next_sequence(uint32_t seq);
 
 /* ---- native GGUF reader (replaces the Java-side parse and per-tensor Panama copies:
  * format/GGUF.java:60-110,123-165, model/loader/LlamaModelLoader.java:49-67,125-188,

@@ -47,6 +47,7 @@ SIGNATURES = {
     "jl_kv_create": (_I32, [_P, _I32, _I32, _I32, _I32, _I32]),
     "jl_kv_publish_block_table": (_I32, [_P, _P, _I64]),
     "jl_kv_bytes_per_block": (_I64, [_P]),
+    "jl_kv_fill": (_I32, [_P, C.c_uint16]),
     "jl_kv_read_row": (_I32, [_P, _I32, _I32, _I32, _I32, _P]),
     "jl_decode": (_I32, [_P, _I32, _P, _P, _P, _P, _P, _P]),
     "jl_generate": (_I32, [_P, _I32, _P, _P, _P, _P, _I32, _P]),
@@ -74,6 +75,7 @@ SIGNATURES = {
     "jl_tp_exchange_mode": (_I32, [_P]),
     "jl_debug_peer_wait_timeout": (_I32, [_P, _I32]),
     "jl_tp_exchange_note": (C.c_char_p, [_P]),
+    "jl_debug_tp_next_sequence": (C.c_uint32, [C.c_uint32]),
     "jl_gemv_argmax_static": (_I32, [_I32, _I64, _I64, _P, _P, _P, C.c_float, _P, _P, _P]),
     "jl_static_last_error": (C.c_char_p, []),
     "jl_static_status": (_I32, [_P]),

@@ -315,6 +315,11 @@ class KvStorage:
         r = self._req
         return 2 * r.kvDim * r.blockSizeTokens * r.numberOfLayers * (2 if r.fp16KeyValue else 4)
 
+    def fill(self, half_bits: int = 0x7E00) -> None:
+        """Every K and V element becomes this binary16 pattern (default: NaN, the reference's poison)."""
+        dev = self._model.dev
+        dev._check(dev._lib.jl_kv_fill(dev.handle, half_bits))
+
     def readRow(self, which: str, slot: int, layer: int, pos: int) -> np.ndarray:
         """One position's K or V row as raw binary16 bits (test access)."""
         out = np.empty(self._req.kvDim, dtype=np.uint16)

@@ -282,23 +282,17 @@ void drop_graphs(jl_ctx *ctx) {
     ctx->graphs.clear();
 }
 
-void free_model(jl_ctx *ctx) {
+// The per-step workspace jl_model_finalize allocates (step buffers, tensor-parallel inboxes and
+// mappings, token history): released before a model is finalised again -- uploading a tensor after
+// a finalize puts the model back into the "not finalised" state -- and with the model.
+void free_workspace(jl_ctx *ctx) {
     drop_graphs(ctx);
-    for (int r = 0; r < JL_ROLE_COUNT; ++r) {
-        if (ctx->global[r].data) cudaFree(ctx->global[r].data);
-        ctx->global[r] = DevTensor();
-        for (auto &t : ctx->layer[r])
-            if (t.data) cudaFree(t.data);
-        ctx->layer[r].clear();
-    }
-    void *bufs[] = {ctx->rope_cos, ctx->rope_sin, ctx->x,       ctx->q,        ctx->k,
-                    ctx->v,        ctx->xb,       ctx->hb,      ctx->hb2,     ctx->logits,   ctx->d_tokens,
-                    ctx->d_positions, ctx->d_slots, ctx->d_out, ctx->d_active, ctx->att_partial,
-                    ctx->att_count, ctx->amax_val, ctx->amax_idx, ctx->amax_count};
+    void *bufs[] = {ctx->x,        ctx->q,        ctx->k,      ctx->v,         ctx->xb,           ctx->hb,
+                    ctx->hb2,      ctx->logits,   ctx->d_tokens, ctx->d_positions, ctx->d_slots,  ctx->d_out,
+                    ctx->d_active, ctx->att_partial, ctx->att_count, ctx->amax_val, ctx->amax_idx, ctx->amax_count};
     for (void *b : bufs)
         if (b) cudaFree(b);
-    ctx->rope_cos = ctx->rope_sin = ctx->x = ctx->q = ctx->k = ctx->v = ctx->xb = ctx->hb = ctx->hb2 =
-        ctx->logits = nullptr;
+    ctx->x = ctx->q = ctx->k = ctx->v = ctx->xb = ctx->hb = ctx->hb2 = ctx->logits = nullptr;
     ctx->d_tokens = ctx->d_positions = ctx->d_slots = ctx->d_out = nullptr;
     ctx->d_active = nullptr;
     ctx->att_partial = nullptr;
@@ -328,9 +322,26 @@ void free_model(jl_ctx *ctx) {
     if (ctx->d_step) cudaFree(ctx->d_step);
     ctx->d_history = ctx->d_step = nullptr;
     ctx->history_cap = 0;
-    ctx->counters.weight_bytes = 0;
+    if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
+    ctx->h_stage = nullptr;
     ctx->counters.workspace_bytes = 0;
-    ctx->has_model = ctx->finalized = false;
+    ctx->finalized = false;
+}
+
+void free_model(jl_ctx *ctx) {
+    free_workspace(ctx);
+    for (int r = 0; r < JL_ROLE_COUNT; ++r) {
+        if (ctx->global[r].data) cudaFree(ctx->global[r].data);
+        ctx->global[r] = DevTensor();
+        for (auto &t : ctx->layer[r])
+            if (t.data) cudaFree(t.data);
+        ctx->layer[r].clear();
+    }
+    if (ctx->rope_cos) cudaFree(ctx->rope_cos);
+    if (ctx->rope_sin) cudaFree(ctx->rope_sin);
+    ctx->rope_cos = ctx->rope_sin = nullptr;
+    ctx->counters.weight_bytes = 0;
+    ctx->has_model = false;
 }
 
 void free_kv(jl_ctx *ctx) {
@@ -400,23 +411,32 @@ int tp_push_setup(jl_ctx *ctx) {
     ctx->tp_best_cap = 2 * size_t(ctx->row_cap);
     const size_t packets = 2 * size_t(tp) * (ctx->tp_reduce_cap + ctx->tp_best_cap);
     int rc;
-    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->tp_inbox), packets * sizeof(uint2)))) return rc;
-    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->tp_ctr), 4 * sizeof(unsigned)))) return rc;
-    const unsigned ctr0[4] = {1u, 0u, 1u, 0u};
-    JL_CUDA(ctx, cudaMemsetAsync(ctx->tp_inbox, 0, packets * sizeof(uint2), ctx->stream));
-    JL_CUDA(ctx, cudaMemcpyAsync(ctx->tp_ctr, ctr0, sizeof ctr0, cudaMemcpyHostToDevice, ctx->stream));
-    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    ctx->counters.workspace_bytes += packets * sizeof(uint2);
+    // A failure on this rank alone must not leave the others waiting in the gathers below: from here
+    // on a local failure only clears `local_ok`, which travels to every rank as ok = 0 and turns the
+    // path off everywhere. (The gather buffer itself is the one exception: without it this rank
+    // cannot take part at all, and the error is returned.)
+    float *d_info = nullptr;  // [1 + tp] records: own, then the gathered ones
+    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&d_info), (1 + tp) * sizeof(TpPeerInfo)))) return rc;
+    bool local_ok = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->tp_inbox), packets * sizeof(uint2)) == JL_OK &&
+                    dev_alloc(ctx, reinterpret_cast<void **>(&ctx->tp_ctr), 4 * sizeof(unsigned)) == JL_OK;
+    if (local_ok) {
+        const unsigned ctr0[4] = {1u, 0u, 1u, 0u};
+        cudaError_t e = cudaMemsetAsync(ctx->tp_inbox, 0, packets * sizeof(uint2), ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(ctx->tp_ctr, ctr0, sizeof ctr0, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        local_ok = e == cudaSuccess;
+        cudaGetLastError();
+        if (local_ok) ctx->counters.workspace_bytes += packets * sizeof(uint2);
+    }
+    if (!local_ok) ctx->tp_note = "this rank could not allocate its inbox";
 
     TpPeerInfo mine = {};
     mine.ptr = reinterpret_cast<unsigned long long>(ctx->tp_inbox);
     mine.pid = static_cast<long long>(getpid());
     mine.device = ctx->device;
-    mine.ok = cudaIpcGetMemHandle(&mine.handle, ctx->tp_inbox) == cudaSuccess ? 1 : 0;
+    mine.ok = local_ok && cudaIpcGetMemHandle(&mine.handle, ctx->tp_inbox) == cudaSuccess ? 1 : 0;
     cudaGetLastError();
     const size_t words = sizeof(TpPeerInfo) / 4;
-    float *d_info = nullptr;  // [1 + tp] records: own, then the gathered ones
-    if ((rc = dev_alloc(ctx, reinterpret_cast<void **>(&d_info), (1 + tp) * sizeof(TpPeerInfo)))) return rc;
     std::vector<TpPeerInfo> all(tp);
     auto gather = [&]() -> int {
         cudaError_t e = cudaMemcpyAsync(d_info, &mine, sizeof mine, cudaMemcpyHostToDevice, ctx->stream);
@@ -432,7 +452,7 @@ int tp_push_setup(jl_ctx *ctx) {
     // map the peers' inboxes
     bool ok = rc == JL_OK;
     for (int r = 0; ok && r < tp; ++r) ok = all[r].ok == 1;
-    if (rc == JL_OK && !ok) ctx->tp_note = "a rank could not export its inbox";
+    if (rc == JL_OK && !ok && ctx->tp_note.empty()) ctx->tp_note = "a rank could not export its inbox";
     for (int r = 0; ok && r < tp; ++r) {
         if (r == ctx->tp_rank) {
             ctx->tp_peers.of[r] = ctx->tp_inbox;
@@ -973,7 +993,6 @@ int32_t jl_destroy(jl_ctx *ctx) {
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
     if (ctx->gemm_counters) cudaFree(ctx->gemm_counters);
-    if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->tev0) cudaEventDestroy(ctx->tev0);
@@ -1151,6 +1170,13 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     JL_REQUIRE(ctx, d.tied_embeddings || ctx->global[JL_ROLE_OUTPUT].data, JL_ERR_STATE,
                "output.weight missing and embeddings are not tied");
     JL_REQUIRE(ctx, ctx->rope_cos != nullptr, JL_ERR_STATE, "RoPE tables missing");
+    cudaSetDevice(ctx->device);
+    if (ctx->x != nullptr) {
+        // Finalised before, then a tensor was replaced: the old workspace goes first. (Under tensor
+        // parallelism every rank must then finalise again: setting up the peer exchange is collective.)
+        JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        free_workspace(ctx);
+    }
     if (ctx->tp_size > 1 && !ctx->global[JL_ROLE_OUTPUT].data) {
         const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
         if (emb.has_tmap) {
@@ -1236,8 +1262,6 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     JL_CUDA(ctx, cudaMemsetAsync(ctx->d_out, 0, R * 4, ctx->stream));
     JL_CUDA(ctx, cudaMemsetAsync(ctx->amax_count, 0, B * 4, ctx->stream));
     JL_CUDA(ctx, cudaMemsetAsync(ctx->d_active, 0, R, ctx->stream));
-    if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
-    ctx->h_stage = nullptr;
     JL_CUDA(ctx, cudaMallocHost(reinterpret_cast<void **>(&ctx->h_stage), (5 * R + 1) * 4));
     JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     ctx->counters.workspace_bytes = ws;
@@ -1306,6 +1330,18 @@ int32_t jl_kv_publish_block_table(jl_ctx *ctx, const int32_t *table, int64_t n) 
                                  cudaMemcpyHostToDevice, ctx->stream));
     JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     ctx->counters.h2d_bytes += n * 4;
+    return JL_OK;
+}
+
+int32_t jl_kv_fill(jl_ctx *ctx, uint16_t half_bits) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->has_kv, JL_ERR_STATE, "jl_kv_create must come first");
+    cudaSetDevice(ctx->device);
+    const size_t elems = size_t(ctx->total_blocks + 1) * ctx->desc.layers * ctx->block_tokens * ctx->kv_dim;
+    const uint32_t word = uint32_t(half_bits) | (uint32_t(half_bits) << 16);
+    JL_CUDA(ctx, fill_launch(reinterpret_cast<uint32_t *>(ctx->kpool), elems / 2, word, ctx->stream));
+    JL_CUDA(ctx, fill_launch(reinterpret_cast<uint32_t *>(ctx->vpool), elems / 2, word, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return JL_OK;
 }
 
@@ -1603,13 +1639,43 @@ int32_t jl_debug_trace(jl_ctx *ctx, uint64_t *out, int32_t max_records) {
 int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters) {
     if (!ctx) return JL_ERR_INVALID;
     JL_REQUIRE(ctx, ctx->finalized, JL_ERR_STATE, "jl_model_finalize must come first");
-    JL_REQUIRE(ctx, op >= 0 && op <= 4 && iters >= 0 && first_layer >= 0, JL_ERR_INVALID,
-               "op must be 0..4 (qkv, attn-out, gate/up, down, vocabulary)");
+    JL_REQUIRE(ctx, op >= 0 && op <= 5 && iters >= 0 && first_layer >= 0, JL_ERR_INVALID,
+               "op must be 0..5 (qkv, attn-out, gate/up, down, vocabulary, attention)");
+    JL_REQUIRE(ctx, op != 5 || ctx->has_kv, JL_ERR_STATE, "the attention operator needs jl_kv_create first");
     cudaSetDevice(ctx->device);
     const jl_model_desc &d = ctx->desc;
     uint64_t launches = 0;
     for (int i = 0; i < iters; ++i) {
         const int l = (first_layer + i) % d.layers;
+        if (op == 5) {
+            // Row 0 at the position and slot the last step left on the device: rotates and appends
+            // whatever the q/k/v buffers hold, then attends over the slot's pages of layer l.
+            AttnArgs t = {};
+            t.q = ctx->q;
+            t.k = ctx->k;
+            t.v = ctx->v;
+            t.out = ctx->xb;
+            t.rope_cos = ctx->rope_cos;
+            t.rope_sin = ctx->rope_sin;
+            t.positions = ctx->d_positions;
+            t.slots = ctx->d_slots;
+            t.active = nullptr;
+            t.kv = {ctx->kpool, ctx->vpool, ctx->block_table, ctx->blocks_per_slot, ctx->block_tokens, d.layers,
+                    ctx->kv_dim};
+            t.layer = l;
+            t.heads = ctx->l_heads;
+            t.kv_heads = ctx->l_kv_heads;
+            t.head_dim = d.head_dim;
+            t.dim = ctx->l_qdim;
+            t.nsplit = attn_splits_for_width(ctx, 1);
+            t.append = 1;
+            t.partial = ctx->att_partial;
+            t.counters = ctx->att_count;
+            cudaError_t e = attention_launch(t, 1, ctx->stream, ctx->use_pdl);
+            if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
+            ++launches;
+            continue;
+        }
         GemvArgs a = {};
         a.cols = d.dim;
         a.mode = kGemvPlain;
@@ -1918,6 +1984,8 @@ int32_t jl_flush_l2(jl_ctx *ctx) {
     JL_CUDA(ctx, fill_launch(ctx->flush_buf, ctx->flush_words, 0u, ctx->stream));
     return JL_OK;
 }
+
+uint32_t jl_debug_tp_next_sequence(uint32_t seq) { return tp_next_sequence(seq); }
 
 int32_t jl_debug_peer_wait_timeout(jl_ctx *ctx, int32_t timeout_ms) {
     if (!ctx) return JL_ERR_INVALID;

@@ -209,8 +209,15 @@ int32_t jl_gguf_open(const char *path, jl_gguf **out) {
         const TensorInfo &t = kv.second;
         const int64_t rb = type_row_bytes(t.type, t.dims[0]);
         if (rb < 0) continue;  // a type this library does not use; refused only if a needed tensor has it
-        const uint64_t rows = t.dims[1] * t.dims[2] * t.dims[3];
-        if (t.offset % g->alignment != 0 || g->data_offset + t.offset + uint64_t(rb) * rows > g->size) {
+        // Every product and sum below can wrap in a crafted file, and a wrapped value would pass the
+        // comparison with the file size: each step is checked.
+        uint64_t rows = 0, bytes = 0, end = 0;
+        const bool overflow = __builtin_mul_overflow(uint64_t(t.dims[1]), uint64_t(t.dims[2]), &rows) ||
+                              __builtin_mul_overflow(rows, uint64_t(t.dims[3]), &rows) ||
+                              __builtin_mul_overflow(uint64_t(rb), rows, &bytes) ||
+                              __builtin_add_overflow(uint64_t(g->data_offset), uint64_t(t.offset), &end) ||
+                              __builtin_add_overflow(end, bytes, &end);
+        if (overflow || t.offset % g->alignment != 0 || end > g->size) {
             const std::string msg = "GPUL-CFG-002: tensor '" + kv.first + "' lies outside the file or is misaligned";
             jl_gguf_close(g);  // frees the map the name lives in: the message is built first
             return gguf_fail(JL_ERR_INVALID, msg);

@@ -53,7 +53,7 @@ __device__ __forceinline__ void advance_sequence(unsigned *ctr, unsigned seq) {
         if (arrived == gridDim.x - 1) {
             ctr[1] = 0u;
             __threadfence();
-            *reinterpret_cast<volatile unsigned *>(&ctr[0]) = seq + 1u == 0u ? 1u : seq + 1u;
+            *reinterpret_cast<volatile unsigned *>(&ctr[0]) = tp_next_sequence(seq);
         }
     }
 }

@@ -49,4 +49,8 @@ struct TpBestArgs {
 cudaError_t tp_push_reduce_launch(const TpReduceArgs &a, cudaStream_t stream, bool programmatic);
 cudaError_t tp_push_best_launch(const TpBestArgs &a, cudaStream_t stream, bool programmatic);
 
+// The sequence number after `seq`. Two inbox slots alternate by its lowest bit and 0 means "never
+// written", so the step from 0xFFFFFFFF must skip 0 and still change parity: it goes to 2.
+__host__ __device__ inline unsigned tp_next_sequence(unsigned seq) { return seq + 1u == 0u ? 2u : seq + 1u; }
+
 }  // namespace jl

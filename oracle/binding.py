@@ -176,6 +176,16 @@ class Model:
         p = lib().orc_state_vcache(self._s, layer)
         return np.ctypeslib.as_array(p, shape=((pos + 1) * kv,))[pos * kv:(pos + 1) * kv].copy()
 
+    def fill_cache(self, depth: int, rng) -> None:
+        """Writes seeded random binary16 rows (|v| < 1) into positions [0, depth) of every layer's K and V
+        cache: a stand-in for a prefill when only the cost of attention at that depth matters."""
+        kv = self.config.kvDim
+        L = lib()
+        for layer in range(self.config.numberOfLayers):
+            for getter in (L.orc_state_kcache, L.orc_state_vcache):
+                view = np.ctypeslib.as_array(getter(self._s, layer), shape=(depth * kv,))
+                view[:] = (rng.random(depth * kv, dtype=np.float32) - 0.5).astype(np.float16).view(np.uint16)
+
     def close(self):
         L = lib()
         if self._s:

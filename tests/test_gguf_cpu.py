@@ -69,3 +69,29 @@ def test_malformed_files_are_refused(built, tmp_path):
         jl.GgufFile(header_cut)
     with pytest.raises(ValueError, match="cannot open"):
         jl.GgufFile(tmp_path / "absent.gguf")
+
+
+def test_tensor_infos_that_overflow_64_bits_are_refused(built, tmp_path):
+    """Dimensions or an offset chosen so that offset + rows * row bytes wraps around 2^64 and lands
+    back inside the file must not pass the bounds check."""
+    path, tensors = _write(tmp_path)
+    raw = bytearray(path.read_bytes())
+    (role, layer), _ = list(tensors.items())[-1]
+    name = tensor_name(role, layer).encode()
+    at = raw.index(struct.pack("<Q", len(name)) + name) + 8 + len(name)
+    (n_dims,) = struct.unpack_from("<I", raw, at)
+    dims_at, type_at = at + 4, at + 4 + 8 * n_dims
+    off_at = type_at + 4
+    huge_offset = bytearray(raw)
+    struct.pack_into("<Q", huge_offset, off_at, 0xFFFFFFFFFFFFFF00)  # aligned, and wraps when the size is added
+    p1 = tmp_path / "huge_offset.gguf"
+    p1.write_bytes(bytes(huge_offset))
+    with pytest.raises(ValueError, match="outside the file"):
+        jl.GgufFile(p1)
+    if n_dims >= 2:
+        huge_rows = bytearray(raw)
+        struct.pack_into("<Q", huge_rows, dims_at + 8, 1 << 62)  # rows * row bytes wraps
+        p2 = tmp_path / "huge_rows.gguf"
+        p2.write_bytes(bytes(huge_rows))
+        with pytest.raises(ValueError, match="outside the file"):
+            jl.GgufFile(p2)

@@ -246,3 +246,40 @@ def test_wide_batch_decode_on_the_tensor_core_path(dev, oracle):
             if top2[1] - top2[0] > 5e-3:
                 assert out[b] == int(np.argmax(want))
             positions[b] += 1
+
+
+@pytest.mark.parametrize("width", [2, 4])
+def test_two_slots_share_the_physical_blocks_of_a_common_prefix(dev, oracle, width):
+    """Prefix sharing as the reference's PrefixCache hands it out (runtime/kv/PrefixCache.java,
+    BATCHED_DECODE.md:245-265): slots whose block tables point at the same physical blocks for the
+    prompt they have in common. The prefix is written once, through slot 0; every slot then decodes
+    its own continuation into blocks of its own and must match an oracle sequence that saw prefix +
+    continuation. Width 2 runs the mat-vec path, width 4 the tensor-core path."""
+    cfg = small_config(layers=2, ctx=64)
+    bps, prefix = 4, 32                           # two full 16-token blocks are shared
+    table = np.full(width * bps, jl.UNMAPPED, dtype=np.int32)
+    for b in range(width):
+        table[b * bps:b * bps + 2] = [0, 1]       # the shared physical blocks
+        table[b * bps + 2:b * bps + 4] = [2 + 2 * b, 3 + 2 * b]
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=71, max_batch=width, slots=width, block_table=table,
+             total_blocks=2 + 2 * width, std=0.05)
+    rng = np.random.default_rng(12)
+    common = [int(v) for v in rng.integers(0, cfg.vocabularySize, size=prefix)]
+    p.boundary.prefill(common, 0)                 # slot 0 writes blocks 0 and 1 for everybody
+    seqs = [p.new_oracle_sequence() for _ in range(width)]
+    for om in seqs:
+        for pos, tok in enumerate(common):
+            om.forward_no_logits(tok, pos)
+    bar = LOGIT_EXPECT if width < 4 else TENSOR_CORE_LOGIT_EXPECT
+    for step in range(10):
+        toks = [int(v) for v in rng.integers(0, cfg.vocabularySize, size=width)]
+        pos = prefix + step
+        out, logits = p.executor.decodeStep(jl.BatchSlots([True] * width, toks, [pos] * width, list(range(width))),
+                                            wantLogits=True)
+        for b in range(width):
+            want = seqs[b].forward(toks[b], pos)
+            assert float(np.max(np.abs(logits[b] - want))) < bar, (step, b)
+    # the shared blocks still hold what slot 0 wrote: nobody's continuation touched them
+    for b in range(1, width):
+        for which in ("k", "v"):
+            assert np.array_equal(p.kv.readRow(which, b, 0, prefix - 1), p.kv.readRow(which, 0, 0, prefix - 1))

@@ -72,3 +72,20 @@ def test_tall_product_goes_in_token_slabs(dev, oracle):
     sample = [0, 63, 64, 1023, 1024, 1025, 1099]
     want = oracle.matmul(t, w, x[sample], rows, cols)
     assert rel_l2(got[sample], want) < EXPECT
+
+
+@pytest.mark.parametrize("t", FORMATS)
+def test_widest_sweep_batch(dev, oracle, t):
+    """N = 2048, the widest batch of the standalone sweep, on the 14336 x 4096 shape: sampled token
+    rows against the oracle (the full product is 120 G multiply-adds on the CPU), rows on either side
+    of token-tile boundaries among them."""
+    rows, cols, n = 14336, 4096, 2048
+    w = jl.synth_tensor(t, rows * cols, seed=29 + int(t))
+    x = np.random.default_rng(8).standard_normal((n, cols)).astype(np.float32)
+    got = dev.matmul(t, w, rows, cols, x)
+    assert got.shape == (n, rows)
+    sample = [0, 127, 128, 1023, 1024, 1900, 2047]
+    want = oracle.matmul(t, w, x[sample], rows, cols)
+    err = rel_l2(got[sample], want)
+    assert err < BAR and err < EXPECT, err
+    assert np.all(np.isfinite(got))

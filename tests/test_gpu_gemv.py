@@ -36,8 +36,9 @@ def test_sweep_shapes_single_vector(dev, oracle, t, rows, cols):
     assert err < BAR and err < EXPECT, err
 
 
-def test_vocabulary_shape_q4_k(dev, oracle):
-    rows, cols, t = 128256, 4096, GGMLType.Q4_K
+@pytest.mark.parametrize("t", FORMATS)
+def test_vocabulary_shape(dev, oracle, t):
+    rows, cols = 128256, 4096
     w = jl.synth_tensor(t, rows * cols, seed=99)
     x = np.random.default_rng(2).standard_normal(cols).astype(np.float32)
     got, want = dev.matmul(t, w, rows, cols, x), oracle.matmul(t, w, x, rows, cols)

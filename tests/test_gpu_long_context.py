@@ -1,0 +1,84 @@
+"""Attention at the key counts the benchmark configurations run at, against the oracle fed token
+by token. The key/value pools are poisoned with binary16 NaN first, as the reference's own
+verification runs do (docs/architecture/verification.md:427-431): a read of any page the sequence
+has not written turns the logits into NaN.
+
+Covered here and nowhere else: more than 1024 keys for one sequence (several clusters per KV head
+whose results meet in global memory), a chunked prompt of 1500 tokens, and a launch whose CTAs see
+more pages than the kernel keeps page bases for in shared memory (one-token pages, eight rows)."""
+import numpy as np
+import pytest
+
+import jitllm_b200 as jl
+from jitllm_b200 import GGMLType
+
+pytestmark = pytest.mark.gpu
+LOGIT_BAR = 1e-2
+
+
+def _config(heads, kv_heads, head, ctx):
+    return jl.Configuration(dim=heads * head, hiddenDim=768, numberOfLayers=2, numberOfHeads=heads,
+                            numberOfKeyValueHeads=kv_heads, vocabularySize=1024, contextLength=ctx)
+
+
+@pytest.mark.parametrize("t", [GGMLType.Q4_K, GGMLType.Q8_0])
+def test_one_sequence_long_prompt_then_decode(dev, oracle, t):
+    cfg = _config(heads=4, kv_heads=1, head=128, ctx=4096)
+    tensors = jl.synth_model_tensors(cfg, t, seed=5, std=0.05)
+    om = oracle.Model(cfg, tensors)
+    cr, ci = om.rope_tables()
+    model = jl.load_model(dev, cfg, tensors, cr, ci)
+    bps = cfg.contextLength // 16
+    kv = model.createKvStorage(jl.KvStorageRequest(bps, bps, 1, 16, cfg.numberOfLayers, cfg.kvDim))
+    kv.publishBlockTable(np.random.default_rng(1).permutation(bps).astype(np.int32))  # scattered pages
+    kv.fill(0x7E00)
+    P, steps = 1500, 24
+    toks = np.random.default_rng(2).integers(0, cfg.vocabularySize, size=P + steps)
+    bound = jl.B200InvocationBoundary(model, kvSlot=0)
+    bound.prefill([int(v) for v in toks[:P]], 0)
+    for pos in range(P):
+        om.forward_no_logits(int(toks[pos]), pos)
+    worst = 0.0
+    for pos in range(P, P + steps):
+        want = om.forward(int(toks[pos]), pos)
+        got = bound.invoke(int(toks[pos]), pos)
+        assert np.all(np.isfinite(got.logits)), pos  # nothing read from a poisoned page
+        worst = max(worst, float(np.max(np.abs(got.logits - want))))
+        assert got.sampledToken == int(np.argmax(got.logits))
+    assert worst < LOGIT_BAR, worst
+    kv.close()
+
+
+def test_wide_batch_with_more_pages_than_the_page_cache(dev, oracle):
+    """Eight sequences of about 1150 tokens on one-token pages: every CTA walks more pages than it
+    keeps bases for, so the table is consulted directly for the rest."""
+    cfg = _config(heads=8, kv_heads=8, head=64, ctx=1280)
+    t = GGMLType.Q8_0
+    tensors = jl.synth_model_tensors(cfg, t, seed=9, std=0.05)
+    width, P, steps = 8, 1140, 6
+    model = jl.load_model(dev, cfg, tensors, *oracle.Model(cfg, tensors).rope_tables(), maxBatch=width)
+    bps = cfg.contextLength
+    kv = model.createKvStorage(jl.KvStorageRequest(width * bps, bps, width, 1, cfg.numberOfLayers, cfg.kvDim))
+    kv.publishBlockTable(np.random.default_rng(3).permutation(width * bps).astype(np.int32))
+    kv.fill(0x7E00)
+    rng = np.random.default_rng(4)
+    prompts = rng.integers(0, cfg.vocabularySize, size=(width, P + steps))
+    seqs = []
+    for b in range(width):
+        jl.B200InvocationBoundary(model, kvSlot=b, copyLogits=False).prefill([int(v) for v in prompts[b, :P]], 0)
+        om = oracle.Model(cfg, tensors)
+        for pos in range(P):
+            om.forward_no_logits(int(prompts[b, pos]), pos)
+        seqs.append(om)
+    ex = jl.B200BatchExecutor(model)
+    worst = 0.0
+    for s in range(steps):
+        pos = P + s
+        toks = [int(prompts[b, pos]) for b in range(width)]
+        out, logits = ex.decodeStep(jl.BatchSlots([True] * width, toks, [pos] * width, list(range(width))), wantLogits=True)
+        for b in range(width):
+            want = seqs[b].forward(toks[b], pos)
+            assert np.all(np.isfinite(logits[b])), (s, b)
+            worst = max(worst, float(np.max(np.abs(logits[b] - want))))
+    assert worst < LOGIT_BAR, worst
+    kv.close()

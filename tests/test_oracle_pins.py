@@ -78,10 +78,14 @@ def test_fp16_known_answers(oracle):
     assert L.orc_f16_to_f32(0x0001) == 2.0 ** -24
 
 
-def test_fp16_rounds_like_ieee_over_two_million_samples(oracle):
-    # same sampling recipe as Fp16BitsTest.sample: new Random(7), kind = i & 3
+def test_fp16_rounds_like_ieee_on_the_reference_sample_recipe(oracle):
+    """Fp16BitsTest.roundsIdenticallyToFloatToFloat16 (src/test/java/org/beehive/jitllm/backend/tornado/
+    kernels/Fp16BitsTest.java:20-35,56-70): new Random(7), kind = i & 3, the four kinds exactly as
+    written there -- weight-shaped, wide, tiny (1e-6) and real Q8_0 products whose scale has been
+    through binary16 once. The Java loop draws two million samples; the Python generator is slow,
+    so the first 200 000 of the same sequence are replayed."""
     rnd = JavaRandom(7)
-    n = 200_000  # python LCG is slow; the recipe is the same, the count is smaller
+    n = 200_000
     vals = np.empty(n, dtype=np.float32)
     for i in range(n):
         kind = i & 3
@@ -91,13 +95,15 @@ def test_fp16_rounds_like_ieee_over_two_million_samples(oracle):
         elif kind == 1:
             vals[i] = (f - np.float32(0.5)) * np.float32(130000)
         elif kind == 2:
-            vals[i] = (f - np.float32(0.5)) * np.float32(1e-4)
+            vals[i] = (f - np.float32(0.5)) * np.float32(1e-6)
         else:
-            vals[i] = np.float32(rnd.next_int_bound(255) - 127) * (f * np.float32(0.05))
+            scale = np.float32(np.float16(f * np.float32(0.05)))  # Float.float16ToFloat(Float.floatToFloat16(..))
+            vals[i] = np.float32(rnd.next_int_bound(255) - 127) * scale
     want = vals.astype(np.float16).view(np.uint16)
+    keep = (want != 0x7C00) & (want != 0xFC00) & np.isfinite(vals)  # the reference skips what overflows
     L = oracle.lib()
     got = np.array([L.orc_f32_to_f16(float(v)) for v in vals], dtype=np.uint16)
-    assert np.array_equal(got, want)
+    assert np.array_equal(got[keep], want[keep])
     back = np.array([L.orc_f16_to_f32(int(h)) for h in got[:20000]], dtype=np.float32)
     assert np.array_equal(back.view(np.uint32), got[:20000].view(np.float16).astype(np.float32).view(np.uint32))
 

@@ -185,3 +185,17 @@ def test_two_ranks_over_gloo_match_one_rank():
         assert np.linalg.norm(have - want) <= 1e-4 * np.linalg.norm(want)
         token = int(np.argmax(want))
         assert got[0]["tokens"][pos] == token and got[1]["tokens"][pos] == token
+
+
+def test_exchange_sequence_keeps_alternating_slots_across_the_wrap():
+    """The peer exchange picks one of two inbox slots by the parity of a 32-bit sequence number that
+    lives on the device for the life of the model. Two exchanges in a row must never share a slot
+    (a peer one exchange ahead would overwrite a packet not yet read), not even when the counter
+    wraps, and 0 means "never written"."""
+    from jitllm_b200 import _lib
+    nxt = _lib.load().jl_debug_tp_next_sequence
+    for seq in (1, 2, 3, 0x7FFFFFFF, 0x80000000, 0xFFFFFFFD, 0xFFFFFFFE, 0xFFFFFFFF):
+        n = nxt(seq)
+        assert n != 0
+        assert (n & 1) != (seq & 1), hex(seq)
+    assert nxt(0xFFFFFFFF) == 2 and nxt(5) == 6
