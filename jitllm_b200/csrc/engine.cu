@@ -21,6 +21,8 @@
 
 #include <unistd.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 using namespace jl;
 
 namespace {
@@ -564,6 +566,35 @@ int tp_global_argmax(jl_ctx *ctx, int n, uint64_t *launches) {
     return JL_OK;
 }
 
+// NVTX ranges around the sublayers of a step while it is enqueued (or captured into its graph), so
+// that a timeline tool shows "L3.attention" / "L3.ffn" instead of a run of anonymous launches: the
+// build's counterpart of the reference's per-task-graph profiler names
+// (backend/tornado/TornadoMetricsReporter.java:52-78). Off unless JITLLM_B200_NVTX=1.
+struct NvtxRange {
+    bool on;
+    NvtxRange(const char *what, int layer) {
+        static const bool enabled = env_flag("JITLLM_B200_NVTX", false);
+        on = enabled;
+        if (on) {
+            char name[48];
+            if (layer >= 0) snprintf(name, sizeof name, "L%d.%s", layer, what);
+            else snprintf(name, sizeof name, "%s", what);
+            nvtxRangePushA(name);
+        }
+    }
+    void next(const char *what, int layer) {
+        if (!on) return;
+        nvtxRangePop();
+        char name[48];
+        if (layer >= 0) snprintf(name, sizeof name, "L%d.%s", layer, what);
+        else snprintf(name, sizeof name, "%s", what);
+        nvtxRangePushA(name);
+    }
+    ~NvtxRange() {
+        if (on) nvtxRangePop();
+    }
+};
+
 int attn_splits_for_width(const jl_ctx *ctx, int width) {
     return attention_splits(ctx->sm_count, width, ctx->l_kv_heads);
 }
@@ -601,8 +632,6 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
     g.counters = ctx->gemm_counters;
     g.counters_len = kGemmCounters;
     g.sm_count = ctx->sm_count;
-    static const int gemm_dbg = [] { const char *v = getenv("JITLLM_B200_GEMM_DEBUG"); return v ? atoi(v) : 0; }();
-    g.debug = gemm_dbg;
     cudaError_t e = gemm_tc_launch(g, ctx->stream);
     if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-matrix launch failed: %s", cudaGetErrorString(e));
     ++*launches;
@@ -641,6 +670,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
     for (int l = 0; l < d.layers; ++l) {
         const float *attn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
         const float *ffn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
+        NvtxRange range("attention", l);
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, attn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream, ctx->xb16,
                                            static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2),
                   "rmsnorm");
@@ -689,6 +719,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
         } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->x, ctx->x, launches, 1))) {
             return rc;
         }
+        range.next("ffn", l);
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, ffn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream, ctx->xb16,
                                            static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2),
                   "rmsnorm");
@@ -753,6 +784,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
         const float *ffn_norm =
             reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
+        NvtxRange range("attention", l);
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
             a.nseg = 3;
@@ -811,6 +843,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             if ((rc = launch_gemv(ctx, a, int(wo.rows), launches))) return rc;
         }
         if (tp && (rc = tp_reduce_into_x(ctx, width, launches))) return rc;
+        range.next("ffn", l);
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
             a.nseg = 2;
@@ -843,6 +876,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
         if (tp && (rc = tp_reduce_into_x(ctx, width, launches))) return rc;
     }
     if (with_logits) {
+        NvtxRange range("logits", -1);
         const DevTensor wc = wcls_of(ctx);
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};

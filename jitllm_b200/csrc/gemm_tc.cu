@@ -532,7 +532,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     break;
                 }
                 const CUtensorMap *tmap = tr.seg == 0 ? &tm0 : (tr.seg == 1 ? &tm1 : &tm2);
-                if (a.debug & 8) {  // timing experiment: no copy at all, the stage is declared full
+                if (JL_TRACE_MODE(8)) {  // trace build, timing experiment: no copy at all, the stage is declared full
                     mbar_arrive(raw_full + st);
                     continue;
                 }
@@ -604,11 +604,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         for (int k16 = 0; k16 < 4; ++k16) {
                             const uint32_t ka = uint32_t(atom * 4 + k16) * 8u;  // eight columns per K = 16
                             const uint64_t kb = uint64_t((atom * S::b_sub + k16 * 32) >> 4);
-                            if (a.debug & 4) continue;
+                            if (JL_TRACE_MODE(4)) continue;  // trace build only
                             umma_f16_tmem_a(tmem_d, ta0 + ka, db0 + kb, idesc, (first && atom == 0 && k16 == 0) ? 0u : 1u);
                         }
                     }
-                    if ((a.debug & 36) == 36) mbar_arrive(a_free + s);  // timing experiment, only without MMAs
+                    if (JL_TRACE_MODE(4) && JL_TRACE_MODE(32)) mbar_arrive(a_free + s);  // trace build, only without MMAs
                     else umma_commit(a_free + s);  // arrives when every MMA issued so far has completed
                     if (f + 1 == seg_end && j == 1) {
                         umma_commit(acc_full);
@@ -690,7 +690,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #endif
                 if (ok) {
                 uint8_t *b_st = base + S::b_off + s * S::b_stage;
-                if (!(a.debug & 1)) {
+                if (!JL_TRACE_MODE(1)) {  // always true outside the trace build
                     tc_fence_after();  // the stage's previous MMAs are complete (a_free): order the store after them
                     uint32_t first[16], second[16];
                     dequant64_to_half<TYPE>(row_u32, 2 * j + a_unit, first, second);
@@ -709,7 +709,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                 for (int uu = 0; uu < kBPerThread; ++uu) {
                     const int ch = g_tid + uu * kGroupThreads;
-                    if (ch < kBChunks && !(a.debug & 2)) {
+                    if (ch < kBChunks && !JL_TRACE_MODE(2)) {
                         const int t = ch >> 4, kc = ch & 15;
                         const int atom = kc >> 3, c = kc & 7;
                         const float x[8] = {xv[uu][0].x, xv[uu][0].y, xv[uu][0].z, xv[uu][0].w,

@@ -42,7 +42,6 @@ struct GemmArgs {
     unsigned *counters;
     int counters_len;
     int sm_count;
-    int debug;  // timing experiments only: 1 skip weight conversion, 2 skip activation conversion, 4 skip MMA
 };
 
 // Sets the shared-memory attribute of every instantiation (call once, outside stream capture).
