@@ -84,6 +84,16 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = Fa
     return target
 
 
+def build_microbench(verbose: bool = False) -> Path:
+    """The stand-alone bulk-copy bandwidth benchmark (not part of the library)."""
+    LIB.mkdir(exist_ok=True)
+    target = LIB / "bulk_copy_bench"
+    src = CSRC / "microbench" / "bulk_copy_bench.cu"
+    if _stale(target, [src]):
+        _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", str(target), str(src)], verbose)
+    return target
+
+
 def build_synth(force: bool = False, verbose: bool = False) -> Path:
     LIB.mkdir(exist_ok=True)
     target = LIB / "libjl_synth.so"
@@ -101,6 +111,8 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
 if __name__ == "__main__":
     if "--ptxas" in sys.argv:
         build_cuda(force=True, ptxas_info=True)
+    elif "--microbench" in sys.argv:
+        build_microbench(verbose=True)
     elif "--trace" in sys.argv:
         build_cuda(force="--force" in sys.argv, verbose=True, trace=True)
     else:

@@ -499,6 +499,23 @@ int tp_push_setup(jl_ctx *ctx) {
     return JL_OK;
 }
 
+// Whether the mat-vec kernel itself does the all-reduce of a row-parallel projection (its epilogue
+// pushes partial rows to the peers and collects theirs): needs the peer-memory path.
+bool tp_fused(const jl_ctx *ctx) {
+    static const bool want = env_flag("JITLLM_B200_TP_FUSE", true);
+    return want && ctx->tp_size > 1 && ctx->tp_push && size_t(ctx->desc.dim) <= ctx->tp_reduce_cap;
+}
+void tp_fill_reduce(const jl_ctx *ctx, GemvArgs &a, int batch_row) {
+    a.tpr.inbox = ctx->tp_peers;
+    a.tpr.base = 0;
+    a.tpr.cap = ctx->tp_reduce_cap;
+    a.tpr.tp = ctx->tp_size;
+    a.tpr.rank = ctx->tp_rank;
+    a.tpr.row_offset = batch_row * ctx->desc.dim;
+    a.tpr.ctr = ctx->tp_ctr;
+    a.tpr.timeout_ns = ctx->tp_timeout_ns;
+}
+
 // Row-parallel epilogue under tensor parallelism: all-reduce the partial projections of `n` rows
 // and add the sum into the residual stream (one NCCL all-reduce per sublayer).
 int tp_reduce_into_x(jl_ctx *ctx, int n, uint64_t *launches) {
@@ -765,6 +782,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
     const jl_model_desc &d = ctx->desc;
     const int dim = d.dim, kv_dim = ctx->kv_dim, hidden = ctx->l_hidden, qdim = ctx->l_qdim;
     const bool tp = ctx->tp_size > 1;
+    const bool fused = tp_fused(ctx);
     const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
     cudaError_t e = embedding_launch(emb.type, emb.data, ctx->d_tokens, ctx->d_active, ctx->x, dim,
                                      width, ctx->stream, false);
@@ -831,10 +849,11 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             GemvArgs a = {};
             a.nseg = 1;
             float *xr = ctx->x + size_t(b) * dim;
-            if (tp)
+            if (tp && !fused)
                 a.seg[0] = {wo.data, ctx->part + size_t(b) * dim, nullptr, int(wo.rows)};
             else
                 a.seg[0] = {wo.data, xr, xr, int(wo.rows)};
+            if (fused) tp_fill_reduce(ctx, a, b);
             a.cols = int(wo.cols);
             a.type = wo.type;
             a.mode = kGemvPlain;
@@ -842,7 +861,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.active = ctx->d_active + b;
             if ((rc = launch_gemv(ctx, a, int(wo.rows), launches))) return rc;
         }
-        if (tp && (rc = tp_reduce_into_x(ctx, width, launches))) return rc;
+        if (tp && !fused && (rc = tp_reduce_into_x(ctx, width, launches))) return rc;
         range.next("ffn", l);
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
@@ -862,10 +881,11 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             GemvArgs a = {};
             a.nseg = 1;
             float *xr = ctx->x + size_t(b) * dim;
-            if (tp)
+            if (tp && !fused)
                 a.seg[0] = {w2.data, ctx->part + size_t(b) * dim, nullptr, int(w2.rows)};
             else
                 a.seg[0] = {w2.data, xr, xr, int(w2.rows)};
+            if (fused) tp_fill_reduce(ctx, a, b);
             a.cols = int(w2.cols);
             a.type = w2.type;
             a.mode = kGemvPlain;
@@ -873,7 +893,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.active = ctx->d_active + b;
             if ((rc = launch_gemv(ctx, a, int(w2.rows), launches))) return rc;
         }
-        if (tp && (rc = tp_reduce_into_x(ctx, width, launches))) return rc;
+        if (tp && !fused && (rc = tp_reduce_into_x(ctx, width, launches))) return rc;
     }
     if (with_logits) {
         NvtxRange range("logits", -1);

@@ -123,8 +123,8 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
@@ -639,6 +639,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int tok0 = 0;
         bool a_valid = false;
         bool ok = true;
+        // An operand stage is published (a_full) one stage late: the tensor-memory stores of stage i
+        // are waited for after stage i + 1 has been converted, when they have long landed, instead
+        // of right after they were issued. With fewer than three operand stages the stage that has
+        // to become free next would be the unpublished one, so there the stage is published at once.
+        constexpr bool kDefer = ST >= 3;
+        int pending = -1;
+        auto publish = [&]() {
+            if (pending < 0) return;
+            tmem_wait_st();
+            tc_fence_before();
+            if (!XT) fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_full + pending);
+            pending = -1;
+        };
         int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
         for (long long f = lo; f < hi && ok && *abort_flag == 0u; ++f, ++i) {
             if (++r == raw_total) {
@@ -702,9 +717,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     // its 64 weights are columns a_unit * 32 .. + 31 of the stage
                     const uint32_t col0 = tmem_d + (uint32_t(a_row & ~31) << 16) + TmemPlan<NT>::a_stage0 +
                                           uint32_t(s) * kTmemAStageCols + uint32_t(a_unit) * 32u;
+                    publish();  // the previous stage of this group: its stores were issued a whole conversion ago
                     tmem_st16(col0, first);
                     tmem_st16(col0 + 16u, second);
-                    tc_fence_before();
+                } else {
+                    publish();
                 }
 #pragma unroll
                 for (int uu = 0; uu < kBPerThread; ++uu) {
@@ -727,10 +744,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     }
                 }
                 // Generic-proxy writes to shared memory (the B operand, when converted here) must be
-                // visible to the tensor core's async-proxy reads; the A operand went to tensor memory.
-                if (!XT) fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(a_full + s);
+                // visible to the tensor core's async-proxy reads; the A operand went to tensor memory:
+                // both are settled in publish().
+                pending = s;
+                if (!kDefer) publish();
                 }
             }
             if (!ok) break;
@@ -745,6 +762,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const long long seg_begin = u_lo > lo ? u_lo : lo;
             const bool whole = seg_begin == u_lo && seg_end == u_lo + raw_total;
             const GemmSeg seg = a.seg[tr.seg];
+            publish();  // the accumulator cannot finish before the last stage is published
 #ifdef JL_TRACE
             const long long tq2 = clock64();
 #endif

@@ -398,6 +398,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
 #endif
             named_bar_sync(kBarConsumers, kConsumers);
             // One thread per job: add the chunks in order, finish, store.
+            unsigned tp_seq = 0;
+            unsigned long long tp_t0 = 0, tp_limit = 0;
+            if (MODE == kGemvPlain && a.tpr.tp > 1) {
+                tp_seq = *reinterpret_cast<volatile unsigned *>(&a.tpr.ctr[0]);  // moves on only after every CTA is done
+                tp_t0 = tpx::global_ns();
+                tp_limit = tpx::patience(a.status, a.tpr.timeout_ns);
+            }
             if (norm && ph == 0 && !mbar_wait_bounded_u32(rms_bar_u32, 0)) failed = true;
             const float rms = norm ? scratch[kWarps] : 1.0f;
             for (int idx = tid; idx < G * PJ; idx += kConsumers) {
@@ -422,6 +429,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
                     v *= rms;
                     int seg, row;
                     locate(a, job0 + lj, seg, row);
+                    if (a.tpr.tp > 1) {
+                        // Row-parallel projection under tensor parallelism: v is this GPU's share of the
+                        // row. Push it to the peers, collect theirs, add in rank order.
+                        const GemvTpReduce &t = a.tpr;
+                        const size_t at = size_t(t.row_offset) + row;
+                        const size_t slot_at = t.base + size_t(tp_seq & 1u) * t.tp * t.cap;
+                        for (int k = 1; k < t.tp; ++k) {
+                            const int r = (t.rank + k) % t.tp;  // every GPU starts with a different peer
+                            tpx::store_packet(t.inbox.of[r] + slot_at + size_t(t.rank) * t.cap + at, __float_as_uint(v), tp_seq);
+                        }
+                        const uint2 *own = t.inbox.of[t.rank] + slot_at + at;
+                        float sum = 0.f;
+                        for (int r = 0; r < t.tp; ++r) {
+                            const float pv = r == t.rank ? v
+                                                         : __uint_as_float(tpx::wait_packet(own + size_t(r) * t.cap, tp_seq, tp_t0,
+                                                                                            tp_limit, a.status));
+                            sum = r == 0 ? pv : sum + pv;
+                        }
+                        v = sum;
+                    }
                     if (a.seg[seg].res != nullptr) v = (nphases == 1 ? res_pre : a.seg[seg].res[row]) + v;
                     a.seg[seg].y[row] = v;
                     if (v > best_v || (v == best_v && row < best_i)) {
@@ -447,6 +474,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
         pdl_wait();
     }
 
+    if (MODE == kGemvPlain && a.tpr.tp > 1) {
+        // The last CTA to finish moves the exchange's sequence number on; every CTA has read it by then.
+        named_bar_sync(kBarConsumers, kConsumers);
+        if (tid == 0) {
+            const unsigned seq = *reinterpret_cast<volatile unsigned *>(&a.tpr.ctr[0]);
+            __threadfence();
+            const unsigned arrived = atomicAdd(&a.tpr.ctr[1], 1u);
+            if (arrived == gridDim.x - 1) {
+                a.tpr.ctr[1] = 0u;
+                __threadfence();
+                *reinterpret_cast<volatile unsigned *>(&a.tpr.ctr[0]) = tp_next_sequence(seq);
+            }
+        }
+    }
     if (a.argmax_val != nullptr) {
         // Warp, block, then grid reduction of (value, first index).
 #pragma unroll

@@ -3,6 +3,7 @@
 #pragma once
 
 #include "formats.cuh"
+#include "tp_exchange.cuh"
 
 namespace jl {
 
@@ -15,6 +16,20 @@ struct GemvSeg {
 };
 
 enum GemvMode : int { kGemvPlain = 0, kGemvGateUp = 1 };
+
+// Tensor parallelism: the all-reduce that follows a row-parallel projection (output projection, down
+// projection), done by the mat-vec's own epilogue over peer memory. Every rank cuts its rows into
+// the same CTA ranges; the thread that finishes row r on this GPU stores its partial sum into every
+// peer's inbox, collects the peers' partial sums of the same row from its own inbox, adds them in
+// rank order (every GPU gets the same bits) to the residual and writes the row. tp == 0: off.
+struct GemvTpReduce {
+    TpInboxes inbox;
+    size_t base, cap;   // the reduce region of an inbox and its packets per (slot, source rank)
+    int tp, rank;
+    int row_offset;     // index of this launch's row 0 inside that region (batch row * dim)
+    unsigned *ctr;      // [0] sequence of this exchange, [1] CTA arrivals; advanced by the last CTA
+    unsigned long long timeout_ns;
+};
 
 struct GemvArgs {
     GemvSeg seg[3];
@@ -32,6 +47,7 @@ struct GemvArgs {
     unsigned *argmax_count;  // zero on entry, zero again on exit
     int *out_token;
     int *status;  // device status word, see common.cuh
+    GemvTpReduce tpr;  // plain launches of one matrix with a residual only
 };
 
 // Geometry of one launch. A CTA has 16 consumer warps and one producer warp. A row is cut into

@@ -303,6 +303,9 @@ struct AttnSmem {
     float part[kAttnMaxCluster][G][HD + 2];  // in the cluster's first CTA: every CTA's result
     float wgt[G][kAttnMaxFold];
     float inv_l[G];
+    float rope[2][HD / 2];    // cos and sin of this row's position
+    alignas(16) uint32_t knew[HD / 2];    // the new key, rotated and rounded: binary16 pairs as they go to the page
+    alignas(16) uint32_t vnew[HD / 2];    // the new value, rounded
     long long page_base[kAttnPages];
     int is_last;
 };
@@ -379,6 +382,10 @@ __global__ void __launch_bounds__(AttnShape<HD, G, WIDE>::threads, WIDE ? 2 : 1)
         const int64_t phys = a.kv.block_table[int64_t(slot) * a.kv.blocks_per_slot + first_page + pg];
         sm.page_base[pg] = phys * block_stride + int64_t(a.layer) * bt * a.kv.kv_dim + int64_t(kvh) * HD;
     }
+    // The RoPE row of this position (the tables never change) goes to shared memory now, so that
+    // nothing after the wait below has to fetch it.
+    for (int i = tid; i < HD; i += kAttnThreads)
+        sm.rope[i / (HD / 2)][i % (HD / 2)] = (i < HD / 2 ? a.rope_cos : a.rope_sin)[size_t(pos) * (HD / 2) + i % (HD / 2)];
     __syncthreads();
     // Each warp takes a contiguous run of keys so that consecutive keys share a page. The new key
     // of a decode launch goes to the last warp of the first CTA, behind that warp's old keys.
@@ -417,8 +424,7 @@ __global__ void __launch_bounds__(AttnShape<HD, G, WIDE>::threads, WIDE ? 2 : 1)
             }
         }
     };
-    const float *cr = a.rope_cos + size_t(pos) * (HD / 2);
-    const float *ci = a.rope_sin + size_t(pos) * (HD / 2);
+    const float *cr = sm.rope[0], *ci = sm.rope[1];
     if (dec) {
         load_batch(w0);
         pdl_wait();
@@ -432,6 +438,29 @@ __global__ void __launch_bounds__(AttnShape<HD, G, WIDE>::threads, WIDE ? 2 : 1)
         const int d0 = 2 * i;
         sm.q[g][d0 / DK][d0 % DK] = __fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]));
         sm.q[g][d0 / DK][d0 % DK + 1] = __fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]));
+    }
+    if (dec && split == 0) {
+        // The new key of this step: rotate k, round k and v to fp16 as the append does, write them to
+        // the page and keep the rounded pairs in shared memory for the warp that attends to them. The
+        // threads that do this are the upper ones, so that it runs beside the staging of q above.
+        const int64_t off = kv_offset(a.kv, slot, pos, a.layer) + int64_t(kvh) * HD;
+        const float *kh = a.k + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
+        const float *vh = a.v + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
+        for (int idx = kAttnThreads - 1 - tid; idx < HD; idx += kAttnThreads) {
+            const int i = idx % (HD / 2);
+            __half2 h;
+            if (idx < HD / 2) {
+                const float v0 = kh[2 * i], v1 = kh[2 * i + 1];
+                h = __halves2half2(__float2half_rn(__fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]))),
+                                   __float2half_rn(__fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]))));
+                sm.knew[i] = *reinterpret_cast<const uint32_t *>(&h);
+                *reinterpret_cast<__half2 *>(a.kv.kpool + off + 2 * i) = h;
+            } else {
+                h = __halves2half2(__float2half_rn(vh[2 * i]), __float2half_rn(vh[2 * i + 1]));
+                sm.vnew[i] = *reinterpret_cast<const uint32_t *>(&h);
+                *reinterpret_cast<__half2 *>(a.kv.vpool + off + 2 * i) = h;
+            }
+        }
     }
     __syncthreads();
     trace_mark(trace, 3);
@@ -449,39 +478,17 @@ __global__ void __launch_bounds__(AttnShape<HD, G, WIDE>::threads, WIDE ? 2 : 1)
     for (int t0 = w0; t0 < w1x; t0 += UN) {
         if (!(dec && t0 == w0)) load_batch(t0);
         if (extra && w1 - t0 < UN && w1 >= t0) {
-            // The new key sits in this batch: rotate k, round k and v to fp16 as the append does,
-            // keep the rounded values for this step and write them to the page.
-            const int64_t off = kv_offset(a.kv, slot, pos, a.layer) + int64_t(kvh) * HD;
+            // The new key sits in this batch: its rounded pairs are in shared memory.
             if (ku == w1 - t0) {
-                const float *kh = a.k + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD + qd * DK;
-                uint32_t packed[DK / 2];
 #pragma unroll
-                for (int j = 0; j < DK / 2; ++j) {
-                    const float v0 = kh[2 * j], v1 = kh[2 * j + 1];
-                    const float c = cr[qd * (DK / 2) + j], sn = ci[qd * (DK / 2) + j];
-                    const __half2 h = __halves2half2(__float2half_rn(__fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, sn))),
-                                                     __float2half_rn(__fadd_rn(__fmul_rn(v0, sn), __fmul_rn(v1, c))));
-                    packed[j] = *reinterpret_cast<const uint32_t *>(&h);
-                }
-#pragma unroll
-                for (int i = 0; i < DK / 8; ++i) {
-                    kq[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-                    reinterpret_cast<uint4 *>(a.kv.kpool + off + qd * DK)[i] = kq[i];
-                }
-            }
-            const float *vh = a.v + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD + lane * VEC;
-            uint32_t vnew[VEC / 2];
-#pragma unroll
-            for (int j = 0; j < VEC / 2; ++j) {
-                const __half2 h = __halves2half2(__float2half_rn(vh[2 * j]), __float2half_rn(vh[2 * j + 1]));
-                vnew[j] = *reinterpret_cast<const uint32_t *>(&h);
-                reinterpret_cast<uint32_t *>(a.kv.vpool + off + lane * VEC)[j] = vnew[j];
+                for (int i = 0; i < DK / 8; ++i)
+                    kq[i] = *reinterpret_cast<const uint4 *>(&sm.knew[qd * (DK / 2) + 4 * i]);
             }
 #pragma unroll
             for (int u = 0; u < UN; ++u)
                 if (t0 + u == w1) {
 #pragma unroll
-                    for (int j = 0; j < VEC / 2; ++j) vq[u][j] = vnew[j];
+                    for (int j = 0; j < VEC / 2; ++j) vq[u][j] = sm.vnew[lane * (VEC / 2) + j];
                 }
         }
         // q.k: this lane's quarter of its key against the same quarter of every query head.

@@ -1,5 +1,6 @@
-"""Tensor parallelism on real GPUs: one process per GPU, shards cut by the host, NCCL all-reduce per
-sublayer inside the library. Rank 0 compares the gathered logits and the chosen tokens with the CPU
+"""Tensor parallelism on real GPUs: one process per GPU, shards cut by the host, one all-reduce per
+sublayer inside the library (in the mat-vec's own epilogue over peer memory, as a separate
+peer-memory kernel, or through NCCL: all three are run). Rank 0 compares the gathered logits and the chosen tokens with the CPU
 oracle running the whole model. Skipped when fewer than two GPUs are visible."""
 import os
 import socket
@@ -79,9 +80,10 @@ def _rank_main(rank, size, port, out_dir, fmt_value, width, via_gguf=False):
         dist.destroy_process_group()
 
 
-def _run(size, fmt_value, width, push=True, via_gguf=False):
+def _run(size, fmt_value, width, push=True, via_gguf=False, fuse=True):
     import torch.multiprocessing as mp
     os.environ["JITLLM_B200_TP_PUSH"] = "1" if push else "0"  # inherited by the ranks
+    os.environ["JITLLM_B200_TP_FUSE"] = "1" if fuse else "0"  # all-reduce inside the mat-vec epilogue, or its own kernel
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
@@ -90,13 +92,14 @@ def _run(size, fmt_value, width, push=True, via_gguf=False):
         return [dict(np.load(os.path.join(d, f"rank{r}.npz"))) for r in range(size)]
 
 
-@pytest.mark.parametrize("fmt_value,width,push", [(12, 1, True), (12, 1, False), (8, 1, True), (2, 2, True),
-                                                  (12, 16, True), (12, 16, False)])
-def test_two_gpus_match_the_oracle(oracle, built, fmt_value, width, push):
+@pytest.mark.parametrize("fmt_value,width,push,fuse", [(12, 1, True, True), (12, 1, True, False), (12, 1, False, True),
+                                                       (8, 1, True, True), (2, 2, True, True), (2, 3, True, False),
+                                                       (12, 16, True, True), (12, 16, False, True)])
+def test_two_gpus_match_the_oracle(oracle, built, fmt_value, width, push, fuse):
     if _gpu_count() < 2:
         pytest.skip("needs two GPUs")
     import jitllm_b200 as jl
-    got = _run(2, fmt_value, width, push)
+    got = _run(2, fmt_value, width, push, fuse=fuse)
     expect_mode = "peer-memory" if push else "nccl (disabled by JITLLM_B200_TP_PUSH)"
     assert np.array_equal(got[0]["tokens"], got[1]["tokens"])
     assert np.array_equal(got[0]["logits"], got[1]["logits"])
