@@ -521,7 +521,13 @@ def main():
         # greedy steps. Sums are taken in a different order on N GPUs, so tokens may part ways at a
         # near-tie; the count of identical leading tokens and the logit distance say how close it is.
         t_par = time.time()
-        full = jl.synth_model_tensors(cfg, fmt, args.seed, threads=os.cpu_count() or 1)
+        # the whole model the ranks hold between them: every rank's slices, put back together
+        from jitllm_b200.tensor_parallel import assemble_tensor
+        per_rank = [tensors if r == rank else
+                    jl.synth_model_tensors(cfg, fmt, args.seed, threads=os.cpu_count() or 1, tp=jl.TensorParallel(r, world))
+                    for r in range(world)]
+        full = {key: (per_rank[0][key][0], assemble_tensor(cfg, key[0], [pr[key][1] for pr in per_rank]))
+                for key in per_rank[0]}
         dev1 = jl.Device(local_rank)
         m1 = jl.load_model(dev1, cfg, full, cr, ci, maxBatch=B)
         kv1 = m1.createKvStorage(jl.KvStorageRequest(B * need, bps, B, 16, cfg.numberOfLayers, cfg.kvDim))

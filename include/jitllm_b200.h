@@ -202,7 +202,9 @@ int32_t jl_tp_init(jl_ctx *ctx, const char *nccl_path, const void *id128, int32_
 /* How the ranks exchange the small per-step messages (partial sums of up to 16 rows, the best token
  * of each vocabulary shard) after jl_model_finalize: 0 = single GPU, 1 = NCCL collectives, 2 = one
  * kernel per exchange over peer memory (stores into the other GPUs' inboxes through NVLink; inboxes
- * shared by CUDA IPC between processes). Mode 2 is chosen when every rank could map every inbox;
+ * shared by CUDA IPC between processes), 3 = as 2, with the all-reduce that follows the output and
+ * down projections done by the mat-vec kernel's own epilogue (JITLLM_B200_TP_FUSE=0 gives 2 back).
+ * Modes 2 and 3 are chosen when every rank could map every inbox;
  * jl_tp_exchange_note says why not otherwise. JITLLM_B200_TP_PUSH=0 forces mode 1. A rank that
  * waits longer than JITLLM_B200_TP_TIMEOUT_MS (default 5000) for a peer's message gives up and the
  * step returns JL_ERR_TIMEOUT; the group is then out of step and must be torn down. Larger

@@ -385,10 +385,12 @@ class B200Model:
 
     @property
     def exchangeMode(self) -> str:
-        """How the tensor-parallel ranks trade partial sums: 'single', 'nccl' or 'peer-memory'."""
+        """How the tensor-parallel ranks trade partial sums: 'single', 'nccl', 'peer-memory' (one small
+        kernel per exchange) or 'peer-memory, fused' (the all-reduce of the row-parallel projections
+        happens inside the mat-vec kernel's epilogue; the arg-max exchange stays its own kernel)."""
         mode = self.dev._lib.jl_tp_exchange_mode(self.dev.handle)
         note = (self.dev._lib.jl_tp_exchange_note(self.dev.handle) or b"").decode()
-        return ["single", "nccl", "peer-memory"][mode] + (f" ({note})" if note else "")
+        return ["single", "nccl", "peer-memory", "peer-memory, fused"][mode] + (f" ({note})" if note else "")
 
     @property
     def localKvDim(self) -> int:

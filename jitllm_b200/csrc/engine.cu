@@ -1060,7 +1060,7 @@ const char *jl_last_error(jl_ctx *ctx) { return ctx ? ctx->err.c_str() : g_init_
 
 int32_t jl_tp_exchange_mode(jl_ctx *ctx) {
     if (!ctx || ctx->tp_size <= 1) return 0;
-    return ctx->tp_push ? 2 : 1;
+    return ctx->tp_push ? (tp_fused(ctx) ? 3 : 2) : 1;
 }
 
 const char *jl_tp_exchange_note(jl_ctx *ctx) { return ctx ? ctx->tp_note.c_str() : ""; }

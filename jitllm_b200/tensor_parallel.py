@@ -65,6 +65,17 @@ def local_shape(config, role, size: int) -> Tuple[int, int]:
     return rows, cols
 
 
+def assemble_tensor(config, role, shards) -> np.ndarray:
+    """The whole tensor whose slices, in rank order, are `shards`: the inverse of shard_tensor."""
+    size = len(shards)
+    if size == 1 or (role.name not in ROW_SPLIT and role.name not in COL_SPLIT):
+        return shards[0]
+    rows, _ = config.matrix_shape(role)
+    if role.name in ROW_SPLIT:
+        return np.concatenate([np.ascontiguousarray(s).reshape(-1) for s in shards])
+    return np.ascontiguousarray(np.concatenate([np.ascontiguousarray(s).reshape(rows, -1) for s in shards], axis=1)).reshape(-1)
+
+
 def shard_tensor(config, role, ggml_type, data: np.ndarray, tp: TensorParallel) -> np.ndarray:
     """This GPU's slice of one tensor, as bytes (quantised / F16) or float32 (F32), contiguous."""
     if tp.size == 1:

@@ -100,7 +100,7 @@ def test_two_gpus_match_the_oracle(oracle, built, fmt_value, width, push, fuse):
         pytest.skip("needs two GPUs")
     import jitllm_b200 as jl
     got = _run(2, fmt_value, width, push, fuse=fuse)
-    expect_mode = "peer-memory" if push else "nccl (disabled by JITLLM_B200_TP_PUSH)"
+    expect_mode = ("peer-memory, fused" if fuse else "peer-memory") if push else "nccl (disabled by JITLLM_B200_TP_PUSH)"
     assert np.array_equal(got[0]["tokens"], got[1]["tokens"])
     assert np.array_equal(got[0]["logits"], got[1]["logits"])
     assert got[0]["launches"] > 0

@@ -199,3 +199,18 @@ def test_exchange_sequence_keeps_alternating_slots_across_the_wrap():
         assert n != 0
         assert (n & 1) != (seq & 1), hex(seq)
     assert nxt(0xFFFFFFFF) == 2 and nxt(5) == 6
+
+
+def test_assembling_the_slices_gives_back_the_tensor():
+    import jitllm_b200 as jl
+    from jitllm_b200.tensor_parallel import assemble_tensor, shard_tensor
+    cfg = jl.Configuration(dim=1024, hiddenDim=2048, numberOfLayers=1, numberOfHeads=8, numberOfKeyValueHeads=4,
+                           vocabularySize=512, contextLength=16)
+    for fmt in (jl.GGMLType.Q4_K, jl.GGMLType.Q8_0):
+        for role in (jl.TensorRole.ATTENTION_QUERY, jl.TensorRole.ATTENTION_OUTPUT, jl.TensorRole.FFN_DOWN,
+                     jl.TensorRole.OUTPUT, jl.TensorRole.TOKEN_EMBEDDING):
+            rows, cols = cfg.matrix_shape(role)
+            whole = jl.synth_tensor(fmt, rows * cols, seed=int(role) + 1)
+            for size in (2, 4):
+                shards = [shard_tensor(cfg, role, fmt, whole, jl.TensorParallel(r, size)) for r in range(size)]
+                assert np.array_equal(assemble_tensor(cfg, role, shards), whole), (fmt, role, size)
