@@ -343,6 +343,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
             while (walk.k < k_end) {
                 const int k = walk.k;
                 const int n = walk.rows();
+                // The stages of this step: one, or for a gate/up launch the gate rows' stage and the up
+                // rows' stage. All of their rows are multiplied before anything is reduced, so that the
+                // dot products of up to four rows overlap and one transposed reduction serves them all.
+                constexpr int NV = S * SPJ;
+                uint32_t stage[SPJ];
 #pragma unroll
                 for (int which = 0; which < SPJ; ++which) {
                     if (!failed) {
@@ -362,32 +367,64 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
                         t_wait += clock64() - t_w0;
 #endif
                     }
-                    if (failed) continue;  // keep walking so that every barrier below is still reached
-                    const uint32_t stage = my_ring + slot * stage_bytes;
-                    float acc[S];
+                    stage[which] = my_ring + slot * stage_bytes;
+                    if (!failed && which + 1 < SPJ) {  // the second stage sits in the next slot; both are released below
+                        if (++slot == D) {
+                            slot = 0;
+                            parity ^= 1u;
+                        }
+                    }
+                }
+                if (failed) {  // keep walking so that every barrier below is still reached
+                    walk.advance(a, n);
+                    continue;
+                }
+                float acc[NV];
+#pragma unroll
+                for (int which = 0; which < SPJ; ++which)
 #pragma unroll
                     for (int i = 0; i < S; ++i)
-                        acc[i] = (lane_on && i < n && !JL_TRACE_MODE(1)) ? unit_dot<TYPE>(stage + i * rowb, lane, x) : 0.f;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_u32(my_empty + slot * 8);
-                    if (++slot == D) {
-                        slot = 0;
-                        parity ^= 1u;
-                    }
-                    float *dst = partial + size_t(c) * slots + (g * PJ + (k - ph * PJ)) * SPJ + which;
-                    if constexpr (S == 2) {
-                        // Both rows reduced together: lanes 0-15 end up with row 0, lanes 16-31 with row 1.
-                        const bool up = (lane & 16) != 0;
-                        float keep = up ? acc[1] : acc[0];
-                        const float send = up ? acc[0] : acc[1];
-                        keep += __shfl_xor_sync(0xffffffffu, send, 16);
+                        acc[which * S + i] = (lane_on && i < n && !JL_TRACE_MODE(1)) ? unit_dot<TYPE>(stage[which] + i * rowb, lane, x) : 0.f;
+                __syncwarp();
+                if (lane == 0) {
+                    if (SPJ == 2) mbar_arrive_u32(my_empty + (slot == 0 ? D - 1 : slot - 1) * 8);
+                    mbar_arrive_u32(my_empty + slot * 8);
+                }
+                if (++slot == D) {
+                    slot = 0;
+                    parity ^= 1u;
+                }
+                // partial sums of this step: row i of matrix `which` at dst[i * SPJ + which]
+                float *dst = partial + size_t(c) * slots + (g * PJ + (k - ph * PJ)) * SPJ;
+                if constexpr (NV == 4) {
+                    // Four values reduced together: after the exchanges over lane bits 4 and 3 each
+                    // quarter of the warp holds one of them; lanes 0, 8, 16, 24 end up with the sums.
+                    const bool b4 = (lane & 16) != 0, b3 = (lane & 8) != 0;
+                    float k0 = b4 ? acc[2] : acc[0], k1 = b4 ? acc[3] : acc[1];
+                    const float s0 = b4 ? acc[0] : acc[2], s1 = b4 ? acc[1] : acc[3];
+                    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+                    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+                    float keep = b3 ? k1 : k0;
+                    const float send = b3 ? k0 : k1;
+                    keep += __shfl_xor_sync(0xffffffffu, send, 8);
 #pragma unroll
-                        for (int o = 8; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
-                        if ((lane & 15) == 0 && (lane >> 4) < n) dst[(lane >> 4) * SPJ] = keep;
-                    } else {
-                        const float tot = warp_sum(acc[0]);
-                        if (lane == 0) dst[0] = tot;
-                    }
+                    for (int o = 4; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+                    // quarter q = lane / 8 holds acc[q] = (which = q / S, row i = q % S)
+                    const int q = lane >> 3;
+                    if ((lane & 7) == 0 && (q % S) < n) dst[(q % S) * SPJ + q / S] = keep;
+                } else if constexpr (NV == 2) {
+                    // Both values reduced together: lanes 0-15 end up with the first, lanes 16-31 with the second.
+                    const bool up = (lane & 16) != 0;
+                    float keep = up ? acc[1] : acc[0];
+                    const float send = up ? acc[0] : acc[1];
+                    keep += __shfl_xor_sync(0xffffffffu, send, 16);
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+                    const int q = lane >> 4;  // value index: (which, row) = (q / S, q % S)
+                    if ((lane & 15) == 0 && (q % S) < n) dst[(q % S) * SPJ + q / S] = keep;
+                } else {
+                    const float tot = warp_sum(acc[0]);
+                    if (lane == 0) dst[0] = tot;
                 }
                 walk.advance(a, n);
             }
