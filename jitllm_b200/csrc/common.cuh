@@ -201,13 +201,22 @@ __device__ __forceinline__ void trace_cta_word(int cls, int word, unsigned long 
     if (g_trace_buf != nullptr && blockIdx.x < kTraceCtaMax && cls < kTraceClasses)
         g_trace_buf[kTraceWords * (1 + size_t(g_trace_cap)) + (size_t(cls) * kTraceCtaMax + blockIdx.x) * kTraceCtaWords + word] = v;
 }
+// An event log of CTA 0 in the cells no CTA owns (rows 148..159 of every class: 576 words).
+__device__ __forceinline__ void trace_log(int idx, unsigned long long v) {
+    if (g_trace_buf == nullptr || blockIdx.x != 0 || idx < 0 || idx >= kTraceClasses * 96) return;
+    const int cls = idx / 96, rem = idx % 96;
+    g_trace_buf[kTraceWords * (1 + size_t(g_trace_cap)) + (size_t(cls) * kTraceCtaMax + 148 + rem / 8) * kTraceCtaWords + rem % 8] = v;
+}
 #define JL_TRACE_DEFINE_BIND(fn)                                                              \
     cudaError_t fn(unsigned long long *buf, unsigned cap, int mode) {                        \
         cudaError_t e_ = cudaMemcpyToSymbol(g_trace_buf, &buf, sizeof buf);                   \
         if (e_ == cudaSuccess) e_ = cudaMemcpyToSymbol(g_trace_mode, &mode, sizeof mode);     \
         return e_ != cudaSuccess ? e_ : cudaMemcpyToSymbol(g_trace_cap, &cap, sizeof cap);    \
     }
-#define JL_TRACE_MODE(bit) ((g_trace_mode & (bit)) != 0)
+// The experiment switches, read once per kernel into a local named trace_mode (JL_TRACE_MODE_LOCAL):
+// a test of the global inside a loop would put a global load on the path it is meant to time.
+#define JL_TRACE_MODE_LOCAL const int trace_mode = g_trace_mode
+#define JL_TRACE_MODE(bit) ((trace_mode & (bit)) != 0)
 #else
 __device__ __forceinline__ int trace_begin(int) { return -1; }
 __device__ __forceinline__ void trace_mark(int, int) {}
@@ -215,9 +224,11 @@ __device__ __forceinline__ void trace_word(int, int, unsigned long long) {}
 __device__ __forceinline__ void trace_cta_exit() {}
 __device__ __forceinline__ unsigned long long trace_latest_exit() { return 0ull; }
 __device__ __forceinline__ void trace_cta_word(int, int, unsigned long long) {}
+__device__ __forceinline__ void trace_log(int, unsigned long long) {}
 #define JL_TRACE_DEFINE_BIND(fn) \
     cudaError_t fn(unsigned long long *, unsigned, int) { return cudaSuccess; }
-#define JL_TRACE_MODE(bit) false
+#define JL_TRACE_MODE_LOCAL constexpr int trace_mode = 0
+#define JL_TRACE_MODE(bit) ((trace_mode & (bit)) != 0)
 #endif
 
 // ---- arithmetic helpers -----------------------------------------------------------------------

@@ -46,11 +46,7 @@ JL_TRACE_DEFINE_BIND(gemm_trace_bind)
 namespace {
 
 // Which bounded wait the kernel uses (a build-time experiment switch).
-#ifndef JL_GEMM_SUSPENDING_WAIT
 #define GEMM_WAIT mbar_poll_bounded
-#else
-#define GEMM_WAIT mbar_wait_bounded
-#endif
 
 constexpr int kConvertWarps = 16;
 constexpr int kConvertThreads = kConvertWarps * 32;
@@ -107,14 +103,70 @@ __device__ __forceinline__ void tc_fence_after() {
 }
 // D[tmem] (+)= A * B; fp16 operands, fp32 accumulate, A in tensor memory: lane = row, one 32-bit column =
 // two consecutive K elements (even K in the low half), eight columns per K = 16 step; B in shared memory.
-__device__ __forceinline__ void umma_f16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate) {
+// The eight MMAs of one operand stage (K = 128: two 64-column atoms of four K = 16 steps) and the commit
+// that hands the stage back, issued by one elected lane while the whole warp stays converged: every
+// operand is warp-uniform, so the addresses and descriptors can stay in the uniform datapath instead of
+// being moved there one by one in front of each MMA. The shared-memory descriptor is given as its two
+// 32-bit words; KBm is the descriptor's address step of MMA m, in 16-byte units.
+template <int KB1, int KB2, int KB3, int KB4, int KB5, int KB6, int KB7>
+__device__ __forceinline__ void umma_stage_f16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t b_desc_hi,
+                                                      uint32_t idesc, uint32_t free_bar, uint32_t accumulate_first) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t"
+        ".reg .pred pe, pacc, pone;\n\t"
+        ".reg .b64 bd;\n\t"
+        ".reg .b32 lo, ac;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pacc, %6, 0;\n\t"
+        "setp.eq.b32 pone, 0, 0;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, pacc;\n\t"
+        "add.u32 lo, %2, %7;\n\t add.u32 ac, %1, 8;\n\t mov.b64 bd, {lo, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ac], bd, %4, pone;\n\t"
+        "add.u32 lo, %2, %8;\n\t add.u32 ac, %1, 16;\n\t mov.b64 bd, {lo, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ac], bd, %4, pone;\n\t"
+        "add.u32 lo, %2, %9;\n\t add.u32 ac, %1, 24;\n\t mov.b64 bd, {lo, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ac], bd, %4, pone;\n\t"
+        "add.u32 lo, %2, %10;\n\t add.u32 ac, %1, 32;\n\t mov.b64 bd, {lo, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ac], bd, %4, pone;\n\t"
+        "add.u32 lo, %2, %11;\n\t add.u32 ac, %1, 40;\n\t mov.b64 bd, {lo, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ac], bd, %4, pone;\n\t"
+        "add.u32 lo, %2, %12;\n\t add.u32 ac, %1, 48;\n\t mov.b64 bd, {lo, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ac], bd, %4, pone;\n\t"
+        "add.u32 lo, %2, %13;\n\t add.u32 ac, %1, 56;\n\t mov.b64 bd, {lo, %3};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ac], bd, %4, pone;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n\t"
+        "}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(free_bar), "r"(accumulate_first),
+          "n"(KB1), "n"(KB2), "n"(KB3), "n"(KB4), "n"(KB5), "n"(KB6), "n"(KB7)
         : "memory");
+}
+// A commit by one elected lane of a converged warp.
+__device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_u32(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// mbar_poll_bounded on a shared-window address.
+__device__ __forceinline__ bool mbar_poll_bounded_u32(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 24)) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok != 0) return true;
+        __nanosleep(40);
+    }
+    return false;
 }
 // 16 consecutive 32-bit columns of this thread's lane.
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -125,10 +177,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
 // 32 lanes x 16 consecutive fp32 columns of the accumulator into registers.
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     uint32_t r[16];
@@ -142,17 +190,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 64 fp16 (128 B), groups of
-// eight rows 1024 B apart; `addr` is the shared address of the first element of the K slice.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= uint64_t((addr >> 4) & 0x3FFFu);  // start address, 16-byte units
-    d |= uint64_t(1) << 16;                // leading byte offset (unused for swizzled K-major)
-    d |= uint64_t(1024 >> 4) << 32;        // stride byte offset between 8-row groups
-    d |= uint64_t(1) << 46;                // descriptor version for sm_100
-    d |= uint64_t(2) << 61;                // SWIZZLE_128B
-    return d;
-}
+// Shared-memory matrix descriptor of the B operand: K-major, 128-byte swizzle, rows of 64 fp16
+// (128 B), groups of eight rows 1024 B apart. Low word: bits 0-13 the start address in 16-byte
+// units, bit 16 the (unused) leading byte offset; high word: bits 0-13 the stride between 8-row
+// groups in 16-byte units (1024 >> 4), bit 14 the descriptor version for sm_100, bits 29-31 the
+// swizzle mode (2 = 128 bytes). The issuing thread keeps the low word as a running value.
 // Instruction descriptor: D fp32, A and B fp16, both K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t instr_desc_f16(int n) {
     return (1u << 4) | (uint32_t(n >> 3) << 17) | (uint32_t(kTileM >> 4) << 24);
@@ -279,10 +321,11 @@ __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, in
     }
 }
 
-// 64 consecutive weights of one row (one unit: for Q4_K the two sub-blocks that share 32 bytes of
-// nibbles) as 32 tensor-memory columns: `first` = the first 32 weights, `second` = the next 32.
+// 32 of the 64 consecutive weights of one row's unit as 16 tensor-memory columns: `half` 0 = the
+// first 32 weights, 1 = the next 32 (for Q4_K the low and the high nibbles of the unit's 32 bytes).
+// The two halves are converted and stored one after the other so that only 16 results are live.
 template <int TYPE>
-__device__ __forceinline__ void dequant64_to_half(uint32_t row_u32, int unit, uint32_t (&first)[16], uint32_t (&second)[16]) {
+__device__ __forceinline__ void dequant32_to_cols(uint32_t row_u32, int unit, int half, uint32_t (&out)[16]) {
     if constexpr (TYPE == kQ4_K) {
         const uint4 hdr = lds128(row_u32);
         const uint4 q0 = lds128(row_u32 + 16 + unit * 32);
@@ -296,39 +339,32 @@ __device__ __forceinline__ void dequant64_to_half(uint32_t row_u32, int unit, ui
             scw = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
             mw = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
         }
-        const int sh = (unit & 1) * 16;
-        const float ds0 = __fmul_rn(d, float((scw >> sh) & 0xFFu)), ds1 = __fmul_rn(d, float((scw >> (sh + 8)) & 0xFFu));
-        const float mm0 = __fmul_rn(dmin, float((mw >> sh) & 0xFFu)), mm1 = __fmul_rn(dmin, float((mw >> (sh + 8)) & 0xFFu));
+        const int sh = (unit & 1) * 16 + half * 8;
+        const float ds = __fmul_rn(d, float((scw >> sh) & 0xFFu));
+        const float mm = __fmul_rn(dmin, float((mw >> sh) & 0xFFu));
         // One byte permute puts a nibble into bits 16-19 of 0x43000000: the float 128 + q, exactly. With
         // c = -(128 * ds + mm), fma(ds, 128 + q, c) is ds * q - mm rounded once (c itself is off by at
         // most 2^-17 of ds, far below the binary16 rounding that follows), so a weight costs one
         // permute and one fused multiply-add, and no conversion unit.
-        const float c0f = -__fmaf_rn(128.0f, ds0, mm0), c1f = -__fmaf_rn(128.0f, ds1, mm1);
+        const float cf = -__fmaf_rn(128.0f, ds, mm);
         const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const int nib = half * 4;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const uint32_t vl = qw[i] & 0x0F0F0F0Fu, vh = (qw[i] >> 4) & 0x0F0F0F0Fu;
-            const float a0 = __uint_as_float(__byte_perm(vl, 0x43000000u, 0x7054));
-            const float a1 = __uint_as_float(__byte_perm(vl, 0x43000000u, 0x7154));
-            const float a2 = __uint_as_float(__byte_perm(vl, 0x43000000u, 0x7254));
-            const float a3 = __uint_as_float(__byte_perm(vl, 0x43000000u, 0x7354));
-            const float b0 = __uint_as_float(__byte_perm(vh, 0x43000000u, 0x7054));
-            const float b1 = __uint_as_float(__byte_perm(vh, 0x43000000u, 0x7154));
-            const float b2 = __uint_as_float(__byte_perm(vh, 0x43000000u, 0x7254));
-            const float b3 = __uint_as_float(__byte_perm(vh, 0x43000000u, 0x7354));
-            first[2 * i] = pack_half2(__fmaf_rn(ds0, a0, c0f), __fmaf_rn(ds0, a1, c0f));
-            first[2 * i + 1] = pack_half2(__fmaf_rn(ds0, a2, c0f), __fmaf_rn(ds0, a3, c0f));
-            second[2 * i] = pack_half2(__fmaf_rn(ds1, b0, c1f), __fmaf_rn(ds1, b1, c1f));
-            second[2 * i + 1] = pack_half2(__fmaf_rn(ds1, b2, c1f), __fmaf_rn(ds1, b3, c1f));
+            const uint32_t v = (qw[i] >> nib) & 0x0F0F0F0Fu;
+            const float a0 = __uint_as_float(__byte_perm(v, 0x43000000u, 0x7054));
+            const float a1 = __uint_as_float(__byte_perm(v, 0x43000000u, 0x7154));
+            const float a2 = __uint_as_float(__byte_perm(v, 0x43000000u, 0x7254));
+            const float a3 = __uint_as_float(__byte_perm(v, 0x43000000u, 0x7354));
+            out[2 * i] = pack_half2(__fmaf_rn(ds, a0, cf), __fmaf_rn(ds, a1, cf));
+            out[2 * i + 1] = pack_half2(__fmaf_rn(ds, a2, cf), __fmaf_rn(ds, a3, cf));
         }
     } else {
-        uint4 c0[4], c1[4];
-        dequant32_to_half<TYPE>(row_u32, unit, 0, c0);
-        dequant32_to_half<TYPE>(row_u32, unit, 1, c1);
+        uint4 c[4];
+        dequant32_to_half<TYPE>(row_u32, unit, half, c);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            first[4 * c] = c0[c].x; first[4 * c + 1] = c0[c].y; first[4 * c + 2] = c0[c].z; first[4 * c + 3] = c0[c].w;
-            second[4 * c] = c1[c].x; second[4 * c + 1] = c1[c].y; second[4 * c + 2] = c1[c].z; second[4 * c + 3] = c1[c].w;
+        for (int k = 0; k < 4; ++k) {
+            out[4 * k] = c[k].x; out[4 * k + 1] = c[k].y; out[4 * k + 2] = c[k].z; out[4 * k + 3] = c[k].w;
         }
     }
 }
@@ -357,7 +393,12 @@ struct GemmSmem {
     static constexpr int b_off = 0;
     static constexpr int raw_off = stages * b_stage;
     static constexpr int bar_off = raw_off + raw_bytes;
+#ifdef JL_TRACE
+    static constexpr int log_off = bar_off + 256;  // trace build: an event log of 512 words, copied out at the end
+    static constexpr int total = log_off + 4096 + 1024;
+#else
     static constexpr int total = bar_off + 256 + 1024;
+#endif
 };
 static_assert(GemmSmem<kQ8_0, 64>::total <= 227 * 1024 && GemmSmem<kQ4_K, 64>::total <= 227 * 1024 &&
                   GemmSmem<kQ4_K, 16>::total <= 227 * 1024 && GemmSmem<kQ8_0, 32>::total <= 227 * 1024,
@@ -459,9 +500,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     constexpr int RS = R::stages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int trace = trace_begin(kTraceGemm);
+    JL_TRACE_MODE_LOCAL;
     // 1024-byte aligned base: the swizzle pattern is a function of the shared address.
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int ST = S::stages;
+#ifdef JL_TRACE
+    unsigned long long *slog = reinterpret_cast<unsigned long long *>(base + S::log_off);
+    const bool logging = blockIdx.x == 0 && a.nseg == 2;
+    if (tid < 512) slog[tid] = 0ull;
+#define SLOG(idx, cond) do { if (logging && (cond)) slog[(idx)] = static_cast<unsigned long long>(clock64()); } while (0)
+#else
+#define SLOG(idx, cond) do { } while (0)
+#endif
     uint64_t *a_free = reinterpret_cast<uint64_t *>(base + S::bar_off);  // [ST] tensor core done with operand stage
     uint64_t *a_full = a_free + ST;                                       // [ST] operand stage written
     uint64_t *raw_full = a_full + ST;                                     // [RS] raw bytes landed
@@ -505,7 +555,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const uint32_t tmem_d = *tmem_ptr;
     trace_mark(trace, 2);
 #ifdef JL_TRACE
-    long long tw_raw = 0, tw_free = 0, tw_acc = 0, tw_epi = 0;
+    long long tw_raw = 0, tw_free = 0, tw_acc = 0, tw_epi = 0, tw_pub = 0, tw_cvt = 0;
 #endif
 
     if (warp == kConvertWarps + 1) {
@@ -531,6 +581,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     atomicExch(a.status, kDevTimeout);
                     break;
                 }
+                SLOG(160 + (i - 4), i >= 4 && i < 12);
                 const CUtensorMap *tmap = tr.seg == 0 ? &tm0 : (tr.seg == 1 ? &tm1 : &tm2);
                 if (JL_TRACE_MODE(8)) {  // trace build, timing experiment: no copy at all, the stage is declared full
                     mbar_arrive(raw_full + st);
@@ -559,6 +610,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     if (!ok) break;
                     uint8_t *b_st = base + S::b_off + s * S::b_stage;
                     const int k0 = r * kRawK + j * kStageK;
+                    SLOG(176 + (q - 8), q >= 8 && q < 24);
+                    if (JL_TRACE_MODE(64)) {  // trace build, timing experiment: no activation copy
+                        mbar_arrive(a_full + s);
+                        continue;
+                    }
                     mbar_expect_tx(a_full + s, S::b_stage);
 #pragma unroll
                     for (int atom = 0; atom < 2; ++atom) {
@@ -576,51 +632,82 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
     } else if (warp == kConvertWarps) {
         // ---- tensor-core issue ---------------------------------------------------------------
-        if (lane == 0) {
+        // An operand stage is only handed back (a_free) once its eight MMAs are issued, so this
+        // warp's instruction count per stage is on the kernel's critical path: it shares its scheduler
+        // with four conversion warps that are always ready to issue. The loop carries the stage index,
+        // the barrier parity, the tensor-memory column and the descriptor's address word as running
+        // values, the descriptor's constant upper word is built once, and the whole warp runs the loop
+        // converged (one elected lane issues), so every operand is warp-uniform.
+        {
             constexpr uint32_t idesc = instr_desc_f16(2 * NT);
-            int i = 0, done = 0;
-            int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
-            for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
-                if (++r == raw_total) {
-                    r = 0;
-                    ++u;
-                }
-                const long long u_lo = (long long)u * raw_total;
-                const long long seg_begin = u_lo > lo ? u_lo : lo;
+            constexpr uint32_t desc_hi = uint32_t(1024 >> 4) | (1u << 14) | (2u << 29);  // SBO, version, 128-byte swizzle
+            constexpr uint32_t b_step = uint32_t(S::b_stage >> 4);
+            constexpr int kAtom = S::b_sub >> 4;  // descriptor step between the two 64-column atoms
+            const uint32_t a_col0 = tmem_d + TmemPlan<NT>::a_stage0;
+            const uint32_t b_lo0 = ((smem_u32(base + S::b_off) >> 4) & 0x3FFFu) | (1u << 16);
+            const uint32_t full0 = smem_u32(a_full), free0 = smem_u32(a_free), acc_full_u32 = smem_u32(acc_full);
+            int s = 0, done = 0;
+#ifdef JL_TRACE
+            int qlog = 0;
+#endif
+            uint32_t parity = 0, a_col = a_col0, b_lo = b_lo0;
+            bool ok = true;
+            long long f = lo;
+            while (f < hi && ok && *abort_flag == 0u) {
+                const long long u_lo = f / raw_total * raw_total;
                 const long long seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
-                bool ok = true;
-                for (int j = 0; j < 2 && ok; ++j) {
-                    const int q = 2 * i + j, s = q % ST;
-                    ok = GEMM_WAIT(a_full + s, uint32_t(q / ST) & 1u);
-                    const bool first = f == seg_begin && j == 0;
-                    if (ok && first && done > 0) ok = GEMM_WAIT(acc_empty, uint32_t(done - 1) & 1u);
+                const int nstage = 2 * int(seg_end - f);  // operand stages of this CTA's share of the tile
+#ifdef JL_TRACE
+                const long long tm2_ = clock64();
+#endif
+                if (done > 0) ok = GEMM_WAIT(acc_empty, uint32_t(done - 1) & 1u);
+#ifdef JL_TRACE
+                tw_cvt += clock64() - tm2_;
+#endif
+                for (int k = 0; k < nstage && ok; ++k) {
+#ifdef JL_TRACE
+                    const long long tm0_ = clock64();
+#endif
+                    ok = mbar_poll_bounded_u32(full0 + 8u * uint32_t(s), parity);
+#ifdef JL_TRACE
+                    tw_pub += clock64() - tm0_;
+#endif
                     if (!ok) break;
+                    SLOG(128 + (qlog - 8) * 2, lane == 0 && qlog >= 8 && qlog < 24);
+                    __syncwarp();  // elect.sync below names every lane
                     tc_fence_after();
-                    const uint32_t ta0 = tmem_d + TmemPlan<NT>::a_stage0 + uint32_t(s) * kTmemAStageCols;
-                    const uint64_t db0 = smem_desc_sw128(smem_u32(base + S::b_off + s * S::b_stage));
-#pragma unroll
-                    for (int atom = 0; atom < 2; ++atom) {
-#pragma unroll
-                        for (int k16 = 0; k16 < 4; ++k16) {
-                            const uint32_t ka = uint32_t(atom * 4 + k16) * 8u;  // eight columns per K = 16
-                            const uint64_t kb = uint64_t((atom * S::b_sub + k16 * 32) >> 4);
-                            if (JL_TRACE_MODE(4)) continue;  // trace build only
-                            umma_f16_tmem_a(tmem_d, ta0 + ka, db0 + kb, idesc, (first && atom == 0 && k16 == 0) ? 0u : 1u);
-                        }
-                    }
-                    if (JL_TRACE_MODE(4) && JL_TRACE_MODE(32)) mbar_arrive(a_free + s);  // trace build, only without MMAs
-                    else umma_commit(a_free + s);  // arrives when every MMA issued so far has completed
-                    if (f + 1 == seg_end && j == 1) {
-                        umma_commit(acc_full);
-                        ++done;
+                    umma_stage_f16_tmem_a<2, 4, 6, kAtom, kAtom + 2, kAtom + 4, kAtom + 6>(
+                        tmem_d, a_col, b_lo, desc_hi, idesc, free0 + 8u * uint32_t(s), k == 0 ? 0u : 1u);
+                    SLOG(128 + (qlog - 8) * 2 + 1, lane == 0 && qlog >= 8 && qlog < 24);
+#ifdef JL_TRACE
+                    ++qlog;
+#endif
+                    if (++s == ST) {
+                        s = 0;
+                        parity ^= 1u;
+                        a_col = a_col0;
+                        b_lo = b_lo0;
+                    } else {
+                        a_col += kTmemAStageCols;
+                        b_lo += b_step;
                     }
                 }
-                if (!ok) {
-                    *abort_flag = 1u;
-                    atomicExch(a.status, kDevTimeout);
-                    break;
-                }
+                if (!ok) break;
+                __syncwarp();
+                umma_commit_elect(acc_full_u32);
+                ++done;
+                f = seg_end;
             }
+            if (!ok && lane == 0) {
+                *abort_flag = 1u;
+                atomicExch(a.status, kDevTimeout);
+            }
+#ifdef JL_TRACE
+            if (lane == 0) {
+                trace_cta_word(4, 0, static_cast<unsigned long long>(tw_pub));  // issue warp: waits for full operand stages
+                trace_cta_word(4, 1, static_cast<unsigned long long>(tw_cvt));  // ... and for the accumulator to be read out
+            }
+#endif
         }
     } else {
         // ---- operand conversion and epilogue (warps 0-15) -------------------------------------
@@ -634,7 +721,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // converting activations inside the kernel (no pre-split buffer) is kept for tiles up to 64 tokens
         constexpr int kBPerThread = (!XT && NT <= 64) ? (kBChunks + kGroupThreads - 1) / kGroupThreads : 0;
         const int lane_grp = warp & 3, col_grp = warp >> 2;  // epilogue: TMEM lanes 32*lane_grp, columns 16*col_grp
-        int i = 0, done = 0, cur_u = -1, fix_phase = 0;
+        int i = 0, done = 0, fix_phase = 0;
         TileRef tr = {0, 0};
         int tok0 = 0;
         bool a_valid = false;
@@ -645,41 +732,53 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // to become free next would be the unpublished one, so there the stage is published at once.
         constexpr bool kDefer = ST >= 3;
         int pending = -1;
+        const uint32_t raw_full0 = smem_u32(raw_full), raw_empty0 = smem_u32(raw_empty);
+        const uint32_t a_free0 = smem_u32(a_free), a_full0 = smem_u32(a_full);
         auto publish = [&]() {
             if (pending < 0) return;
             tmem_wait_st();
             tc_fence_before();
             if (!XT) fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(a_full + pending);
+            if (lane == 0) mbar_arrive_u32(a_full0 + 8u * uint32_t(pending));
             pending = -1;
         };
-        int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
-        for (long long f = lo; f < hi && ok && *abort_flag == 0u; ++f, ++i) {
-            if (++r == raw_total) {
-                r = 0;
-                ++u;
-            }
-            if (u != cur_u) {
-                cur_u = u;
-                tr = locate_tile(a, u / n_tiles);
-                tok0 = (u % n_tiles) * NT;
-                a_valid = tr.row0 + a_row < a.seg[tr.seg].rows;
-            }
-            const int st = i % RS;
+        // The loop's indices are running values (raw ring slot and parity, this group's operand stage
+        // and how often it has wrapped): with four conversion warps on every scheduler, scalar
+        // bookkeeping between two conversions costs several cycles per instruction.
+        const uint32_t raw_row0 = smem_u32(base + S::raw_off) + uint32_t(a_row) * R::row_bytes;
+        // this thread's row is TMEM lane a_row (its warp may touch lanes 32 * (warp % 4) ..); its 64
+        // weights are columns a_unit * 32 .. + 31 of the operand stage
+        const uint32_t tm_col0 = tmem_d + (uint32_t(a_row & ~31) << 16) + TmemPlan<NT>::a_stage0 + uint32_t(a_unit) * 32u;
+        int st = 0, s = grp % ST, rev = grp / ST;
+        uint32_t raw_par = 0;
+        long long f = lo;
+        while (f < hi && ok && *abort_flag == 0u) {
+            const int u = int(f / raw_total);
+            const long long u_lo = (long long)u * raw_total;
+            const long long seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
+            const int nraw = int(seg_end - f);
+            int r = int(f - u_lo);
+            tr = locate_tile(a, u / n_tiles);
+            tok0 = (u % n_tiles) * NT;
+            a_valid = tr.row0 + a_row < a.seg[tr.seg].rows;
+          for (int it = 0; it < nraw && *abort_flag == 0u; ++it, ++r, ++i) {
 #ifdef JL_TRACE
             const long long tq0 = clock64();
+            const bool lgw = (tid == 0 || tid == 256 || tid == 96) && i >= 4 && i < 12;
+            const int lg = (tid == 0 ? 0 : (tid == 256 ? 40 : 80)) + (i - 4) * 5;
+            SLOG(lg, lgw);
 #endif
-            ok = GEMM_WAIT(raw_full + st, uint32_t(i / RS) & 1u);
+            ok = mbar_poll_bounded_u32(raw_full0 + 8u * uint32_t(st), raw_par);
 #ifdef JL_TRACE
             tw_raw += clock64() - tq0;
+            SLOG(lg + 1, lgw);
             if (i == 0) trace_mark(trace, 3);
 #endif
             if (!ok) break;
-            const uint32_t row_u32 = smem_u32(base + S::raw_off + st * R::stage_bytes) + uint32_t(a_row) * R::row_bytes;
+            const uint32_t row_u32 = raw_row0 + uint32_t(st) * R::stage_bytes;
             {
                 const int j = grp;
-                const int q = 2 * i + j, s = q % ST;
                 const int k0 = r * kRawK + j * kStageK;
                 // Activations first: their loads are in flight while the weights are converted.
                 float4 xv[kBPerThread > 0 ? kBPerThread : 1][2];
@@ -699,27 +798,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #ifdef JL_TRACE
                 const long long tq1 = clock64();
 #endif
-                if (q >= ST) ok = GEMM_WAIT(a_free + s, uint32_t(q / ST - 1) & 1u);
+                if (rev > 0) ok = mbar_poll_bounded_u32(a_free0 + 8u * uint32_t(s), uint32_t(rev - 1) & 1u);
 #ifdef JL_TRACE
                 tw_free += clock64() - tq1;
+                SLOG(lg + 2, lgw);
 #endif
                 if (ok) {
                 uint8_t *b_st = base + S::b_off + s * S::b_stage;
                 if (!JL_TRACE_MODE(1)) {  // always true outside the trace build
                     tc_fence_after();  // the stage's previous MMAs are complete (a_free): order the store after them
-                    uint32_t first[16], second[16];
-                    dequant64_to_half<TYPE>(row_u32, 2 * j + a_unit, first, second);
-                    if (!a_valid) {  // rows past the end of the matrix (bottom tile only)
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) first[c] = second[c] = 0u;
-                    }
-                    // this thread's row is TMEM lane a_row (its warp may touch lanes 32 * (warp % 4) ..);
-                    // its 64 weights are columns a_unit * 32 .. + 31 of the stage
-                    const uint32_t col0 = tmem_d + (uint32_t(a_row & ~31) << 16) + TmemPlan<NT>::a_stage0 +
-                                          uint32_t(s) * kTmemAStageCols + uint32_t(a_unit) * 32u;
+                    const uint32_t col0 = tm_col0 + uint32_t(s) * kTmemAStageCols;
+#ifdef JL_TRACE
+                    const long long tq4 = clock64();
+#endif
                     publish();  // the previous stage of this group: its stores were issued a whole conversion ago
-                    tmem_st16(col0, first);
-                    tmem_st16(col0 + 16u, second);
+#ifdef JL_TRACE
+                    const long long tq5 = clock64();
+                    tw_pub += tq5 - tq4;
+#endif
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        uint32_t cols[16];
+                        dequant32_to_cols<TYPE>(row_u32, 2 * j + a_unit, hf, cols);
+                        if (!a_valid) {  // rows past the end of the matrix (bottom tile only)
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) cols[c] = 0u;
+                        }
+                        tmem_st16(col0 + 16u * hf, cols);
+                    }
+#ifdef JL_TRACE
+                    tw_cvt += clock64() - tq5;
+                    SLOG(lg + 3, lgw);
+#endif
                 } else {
                     publish();
                 }
@@ -748,16 +858,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 // both are settled in publish().
                 pending = s;
                 if (!kDefer) publish();
+                s += 2;
+                if (s >= ST) {
+                    s -= ST;
+                    ++rev;
+                }
                 }
             }
             if (!ok) break;
             // This warp has read both halves of the raw stage: hand its share back.
             __syncwarp();
-            if (lane == 0) mbar_arrive(raw_empty + st);
-
-            const long long u_lo = (long long)u * raw_total;
-            const long long seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
-            if (f + 1 != seg_end) continue;
+            if (lane == 0) mbar_arrive_u32(raw_empty0 + 8u * uint32_t(st));
+            SLOG(lg + 4, lgw);
+            if (++st == RS) {
+                st = 0;
+                raw_par ^= 1u;
+            }
+          }
+            if (!ok || *abort_flag != 0u) break;
             // ---- this CTA's share of output tile u is complete -----------------------------------
             const long long seg_begin = u_lo > lo ? u_lo : lo;
             const bool whole = seg_begin == u_lo && seg_end == u_lo + raw_total;
@@ -826,11 +944,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #ifdef JL_TRACE
             tw_epi += clock64() - tq3;
 #endif
+            f = seg_end;
         }
 #ifdef JL_TRACE
         trace_mark(trace, 4);
         trace_word(trace, 6, (static_cast<unsigned long long>(tw_raw) << 32) | static_cast<unsigned long long>(tw_free & 0xffffffffll));
         trace_word(trace, 7, (static_cast<unsigned long long>(tw_acc) << 32) | static_cast<unsigned long long>(tw_epi & 0xffffffffll));
+        if (tid == 0) {  // this CTA's own sums, in the per-CTA cells
+            trace_cta_word(5, 0, static_cast<unsigned long long>(tw_pub));
+            trace_cta_word(5, 1, static_cast<unsigned long long>(tw_cvt));
+            trace_cta_word(5, 2, static_cast<unsigned long long>(tw_raw));
+            trace_cta_word(5, 3, static_cast<unsigned long long>(tw_free));
+            trace_cta_word(5, 4, static_cast<unsigned long long>(tw_acc));
+            trace_cta_word(5, 5, static_cast<unsigned long long>(tw_epi));
+            trace_cta_word(5, 6, static_cast<unsigned long long>(i));
+        }
 #endif
         if (!ok && lane == 0) {
             *abort_flag = 1u;
@@ -840,6 +968,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     tc_fence_before();
     __syncthreads();
     if (warp == kConvertWarps) tmem_dealloc(tmem_d, tmem_cols);
+#ifdef JL_TRACE
+    if (logging && tid < 512) trace_log(tid, slog[tid]);
+#endif
     trace_mark(trace, 5);
 }
 

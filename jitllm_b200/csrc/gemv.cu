@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
     constexpr int SPJ = (MODE == kGemvGateUp) ? 2 : 1;  // row streams per job
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int trace = trace_begin(kTraceGemv);
+    JL_TRACE_MODE_LOCAL;
     if (a.active != nullptr && *a.active == 0) {
         // Still wait: a grid that finished without waiting would let its successor run ahead of
         // the grid before this one.
