@@ -213,7 +213,6 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 template <int TYPE>
 struct RawFmt {
     static constexpr int row_bytes = (TYPE == kQ8_0) ? 272 : 144;  // 256 columns of one row
-    static constexpr int stages = (TYPE == kQ8_0) ? 2 : 3;
     static constexpr int stage_bytes = kTileM * row_bytes;
 };
 
@@ -383,23 +382,32 @@ template <int TYPE, int NT>
 struct GemmSmem {
     static constexpr int b_sub = 2 * NT * 128;         // one 64-column atom of B: hi rows, then lo rows
     static constexpr int b_stage = 2 * b_sub;
-    static constexpr int raw_bytes = RawFmt<TYPE>::stages * RawFmt<TYPE>::stage_bytes;
-    static constexpr int budget = 227 * 1024 - 1024 /*alignment slack*/ - 256 /*barriers*/ - raw_bytes;
+    static constexpr int bar_bytes = 384;               // barriers, the tensor-memory address and two flags
+#ifdef JL_TRACE
+    static constexpr int log_bytes = 4096;              // trace build: an event log of 512 words, copied out at the end
+#else
+    static constexpr int log_bytes = 0;
+#endif
+    static constexpr int budget = 227 * 1024 - 1024 /*alignment slack*/ - bar_bytes - log_bytes;
     // Operand stages: the A half lives in tensor memory (six stages fit beside the accumulator), the
     // B half in shared memory. Several stages must be in flight to hide the round trip
-    // conversion -> MMA -> commit -> stage free again.
-    static constexpr int fit = budget / b_stage;
+    // conversion -> MMA -> commit -> stage free again. They come first; two raw stages are the
+    // least the raw ring works with.
+    static constexpr int fit = (budget - 2 * RawFmt<TYPE>::stage_bytes) / b_stage;
     static constexpr int stages = fit >= TmemPlan<NT>::a_stages ? TmemPlan<NT>::a_stages : fit;
+    // Raw stages take what is left, up to three: a raw stage is requested when its slot is handed
+    // back and needed that many iterations later. Deeper rings measured slower: every CTA requests
+    // its whole ring at kernel start, and the first stage then lands behind that burst.
+    static constexpr int raw_fit = (budget - stages * b_stage) / RawFmt<TYPE>::stage_bytes;
+    static constexpr int raw_stages = raw_fit > 3 ? 3 : raw_fit;
+    static constexpr int raw_bytes = raw_stages * RawFmt<TYPE>::stage_bytes;
     static constexpr int b_off = 0;
     static constexpr int raw_off = stages * b_stage;
     static constexpr int bar_off = raw_off + raw_bytes;
-#ifdef JL_TRACE
-    static constexpr int log_off = bar_off + 256;  // trace build: an event log of 512 words, copied out at the end
-    static constexpr int total = log_off + 4096 + 1024;
-#else
-    static constexpr int total = bar_off + 256 + 1024;
-#endif
+    static constexpr int log_off = bar_off + bar_bytes;
+    static constexpr int total = log_off + log_bytes + 1024;
 };
+static_assert((2 * 6 + 2 * 8 + 3) * 8 + 64 <= GemmSmem<kQ4_K, 32>::bar_bytes, "barrier block");
 static_assert(GemmSmem<kQ8_0, 64>::total <= 227 * 1024 && GemmSmem<kQ4_K, 64>::total <= 227 * 1024 &&
                   GemmSmem<kQ4_K, 16>::total <= 227 * 1024 && GemmSmem<kQ8_0, 32>::total <= 227 * 1024,
               "shared memory budget");
@@ -426,9 +434,13 @@ __device__ __forceinline__ TileRef locate_tile(const GemmArgs &a, int tile) {
 }
 
 // The contiguous range of the flattened work list that CTA c owns.
-__device__ __forceinline__ long long range_lo(long long total, int c, int ctas) { return total * c / ctas; }
-__device__ __forceinline__ int cta_of(long long total, long long f, int ctas) {
-    int c = int(f * ctas / total);
+// (The launcher refuses work lists with total * ctas >= 2^32, so the arithmetic stays in 32 bits: a
+// 64-bit division costs about a hundred instructions, and these run at every tile end.)
+__device__ __forceinline__ int range_lo(int total, int c, int ctas) {
+    return int(uint32_t(total) * uint32_t(c) / uint32_t(ctas));
+}
+__device__ __forceinline__ int cta_of(int total, int f, int ctas) {
+    int c = int(uint32_t(f) * uint32_t(ctas) / uint32_t(total));
     while (c + 1 < ctas && range_lo(total, c + 1, ctas) <= f) ++c;
     while (c > 0 && range_lo(total, c, ctas) > f) --c;
     return c;
@@ -438,8 +450,8 @@ __device__ __forceinline__ int cta_of(long long total, long long f, int ctas) {
 // that its registers (every contributor's load is issued before the first add: the fold costs about
 // one L2 round trip per item instead of one per contributor) do not weigh on the conversion loop.
 template <int NT>
-__device__ __noinline__ void fold_partials(const GemmArgs &a, const GemmSeg &seg, int row0, int tok0, long long u_lo,
-                                           long long total, int ctas, int c_first, int c_last, int tid) {
+__device__ __noinline__ void fold_partials(const GemmArgs &a, const GemmSeg &seg, int row0, int tok0, int c_first, int c_last,
+                                           int tid) {
     const int ntok = min(NT, a.n - tok0);
     const int ncontrib = c_last - c_first + 1;
     const size_t slot_floats = size_t(kTileM) * NT;
@@ -450,7 +462,7 @@ __device__ __noinline__ void fold_partials(const GemmArgs &a, const GemmSeg &seg
         for (int k = 0; k < 8; ++k) {
             if (k < ncontrib) {
                 const int c = c_first + k;
-                const int which = range_lo(total, c, ctas) > u_lo ? 0 : 1;
+                const int which = k == 0 ? 1 : 0;  // only the first contributor's range starts before the tile
                 pv[k] = __ldcg(reinterpret_cast<const float4 *>(a.scratch + (size_t(c) * 2 + which) * slot_floats +
                                                                 t * kTileM + rr));
             } else {
@@ -468,7 +480,7 @@ __device__ __noinline__ void fold_partials(const GemmArgs &a, const GemmSeg &seg
             }
         }
         for (int c = c_first + 8; c <= c_last; ++c) {  // more than eight contributors: rare
-            const int which = range_lo(total, c, ctas) > u_lo ? 0 : 1;
+            const int which = 0;
             const float4 more = __ldcg(reinterpret_cast<const float4 *>(a.scratch + (size_t(c) * 2 + which) * slot_floats +
                                                                         t * kTileM + rr));
             sum.x += more.x;
@@ -497,7 +509,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     extern __shared__ uint8_t smem_raw[];
     using S = GemmSmem<TYPE, NT>;
     using R = RawFmt<TYPE>;
-    constexpr int RS = R::stages;
+    constexpr int RS = S::raw_stages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int trace = trace_begin(kTraceGemm);
     JL_TRACE_MODE_LOCAL;
@@ -519,8 +531,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint64_t *acc_full = raw_empty + RS;                                  // accumulator finished
     uint64_t *acc_empty = acc_full + 1;                                   // accumulator read out
     uint64_t *fix_bar = acc_empty + 1;                                    // conversion warps' own barrier
-    uint32_t *tmem_ptr = reinterpret_cast<uint32_t *>(base + S::bar_off + 192);
-    volatile uint32_t *last_flag = tmem_ptr + 1;
+    uint32_t *tmem_ptr = reinterpret_cast<uint32_t *>(base + S::bar_off + S::bar_bytes - 16);
+    volatile uint32_t *fold_flags = reinterpret_cast<uint32_t *>(base + S::bar_off + S::bar_bytes - 64);  // two sets of four
     volatile uint32_t *abort_flag = tmem_ptr + 2;
     constexpr uint32_t tmem_cols = kTmemCols;
 
@@ -528,9 +540,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int s = 0; s < a.nseg; ++s) tiles += (a.seg[s].rows + kTileM - 1) / kTileM;
     const int n_tiles = (a.n + NT - 1) / NT;
     const int raw_total = a.cols / kRawK;
-    const long long total = (long long)tiles * n_tiles * raw_total;
+    const int total = tiles * n_tiles * raw_total;
     const int ctas = gridDim.x;
-    const long long lo = range_lo(total, blockIdx.x, ctas), hi = range_lo(total, blockIdx.x + 1, ctas);
+    const int lo = range_lo(total, blockIdx.x, ctas), hi = range_lo(total, blockIdx.x + 1, ctas);
 
     if (warp == kConvertWarps) tmem_alloc(tmem_ptr, tmem_cols);
     if (tid == 0) {
@@ -546,7 +558,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         mbar_init(acc_empty, kConvertWarps);
         mbar_init(fix_bar, kConvertWarps);
         mbar_fence_init();
-        *last_flag = 0u;
         *abort_flag = 0u;
     }
     tc_fence_before();
@@ -565,8 +576,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             fence_proxy_async();
             int i = 0, cur_u = -1;
             TileRef tr = {0, 0};
-            int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
-            for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
+            int u = lo / raw_total, r = lo - u * raw_total - 1;
+            for (int f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
                 if (++r == raw_total) {
                     r = 0;
                     ++u;
@@ -596,8 +607,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // ---- activation tiles by TMA (pre-split binary16 hi / lo rows), one request set per operand stage
         if (lane == 0 && XT) {
             int i = 0;
-            int u = int(lo / raw_total), r = int(lo - (long long)u * raw_total) - 1;
-            for (long long f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
+            int u = lo / raw_total, r = lo - u * raw_total - 1;
+            for (int f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
                 if (++r == raw_total) {
                     r = 0;
                     ++u;
@@ -652,11 +663,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #endif
             uint32_t parity = 0, a_col = a_col0, b_lo = b_lo0;
             bool ok = true;
-            long long f = lo;
+            int f = lo;
             while (f < hi && ok && *abort_flag == 0u) {
-                const long long u_lo = f / raw_total * raw_total;
-                const long long seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
-                const int nstage = 2 * int(seg_end - f);  // operand stages of this CTA's share of the tile
+                const int u_lo = f / raw_total * raw_total;
+                const int seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
+                const int nstage = 2 * (seg_end - f);  // operand stages of this CTA's share of the tile
 #ifdef JL_TRACE
                 const long long tm2_ = clock64();
 #endif
@@ -721,7 +732,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // converting activations inside the kernel (no pre-split buffer) is kept for tiles up to 64 tokens
         constexpr int kBPerThread = (!XT && NT <= 64) ? (kBChunks + kGroupThreads - 1) / kGroupThreads : 0;
         const int lane_grp = warp & 3, col_grp = warp >> 2;  // epilogue: TMEM lanes 32*lane_grp, columns 16*col_grp
-        int i = 0, done = 0, fix_phase = 0;
+        int i = 0, done = 0, fix_phase = 0, fold_turn = 0;
         TileRef tr = {0, 0};
         int tok0 = 0;
         bool a_valid = false;
@@ -752,13 +763,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const uint32_t tm_col0 = tmem_d + (uint32_t(a_row & ~31) << 16) + TmemPlan<NT>::a_stage0 + uint32_t(a_unit) * 32u;
         int st = 0, s = grp % ST, rev = grp / ST;
         uint32_t raw_par = 0;
-        long long f = lo;
+        int f = lo;
         while (f < hi && ok && *abort_flag == 0u) {
-            const int u = int(f / raw_total);
-            const long long u_lo = (long long)u * raw_total;
-            const long long seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
-            const int nraw = int(seg_end - f);
-            int r = int(f - u_lo);
+            const int u = f / raw_total;
+            const int u_lo = u * raw_total;
+            const int seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
+            const int nraw = seg_end - f;
+            int r = f - u_lo;
             tr = locate_tile(a, u / n_tiles);
             tok0 = (u % n_tiles) * NT;
             a_valid = tr.row0 + a_row < a.seg[tr.seg].rows;
@@ -877,7 +888,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
             if (!ok || *abort_flag != 0u) break;
             // ---- this CTA's share of output tile u is complete -----------------------------------
-            const long long seg_begin = u_lo > lo ? u_lo : lo;
+            const int seg_begin = u_lo > lo ? u_lo : lo;
             const bool whole = seg_begin == u_lo && seg_end == u_lo + raw_total;
             const GemmSeg seg = a.seg[tr.seg];
             publish();  // the accumulator cannot finish before the last stage is published
@@ -924,22 +935,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (!whole) {
                 // The CTA that arrives last adds the partial tiles in CTA order. The barrier orders
                 // every thread's partial stores before thread 0's fence, which is cumulative.
+                // Thread 0 alone works out who contributes (integer divisions) and leaves the answer
+                // in one of two sets of flag words, taken in turn, so that a set is not rewritten
+                // while a slower warp still reads it.
                 ok = convert_warps_sync(fix_bar, fix_phase);
                 if (!ok) break;
-                const int c_first = cta_of(total, u_lo, ctas), c_last = cta_of(total, u_lo + raw_total - 1, ctas);
+                volatile uint32_t *fl = fold_flags + 4 * (fold_turn & 1);
+                ++fold_turn;
                 if (tid == 0) {
+                    const int c_first = cta_of(total, u_lo, ctas), c_last = cta_of(total, u_lo + raw_total - 1, ctas);
                     __threadfence();
                     const unsigned prev = atomicAdd(a.counters + u, 1u);
-                    *last_flag = prev == unsigned(c_last - c_first) ? 1u : 0u;
+                    fl[1] = uint32_t(c_first);
+                    fl[2] = uint32_t(c_last);
+                    fl[0] = prev == unsigned(c_last - c_first) ? 1u : 0u;
                 }
                 ok = convert_warps_sync(fix_bar, fix_phase);
                 if (!ok) break;
-                if (*last_flag != 0u) {
+                if (fl[0] != 0u) {
                     __threadfence();
-                    fold_partials<NT>(a, seg, tr.row0, tok0, u_lo, total, ctas, c_first, c_last, tid);
+                    fold_partials<NT>(a, seg, tr.row0, tok0, int(fl[1]), int(fl[2]), tid);
                     if (tid == 0) a.counters[u] = 0u;
                 }
-                ok = convert_warps_sync(fix_bar, fix_phase);  // last_flag is reused by the next partial tile
             }
 #ifdef JL_TRACE
             tw_epi += clock64() - tq3;
@@ -992,6 +1009,7 @@ cudaError_t launch_nt(const GemmArgs &a, cudaStream_t stream) {
         if (per > raw_total / 2) per = raw_total / 2 > 0 ? raw_total / 2 : 1;
         ctas = units * per;
     }
+    if (total * ctas >= (1ll << 32)) return cudaErrorInvalidValue;  // the kernel's work-list arithmetic is 32-bit
     if (a.scratch == nullptr || a.counters == nullptr || tiles * n_tiles > a.counters_len ||
         size_t(ctas) * 2 * kTileM * NT > a.scratch_floats)
         return cudaErrorInvalidValue;
