@@ -224,18 +224,47 @@ __device__ __forceinline__ __half2 bytes_to_half2_plus1024(uint32_t v, uint32_t 
 }
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<const uint32_t *>(&h); }
 
-// 32 consecutive weights of one row out of a raw stage in shared memory: `row_u32` is the shared
-// address of the row's 256-column slice, `unit` the 64-column unit inside it (0..3), `half` the
-// 32-column half of the unit. Result: the weights rounded to fp16, as four 16-byte chunks.
+// Operand order. Inside every group of four consecutive K elements the tensor-memory columns (and the
+// activation rows, see the in-kernel activation conversion below and split4_store in ops.cu) hold
+// the pairs (k0, k2) and (k1, k3): a sum over K does not care about the order as long as both
+// operands agree, and the bytes 0 and 2 of a 32-bit word come out together with one logic operation.
+
+// What a thread keeps of its 64-weight unit between the two 32-weight halves it converts.
 template <int TYPE>
-__device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, int half, uint4 (&out)[4]) {
+struct UnitRegs;
+
+template <>
+struct UnitRegs<kQ4_K> {
+    uint32_t qw[8];         // the unit's 32 bytes: low nibbles = first half, high nibbles = second
+    __half2 d2;             // the super-block scale, exact (it is stored as binary16)
+    __half2 sc2[2], off2[2];  // per half: the 6-bit scale as a number, and -base * scale
+    __half2 chi2[2], clo2[2];  // per half: -dmin * m as an exact binary16 pair (17 significant bits)
+};
+template <>
+struct UnitRegs<kQ4_0> {
+    uint32_t t[9];  // two 18-byte blocks
+};
+template <>
+struct UnitRegs<kQ8_0> {
+    uint32_t base;  // shared address of the unit (two 34-byte blocks); its halves are loaded one at a time
+};
+
+__device__ __forceinline__ __half2 u32_as_half2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
+
+// Loads a unit: `row_u32` is the shared address of the row's 256-column slice of a raw stage, `unit`
+// the 64-column unit inside it (0..3).
+template <int TYPE>
+__device__ __forceinline__ void unit_load(uint32_t row_u32, int unit, UnitRegs<TYPE> &r) {
     if constexpr (TYPE == kQ4_K) {
         // tensor/standard/Q4_KFloatTensor.java:68-122: unit p holds sub-blocks 2p (low nibbles) and
-        // 2p+1 (high nibbles) of the same 32 bytes; w = (d*sc)*q - dmin*m in fp32.
+        // 2p+1 (high nibbles) of the same 32 bytes; w = (d*sc)*q - dmin*m.
         const uint4 hdr = lds128(row_u32);
         const uint4 q0 = lds128(row_u32 + 16 + unit * 32);
         const uint4 q1 = lds128(row_u32 + 32 + unit * 32);
-        const float d = half_bits_to_float(hdr.x & 0xFFFFu), dmin = half_bits_to_float(hdr.x >> 16);
+        r.qw[0] = q0.x; r.qw[1] = q0.y; r.qw[2] = q0.z; r.qw[3] = q0.w;
+        r.qw[4] = q1.x; r.qw[5] = q1.y; r.qw[6] = q1.z; r.qw[7] = q1.w;
+        r.d2 = u32_as_half2(__byte_perm(hdr.x, 0u, 0x1010));
+        const float dmin = half_bits_to_float(hdr.x >> 16);
         uint32_t scw, mw;
         if (unit < 2) {
             scw = hdr.y & 0x3F3F3F3Fu;
@@ -244,126 +273,85 @@ __device__ __forceinline__ void dequant32_to_half(uint32_t row_u32, int unit, in
             scw = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
             mw = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
         }
-        const int sh = (unit & 1) * 16 + half * 8;
-        const float ds = __fmul_rn(d, float((scw >> sh) & 0xFFu));
-        const float mm = __fmul_rn(dmin, float((mw >> sh) & 0xFFu));
-        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        const int nib = half * 4;
+        const int sh = (unit & 1) * 16;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float w[8];
+        for (int h = 0; h < 2; ++h) {
+            // 0x6400 | n is 1024 + n in binary16: the 6-bit scale and minimum become numbers without
+            // the conversion unit.
+            const uint32_t scb = (scw >> (sh + 8 * h)) & 0xFFu, mb = (mw >> (sh + 8 * h)) & 0xFFu;
+            const __half2 k1024 = u32_as_half2(0x64006400u);
+            r.sc2[h] = __hsub2(u32_as_half2(0x64006400u | scb | (scb << 16)), k1024);
+            r.off2[h] = __hmul2(r.sc2[h], u32_as_half2(h == 0 ? 0xE400E400u : 0xD400D400u));  // * -1024, * -64: exact
+            const float c = -__fmul_rn(dmin, __half2float(__low2half(__hsub2(u32_as_half2(0x64006400u | mb), k1024))));
+            const __half chi = __float2half_rn(c);
+            const __half clo = __float2half_rn(c - __half2float(chi));  // exact: c has 17 significant bits
+            r.chi2[h] = __half2half2(chi);
+            r.clo2[h] = __half2half2(clo);
+        }
+    } else if constexpr (TYPE == kQ4_0) {
+        const uint32_t base = row_u32 + unit * 36;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const uint32_t v = (qw[2 * c + i] >> nib) & 0x0F0F0F0Fu;
-                // One byte permute builds the float 2^23 + q (0x4B0000qq): the integer code without a
-                // conversion unit. The product and the subtraction are fused: the operand is rounded
-                // to binary16 right after, and a fused and an unfused fp32 result round alike there.
-                const float q0 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440)) - 8388608.0f;
-                const float q1 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7441)) - 8388608.0f;
-                const float q2 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7442)) - 8388608.0f;
-                const float q3 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7443)) - 8388608.0f;
-                w[i * 4 + 0] = __fmaf_rn(ds, q0, -mm);
-                w[i * 4 + 1] = __fmaf_rn(ds, q1, -mm);
-                w[i * 4 + 2] = __fmaf_rn(ds, q2, -mm);
-                w[i * 4 + 3] = __fmaf_rn(ds, q3, -mm);
-            }
-            out[c] = make_uint4(pack_half2(w[0], w[1]), pack_half2(w[2], w[3]), pack_half2(w[4], w[5]),
-                                pack_half2(w[6], w[7]));
+        for (int i = 0; i < 9; ++i) r.t[i] = lds32(base + 4 * i);
+    } else {
+        r.base = row_u32 + unit * 68;
+    }
+}
+
+// 32 of the unit's 64 consecutive weights as 16 tensor-memory columns, each weight rounded to binary16:
+// `half` 0 = the first 32 weights, 1 = the next 32. The two halves are converted and stored one after
+// the other so that only 16 results are live.
+template <int TYPE>
+__device__ __forceinline__ void unit_convert(const UnitRegs<TYPE> &r, int half, uint32_t (&out)[16]) {
+    if constexpr (TYPE == kQ4_K) {
+        // The conversion runs on the floating-point pipe, two weights per instruction: one logic
+        // operation drops two nibbles into the mantissas of a binary16 pair (0x6400 | q = 1024 + q for
+        // the low nibbles, 0x5400 | (q << 4) = 64 + q for the high ones, both exact), one fused
+        // multiply-add makes t = sc * q out of it (an integer below 1024: exact), a second one
+        // d * t + c_hi rounds once, and the last addition brings in c_lo, the 6 bits of dmin * m that
+        // c_hi cannot hold. The result is within two binary16 roundings of d * sc * q - dmin * m.
+        const uint32_t mask = half == 0 ? 0x000F000Fu : 0x00F000F0u, magic = half == 0 ? 0x64006400u : 0x54005400u;
+        const __half2 sc2 = r.sc2[half], off2 = r.off2[half], chi2 = r.chi2[half], clo2 = r.clo2[half];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const __half2 e = u32_as_half2((r.qw[i] & mask) | magic);         // bytes 0 and 2 of the word
+            const __half2 o = u32_as_half2(((r.qw[i] >> 8) & mask) | magic);  // bytes 1 and 3
+            const __half2 we = __hadd2(__hfma2(r.d2, __hfma2(sc2, e, off2), chi2), clo2);
+            const __half2 wo = __hadd2(__hfma2(r.d2, __hfma2(sc2, o, off2), chi2), clo2);
+            out[2 * i] = h2_bits(we);
+            out[2 * i + 1] = h2_bits(wo);
         }
     } else if constexpr (TYPE == kQ4_0) {
         // tensor/standard/Q4_0FloatTensor.java:56-79: a unit is two 18-byte blocks; element i < 16
         // is the low nibble of byte i, element i >= 16 the high nibble of byte i - 16; w = (q-8)*d.
         // (q-8) is exact in fp16 and d is fp16, so one half-precision multiply rounds exactly like
         // the reference's fp32 product narrowed to fp16.
-        const uint32_t base = row_u32 + unit * 36 + half * 16;
-        uint32_t t[5];
-#pragma unroll
-        for (int i = 0; i < 5; ++i) t[i] = lds32(base + 4 * i);
-        const uint32_t dbits = half == 0 ? (t[0] & 0xFFFFu) : (t[0] >> 16);
-        const uint32_t d2u = dbits | (dbits << 16);
-        const __half2 d2 = *reinterpret_cast<const __half2 *>(&d2u);
+        const uint32_t dbits = half == 0 ? (r.t[0] & 0xFFFFu) : (r.t[4] >> 16);
+        const __half2 d2 = u32_as_half2(dbits | (dbits << 16));
         const __half2 off = __float2half2_rn(1032.0f);
-        uint32_t lo[8], hi[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t q = half == 0 ? __funnelshift_r(t[i], t[i + 1], 16) : t[1 + i];
+            const uint32_t q = half == 0 ? __funnelshift_r(r.t[i], r.t[i + 1], 16) : r.t[5 + i];
             const uint32_t l4 = q & 0x0F0F0F0Fu, h4 = (q >> 4) & 0x0F0F0F0Fu;
-            lo[2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(l4, 0x4140u), off), d2));
-            lo[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(l4, 0x4342u), off), d2));
-            hi[2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(h4, 0x4140u), off), d2));
-            hi[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(h4, 0x4342u), off), d2));
+            out[2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(l4, 0x4240u), off), d2));
+            out[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(l4, 0x4341u), off), d2));
+            out[8 + 2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(h4, 0x4240u), off), d2));
+            out[8 + 2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(h4, 0x4341u), off), d2));
         }
-        out[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        out[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-        out[2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        out[3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
     } else {
         // tensor/standard/Q8_0FloatTensor.java:53-61: a unit is two 34-byte blocks; w = q * d, again
         // one exact-input half-precision multiply.
-        const uint32_t base = row_u32 + unit * 68 + half * 32;
+        const uint32_t base = r.base + half * 32;
         uint32_t t[9];
 #pragma unroll
         for (int i = 0; i < 9; ++i) t[i] = lds32(base + 4 * i);
         const uint32_t dbits = half == 0 ? (t[0] & 0xFFFFu) : (t[0] >> 16);
-        const uint32_t d2u = dbits | (dbits << 16);
-        const __half2 d2 = *reinterpret_cast<const __half2 *>(&d2u);
+        const __half2 d2 = u32_as_half2(dbits | (dbits << 16));
         const __half2 off = __float2half2_rn(1152.0f);  // 1024 + the 128 added by the sign flip
-        uint32_t h[16];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const uint32_t q = (half == 0 ? __funnelshift_r(t[i], t[i + 1], 16) : t[1 + i]) ^ 0x80808080u;
-            h[2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(q, 0x4140u), off), d2));
-            h[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(q, 0x4342u), off), d2));
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) out[c] = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
-    }
-}
-
-// 32 of the 64 consecutive weights of one row's unit as 16 tensor-memory columns: `half` 0 = the
-// first 32 weights, 1 = the next 32 (for Q4_K the low and the high nibbles of the unit's 32 bytes).
-// The two halves are converted and stored one after the other so that only 16 results are live.
-template <int TYPE>
-__device__ __forceinline__ void dequant32_to_cols(uint32_t row_u32, int unit, int half, uint32_t (&out)[16]) {
-    if constexpr (TYPE == kQ4_K) {
-        const uint4 hdr = lds128(row_u32);
-        const uint4 q0 = lds128(row_u32 + 16 + unit * 32);
-        const uint4 q1 = lds128(row_u32 + 32 + unit * 32);
-        const float d = half_bits_to_float(hdr.x & 0xFFFFu), dmin = half_bits_to_float(hdr.x >> 16);
-        uint32_t scw, mw;
-        if (unit < 2) {
-            scw = hdr.y & 0x3F3F3F3Fu;
-            mw = hdr.z & 0x3F3F3F3Fu;
-        } else {
-            scw = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-            mw = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-        }
-        const int sh = (unit & 1) * 16 + half * 8;
-        const float ds = __fmul_rn(d, float((scw >> sh) & 0xFFu));
-        const float mm = __fmul_rn(dmin, float((mw >> sh) & 0xFFu));
-        // One byte permute puts a nibble into bits 16-19 of 0x43000000: the float 128 + q, exactly. With
-        // c = -(128 * ds + mm), fma(ds, 128 + q, c) is ds * q - mm rounded once (c itself is off by at
-        // most 2^-17 of ds, far below the binary16 rounding that follows), so a weight costs one
-        // permute and one fused multiply-add, and no conversion unit.
-        const float cf = -__fmaf_rn(128.0f, ds, mm);
-        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        const int nib = half * 4;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t v = (qw[i] >> nib) & 0x0F0F0F0Fu;
-            const float a0 = __uint_as_float(__byte_perm(v, 0x43000000u, 0x7054));
-            const float a1 = __uint_as_float(__byte_perm(v, 0x43000000u, 0x7154));
-            const float a2 = __uint_as_float(__byte_perm(v, 0x43000000u, 0x7254));
-            const float a3 = __uint_as_float(__byte_perm(v, 0x43000000u, 0x7354));
-            out[2 * i] = pack_half2(__fmaf_rn(ds, a0, cf), __fmaf_rn(ds, a1, cf));
-            out[2 * i + 1] = pack_half2(__fmaf_rn(ds, a2, cf), __fmaf_rn(ds, a3, cf));
-        }
-    } else {
-        uint4 c[4];
-        dequant32_to_half<TYPE>(row_u32, unit, half, c);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            out[4 * k] = c[k].x; out[4 * k + 1] = c[k].y; out[4 * k + 2] = c[k].z; out[4 * k + 3] = c[k].w;
+            out[2 * i] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(q, 0x4240u), off), d2));
+            out[2 * i + 1] = h2_bits(__hmul2(__hsub2(bytes_to_half2_plus1024(q, 0x4341u), off), d2));
         }
     }
 }
@@ -592,7 +580,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     atomicExch(a.status, kDevTimeout);
                     break;
                 }
-                SLOG(160 + (i - 4), i >= 4 && i < 12);
+                SLOG(300 + (i - 4), i >= 4 && i < 12);
                 const CUtensorMap *tmap = tr.seg == 0 ? &tm0 : (tr.seg == 1 ? &tm1 : &tm2);
                 if (JL_TRACE_MODE(8)) {  // trace build, timing experiment: no copy at all, the stage is declared full
                     mbar_arrive(raw_full + st);
@@ -621,7 +609,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     if (!ok) break;
                     uint8_t *b_st = base + S::b_off + s * S::b_stage;
                     const int k0 = r * kRawK + j * kStageK;
-                    SLOG(176 + (q - 8), q >= 8 && q < 24);
+                    SLOG(320 + (q - 8), q >= 8 && q < 24);
                     if (JL_TRACE_MODE(64)) {  // trace build, timing experiment: no activation copy
                         mbar_arrive(a_full + s);
                         continue;
@@ -684,12 +672,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     tw_pub += clock64() - tm0_;
 #endif
                     if (!ok) break;
-                    SLOG(128 + (qlog - 8) * 2, lane == 0 && qlog >= 8 && qlog < 24);
+                    SLOG(256 + (qlog - 8) * 2, lane == 0 && qlog >= 8 && qlog < 24);
                     __syncwarp();  // elect.sync below names every lane
                     tc_fence_after();
                     umma_stage_f16_tmem_a<2, 4, 6, kAtom, kAtom + 2, kAtom + 4, kAtom + 6>(
                         tmem_d, a_col, b_lo, desc_hi, idesc, free0 + 8u * uint32_t(s), k == 0 ? 0u : 1u);
-                    SLOG(128 + (qlog - 8) * 2 + 1, lane == 0 && qlog >= 8 && qlog < 24);
+                    SLOG(256 + (qlog - 8) * 2 + 1, lane == 0 && qlog >= 8 && qlog < 24);
 #ifdef JL_TRACE
                     ++qlog;
 #endif
@@ -735,7 +723,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int i = 0, done = 0, fix_phase = 0, fold_turn = 0;
         TileRef tr = {0, 0};
         int tok0 = 0;
-        bool a_valid = false;
         bool ok = true;
         // An operand stage is published (a_full) one stage late: the tensor-memory stores of stage i
         // are waited for after stage i + 1 has been converted, when they have long landed, instead
@@ -772,12 +759,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             int r = f - u_lo;
             tr = locate_tile(a, u / n_tiles);
             tok0 = (u % n_tiles) * NT;
-            a_valid = tr.row0 + a_row < a.seg[tr.seg].rows;
           for (int it = 0; it < nraw && *abort_flag == 0u; ++it, ++r, ++i) {
 #ifdef JL_TRACE
             const long long tq0 = clock64();
             const bool lgw = (tid == 0 || tid == 256 || tid == 96) && i >= 4 && i < 12;
-            const int lg = (tid == 0 ? 0 : (tid == 256 ? 40 : 80)) + (i - 4) * 5;
+            const int lg = (tid == 0 ? 0 : (tid == 256 ? 80 : 160)) + (i - 4) * 10;
             SLOG(lg, lgw);
 #endif
             ok = mbar_poll_bounded_u32(raw_full0 + 8u * uint32_t(st), raw_par);
@@ -827,14 +813,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const long long tq5 = clock64();
                     tw_pub += tq5 - tq4;
 #endif
+                    // (Rows past the end of a matrix, in its bottom tile, need no care: the copy engine
+                    // fills them with zero bytes, which every format converts to zero weights.)
+                    SLOG(lg + 5, lgw);
+                    UnitRegs<TYPE> unit_regs;
+                    unit_load<TYPE>(row_u32, 2 * j + a_unit, unit_regs);
+#ifdef JL_TRACE
+                    if (logging && lgw) {  // the stamp waits for the header arithmetic
+                        if constexpr (TYPE == kQ4_K) {
+                            if (h2_bits(unit_regs.clo2[1]) == 0x12345678u) slog[500] = 1;
+                        }
+                        slog[lg + 6] = static_cast<unsigned long long>(clock64());
+                    }
+#endif
 #pragma unroll
                     for (int hf = 0; hf < 2; ++hf) {
                         uint32_t cols[16];
-                        dequant32_to_cols<TYPE>(row_u32, 2 * j + a_unit, hf, cols);
-                        if (!a_valid) {  // rows past the end of the matrix (bottom tile only)
-#pragma unroll
-                            for (int c = 0; c < 16; ++c) cols[c] = 0u;
+                        unit_convert<TYPE>(unit_regs, hf, cols);
+#ifdef JL_TRACE
+                        if (logging && lgw) {
+                            if (cols[15] == 0x12345678u) slog[501] = 1;
+                            slog[lg + 7 + hf] = static_cast<unsigned long long>(clock64());
                         }
+#endif
                         tmem_st16(col0 + 16u * hf, cols);
                     }
 #ifdef JL_TRACE
@@ -858,10 +859,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         const uint32_t off = sw128_offset(t, c);
                         uint8_t *bh = b_st + size_t(atom) * S::b_sub;
                         uint8_t *bl = bh + NT * 128;  // the lo rows follow the hi rows of the same atom
-                        *reinterpret_cast<uint4 *>(bh + off) = make_uint4(pack_half2(x[0], x[1]), pack_half2(x[2], x[3]),
-                                                                         pack_half2(x[4], x[5]), pack_half2(x[6], x[7]));
-                        *reinterpret_cast<uint4 *>(bl + off) = make_uint4(pack_half2(xl[0], xl[1]), pack_half2(xl[2], xl[3]),
-                                                                         pack_half2(xl[4], xl[5]), pack_half2(xl[6], xl[7]));
+                        // pairs (k0, k2), (k1, k3) inside every group of four: the operand order
+                        *reinterpret_cast<uint4 *>(bh + off) = make_uint4(pack_half2(x[0], x[2]), pack_half2(x[1], x[3]),
+                                                                         pack_half2(x[4], x[6]), pack_half2(x[5], x[7]));
+                        *reinterpret_cast<uint4 *>(bl + off) = make_uint4(pack_half2(xl[0], xl[2]), pack_half2(xl[1], xl[3]),
+                                                                         pack_half2(xl[4], xl[6]), pack_half2(xl[5], xl[7]));
                     }
                 }
                 // Generic-proxy writes to shared memory (the B operand, when converted here) must be

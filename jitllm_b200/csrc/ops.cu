@@ -69,15 +69,22 @@ __global__ void add_rows_kernel(float *x, const float *y, size_t total) {
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) x[i] = x[i] + y[i];
 }
 
+// Four consecutive activations as binary16 hi and lo parts (x = hi + lo), the tensor-core path's
+// activation format. Inside each group of four the pairs are (x0, x2) and (x1, x3): the weight
+// conversion gets the nibbles of bytes 0 and 2 of a word with one logic operation, and a sum over K
+// does not care about the order as long as both operands use the same one.
+__device__ __forceinline__ void split4_store(const float4 v, uint2 *hi, uint2 *lo) {
+    const __half2 h0 = __floats2half2_rn(v.x, v.z), h1 = __floats2half2_rn(v.y, v.w);
+    const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
+    const __half2 l0 = __floats2half2_rn(v.x - b0.x, v.z - b0.y), l1 = __floats2half2_rn(v.y - b1.x, v.w - b1.y);
+    *hi = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+    *lo = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
+}
+
 __global__ void split_rows_kernel(const float4 *x, size_t total4, uint2 *hi, uint2 *lo) {
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total4; i += stride) {
-        const float4 v = x[i];
-        const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
-        const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
-        const __half2 l0 = __floats2half2_rn(v.x - b0.x, v.y - b0.y), l1 = __floats2half2_rn(v.z - b1.x, v.w - b1.y);
-        hi[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
-        lo[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
+        split4_store(x[i], hi + i, lo + i);
     }
 }
 
@@ -160,13 +167,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const float 
         r.z = __fmul_rn(g.z, __fmul_rn(ss, u.z));
         r.w = __fmul_rn(g.w, __fmul_rn(ss, u.w));
         o4[i] = r;
-        if (hr != nullptr) {
-            const __half2 h0 = __floats2half2_rn(r.x, r.y), h1 = __floats2half2_rn(r.z, r.w);
-            const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
-            const __half2 l0 = __floats2half2_rn(r.x - b0.x, r.y - b0.y), l1 = __floats2half2_rn(r.z - b1.x, r.w - b1.y);
-            hr[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
-            lr[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
-        }
+        if (hr != nullptr) split4_store(r, hr + i, lr + i);
     };
 #pragma unroll
     for (int k = 0; k < kNormBatch; ++k) {
@@ -189,13 +190,7 @@ __global__ void swiglu_rows_kernel(float4 *g, const float4 *u, size_t total4, ui
         r.z = (v.z / (1.0f + expf(-v.z))) * w.z;
         r.w = (v.w / (1.0f + expf(-v.w))) * w.w;
         g[i] = r;
-        if (hi != nullptr) {
-            const __half2 h0 = __floats2half2_rn(r.x, r.y), h1 = __floats2half2_rn(r.z, r.w);
-            const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
-            const __half2 l0 = __floats2half2_rn(r.x - b0.x, r.y - b0.y), l1 = __floats2half2_rn(r.z - b1.x, r.w - b1.y);
-            hi[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
-            lo[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
-        }
+        if (hi != nullptr) split4_store(r, hi + i, lo + i);
     }
 }
 
