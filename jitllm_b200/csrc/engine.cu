@@ -540,7 +540,7 @@ int tp_reduce_into_x(jl_ctx *ctx, int n, uint64_t *launches) {
     }
     int rc = tp_all_reduce(ctx, ctx->part, count);
     if (rc) return rc;
-    cudaError_t e = add_rows_launch(ctx->x, ctx->part, size_t(n) * ctx->desc.dim, ctx->stream);
+    cudaError_t e = add_rows_launch(ctx->x, ctx->part, size_t(n) * ctx->desc.dim, ctx->stream, ctx->use_pdl);
     if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "residual add launch failed: %s", cudaGetErrorString(e));
     ++*launches;
     return JL_OK;
@@ -626,7 +626,8 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
         if (!presplit) {  // otherwise the producing kernel already wrote the hi / lo rows
             const int cols = int(w[0]->cols);
             char *buf = static_cast<char *>(in_kind == 2 ? ctx->hb16 : ctx->xb16);
-            cudaError_t e = split_rows_launch(x, size_t(n) * cols, buf, buf + size_t(ctx->row_cap) * cols * 2, ctx->stream);
+            cudaError_t e = split_rows_launch(x, size_t(n) * cols, buf, buf + size_t(ctx->row_cap) * cols * 2, ctx->stream,
+                                              ctx->use_pdl);
             if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "activation split launch failed: %s", cudaGetErrorString(e));
             ++*launches;
         }
@@ -649,6 +650,7 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
     g.counters = ctx->gemm_counters;
     g.counters_len = kGemmCounters;
     g.sm_count = ctx->sm_count;
+    g.programmatic = ctx->use_pdl;
     cudaError_t e = gemm_tc_launch(g, ctx->stream);
     if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-matrix launch failed: %s", cudaGetErrorString(e));
     ++*launches;
@@ -681,7 +683,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
     const DevTensor &emb = ctx->global[JL_ROLE_TOKEN_EMBEDDING];
     const KvGeom kvg = {ctx->kpool, ctx->vpool, ctx->block_table, ctx->blocks_per_slot, ctx->block_tokens,
                         d.layers, kv_dim};
-    JL_LAUNCH(ctx, embedding_launch(emb.type, emb.data, ctx->d_tokens, ctx->d_active, ctx->x, dim, n, ctx->stream, false),
+    JL_LAUNCH(ctx, embedding_launch(emb.type, emb.data, ctx->d_tokens, ctx->d_active, ctx->x, dim, n, ctx->stream, ctx->use_pdl),
               "embedding");
     int rc;
     for (int l = 0; l < d.layers; ++l) {
@@ -689,7 +691,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
         const float *ffn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
         NvtxRange range("attention", l);
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, attn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream, ctx->xb16,
-                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2),
+                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2, ctx->use_pdl),
                   "rmsnorm");
         {
             const DevTensor *ws[3] = {&ctx->layer[JL_ROLE_ATTENTION_QUERY][l], &ctx->layer[JL_ROLE_ATTENTION_KEY][l],
@@ -705,7 +707,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
         }
         if (!own_sequences)
             JL_LAUNCH(ctx, kv_append_launch(ctx->k, ctx->v, ctx->rope_cos, ctx->rope_sin, ctx->d_positions, ctx->d_slots,
-                                            ctx->d_active, kvg, l, d.head_dim, n, ctx->stream),
+                                            ctx->d_active, kvg, l, d.head_dim, n, ctx->stream, ctx->use_pdl),
                       "kv append");
         {
             AttnArgs a = {};
@@ -728,7 +730,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             a.append = own_sequences ? 1 : 0;
             a.partial = ctx->att_partial;
             a.counters = ctx->att_count;
-            JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, false), "attention");
+            JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, ctx->use_pdl), "attention");
         }
         if (ctx->tp_size > 1) {
             if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->part, nullptr, launches, 1))) return rc;
@@ -738,7 +740,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
         }
         range.next("ffn", l);
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, ffn_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream, ctx->xb16,
-                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2),
+                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2, ctx->use_pdl),
                   "rmsnorm");
         {
             const DevTensor *ws[2] = {&ctx->layer[JL_ROLE_FFN_GATE][l], &ctx->layer[JL_ROLE_FFN_UP][l]};
@@ -751,7 +753,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             }
         }
         JL_LAUNCH(ctx, swiglu_rows_launch(ctx->hb, ctx->hb2, ctx->l_hidden, n, ctx->stream, ctx->hb16,
-                                          static_cast<char *>(ctx->hb16) + size_t(ctx->row_cap) * ctx->l_hidden * 2),
+                                          static_cast<char *>(ctx->hb16) + size_t(ctx->row_cap) * ctx->l_hidden * 2, ctx->use_pdl),
                   "swiglu");
         if (ctx->tp_size > 1) {
             if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_FFN_DOWN][l], ctx->hb, n, ctx->part, nullptr, launches, 2, true))) return rc;
@@ -763,15 +765,16 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
     if (with_logits) {
         const float *out_norm = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
         JL_LAUNCH(ctx, rmsnorm_rows_launch(ctx->x, out_norm, d.rms_eps, ctx->xb, dim, n, ctx->d_active, ctx->stream, ctx->xb16,
-                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2),
+                                           static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * dim * 2, ctx->use_pdl),
                   "rmsnorm");
         if ((rc = launch_gemm(ctx, wcls_of(ctx), ctx->xb, n, ctx->logits, nullptr, launches, 0, true))) return rc;
-        JL_LAUNCH(ctx, argmax_rows_launch(ctx->logits, ctx->l_vocab, n, ctx->d_active, ctx->d_out, ctx->stream), "argmax");
+        JL_LAUNCH(ctx, argmax_rows_launch(ctx->logits, ctx->l_vocab, n, ctx->d_active, ctx->d_out, ctx->stream, ctx->use_pdl),
+                  "argmax");
         if (ctx->tp_size > 1 && (rc = tp_global_argmax(ctx, n, launches))) return rc;
     }
     if (advance)
         JL_LAUNCH(ctx, advance_launch(ctx->d_tokens, ctx->d_positions, ctx->d_out, ctx->d_active, ctx->d_history,
-                                      ctx->d_step, n, ctx->stream, false),
+                                      ctx->d_step, n, ctx->stream, ctx->use_pdl),
                   "advance");
     return JL_OK;
 }

@@ -553,6 +553,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     tc_fence_after();
     const uint32_t tmem_d = *tmem_ptr;
     trace_mark(trace, 2);
+    // The next kernel may start its preamble now; what of this kernel depends on the one before it
+    // (activations, residuals, the outputs and the partial-tile workspace it writes) waits below:
+    // the activation-copy thread and the conversion warps do, the weight-copy thread does not.
+    pdl_launch_dependents();
 #ifdef JL_TRACE
     long long tw_raw = 0, tw_free = 0, tw_acc = 0, tw_epi = 0, tw_pub = 0, tw_cvt = 0;
 #endif
@@ -594,6 +598,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     } else if (warp == kConvertWarps + 2) {
         // ---- activation tiles by TMA (pre-split binary16 hi / lo rows), one request set per operand stage
         if (lane == 0 && XT) {
+            pdl_wait();
             int i = 0;
             int u = lo / raw_total, r = lo - u * raw_total - 1;
             for (int f = lo; f < hi && *abort_flag == 0u; ++f, ++i) {
@@ -713,6 +718,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // Two groups of eight warps take alternate operand stages (group 0 the first 128 columns of
         // every raw stage, group 1 the second): a thread converts a whole 64-column unit of its row,
         // so block headers, scale unpacking and barrier traffic are paid once per 64 weights.
+        pdl_wait();
         constexpr int kGroupThreads = kConvertThreads / 2;
         const int grp = warp >> 3, g_tid = tid & (kGroupThreads - 1);
         const int a_row = g_tid & 127, a_unit = g_tid >> 7;  // a_unit: which 64-column unit of the 128
@@ -1018,13 +1024,18 @@ cudaError_t launch_nt(const GemmArgs &a, cudaStream_t stream) {
     CUtensorMap maps[4];
     for (int s = 0; s < 3; ++s) memcpy(&maps[s], a.seg[s < a.nseg ? s : 0].tmap->bytes, sizeof(CUtensorMap));
     memcpy(&maps[3], (a.xmap != nullptr ? a.xmap : a.seg[0].tmap)->bytes, sizeof(CUtensorMap));
-    if (a.xmap != nullptr)
-        gemm_tc_kernel<TYPE, NT, true><<<dim3(unsigned(ctas)), kGemmThreads, GemmSmem<TYPE, NT>::total, stream>>>(
-            a, maps[0], maps[1], maps[2], maps[3]);
-    else
-        gemm_tc_kernel<TYPE, NT, false><<<dim3(unsigned(ctas)), kGemmThreads, GemmSmem<TYPE, NT>::total, stream>>>(
-            a, maps[0], maps[1], maps[2], maps[3]);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(ctas));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = GemmSmem<TYPE, NT>::total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.programmatic ? 1 : 0;
+    if (a.xmap != nullptr) return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, NT, true>, a, maps[0], maps[1], maps[2], maps[3]);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, NT, false>, a, maps[0], maps[1], maps[2], maps[3]);
 }
 
 template <int TYPE>

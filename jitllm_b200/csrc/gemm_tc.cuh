@@ -42,6 +42,10 @@ struct GemmArgs {
     unsigned *counters;
     int counters_len;
     int sm_count;
+    // Launch with the programmatic-dependent-launch attribute: the kernel's preamble and the first
+    // weight copies (weights depend on no kernel) run while the kernel before it drains; everything
+    // that reads activations or writes results waits for that kernel first.
+    bool programmatic;
 };
 
 // Sets the shared-memory attribute of every instantiation (call once, outside stream capture).

@@ -64,7 +64,15 @@ __device__ __forceinline__ int64_t kv_offset(const KvGeom &g, int slot, int pos,
            int64_t(within) * g.kv_dim;
 }
 
+// The row kernels below take part in chains of programmatic dependent launches: each lets the next
+// kernel start its preamble at once (a matrix-matrix kernel then streams its first weights while this
+// one runs) and waits for the kernel before it. Every CTA waits, also one that then has nothing to do:
+// a grid whose CTAs left without waiting would count as complete while its predecessor still runs,
+// and the next kernel's wait covers only its own predecessor. The embedding and the advance kernel
+// wait before they release: whatever starts after them may read the step's positions at once.
 __global__ void add_rows_kernel(float *x, const float *y, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) x[i] = x[i] + y[i];
 }
@@ -82,6 +90,8 @@ __device__ __forceinline__ void split4_store(const float4 v, uint2 *hi, uint2 *l
 }
 
 __global__ void split_rows_kernel(const float4 *x, size_t total4, uint2 *hi, uint2 *lo) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total4; i += stride) {
         split4_store(x[i], hi + i, lo + i);
@@ -126,6 +136,8 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const float 
     const int row = blockIdx.x;
     const int trace = trace_begin(kTraceRows);
     trace_word(trace, 7, 1);
+    pdl_launch_dependents();
+    pdl_wait();
     if (active != nullptr && active[row] == 0) return;
     __shared__ float part[9];
     const int n4 = dim / 4;
@@ -181,6 +193,8 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const float 
 __global__ void swiglu_rows_kernel(float4 *g, const float4 *u, size_t total4, uint2 *hi, uint2 *lo) {
     const int trace = trace_begin(kTraceRows);
     trace_word(trace, 7, 2);
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total4; i += stride) {
         const float4 v = g[i], w = u[i];
@@ -198,6 +212,8 @@ __global__ void kv_append_kernel(const float *k, const float *v, const float *ro
                                  const int32_t *positions, const int32_t *slots, const uint8_t *active,
                                  KvGeom kv, int layer, int head_dim) {
     const int row = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (active != nullptr && active[row] == 0) return;
     const int pos = positions[row], slot = slots[row];
     const int64_t off = kv_offset(kv, slot, pos, layer);
@@ -216,6 +232,8 @@ __global__ void kv_append_kernel(const float *k, const float *v, const float *ro
 
 __global__ void argmax_rows_kernel(const float *logits, int vocab, const uint8_t *active, int32_t *out) {
     const int row = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (active != nullptr && active[row] == 0) return;
     const float *lr = logits + size_t(row) * vocab;
     float bv = -INFINITY;
@@ -816,47 +834,62 @@ cudaError_t advance_launch(int32_t *tokens, int32_t *positions, const int32_t *s
                               step_counter, width);
 }
 
+// One launch configuration for the row kernels, with or without the programmatic-dependent-launch attribute.
+struct RowLaunch {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1] = {};
+    RowLaunch(int grid, int block, cudaStream_t stream, bool programmatic) {
+        cfg.gridDim = dim3(unsigned(grid));
+        cfg.blockDim = dim3(unsigned(block));
+        cfg.stream = stream;
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = programmatic ? 1 : 0;
+    }
+};
+
 cudaError_t rmsnorm_rows_launch(const float *x, const float *w, float eps, float *out, int dim, int n,
-                                const uint8_t *active, cudaStream_t stream, void *hi, void *lo) {
-    rmsnorm_rows_kernel<<<n, kNormThreads, 0, stream>>>(x, w, eps, out, dim, active, static_cast<uint2 *>(hi),
-                                                        static_cast<uint2 *>(lo));
-    return cudaGetLastError();
+                                const uint8_t *active, cudaStream_t stream, void *hi, void *lo, bool programmatic) {
+    RowLaunch l(n, kNormThreads, stream, programmatic);
+    return cudaLaunchKernelEx(&l.cfg, rmsnorm_rows_kernel, x, w, eps, out, dim, active, static_cast<uint2 *>(hi),
+                              static_cast<uint2 *>(lo));
 }
 
-cudaError_t swiglu_rows_launch(float *g, const float *u, int hidden, int n, cudaStream_t stream, void *hi, void *lo) {
+cudaError_t swiglu_rows_launch(float *g, const float *u, int hidden, int n, cudaStream_t stream, void *hi, void *lo,
+                               bool programmatic) {
     const size_t total4 = size_t(hidden) * n / 4;
     const int grid = static_cast<int>((total4 + 255) / 256 < 148 * 8 ? (total4 + 255) / 256 : 148 * 8);
-    swiglu_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<float4 *>(g), reinterpret_cast<const float4 *>(u), total4,
-                                                 static_cast<uint2 *>(hi), static_cast<uint2 *>(lo));
-    return cudaGetLastError();
+    RowLaunch l(grid, 256, stream, programmatic);
+    return cudaLaunchKernelEx(&l.cfg, swiglu_rows_kernel, reinterpret_cast<float4 *>(g), reinterpret_cast<const float4 *>(u),
+                              total4, static_cast<uint2 *>(hi), static_cast<uint2 *>(lo));
 }
 
 cudaError_t kv_append_launch(const float *k, const float *v, const float *rope_cos, const float *rope_sin,
                              const int32_t *positions, const int32_t *slots, const uint8_t *active,
-                             KvGeom kv, int layer, int head_dim, int n, cudaStream_t stream) {
-    kv_append_kernel<<<n, 256, 0, stream>>>(k, v, rope_cos, rope_sin, positions, slots, active, kv, layer,
-                                            head_dim);
-    return cudaGetLastError();
+                             KvGeom kv, int layer, int head_dim, int n, cudaStream_t stream, bool programmatic) {
+    RowLaunch l(n, 256, stream, programmatic);
+    return cudaLaunchKernelEx(&l.cfg, kv_append_kernel, k, v, rope_cos, rope_sin, positions, slots, active, kv, layer, head_dim);
 }
 
 cudaError_t argmax_rows_launch(const float *logits, int vocab, int n, const uint8_t *active, int32_t *out,
-                               cudaStream_t stream) {
-    argmax_rows_kernel<<<n, 1024, 0, stream>>>(logits, vocab, active, out);
-    return cudaGetLastError();
+                               cudaStream_t stream, bool programmatic) {
+    RowLaunch l(n, 1024, stream, programmatic);
+    return cudaLaunchKernelEx(&l.cfg, argmax_rows_kernel, logits, vocab, active, out);
 }
 
-cudaError_t add_rows_launch(float *x, const float *y, size_t total, cudaStream_t stream) {
+cudaError_t add_rows_launch(float *x, const float *y, size_t total, cudaStream_t stream, bool programmatic) {
     const int grid = static_cast<int>((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
-    add_rows_kernel<<<grid, 256, 0, stream>>>(x, y, total);
-    return cudaGetLastError();
+    RowLaunch l(grid, 256, stream, programmatic);
+    return cudaLaunchKernelEx(&l.cfg, add_rows_kernel, x, y, total);
 }
 
-cudaError_t split_rows_launch(const float *x, size_t total, void *hi, void *lo, cudaStream_t stream) {
+cudaError_t split_rows_launch(const float *x, size_t total, void *hi, void *lo, cudaStream_t stream, bool programmatic) {
     const size_t total4 = total / 4;  // row lengths are multiples of 256
     const int grid = static_cast<int>((total4 + 255) / 256 < 148 * 8 ? (total4 + 255) / 256 : 148 * 8);
-    split_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4 *>(x), total4, static_cast<uint2 *>(hi),
-                                                static_cast<uint2 *>(lo));
-    return cudaGetLastError();
+    RowLaunch l(grid, 256, stream, programmatic);
+    return cudaLaunchKernelEx(&l.cfg, split_rows_kernel, reinterpret_cast<const float4 *>(x), total4, static_cast<uint2 *>(hi),
+                              static_cast<uint2 *>(lo));
 }
 
 cudaError_t tp_pack_best_launch(const float *logits, const int32_t *idx, int l_vocab, int index_offset, int n,

@@ -54,24 +54,28 @@ cudaError_t advance_launch(int32_t *tokens, int32_t *positions, const int32_t *s
 // out[r] = w * (rsqrt(mean(x[r]^2) + eps) * x[r])   (inference/op/CpuOperations.java:55-73)
 // hi / lo: optional binary16 split of the result (x = hi + lo), contiguous [n][dim] each.
 cudaError_t rmsnorm_rows_launch(const float *x, const float *w, float eps, float *out, int dim, int n,
-                                const uint8_t *active, cudaStream_t stream, void *hi = nullptr, void *lo = nullptr);
+                                const uint8_t *active, cudaStream_t stream, void *hi = nullptr, void *lo = nullptr,
+                                bool programmatic = false);
 // g[r] = silu(g[r]) * u[r]                          (inference/op/CpuOperations.java:255-260)
 // hi / lo: optional binary16 split of the result (x = hi + lo), contiguous [n][hidden] each.
 cudaError_t swiglu_rows_launch(float *g, const float *u, int hidden, int n, cudaStream_t stream, void *hi = nullptr,
-                               void *lo = nullptr);
+                               void *lo = nullptr, bool programmatic = false);
 // RoPE on k, then k and v rounded to fp16 into the page of (slot, position) of every row
 // (inference/op/CpuOperations.java:94-147).
 cudaError_t kv_append_launch(const float *k, const float *v, const float *rope_cos, const float *rope_sin,
                              const int32_t *positions, const int32_t *slots, const uint8_t *active,
-                             KvGeom kv, int layer, int head_dim, int n, cudaStream_t stream);
+                             KvGeom kv, int layer, int head_dim, int n, cudaStream_t stream, bool programmatic = false);
 // out[r] = first index of the maximum of logits[r]  (inference/Logits.java:49-60)
 cudaError_t argmax_rows_launch(const float *logits, int vocab, int n, const uint8_t *active, int32_t *out,
-                               cudaStream_t stream);
+                               cudaStream_t stream, bool programmatic = false);
 
 // x[i] += y[i]
-cudaError_t add_rows_launch(float *x, const float *y, size_t total, cudaStream_t stream);
+cudaError_t add_rows_launch(float *x, const float *y, size_t total, cudaStream_t stream, bool programmatic = false);
 // x = hi + lo with hi, lo binary16 (22 significant bits): the tensor-core path's activation format.
-cudaError_t split_rows_launch(const float *x, size_t total, void *hi, void *lo, cudaStream_t stream);
+cudaError_t split_rows_launch(const float *x, size_t total, void *hi, void *lo, cudaStream_t stream,
+                              bool programmatic = false);
+// (programmatic: launch with the programmatic-dependent-launch attribute; the row kernels always wait for
+// the kernel before them and release the one after them at their start.)
 // best[r] = (logits[r][idx[r]], idx[r] + index_offset) for the n rows of this GPU's vocabulary shard.
 cudaError_t tp_pack_best_launch(const float *logits, const int32_t *idx, int l_vocab, int index_offset, int n,
                                 float *best, cudaStream_t stream);
