@@ -77,6 +77,10 @@ def parse_args():
     ap.add_argument("--profile-op", type=int, default=-1,
                     help="launch one matrix-vector operator (0 qkv, 1 out, 2 gate/up, 3 down, 4 vocab) "
                          "--steps times and exit: the small case ncu captures are taken on")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the launch timeline of one decode step (--batch sequences) from the trace build of the "
+                         "library: run as JITLLM_B200_TRACE=1 python bench.py --timeline ... after "
+                         "python jitllm_b200/build.py --trace")
     return ap.parse_args()
 
 
@@ -258,6 +262,66 @@ def cpu_sample_text(done, depth, dt):
             f"seeded random rows, no CPU prefill), all layers, scalar summation mode, {dt:.1f} s")
 
 
+def run_timeline(jl, args):
+    """One decode step of --batch sequences as a table of launches, from the stamps the trace build of the
+    library leaves (first CTA of every launch: entry, dependency resolved, operands staged, loop done, exit)."""
+    if os.environ.get("JITLLM_B200_TRACE") != "1":
+        print("--timeline needs the trace build: JITLLM_B200_TRACE=1 python bench.py --timeline ...", file=sys.stderr)
+        return 2
+    dims = ARCHS[args.arch]
+    cfg = jl.Configuration(dim=dims[0], hiddenDim=dims[1], numberOfLayers=dims[2], numberOfHeads=dims[3],
+                           numberOfKeyValueHeads=dims[4], vocabularySize=dims[5], contextLength=dims[6],
+                           tiedEmbeddings=dims[7])
+    B, P = args.batch, args.prompt
+    tensors = jl.synth_model_tensors(cfg, jl.GGMLType[args.format], args.seed, threads=os.cpu_count())
+    cr, ci = jl.precomputeFreqsCis(cfg.contextLength, cfg.headSize, cfg.ropeTheta)
+    dev = jl.Device(0)
+    model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=B)
+    bps = cfg.contextLength // 16
+    need = (P + 64 + 15) // 16
+    kv = model.createKvStorage(jl.KvStorageRequest(B * need, bps, B, 16, cfg.numberOfLayers, cfg.kvDim))
+    table = np.full(B * bps, jl.UNMAPPED, dtype=np.int32)
+    for b in range(B):
+        table[b * bps:b * bps + need] = np.arange(b * need, (b + 1) * need)
+    kv.publishBlockTable(table)
+    ex = jl.B200BatchExecutor(model)
+    prompts = np.random.default_rng(args.seed).integers(0, cfg.vocabularySize, size=(B, P))
+    for b in range(B):
+        jl.B200InvocationBoundary(model, kvSlot=b, copyLogits=False).prefill(prompts[b, :P - 1], 0)
+    slots, active = list(range(B)), [True] * B
+    hist = ex.generate(jl.BatchSlots(active, [int(t) for t in prompts[:, P - 1]], [P - 1] * B, slots), 4)
+    dev.synchronize()
+    dev.timer_start()
+    hist = ex.generate(jl.BatchSlots(active, [int(t) for t in hist[-1]], [P + 3] * B, slots), 16)
+    ms = dev.timer_stop() / 16
+    cap = dev._lib.jl_debug_trace(dev.handle, None, 0)  # arm
+    ex.generate(jl.BatchSlots(active, [int(t) for t in hist[-1]], [P + 19] * B, slots), 3)
+    buf = np.zeros(cap * 8, dtype=np.uint64)
+    n = dev._lib.jl_debug_trace(dev.handle, buf.ctypes.data, cap)
+    rec = buf.reshape(cap, 8)[:n].astype(np.int64)
+    rec = rec[np.argsort(rec[:, 1])]
+    step = rec[n // 3: 2 * n // 3]  # the middle one of the three traced steps
+    names = {1: "mat-vec", 2: "attention", 3: "embedding", 4: "advance", 5: "mat-mat", 6: "row kernel", 7: "exchange"}
+    print(f"# one decode step, {args.arch} {args.format}, B={B}, {P + 20} keys; {ms:.3f} ms/step in the trace build; "
+          f"{len(step)} launches; times in us, first CTA of each launch")
+    print("# mat-vec: A = wait for the kernel ahead, B = stage the activations, C = weight loop, D = epilogue to exit")
+    print("# mat-mat: A = set-up (barriers, tensor memory), B = wait for the kernel ahead and for the first weights, "
+          "C = main loop, D = tail; other kernels stamp entry (and exit) only")
+    print("| launch | kernel | entry | A | B | C | D |")
+    print("| ---: | --- | ---: | ---: | ---: | ---: | ---: |")
+    per_layer = max(1, (len(step) - 3) // cfg.numberOfLayers)
+    shown = list(range(min(len(step), 1 + 2 * per_layer))) + list(range(max(0, len(step) - 3), len(step)))
+    for i in sorted(set(shown)):
+        r = step[i]
+        ent, a, b_, c, d = (int(v) for v in r[1:6])
+        def us(x, y):
+            return "%.2f" % ((x - y) / 1e3) if x and y else "-"
+        print(f"| {i} | {names.get(int(r[0]), str(int(r[0])))} | {(ent - int(step[0, 1])) / 1e3:.2f} | {us(a, ent)} | {us(b_, a)} | "
+              f"{us(c, b_)} | {us(d, c) if c else us(d, a)} |")
+    print(f"step span {(int(step[-1, 5] or step[-1, 1]) - int(step[0, 1])) / 1e3:.1f} us; one layer = {per_layer} launches")
+    return 0
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -269,6 +333,8 @@ def main():
 
     if args.sweep:
         return run_sweep(jl, args) if rank == 0 else 0
+    if args.timeline:
+        return run_timeline(jl, args) if rank == 0 else 0
     if args.profile_matmul:
         if rank != 0:
             return 0
