@@ -47,7 +47,7 @@ BYTES_PER_EL = {"Q4_K": 144 / 256, "Q4_0": 18 / 32, "Q8_0": 34 / 32}
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel for the 8B layer
 # shape, from one ncu capture of that launch (the summary is kept with the other profile summaries)
-NCU_TRAFFIC_BYTES = {("Q4_K", 4096, 14336): 66.58e6}
+NCU_TRAFFIC_BYTES = {("Q4_K", 4096, 14336): 66.89e6}
 
 
 def parse_args():
