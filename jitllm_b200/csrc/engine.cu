@@ -686,6 +686,9 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
     JL_LAUNCH(ctx, embedding_launch(emb.type, emb.data, ctx->d_tokens, ctx->d_active, ctx->x, dim, n, ctx->stream, ctx->use_pdl),
               "embedding");
     int rc;
+    // The attention kernel writes its rows in the output projection's operand format as well, when
+    // that projection will read the pre-split buffer (see launch_gemm_segs).
+    const bool attn_presplit = ctx->xb16 != nullptr && n <= ctx->row_cap;
     for (int l = 0; l < d.layers; ++l) {
         const float *attn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
         const float *ffn_norm = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
@@ -730,12 +733,16 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             a.append = own_sequences ? 1 : 0;
             a.partial = ctx->att_partial;
             a.counters = ctx->att_count;
+            if (attn_presplit) {  // the output projection reads these rows as binary16 hi / lo parts
+                a.out_hi = ctx->xb16;
+                a.out_lo = static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * ctx->l_qdim * 2;
+            }
             JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, ctx->use_pdl), "attention");
         }
         if (ctx->tp_size > 1) {
-            if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->part, nullptr, launches, 1))) return rc;
+            if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->part, nullptr, launches, 1, attn_presplit))) return rc;
             if ((rc = tp_reduce_into_x(ctx, n, launches))) return rc;
-        } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->x, ctx->x, launches, 1))) {
+        } else if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->x, ctx->x, launches, 1, attn_presplit))) {
             return rc;
         }
         range.next("ffn", l);

@@ -343,6 +343,18 @@ struct AttnSmem {
 // into the shared memory of the cluster's first CTA, which folds them; only when a context is long
 // enough to use several clusters do their results meet in global memory, where the last cluster
 // to arrive folds them.
+// One attention output element, and its binary16 hi / lo parts at the element's place in the tensor-core
+// path's operand order when the launch asks for them.
+__device__ __forceinline__ void attn_store(const AttnArgs &a, size_t row, int k, float v) {
+    a.out[row * a.dim + k] = v;
+    if (a.out_hi != nullptr) {
+        const int p = (k & ~3) | ((k & 1) << 1) | ((k >> 1) & 1);
+        const __half h = __float2half_rn(v);
+        static_cast<__half *>(a.out_hi)[row * a.dim + p] = h;
+        static_cast<__half *>(a.out_lo)[row * a.dim + p] = __float2half_rn(v - __half2float(h));
+    }
+}
+
 template <int HD, int G, bool WIDE>
 __global__ void __launch_bounds__(AttnShape<HD, G, WIDE>::threads, WIDE ? 2 : 1)
     attn_decode_kernel(const AttnArgs a, const int csize) {
@@ -631,7 +643,7 @@ __global__ void __launch_bounds__(AttnShape<HD, G, WIDE>::threads, WIDE ? 2 : 1)
         }
         const int h = kvh * G + g;
         if (ncl == 1) {
-            a.out[size_t(b) * a.dim + size_t(h) * HD + d] = val / L;
+            attn_store(a, size_t(b), h * HD + d, val / L);
         } else {
             float *p = a.partial + ((size_t(b) * a.heads + h) * ncl_max + cl) * pstride;
             p[d] = val;
@@ -688,7 +700,7 @@ __global__ void __launch_bounds__(AttnShape<HD, G, WIDE>::threads, WIDE ? 2 : 1)
 #pragma unroll
         for (int u = 0; u < kAttnMaxFold; ++u)
             if (u < ncl) val += ld[u] * sm.wgt[g][u];
-        a.out[size_t(b) * a.dim + size_t(kvh * G + g) * HD + d] = val * sm.inv_l[g];
+        attn_store(a, size_t(b), (kvh * G + g) * HD + d, val * sm.inv_l[g]);
     }
     if (tid == 0) a.counters[size_t(b) * a.kv_heads + kvh] = 0u;
 }

@@ -18,6 +18,9 @@ struct KvGeom {
 struct AttnArgs {
     const float *q, *k, *v;  // [width][dim], [width][kv_dim]: projections before RoPE
     float *out;              // [width][dim]
+    // Optional: the same rows as binary16 hi and lo parts (out = hi + lo) in the tensor-core path's operand
+    // order (pairs (k0, k2), (k1, k3) inside every four), [width][dim] each, for the output projection.
+    void *out_hi, *out_lo;
     const float *rope_cos, *rope_sin;  // [ctx][head_dim/2]
     const int32_t *positions, *slots;
     const uint8_t *active;
