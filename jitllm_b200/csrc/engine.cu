@@ -737,7 +737,13 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
                 a.out_hi = ctx->xb16;
                 a.out_lo = static_cast<char *>(ctx->xb16) + size_t(ctx->row_cap) * ctx->l_qdim * 2;
             }
-            JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, ctx->use_pdl), "attention");
+            // A prompt chunk (one sequence, keys appended above) goes through the tiled kernel; decode
+            // batches (one sequence per row) and very short chunks walk the pages row by row.
+            static const int tiled_min = [] { const char *v = getenv("JITLLM_B200_PROMPT_ATTN_MIN_ROWS"); return v ? atoi(v) : 8; }();
+            if (!own_sequences && n >= tiled_min)
+                JL_LAUNCH(ctx, attention_prompt_launch(a, n, ctx->stream, ctx->use_pdl), "prompt attention");
+            else
+                JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, ctx->use_pdl), "attention");
         }
         if (ctx->tp_size > 1) {
             if ((rc = launch_gemm(ctx, ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l], ctx->xb, n, ctx->part, nullptr, launches, 1, attn_presplit))) return rc;

@@ -747,6 +747,218 @@ cudaError_t attn_launch_t(const AttnArgs &a, int width, cudaStream_t stream, boo
                       : attn_launch_w<HD, G, false>(a, width, stream, programmatic);
 }
 
+// ---- prompt attention: a tile of query rows against the pages on the tensor cores -------------------
+// The rows of one prompt chunk all belong to one sequence and their keys are already in the pages, so a
+// CTA can share every key: it takes 16 * RW consecutive rows and the G query heads of one KV head (one warp
+// per head and 16-row block), walks the keys in tiles of 64 staged in shared memory, and keeps the running
+// maximum, the running sum and the 16 x HD output of its rows in registers (online softmax). Products are
+// mma.sync m16n8k16 with fp32 accumulation: S = Q K^T with the rotated query split into two binary16 parts
+// (hi + lo, 22 significant bits; the keys are binary16 in the pages anyway), O += P V with the probabilities
+// rounded to binary16 (they are in [0, 1]). Function of the reference's tensor-core prompt attention
+// (backend/tornado/layers/TensorCoreBatchAttention.java:227-366), not its code; the arithmetic it must match
+// is inference/op/CpuOperations.java:94-235 (score = q.k / sqrt(d), softmax, weighted sum of values).
+template <int HD, int G>
+struct PromptShape {
+    static constexpr int warps = G >= 4 ? G : 4;
+    static constexpr int rw = warps / G;      // 16-row blocks per CTA
+    static constexpr int tq = 16 * rw;        // query rows per CTA
+    static constexpr int tk = 64;             // keys per tile
+    static constexpr int ld = HD + 8;         // padded row of a staged tile, in binary16 elements
+};
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(PromptShape<HD, G>::warps * 32)
+    attn_prompt_kernel(const AttnArgs a, int n) {
+    using P = PromptShape<HD, G>;
+    constexpr int TK = P::tk, LD = P::ld, KS = HD / 16, NB = TK / 8, DB = HD / 8, PS = TK / 16;
+    __shared__ __align__(16) __half ks[TK][LD];
+    __shared__ __align__(16) __half vs[TK][LD];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = warp % G, rb = warp / G;
+    const int kvh = blockIdx.y, head = kvh * G + g;
+    const int cta_row0 = blockIdx.x * P::tq;
+    const int qr = lane >> 2, qc = lane & 3;  // this lane's row of a block (and qr + 8) and column pair
+    pdl_launch_dependents();
+    pdl_wait();
+    const int slot = a.slots[cta_row0];
+    // The two rows of this lane, their positions (-1: no such row, or an inactive one: every key is masked).
+    int row[2], pos[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        row[h] = cta_row0 + rb * 16 + qr + 8 * h;
+        const bool on = row[h] < n && (a.active == nullptr || a.active[row[h]] != 0);
+        pos[h] = on ? a.positions[row[h]] : -1;
+    }
+    // Keys this CTA needs: up to the largest position among its rows.
+    int last = -1;
+    for (int r = cta_row0; r < min(n, cta_row0 + P::tq); ++r)
+        if (a.active == nullptr || a.active[r] != 0) last = max(last, a.positions[r]);
+    // This warp's query block, rotated (inference/op/CpuOperations.java:94-147 applies RoPE to q before the
+    // scores), as A fragments: hi and lo binary16 parts.
+    uint32_t qhi[KS][4], qlo[KS][4];
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+            const int h = f & 1, d0 = 16 * k + 8 * (f >> 1) + 2 * qc;  // a0: row, a1: row + 8, a2 / a3: columns + 8
+            float x0 = 0.f, x1 = 0.f;
+            if (pos[h] >= 0) {
+                const float *qh = a.q + size_t(row[h]) * a.dim + size_t(head) * HD;
+                const float v0 = qh[d0], v1 = qh[d0 + 1];
+                const float cr = a.rope_cos[size_t(pos[h]) * (HD / 2) + d0 / 2], ci = a.rope_sin[size_t(pos[h]) * (HD / 2) + d0 / 2];
+                x0 = __fsub_rn(__fmul_rn(v0, cr), __fmul_rn(v1, ci));
+                x1 = __fadd_rn(__fmul_rn(v0, ci), __fmul_rn(v1, cr));
+            }
+            const __half2 hi = __floats2half2_rn(x0, x1);
+            const float2 back = __half22float2(hi);
+            const __half2 lo = __floats2half2_rn(x0 - back.x, x1 - back.y);
+            qhi[k][f] = *reinterpret_cast<const uint32_t *>(&hi);
+            qlo[k][f] = *reinterpret_cast<const uint32_t *>(&lo);
+        }
+    }
+    float o[DB][4];
+#pragma unroll
+    for (int db = 0; db < DB; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const float inv_sqrt = 1.0f / sqrtf(static_cast<float>(HD));
+    int wl = max(pos[0], pos[1]);  // the largest position among this warp's 16 rows
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) wl = max(wl, __shfl_xor_sync(0xffffffffu, wl, off));
+    const uint32_t vs_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(&vs[0][0]));
+    for (int t0 = 0; t0 <= last; t0 += TK) {
+        __syncthreads();  // everybody is done with the tile before
+        // Stage keys and values t0 .. t0 + 63 of this KV head (16-byte chunks; past the last key: zeros).
+        constexpr int kChunks = TK * HD / 8;
+        for (int c = tid; c < 2 * kChunks; c += P::warps * 32) {
+            const int which = c >= kChunks, cc = which ? c - kChunks : c;
+            const int key = cc / (HD / 8), part = cc % (HD / 8);
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (t0 + key <= last) {
+                const int64_t off = kv_offset(a.kv, slot, t0 + key, a.layer) + int64_t(kvh) * HD + part * 8;
+                val = *reinterpret_cast<const uint4 *>((which ? a.kv.vpool : a.kv.kpool) + off);
+            }
+            *reinterpret_cast<uint4 *>(which ? &vs[key][part * 8] : &ks[key][part * 8]) = val;
+        }
+        __syncthreads();
+        if (t0 > wl) continue;  // every key of this tile lies after this warp's rows
+        // S = Q K^T for 16 rows x 64 keys.
+        float sacc[NB][4];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
+#pragma unroll
+        for (int k = 0; k < KS; ++k) {
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&ks[nb * 8 + qr][16 * k + 2 * qc]);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(&ks[nb * 8 + qr][16 * k + 8 + 2 * qc]);
+                mma_16816(sacc[nb], qhi[k], b0, b1);
+                mma_16816(sacc[nb], qlo[k], b0, b1);
+            }
+        }
+        // Scale, mask what lies after each row's position, and fold the tile into the running softmax.
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int h = c >> 1, key = t0 + nb * 8 + 2 * qc + (c & 1);
+                const float v = key <= pos[h] ? sacc[nb][c] * inv_sqrt : -INFINITY;
+                sacc[nb][c] = v;
+                tmax[h] = fmaxf(tmax[h], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 1));
+            tmax[h] = fmaxf(tmax[h], __shfl_xor_sync(0xffffffffu, tmax[h], 2));
+            const float mn = fmaxf(m[h], tmax[h]);
+            corr[h] = (mn == -INFINITY) ? 1.0f : expf(m[h] - mn);  // exp(-inf) = 0 on the first tile
+            m[h] = mn;
+            l[h] *= corr[h];
+        }
+        uint32_t pa[PS][4];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            float pv[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int h = c >> 1;
+                pv[c] = (m[h] == -INFINITY) ? 0.f : expf(sacc[nb][c] - m[h]);  // exp(-inf) = 0 for masked keys
+                l[h] += pv[c];
+            }
+            const __half2 p01 = __floats2half2_rn(pv[0], pv[1]), p23 = __floats2half2_rn(pv[2], pv[3]);
+            pa[nb >> 1][(nb & 1) * 2] = *reinterpret_cast<const uint32_t *>(&p01);
+            pa[nb >> 1][(nb & 1) * 2 + 1] = *reinterpret_cast<const uint32_t *>(&p23);
+        }
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+            o[db][0] *= corr[0];
+            o[db][1] *= corr[0];
+            o[db][2] *= corr[1];
+            o[db][3] *= corr[1];
+        }
+        // O += P V: the values come out of shared memory transposed (ldmatrix.trans), 16 keys x 8 dimensions a time.
+#pragma unroll
+        for (int j = 0; j < PS; ++j) {
+#pragma unroll
+            for (int db = 0; db < DB; ++db) {
+                uint32_t b0, b1;
+                const uint32_t addr = vs_u32 + uint32_t(((16 * j + (lane & 15)) * LD + db * 8) * 2);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+                mma_16816(o[db], pa[j], b0, b1);
+            }
+        }
+    }
+    // The running sums were kept per lane: add the four lanes of a row, then write out / l.
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int db = 0; db < DB; ++db) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int h = c >> 1;
+            if (pos[h] >= 0) attn_store(a, size_t(row[h]), head * HD + db * 8 + 2 * qc + (c & 1), o[db][c] / l[h]);
+        }
+    }
+}
+
+template <int HD, int G>
+cudaError_t attn_prompt_launch_t(const AttnArgs &a, int n, cudaStream_t stream, bool programmatic) {
+    using P = PromptShape<HD, G>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((n + P::tq - 1) / P::tq, a.kv_heads);
+    cfg.blockDim = dim3(P::warps * 32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, attn_prompt_kernel<HD, G>, a, n);
+}
+
+template <int HD>
+cudaError_t attn_prompt_launch_hd(const AttnArgs &a, int n, cudaStream_t s, bool pdl) {
+    switch (a.heads / a.kv_heads) {
+        case 1: return attn_prompt_launch_t<HD, 1>(a, n, s, pdl);
+        case 2: return attn_prompt_launch_t<HD, 2>(a, n, s, pdl);
+        case 4: return attn_prompt_launch_t<HD, 4>(a, n, s, pdl);
+        case 8: return attn_prompt_launch_t<HD, 8>(a, n, s, pdl);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
 template <int HD>
 cudaError_t attn_launch_hd(const AttnArgs &a, int width, cudaStream_t s, bool pdl) {
     switch (a.heads / a.kv_heads) {
@@ -803,6 +1015,12 @@ int attention_splits(int sm_count, int width, int kv_heads) {
 cudaError_t attention_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
     if (a.head_dim == 128) return attn_launch_hd<128>(a, width, stream, programmatic);
     if (a.head_dim == 64) return attn_launch_hd<64>(a, width, stream, programmatic);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t attention_prompt_launch(const AttnArgs &a, int n, cudaStream_t stream, bool programmatic) {
+    if (a.head_dim == 128) return attn_prompt_launch_hd<128>(a, n, stream, programmatic);
+    if (a.head_dim == 64) return attn_prompt_launch_hd<64>(a, n, stream, programmatic);
     return cudaErrorInvalidValue;
 }
 

@@ -34,6 +34,9 @@ struct AttnArgs {
 
 cudaError_t attention_configure();
 cudaError_t attention_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic);
+// The rows of one prompt chunk (all of one sequence, their keys already in the pages; append = 0): tiles of
+// query rows against tiles of keys on the tensor cores instead of one walk over the pages per row.
+cudaError_t attention_prompt_launch(const AttnArgs &a, int n, cudaStream_t stream, bool programmatic);
 size_t attention_partial_floats(int width, int heads, int nsplit, int head_dim);
 // Key-range splits per (row, KV head) for a launch of `width` rows: cluster size times clusters.
 int attention_splits(int sm_count, int width, int kv_heads);
