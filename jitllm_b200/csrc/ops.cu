@@ -764,7 +764,17 @@ struct PromptShape {
     static constexpr int tq = 16 * rw;        // query rows per CTA
     static constexpr int tk = 64;             // keys per tile
     static constexpr int ld = HD + 8;         // padded row of a staged tile, in binary16 elements
+    static constexpr int pages = 1024;        // page bases kept in shared memory (16 K keys of 16-token pages)
+    static constexpr int tile_halves = tk * ld;
+    // two buffers of a key tile and a value tile each, then the page bases
+    static constexpr int smem_bytes = 2 * 2 * tile_halves * 2 + pages * 8;
 };
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -778,8 +788,9 @@ __global__ void __launch_bounds__(PromptShape<HD, G>::warps * 32)
     attn_prompt_kernel(const AttnArgs a, int n) {
     using P = PromptShape<HD, G>;
     constexpr int TK = P::tk, LD = P::ld, KS = HD / 16, NB = TK / 8, DB = HD / 8, PS = TK / 16;
-    __shared__ __align__(16) __half ks[TK][LD];
-    __shared__ __align__(16) __half vs[TK][LD];
+    extern __shared__ __align__(16) uint8_t prompt_smem[];
+    __half *tiles = reinterpret_cast<__half *>(prompt_smem);  // [buffer][K | V][TK][LD]
+    int64_t *page_base = reinterpret_cast<int64_t *>(prompt_smem + 2 * 2 * P::tile_halves * 2);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = warp % G, rb = warp / G;
     const int kvh = blockIdx.y, head = kvh * G + g;
@@ -831,23 +842,46 @@ __global__ void __launch_bounds__(PromptShape<HD, G>::warps * 32)
     int wl = max(pos[0], pos[1]);  // the largest position among this warp's 16 rows
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) wl = max(wl, __shfl_xor_sync(0xffffffffu, wl, off));
-    const uint32_t vs_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(&vs[0][0]));
-    for (int t0 = 0; t0 <= last; t0 += TK) {
-        __syncthreads();  // everybody is done with the tile before
-        // Stage keys and values t0 .. t0 + 63 of this KV head (16-byte chunks; past the last key: zeros).
+    // Where each page of this sequence starts (for this layer and KV head), once per CTA.
+    const int bt = a.kv.block_tokens;
+    {
+        const int64_t block_stride = int64_t(a.kv.layers) * bt * a.kv.kv_dim;
+        const int npages = last >= 0 ? last / bt + 1 : 0;
+        for (int pg = tid; pg < min(npages, P::pages); pg += P::warps * 32) {
+            const int64_t phys = a.kv.block_table[int64_t(slot) * a.kv.blocks_per_slot + pg];
+            page_base[pg] = phys * block_stride + int64_t(a.layer) * bt * a.kv.kv_dim + int64_t(kvh) * HD;
+        }
+    }
+    __syncthreads();
+    const uint32_t tiles_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(tiles));
+    // Keys and values t0 .. t0 + 63 of this KV head into buffer `buf`, as asynchronous 16-byte copies (past
+    // the last key: zeros), so that the next tile travels while this one is multiplied.
+    auto stage = [&](int t0, int buf) {
         constexpr int kChunks = TK * HD / 8;
         for (int c = tid; c < 2 * kChunks; c += P::warps * 32) {
             const int which = c >= kChunks, cc = which ? c - kChunks : c;
             const int key = cc / (HD / 8), part = cc % (HD / 8);
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (t0 + key <= last) {
-                const int64_t off = kv_offset(a.kv, slot, t0 + key, a.layer) + int64_t(kvh) * HD + part * 8;
-                val = *reinterpret_cast<const uint4 *>((which ? a.kv.vpool : a.kv.kpool) + off);
+            const uint32_t dst = tiles_u32 + uint32_t(((buf * 2 + which) * P::tile_halves + key * LD + part * 8) * 2);
+            const int t = t0 + key;
+            if (t <= last) {
+                const int pg = t / bt;
+                const int64_t base = pg < P::pages ? page_base[pg] : kv_offset(a.kv, slot, t - t % bt, a.layer) + int64_t(kvh) * HD;
+                cp_async_16(dst, (which ? a.kv.vpool : a.kv.kpool) + base + int64_t(t % bt) * a.kv.kv_dim + part * 8);
+            } else {
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
             }
-            *reinterpret_cast<uint4 *>(which ? &vs[key][part * 8] : &ks[key][part * 8]) = val;
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    if (last >= 0) stage(0, 0);
+    for (int t0 = 0, it = 0; t0 <= last; t0 += TK, ++it) {
+        const int buf = it & 1;
+        cp_async_wait_all();  // this thread's copies of tile `it`
+        __syncthreads();      // everybody's copies have landed, and everybody is done with tile it - 1
+        if (t0 + TK <= last) stage(t0 + TK, buf ^ 1);
         if (t0 > wl) continue;  // every key of this tile lies after this warp's rows
+        const __half (*ks)[LD] = reinterpret_cast<const __half (*)[LD]>(tiles + (buf * 2) * P::tile_halves);
+        const uint32_t vs_u32 = tiles_u32 + uint32_t((buf * 2 + 1) * P::tile_halves * 2);
         // S = Q K^T for 16 rows x 64 keys.
         float sacc[NB][4];
 #pragma unroll
@@ -939,6 +973,7 @@ cudaError_t attn_prompt_launch_t(const AttnArgs &a, int n, cudaStream_t stream, 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((n + P::tq - 1) / P::tq, a.kv_heads);
     cfg.blockDim = dim3(P::warps * 32);
+    cfg.dynamicSmemBytes = P::smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -975,6 +1010,9 @@ cudaError_t attn_launch_hd(const AttnArgs &a, int width, cudaStream_t s, bool pd
 namespace {
 template <int HD, int G>
 cudaError_t attn_configure_t() {
+    const cudaError_t ep = cudaFuncSetAttribute(attn_prompt_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                PromptShape<HD, G>::smem_bytes);
+    if (ep != cudaSuccess) return ep;
     const cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, G, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                int(sizeof(AttnSmem<HD, G, false>)));
     if (e != cudaSuccess) return e;
