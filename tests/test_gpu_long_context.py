@@ -82,3 +82,39 @@ def test_wide_batch_with_more_pages_than_the_page_cache(dev, oracle):
             worst = max(worst, float(np.max(np.abs(logits[b] - want))))
     assert worst < LOGIT_BAR, worst
     kv.close()
+
+
+@pytest.mark.parametrize("heads,kv_heads,head", [(8, 1, 64), (4, 2, 64), (2, 2, 128)])
+def test_prompt_tiles_ragged_and_continued(dev, oracle, heads, kv_heads, head):
+    """The tiled prompt attention on ragged chunks: a 37-token prompt (two and a bit 16-row blocks), then a
+    second prompt call of 150 tokens that continues the same sequence at position 37 (its rows attend to
+    keys of the first call), for query-head groups of 8, 2 and 1 per KV head; checked through the logits of
+    the decode steps that follow and through the key rows in the pages."""
+    cfg = _config(heads=heads, kv_heads=kv_heads, head=head, ctx=256)
+    t = GGMLType.Q8_0
+    tensors = jl.synth_model_tensors(cfg, t, seed=21, std=0.05)
+    om = oracle.Model(cfg, tensors)
+    model = jl.load_model(dev, cfg, tensors, *om.rope_tables())
+    bps = cfg.contextLength // 16
+    kv = model.createKvStorage(jl.KvStorageRequest(bps, bps, 1, 16, cfg.numberOfLayers, cfg.kvDim))
+    kv.publishBlockTable(np.random.default_rng(3).permutation(bps).astype(np.int32))
+    kv.fill(0x7E00)
+    first, second, steps = 37, 150, 6
+    toks = np.random.default_rng(4).integers(0, cfg.vocabularySize, size=first + second + steps)
+    bound = jl.B200InvocationBoundary(model, kvSlot=0)
+    bound.prefill([int(v) for v in toks[:first]], 0)
+    bound.prefill([int(v) for v in toks[first:first + second]], first)
+    for pos in range(first + second):
+        om.forward_no_logits(int(toks[pos]), pos)
+    for layer in range(cfg.numberOfLayers):
+        for pos in (0, 36, 37, 100, first + second - 1):
+            got = kv.readRow("k", 0, layer, pos).view(np.float16).astype(np.float32)   # binary16 bit patterns
+            want = om.kcache(layer, pos).view(np.float16).astype(np.float32)
+            assert np.all(np.isfinite(got))
+            assert float(np.max(np.abs(got - want))) <= 4e-3 * float(np.max(np.abs(want))), (layer, pos)
+    for pos in range(first + second, first + second + steps):
+        want = om.forward(int(toks[pos]), pos)
+        got = bound.invoke(int(toks[pos]), pos)
+        assert np.all(np.isfinite(got.logits)), pos
+        assert float(np.max(np.abs(got.logits - want))) < LOGIT_BAR
+    kv.close()
