@@ -77,6 +77,9 @@ def parse_args():
     ap.add_argument("--profile-op", type=int, default=-1,
                     help="launch one matrix-vector operator (0 qkv, 1 out, 2 gate/up, 3 down, 4 vocab) "
                          "--steps times and exit: the small case ncu captures are taken on")
+    ap.add_argument("--prefill-sweep", action="store_true",
+                    help="prompt ingestion rate for prompts of 512, 2048 and 8192 tokens, 1 and 4 sequences (the batched "
+                         "prefill configuration; use --format Q8_0): one JSON line per case")
     ap.add_argument("--timeline", action="store_true",
                     help="print the launch timeline of one decode step (--batch sequences) from the trace build of the "
                          "library: run as JITLLM_B200_TRACE=1 python bench.py --timeline ... after "
@@ -262,6 +265,40 @@ def cpu_sample_text(done, depth, dt):
             f"seeded random rows, no CPU prefill), all layers, scalar summation mode, {dt:.1f} s")
 
 
+def run_prefill_sweep(jl, args):
+    """Prompt tokens per second through jl_prefill (chunks of up to 512 rows: tcgen05 projections, tiled
+    tensor-core attention), CUDA-event time of the whole ingestion, for the batched-prefill configuration."""
+    dims = list(ARCHS[args.arch])
+    dims[6] = max(dims[6], 8192 + 256)
+    cfg = jl.Configuration(dim=dims[0], hiddenDim=dims[1], numberOfLayers=dims[2], numberOfHeads=dims[3],
+                           numberOfKeyValueHeads=dims[4], vocabularySize=dims[5], contextLength=dims[6],
+                           tiedEmbeddings=dims[7])
+    tensors = jl.synth_model_tensors(cfg, jl.GGMLType[args.format], args.seed, threads=os.cpu_count())
+    cr, ci = jl.precomputeFreqsCis(cfg.contextLength, cfg.headSize, cfg.ropeTheta)
+    dev = jl.Device(0)
+    model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=4)
+    bps = cfg.contextLength // 16
+    kv = model.createKvStorage(jl.KvStorageRequest(4 * bps, bps, 4, 16, cfg.numberOfLayers, cfg.kvDim))
+    kv.publishBlockTable(np.arange(4 * bps, dtype=np.int32))
+    flops_per_token = 2.0 * (model_bytes(cfg, args.format) / BYTES_PER_EL[args.format] - cfg.vocabularySize * cfg.dim)
+    warm = np.random.default_rng(1).integers(0, cfg.vocabularySize, size=600)
+    jl.B200InvocationBoundary(model, kvSlot=0, copyLogits=False).prefill(warm, 0)
+    for P in (512, 2048, 8192):
+        for batch in (1, 4):
+            prompts = np.random.default_rng(P + batch).integers(0, cfg.vocabularySize, size=(batch, P))
+            bounds = [jl.B200InvocationBoundary(model, kvSlot=b, copyLogits=False) for b in range(batch)]
+            dev.synchronize()
+            dev.timer_start()
+            for b in range(batch):
+                bounds[b].prefill(prompts[b], 0)
+            ms = dev.timer_stop()
+            rate = batch * P / (ms / 1e3)
+            print(json.dumps({"prefill": {"arch": args.arch, "format": args.format, "prompt": P, "sequences": batch},
+                              "ms": round(ms, 2), "prompt_tok_s": round(rate, 1),
+                              "projection_tflops": round(rate * flops_per_token / 1e12, 1)}), flush=True)
+    return 0
+
+
 def run_timeline(jl, args):
     """One decode step of --batch sequences as a table of launches, from the stamps the trace build of the
     library leaves (first CTA of every launch: entry, dependency resolved, operands staged, loop done, exit)."""
@@ -335,6 +372,8 @@ def main():
         return run_sweep(jl, args) if rank == 0 else 0
     if args.timeline:
         return run_timeline(jl, args) if rank == 0 else 0
+    if args.prefill_sweep:
+        return run_prefill_sweep(jl, args) if rank == 0 else 0
     if args.profile_matmul:
         if rank != 0:
             return 0
