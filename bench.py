@@ -544,6 +544,35 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e_ms = float(t.item())
 
+    # ---- device-side temperature / top-p sampling of the same steps (single GPU): what jl_sample adds to a step,
+    # and the step rate with it, against copying the rows of logits out for a host-side sampler
+    sampling = None
+    if rank == 0 and not use_tp:
+        smp = jl.Sampler.selectSampler(cfg.vocabularySize, 0.8, 0.9, rngSeed=args.seed)
+        n_s = max(4, min(K, 32))
+        s_tok, s_pos, sample_ms = list(tok), pos, 0.0
+        dev.synchronize()
+        s0 = time.perf_counter()
+        for _ in range(n_s):
+            out = ex.decodeStep(jl.BatchSlots(active, s_tok, [s_pos] * B, slots), sampler=smp)
+            sample_ms += dev.counters()["last_step_ms"]
+            s_tok = [int(t) for t in out]
+            s_pos += 1
+        dev.synchronize()
+        s_wall = (time.perf_counter() - s0) * 1000.0
+        dev.synchronize()
+        h0 = time.perf_counter()
+        for _ in range(n_s):
+            ex.decodeStep(jl.BatchSlots(active, s_tok, [s_pos] * B, slots), wantLogits=True)
+            s_pos += 1
+        dev.synchronize()
+        h_wall = (time.perf_counter() - h0) * 1000.0
+        sampling = {"temperature": 0.8, "topp": 0.9, "steps": n_s,
+                    "sample_kernel_us": round(1000.0 * sample_ms / n_s, 1),
+                    "tok_s_with_device_sampling": round(B * n_s / (s_wall / 1000.0), 1),
+                    "tok_s_with_logits_copied_out": round(B * n_s / (h_wall / 1000.0), 1),
+                    "d2h_bytes_per_step": 4 * B, "d2h_bytes_per_step_host_sampler": 4 * B * cfg.vocabularySize}
+
     # ---- per-kernel roofline: each matrix-vector launch shape alone, over all layers' weights
     peak, peak_kind = measured_peak()
     names = {0: "rmsnorm+qkv", 1: "attn-out+residual", 2: "rmsnorm+gate/up+swiglu", 3: "down+residual",
@@ -603,6 +632,7 @@ def main():
                           "frac_of_measured_peak": (weights_b + kv_b) / step_ms / 1e6 / peak,
                           "frac_of_8tbs": (weights_b + kv_b) / step_ms / 1e6 / 8000.0},
         "kernels": ops,
+        "sampling": sampling,
         "setup": {"synth_and_upload_s": round(t_build, 1), "prefill_tok_s": round(B * (P - 1) / t_prefill, 1)},
     }
     if rank == 0 and n_gpus == 1 and B == 1 and args.also_batch > 1 and args.arch in ("8b", "8b4", "tiny", "1b"):
@@ -618,6 +648,14 @@ def main():
         rate, cores, done, dt = cpu_decode_rate(cfg, tensors, args.cpu_seconds, 64, args.seed, depth=depth)
         line["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": cores, "kind": "port",
                                 "sample": cpu_sample_text(done, depth, dt)}
+        # the host-side sampler chain the device sampler replaces (temperature, softmax, top-p), one row, one core
+        from oracle import binding as oracle
+        row = np.random.default_rng(args.seed).standard_normal(cfg.vocabularySize).astype(np.float32)
+        oracle.sample(row, 0.8, 0.9, 0.5)
+        t0 = time.perf_counter()
+        for k in range(5):
+            oracle.sample(row, 0.8, 0.9, 0.1 + 0.2 * k)
+        line["cpu_baseline"]["sampler_ms_per_row"] = round((time.perf_counter() - t0) * 1000.0 / 5, 3)
     else:
         line["cpu_baseline"] = None
     if rank == 0 and use_tp and args.arch != "70b":

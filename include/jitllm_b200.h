@@ -124,6 +124,15 @@ int32_t jl_kv_read_row(jl_ctx *ctx, int32_t which /*0=K,1=V*/, int32_t slot, int
 int32_t jl_decode(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32_t *positions,
                   const int32_t *kv_slots, const uint8_t *active, int32_t *out_tokens,
                   float *out_logits);
+/* Temperature / top-p sampling of the rows of logits the last jl_decode(width) left on the device, in place of
+ * copying them out: replaces the host-side chain Sampler.selectSampler builds for temperature != 0
+ * (inference/sampler/Sampler.java:63-110: scores / temperature, softmax, then CategoricalSampler.java:13-25 when
+ * topp is outside (0,1), else ToppSampler.java:46-103). uniforms[b] is what the caller's generator returned for
+ * this call (rng.nextFloat(1f)); rows that were inactive in the decode get -1. The rows of logits are consumed
+ * (overwritten, as the reference's in-place softmax does), so out_logits of that decode must have been taken
+ * before. last_step_ms reports this call alone. Not available under tensor parallelism. */
+int32_t jl_sample(jl_ctx *ctx, int32_t width, float temperature, float topp, const float *uniforms,
+                  int32_t *out_tokens);
 /* n_steps greedy steps without a host round trip between them: each active row's sampled token is
  * fed back on the device and its position advances (the device-side sampling the reference turns
  * on with -Djitllm.deviceSample, inference/TokenGenerationLoop.java:111-128, carried one step

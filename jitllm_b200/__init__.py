@@ -13,6 +13,7 @@ from .api import (  # noqa: F401
     InsufficientDeviceMemoryError,
     KvStorage,
     KvStorageRequest,
+    Sampler,
     TensorRole,
     UNMAPPED,
     argmax,

@@ -51,6 +51,7 @@ SIGNATURES = {
     "jl_kv_read_row": (_I32, [_P, _I32, _I32, _I32, _I32, _P]),
     "jl_decode": (_I32, [_P, _I32, _P, _P, _P, _P, _P, _P]),
     "jl_generate": (_I32, [_P, _I32, _P, _P, _P, _P, _I32, _P]),
+    "jl_sample": (_I32, [_P, _I32, C.c_float, C.c_float, _P, _P]),
     "jl_prefill": (_I32, [_P, _I32, _P, _I32, _I32]),
     "jl_debug_read": (_I32, [_P, C.c_char_p, _I32, _P, _I64]),
     "jl_dequant": (_I32, [_P, _I32, _P, _I64, _P]),

@@ -436,6 +436,30 @@ class BatchSlots:
         return sum(1 for a in self.active if a)
 
 
+class Sampler:
+    """What Sampler.selectSampler(vocabularySize, temperature, topp, rngSeed) returns
+    (inference/sampler/Sampler.java:63-110), with the arithmetic moved to the device: temperature 0 is
+    greedy (the arg-max every step already returns); otherwise temperature scaling, softmax and
+    categorical or top-p sampling run in jl_sample on the rows of logits the step left on the GPU. The
+    random generator stays on the host, as the reference's does: `rng` is anything with a `random()`
+    method returning a float in [0, 1) (numpy Generator, random.Random); a Java host passes
+    rng.nextFloat(1f). Values are rounded down to a multiple of 2^-24, the granularity of nextFloat."""
+
+    def __init__(self, vocabularySize: int, temperature: float, topp: float, rng=None, rngSeed: int = 0):
+        self.vocabularySize = int(vocabularySize)
+        self.temperature = float(temperature)
+        self.topp = float(topp)
+        self.greedy = self.temperature == 0.0
+        self._rng = rng if rng is not None else np.random.default_rng(rngSeed)
+
+    @staticmethod
+    def selectSampler(vocabularySize: int, temperature: float, topp: float, rngSeed: int) -> "Sampler":
+        return Sampler(vocabularySize, temperature, topp, rngSeed=rngSeed)
+
+    def nextFloat(self) -> np.float32:
+        return np.float32(int(float(self._rng.random()) * (1 << 24)) / float(1 << 24))
+
+
 class B200BatchExecutor:
     """BatchExecutor over the CUDA library: one jl_decode per engine step."""
 
@@ -446,7 +470,11 @@ class B200BatchExecutor:
     def maxBatchSize(self) -> int:
         return self._model.maxBatch
 
-    def decodeStep(self, batch: BatchSlots, wantLogits: bool = False):
+    def decodeStep(self, batch: BatchSlots, wantLogits: bool = False, sampler: "Optional[Sampler]" = None):
+        """One step for every active row. Without a sampler (or with a greedy one) the tokens are the
+        device-side arg-max; with a temperature sampler the rows of logits stay on the device and
+        jl_sample draws from them (inference/sampler/Sampler.java:63-110), one random number per row
+        from the sampler's generator, drawn for every row in row order whether active or not."""
         w = batch.width()
         tokens = np.ascontiguousarray(batch.tokens, dtype=np.int32)
         positions = np.ascontiguousarray(batch.positions, dtype=np.int32)
@@ -457,6 +485,10 @@ class B200BatchExecutor:
         dev = self._model.dev
         dev._check(dev._lib.jl_decode(dev.handle, w, _ptr(tokens), _ptr(positions), _ptr(slots),
                                       _ptr(active), _ptr(out), _ptr(logits)))
+        if sampler is not None and not sampler.greedy:
+            u = np.ascontiguousarray([sampler.nextFloat() for _ in range(w)], dtype=np.float32)
+            dev._check(dev._lib.jl_sample(dev.handle, w, C.c_float(sampler.temperature), C.c_float(sampler.topp),
+                                          _ptr(u), _ptr(out)))
         return (out, logits) if wantLogits else out
 
     def generate(self, batch: BatchSlots, steps: int) -> np.ndarray:

@@ -16,6 +16,7 @@
 
 #include "gemv.cuh"
 #include "ops.cuh"
+#include "sampler.cuh"
 #include "gemm_tc.cuh"
 #include "tp_exchange.cuh"
 
@@ -115,6 +116,8 @@ struct jl_ctx {
     int32_t *d_history = nullptr, *d_step = nullptr;
     size_t history_cap = 0;
     unsigned long long *d_trace = nullptr;  // launch-timeline records (trace build only)
+    float *d_uniforms = nullptr;            // jl_sample: one random number per row
+    int logits_rows = 0;                    // rows of ctx->logits the last jl_decode left valid
     // pinned host staging: tokens | positions | slots | out | active | status
     int32_t *h_stage = nullptr;
 
@@ -1525,9 +1528,51 @@ int32_t jl_decode(jl_ctx *ctx, int32_t width, const int32_t *tokens, const int32
                        gathered.data() + (size_t(k) * width + b) * ctx->l_vocab, size_t(ctx->l_vocab) * 4);
     }
     cudaEventElapsedTime(&ctx->counters.last_step_ms, ctx->ev0, ctx->ev1);
+    ctx->logits_rows = width;
     ctx->counters.decode_calls++;
     ctx->counters.h2d_bytes += width * 13;
     ctx->counters.d2h_bytes += width * 4 + 4 + (out_logits ? size_t(width) * ctx->desc.vocab * 4 : 0);
+    return JL_OK;
+}
+
+int32_t jl_sample(jl_ctx *ctx, int32_t width, float temperature, float topp, const float *uniforms, int32_t *out_tokens) {
+    if (!ctx) return JL_ERR_INVALID;
+    JL_REQUIRE(ctx, ctx->finalized && ctx->has_kv, JL_ERR_STATE, "jl_model_finalize and jl_kv_create must come first");
+    JL_REQUIRE(ctx, uniforms && out_tokens, JL_ERR_INVALID, "uniforms and out_tokens must not be NULL");
+    JL_REQUIRE(ctx, temperature > 0.0f, JL_ERR_INVALID,
+               "temperature must be positive: temperature 0 is greedy decoding, which jl_decode already returns");
+    JL_REQUIRE(ctx, ctx->tp_size == 1, JL_ERR_UNSUPPORTED,
+               "device-side sampling needs the whole row of logits on one GPU: not available under tensor parallelism");
+    JL_REQUIRE(ctx, width >= 1 && width == ctx->logits_rows, JL_ERR_STATE,
+               "jl_sample(width = %d) must follow a jl_decode of the same width (last: %d rows of logits)", width,
+               ctx->logits_rows);
+    for (int b = 0; b < width; ++b)
+        JL_REQUIRE(ctx, uniforms[b] >= 0.0f && uniforms[b] < 1.0f, JL_ERR_INVALID, "uniforms[%d] = %g outside [0, 1)", b,
+                   double(uniforms[b]));
+    cudaSetDevice(ctx->device);
+    if (!ctx->d_uniforms) {
+        int rc = dev_alloc(ctx, reinterpret_cast<void **>(&ctx->d_uniforms), size_t(ctx->row_cap) * 4);
+        if (rc) return rc;
+        ctx->user_allocs.push_back(ctx->d_uniforms);  // released with the context
+        JL_CUDA(ctx, sample_rows_configure());
+    }
+    float *h_u = reinterpret_cast<float *>(ctx->h_stage);
+    int32_t *h_out = ctx->h_stage + 3 * size_t(ctx->row_cap);
+    memcpy(h_u, uniforms, size_t(width) * 4);
+    JL_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->d_uniforms, h_u, size_t(width) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    cudaError_t e = sample_rows_launch(ctx->logits, ctx->desc.vocab, width, ctx->d_active, temperature, topp, ctx->d_uniforms,
+                                       ctx->d_out, ctx->d_out, ctx->stream);  // d_out: the step's arg-max in, the sample out
+    if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "sampling launch failed: %s", cudaGetErrorString(e));
+    ctx->counters.kernel_launches += 1;
+    JL_CUDA(ctx, cudaMemcpyAsync(h_out, ctx->d_out, size_t(width) * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    JL_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    JL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int b = 0; b < width; ++b) out_tokens[b] = h_out[b];
+    cudaEventElapsedTime(&ctx->counters.last_step_ms, ctx->ev0, ctx->ev1);
+    ctx->logits_rows = 0;  // the rows now hold exp(score - max), not logits
+    ctx->counters.h2d_bytes += size_t(width) * 4;
+    ctx->counters.d2h_bytes += size_t(width) * 4;
     return JL_OK;
 }
 

@@ -48,6 +48,8 @@ def lib() -> C.CDLL:
         L.orc_dot.argtypes = [I, P, I64, P, I64]
         L.orc_matmul.argtypes = [I, P, P, P, I, I]
         L.orc_matmul_batch.argtypes = [I, P, P, P, I, I, I]
+        L.orc_sample.restype = I
+        L.orc_sample.argtypes = [P, I, F, F, F, P]
         L.orc_rmsnorm.argtypes = [P, P, P, I, F]
         L.orc_rope.argtypes = [P, P, P, P, I, I, I, I]
         L.orc_swiglu.argtypes = [P, P, I]
@@ -122,6 +124,15 @@ def matmul(t: int, w: np.ndarray, x: np.ndarray, rows: int, cols: int) -> np.nda
     out = np.empty((x.shape[0], rows), dtype=np.float32)
     lib().orc_matmul_batch(int(t), _p(w), _p(x), _p(out), rows, cols, x.shape[0])
     return out
+
+
+def sample(logits: np.ndarray, temperature: float, topp: float, u: float):
+    """The reference's sampler chain on one row (a copy is modified); returns (token, margin): margin is the
+    distance of the scaled random number from the nearest boundary of the cumulative distribution."""
+    row = np.ascontiguousarray(logits, dtype=np.float32).copy()
+    margin = C.c_float()
+    tok = lib().orc_sample(_p(row), int(row.size), C.c_float(temperature), C.c_float(topp), C.c_float(u), C.byref(margin))
+    return int(tok), float(margin.value)
 
 
 class Model:

@@ -761,3 +761,97 @@ const float *orc_state_buffer(const orc_state *s, const char *name) {
 }
 const uint16_t *orc_state_kcache(const orc_state *s, int layer) { return s->kcache[layer]; }
 const uint16_t *orc_state_vcache(const orc_state *s, int layer) { return s->vcache[layer]; }
+
+/* ---- sampler chain (inference/sampler/Sampler.java:63-110) ------------------------------------------------ */
+
+typedef struct {
+    float p;
+    int idx;
+} orc_cand;
+
+static int orc_cand_desc(const void *a, const void *b) {
+    const orc_cand *x = (const orc_cand *)a, *y = (const orc_cand *)b;
+    if (x->p > y->p) return -1;
+    if (x->p < y->p) return 1;
+    return x->idx < y->idx ? -1 : (x->idx > y->idx ? 1 : 0);
+}
+
+int orc_sample(float *logits, int n, float temperature, float topp, float u, float *margin) {
+    if (margin) *margin = 1.0f;
+    if (temperature == 0.0f) { /* Sampler.java:66-68, Logits.java:49-60: first index of the maximum */
+        int best = 0;
+        for (int i = 1; i < n; ++i)
+            if (logits[i] > logits[best]) best = i;
+        return best;
+    }
+    /* Sampler.java:97-99: divideInPlace(temperature), softmaxInPlace (FloatTensor.java:240-256) */
+    for (int i = 0; i < n; ++i) logits[i] = logits[i] / temperature;
+    float mx = logits[0];
+    for (int i = 1; i < n; ++i)
+        if (logits[i] > mx) mx = logits[i];
+    for (int i = 0; i < n; ++i) logits[i] = (float)exp((double)(logits[i] - mx));
+    float sum = 0.0f;
+    for (int i = 0; i < n; ++i) sum += logits[i];
+    for (int i = 0; i < n; ++i) logits[i] = logits[i] / sum;
+    if (topp <= 0.0f || topp >= 1.0f) { /* CategoricalSampler.java:13-25 */
+        float cdf = 0.0f, best = 1.0f;
+        int tok = n - 1, found = 0;
+        for (int i = 0; i < n; ++i) {
+            cdf += logits[i];
+            if (!found && u < cdf) {
+                tok = i;
+                found = 1;
+            }
+            const float gap = fabsf(cdf - u);
+            if (gap < best) best = gap;
+        }
+        if (margin) *margin = best;
+        return tok;
+    }
+    /* ToppSampler.java:46-64: candidates at or above (1 - topp) / (n - 1) */
+    const float cutoff = (1.0f - topp) / (float)(n - 1);
+    orc_cand *c = (orc_cand *)malloc(sizeof(orc_cand) * (size_t)n);
+    int n0 = 0;
+    for (int i = 0; i < n; ++i)
+        if (logits[i] >= cutoff) {
+            c[n0].p = logits[i];
+            c[n0].idx = i;
+            ++n0;
+        }
+    /* ToppSampler.java:70-89: largest first until the running sum exceeds topp */
+    qsort(c, (size_t)n0, sizeof(orc_cand), orc_cand_desc);
+    float cumulative = 0.0f;
+    int last = n0 - 1;
+    for (int i = 0; i < n0; ++i) {
+        cumulative += c[i].p;
+        if (cumulative > topp) {
+            last = i;
+            break;
+        }
+    }
+    /* ToppSampler.java:91-102 */
+    const float r = u * cumulative;
+    float cdf = 0.0f, best = 1.0f;
+    int tok = c[last].idx, found = 0;
+    for (int i = 0; i <= last; ++i) {
+        cdf += c[i].p;
+        if (!found && r < cdf) {
+            tok = c[i].idx;
+            found = 1;
+        }
+        const float gap = fabsf(cdf - r) / cumulative;
+        if (gap < best) best = gap;
+    }
+    /* how close the nucleus boundary itself was to topp */
+    {
+        float run = 0.0f;
+        for (int i = 0; i < n0 && i <= last + 1; ++i) {
+            run += c[i].p;
+            const float gap = fabsf(run - topp);
+            if (gap < best && i >= last - 1) best = gap;
+        }
+    }
+    if (margin) *margin = best;
+    free(c);
+    return tok;
+}

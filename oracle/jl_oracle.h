@@ -115,6 +115,19 @@ const float *orc_state_buffer(const orc_state *s, const char *name);
 const uint16_t *orc_state_kcache(const orc_state *s, int layer);
 const uint16_t *orc_state_vcache(const orc_state *s, int layer);
 
+/* The sampler chain of inference/sampler/Sampler.java:63-110 for one row of logits (modified in place, as
+ * the reference does): temperature 0 = arg-max (first index of the maximum, inference/Logits.java:49-60);
+ * otherwise scores /= temperature, softmaxInPlace (tensor/standard/FloatTensor.java:248-256: max, (float)
+ * Math.exp(f - max), sequential fp32 sum, divide), then CategoricalSampler.sampleToken
+ * (CategoricalSampler.java:13-25) when topp is outside (0,1), else ToppSampler.sampleToken
+ * (ToppSampler.java:46-103). `u` is what rng.nextFloat(1f) returned for this call: the random generator
+ * itself (RandomGeneratorFactory.getDefault()) stays on the caller's side.
+ * Order among equal probabilities: the reference's heap leaves it to its sift order; here ties are taken in
+ * index order (lowest first). When `margin` is not NULL it receives how far, relative to the nucleus mass (or to
+ * 1 for the categorical sampler), the scaled random number was from the nearest boundary of the cumulative
+ * distribution: a sampler that sums in another order may differ only when this is within rounding. */
+int orc_sample(float *logits, int n, float temperature, float topp, float u, float *margin);
+
 #ifdef __cplusplus
 }
 #endif
