@@ -117,6 +117,7 @@ struct jl_ctx {
     size_t history_cap = 0;
     unsigned long long *d_trace = nullptr;  // launch-timeline records (trace build only)
     float *d_uniforms = nullptr;            // jl_sample: one random number per row
+    int batch_attn_min_pairs = 0;           // (rows x KV heads) from which decode batches use attention_batch_launch
     int logits_rows = 0;                    // rows of ctx->logits the last jl_decode left valid
     // pinned host staging: tokens | positions | slots | out | active | status
     int32_t *h_stage = nullptr;
@@ -745,6 +746,10 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             static const int tiled_min = [] { const char *v = getenv("JITLLM_B200_PROMPT_ATTN_MIN_ROWS"); return v ? atoi(v) : 8; }();
             if (!own_sequences && n >= tiled_min)
                 JL_LAUNCH(ctx, attention_prompt_launch(a, n, ctx->stream, ctx->use_pdl), "prompt attention");
+            else if (own_sequences && n >= 4 && n * ctx->l_kv_heads >= ctx->batch_attn_min_pairs)
+                // enough (row, KV head) pairs to fill the GPU with one CTA each: the tensor-core walk; narrower
+                // batches keep the kernel that splits a sequence's keys over a cluster of CTAs
+                JL_LAUNCH(ctx, attention_batch_launch(a, n, ctx->stream, ctx->use_pdl), "batch attention");
             else
                 JL_LAUNCH(ctx, attention_launch(a, n, ctx->stream, ctx->use_pdl), "attention");
         }
@@ -1030,6 +1035,12 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->use_graph = env_flag("JITLLM_B200_GRAPH", true);
     ctx->use_pdl = env_flag("JITLLM_B200_PDL", true);
+    {
+        // enough (row, KV head) pairs to give most SMs a CTA of their own: the tensor-core walk of
+        // attention_batch_launch; narrower batches keep the kernel that splits a sequence's keys over a cluster
+        const char *v = getenv("JITLLM_B200_BATCH_ATTN_MIN_PAIRS");
+        ctx->batch_attn_min_pairs = v ? atoi(v) : (3 * ctx->sm_count) / 4;
+    }
     e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev0);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev1);

@@ -994,6 +994,255 @@ cudaError_t attn_prompt_launch_hd(const AttnArgs &a, int n, cudaStream_t s, bool
     }
 }
 
+// ---- decode attention for wide batches: the query heads of a KV head as the rows of an MMA tile ---------------
+// One CTA per (batch row, KV head). The G query heads that share the KV head are rows 0..G-1 of the 16-row A
+// operand (the other rows are zero), so the scores of all heads against 64 keys are 16 mma.sync per key tile
+// and warp instead of a few thousand scalar multiply-adds, and the kernel runs at the speed the pages arrive.
+// The four warps share the staged key / value tiles (cp.async, one tile ahead, as in the prompt kernel) and
+// split each tile's 64 keys four ways; each keeps its own running maximum, sum and output, merged at the end.
+// The step's own key and value (rotated, rounded to binary16 as the append does) are written to the page and
+// dropped into the staged tile by the CTA itself, so nothing else has to run before it.
+// Arithmetic: inference/op/CpuOperations.java:94-235, as attn_decode_kernel.
+template <int HD, int G>
+struct BatchAttnShape {
+    static constexpr int warps = 4;
+    static constexpr int tk = 32;       // keys per tile: eight per warp
+    static constexpr int depth = 4;     // tile buffers: three tiles in flight while one is used
+    static constexpr int ld = HD + 8;
+    static constexpr int pages = 256;   // page bases kept in shared memory (4 K keys of 16-token pages)
+    static constexpr int tile_halves = tk * ld;
+    static constexpr int merge_floats = warps * G * (HD + 2);  // overlays the tiles once the keys are done
+    static constexpr int smem_bytes = depth * 2 * tile_halves * 2 + pages * 8;  // three CTAs per SM at HD = 128
+    static_assert(merge_floats * 4 <= depth * 2 * tile_halves * 2, "the merge area overlays the tile buffers");
+};
+
+// m16n8k8: D (16 x 8, fp32) += A (16 x 8, two registers) * B (8 x 8, one register)
+__device__ __forceinline__ void mma_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0));
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(BatchAttnShape<HD, G>::warps * 32, 3)
+    attn_batch_kernel(const AttnArgs a) {
+    using P = BatchAttnShape<HD, G>;
+    constexpr int TK = P::tk, LD = P::ld, KS = HD / 16, DB = HD / 8, NBUF = P::depth;
+    constexpr int PARTS = HD / 8;                       // 16-byte chunks per key row
+    constexpr int KEYS_PER_PASS = P::warps * 32 / PARTS;  // key rows one pass of the CTA's threads covers
+    extern __shared__ __align__(16) uint8_t batch_smem[];
+    __half *tiles = reinterpret_cast<__half *>(batch_smem);  // [buffer][K | V][TK][LD]
+    int64_t *page_base = reinterpret_cast<int64_t *>(batch_smem + NBUF * 2 * P::tile_halves * 2);
+    float *merge = reinterpret_cast<float *>(batch_smem);  // after the last tile
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = blockIdx.x, b = blockIdx.y;
+    const int qr = lane >> 2, qc = lane & 3;
+    const bool on = a.active == nullptr || a.active[b] != 0;
+    pdl_launch_dependents();
+    // positions, slots and the block table are not written by anything in this step (see attn_decode_kernel)
+    const int pos = on ? a.positions[b] : -1;
+    const int slot = on ? a.slots[b] : 0;
+    const int bt = a.kv.block_tokens;
+    if (on) {
+        const int64_t block_stride = int64_t(a.kv.layers) * bt * a.kv.kv_dim;
+        for (int pg = tid; pg < min(pos / bt + 1, P::pages); pg += P::warps * 32) {
+            const int64_t phys = a.kv.block_table[int64_t(slot) * a.kv.blocks_per_slot + pg];
+            page_base[pg] = phys * block_stride + int64_t(a.layer) * bt * a.kv.kv_dim + int64_t(kvh) * HD;
+        }
+    }
+    __syncthreads();
+    const uint32_t tiles_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(tiles));
+    auto key_offset = [&](int t) -> int64_t {
+        const int pg = t / bt;
+        const int64_t base = pg < P::pages ? page_base[pg] : kv_offset(a.kv, slot, t - t % bt, a.layer) + int64_t(kvh) * HD;
+        return base + int64_t(t % bt) * a.kv.kv_dim;
+    };
+    // Keys 0 .. pos - 1 come from the pages (this step's key, position pos, is written below). A thread copies the
+    // same 16-byte part of every KEYS_PER_PASS-th key row, of the key tile and of the value tile.
+    const int part = tid % PARTS, key_first = tid / PARTS;
+    auto stage = [&](int t0, int buf) {
+#pragma unroll
+        for (int key = key_first; key < TK; key += KEYS_PER_PASS) {
+            const uint32_t dk = tiles_u32 + uint32_t(((buf * 2) * P::tile_halves + key * LD + part * 8) * 2);
+            const uint32_t dv = dk + uint32_t(P::tile_halves * 2);
+            const int t = t0 + key;
+            if (t < pos) {
+                const int64_t off = key_offset(t) + part * 8;
+                cp_async_16(dk, a.kv.kpool + off);
+                cp_async_16(dv, a.kv.vpool + off);
+            } else {
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dk), "r"(0u) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dv), "r"(0u) : "memory");
+            }
+        }
+        cp_async_commit();
+    };
+    const int ntiles = on ? pos / TK + 1 : 0;
+    // old keys: in flight while the kernel ahead finishes (one commit group per tile slot, empty ones included,
+    // so that "all but the newest NBUF - 2 groups" always means "the tile about to be used")
+#pragma unroll
+    for (int p = 0; p < NBUF - 1; ++p) {
+        if (p < ntiles) stage(p * TK, p);
+        else cp_async_commit();
+    }
+    pdl_wait();
+    if (!on) return;
+    // The G heads' queries, rotated, as rows 0..G-1 of the A operand (hi and lo binary16 parts); rows G..15 are zero.
+    uint32_t qhi[KS][2], qlo[KS][2];  // a0 and a2 of each K step: a1 / a3 (rows 8..15) are zero
+    const float *cr = a.rope_cos + size_t(pos) * (HD / 2), *ci = a.rope_sin + size_t(pos) * (HD / 2);
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+#pragma unroll
+        for (int f = 0; f < 2; ++f) {
+            const int d0 = 16 * k + 8 * f + 2 * qc;
+            float x0 = 0.f, x1 = 0.f;
+            if (qr < G) {
+                const float *qh = a.q + size_t(b) * a.dim + size_t(kvh * G + qr) * HD;
+                const float v0 = qh[d0], v1 = qh[d0 + 1];
+                x0 = __fsub_rn(__fmul_rn(v0, cr[d0 / 2]), __fmul_rn(v1, ci[d0 / 2]));
+                x1 = __fadd_rn(__fmul_rn(v0, ci[d0 / 2]), __fmul_rn(v1, cr[d0 / 2]));
+            }
+            const __half2 hi = __floats2half2_rn(x0, x1);
+            const float2 back = __half22float2(hi);
+            const __half2 lo = __floats2half2_rn(x0 - back.x, x1 - back.y);
+            qhi[k][f] = *reinterpret_cast<const uint32_t *>(&hi);
+            qlo[k][f] = *reinterpret_cast<const uint32_t *>(&lo);
+        }
+    }
+    float o[DB][4];
+#pragma unroll
+    for (int db = 0; db < DB; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
+    float m = -INFINITY, l = 0.f;  // of row qr (a head when qr < G)
+    const float inv_sqrt = 1.0f / sqrtf(static_cast<float>(HD));
+    for (int it = 0; it < ntiles; ++it) {
+        const int t0 = it * TK, buf = it % NBUF;
+        asm volatile("cp.async.wait_group %0;" ::"n"(NBUF - 2) : "memory");  // this thread's copies of tile `it`
+        __syncthreads();  // everybody's copies of it have landed, and everybody is done with tile it - 1
+        if (it + NBUF - 1 < ntiles) stage((it + NBUF - 1) * TK, (it + NBUF - 1) % NBUF);  // into the buffer tile it - 1 used
+        else cp_async_commit();
+        __half *kt = tiles + (buf * 2) * P::tile_halves, *vt = tiles + (buf * 2 + 1) * P::tile_halves;
+        if (it == ntiles - 1) {
+            // This step's key and value: rotate k, round both to binary16, into the page and into the tile.
+            const int64_t off = key_offset(pos);
+            const float *kh = a.k + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
+            const float *vh = a.v + size_t(b) * a.kv.kv_dim + size_t(kvh) * HD;
+            for (int idx = tid; idx < HD; idx += P::warps * 32) {
+                const int i = idx % (HD / 2);
+                __half2 h;
+                if (idx < HD / 2) {
+                    const float v0 = kh[2 * i], v1 = kh[2 * i + 1];
+                    h = __halves2half2(__float2half_rn(__fsub_rn(__fmul_rn(v0, cr[i]), __fmul_rn(v1, ci[i]))),
+                                       __float2half_rn(__fadd_rn(__fmul_rn(v0, ci[i]), __fmul_rn(v1, cr[i]))));
+                    *reinterpret_cast<__half2 *>(kt + (pos - t0) * LD + 2 * i) = h;
+                    *reinterpret_cast<__half2 *>(a.kv.kpool + off + 2 * i) = h;
+                } else {
+                    h = __halves2half2(__float2half_rn(vh[2 * i]), __float2half_rn(vh[2 * i + 1]));
+                    *reinterpret_cast<__half2 *>(vt + (pos - t0) * LD + 2 * i) = h;
+                    *reinterpret_cast<__half2 *>(a.kv.vpool + off + 2 * i) = h;
+                }
+            }
+            __syncthreads();
+        }
+        const int k0 = 8 * warp;  // this warp's eight keys of the tile
+        if (t0 + k0 > pos) continue;
+        // S = Q K^T: 16 rows (heads) x 8 keys
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < KS; ++k) {
+            const uint32_t ah[4] = {qhi[k][0], 0u, qhi[k][1], 0u}, al[4] = {qlo[k][0], 0u, qlo[k][1], 0u};
+            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(kt + (k0 + qr) * LD + 16 * k + 2 * qc);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(kt + (k0 + qr) * LD + 16 * k + 8 + 2 * qc);
+            mma_16816(sacc, ah, b0, b1);
+            mma_16816(sacc, al, b0, b1);
+        }
+        // rows 0..7 are c0 / c1 of each lane: scale, mask the keys after pos, fold into the running soft-max
+        float sv[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) sv[c] = (t0 + k0 + 2 * qc + c <= pos) ? sacc[c] * inv_sqrt : -INFINITY;
+        float tmax = fmaxf(sv[0], sv[1]);
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float mn = fmaxf(m, tmax);
+        const float corr = (mn == -INFINITY) ? 1.0f : expf(m - mn);
+        m = mn;
+        const float p0 = (m == -INFINITY) ? 0.f : expf(sv[0] - m), p1 = (m == -INFINITY) ? 0.f : expf(sv[1] - m);
+        l = l * corr + p0 + p1;
+        const __half2 ph = __floats2half2_rn(p0, p1);
+        const uint32_t pa0 = *reinterpret_cast<const uint32_t *>(&ph);  // a0: rows 0..7, keys 2 qc, 2 qc + 1; a1 (rows 8..15) is zero
+        const uint32_t vt_u32 = tiles_u32 + uint32_t((buf * 2 + 1) * P::tile_halves * 2);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+            o[db][0] *= corr;
+            o[db][1] *= corr;
+            uint32_t b0;
+            const uint32_t addr = vt_u32 + uint32_t(((k0 + (lane & 7)) * LD + db * 8) * 2);
+            asm volatile("ldmatrix.sync.aligned.m8n8.x1.trans.shared.b16 {%0}, [%1];" : "=r"(b0) : "r"(addr));
+            mma_1688(o[db], pa0, 0u, b0);
+        }
+    }
+    // Merge the four warps (each saw a quarter of every tile's keys): per head the maxima, sums and outputs.
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // everybody is done with the tiles: their memory becomes the merge area
+    if (qr < G) {
+        float *mine = merge + (warp * G + qr) * (HD + 2);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+            mine[db * 8 + 2 * qc] = o[db][0];
+            mine[db * 8 + 2 * qc + 1] = o[db][1];
+        }
+        if (qc == 0) {
+            mine[HD] = m;
+            mine[HD + 1] = l;
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += P::warps * 32) {
+        const int g = idx / HD, d = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < P::warps; ++w) M = fmaxf(M, merge[(w * G + g) * (HD + 2) + HD]);
+        float val = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < P::warps; ++w) {
+            const float *pw = merge + (w * G + g) * (HD + 2);
+            const float wgt = (pw[HD] == -INFINITY) ? 0.f : expf(pw[HD] - M);
+            val += pw[d] * wgt;
+            L += pw[HD + 1] * wgt;
+        }
+        attn_store(a, size_t(b), (kvh * G + g) * HD + d, val / L);
+    }
+}
+
+template <int HD, int G>
+cudaError_t attn_batch_launch_t(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
+    using P = BatchAttnShape<HD, G>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.kv_heads, width);
+    cfg.blockDim = dim3(P::warps * 32);
+    cfg.dynamicSmemBytes = P::smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, attn_batch_kernel<HD, G>, a);
+}
+
+template <int HD>
+cudaError_t attn_batch_launch_hd(const AttnArgs &a, int width, cudaStream_t s, bool pdl) {
+    switch (a.heads / a.kv_heads) {
+        case 1: return attn_batch_launch_t<HD, 1>(a, width, s, pdl);
+        case 2: return attn_batch_launch_t<HD, 2>(a, width, s, pdl);
+        case 4: return attn_batch_launch_t<HD, 4>(a, width, s, pdl);
+        case 8: return attn_batch_launch_t<HD, 8>(a, width, s, pdl);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
 template <int HD>
 cudaError_t attn_launch_hd(const AttnArgs &a, int width, cudaStream_t s, bool pdl) {
     switch (a.heads / a.kv_heads) {
@@ -1013,6 +1262,9 @@ cudaError_t attn_configure_t() {
     const cudaError_t ep = cudaFuncSetAttribute(attn_prompt_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 PromptShape<HD, G>::smem_bytes);
     if (ep != cudaSuccess) return ep;
+    const cudaError_t eb = cudaFuncSetAttribute(attn_batch_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                BatchAttnShape<HD, G>::smem_bytes);
+    if (eb != cudaSuccess) return eb;
     const cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD, G, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                int(sizeof(AttnSmem<HD, G, false>)));
     if (e != cudaSuccess) return e;
@@ -1053,6 +1305,12 @@ int attention_splits(int sm_count, int width, int kv_heads) {
 cudaError_t attention_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
     if (a.head_dim == 128) return attn_launch_hd<128>(a, width, stream, programmatic);
     if (a.head_dim == 64) return attn_launch_hd<64>(a, width, stream, programmatic);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t attention_batch_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic) {
+    if (a.head_dim == 128) return attn_batch_launch_hd<128>(a, width, stream, programmatic);
+    if (a.head_dim == 64) return attn_batch_launch_hd<64>(a, width, stream, programmatic);
     return cudaErrorInvalidValue;
 }
 

@@ -37,6 +37,9 @@ cudaError_t attention_launch(const AttnArgs &a, int width, cudaStream_t stream, 
 // The rows of one prompt chunk (all of one sequence, their keys already in the pages; append = 0): tiles of
 // query rows against tiles of keys on the tensor cores instead of one walk over the pages per row.
 cudaError_t attention_prompt_launch(const AttnArgs &a, int n, cudaStream_t stream, bool programmatic);
+// A decode batch of at least four rows (one sequence per row, append = 1): one CTA per (row, KV head) with the
+// query heads as the rows of a tensor-core tile; rotates and appends the step's own key and value itself.
+cudaError_t attention_batch_launch(const AttnArgs &a, int width, cudaStream_t stream, bool programmatic);
 size_t attention_partial_floats(int width, int heads, int nsplit, int head_dim);
 // Key-range splits per (row, KV head) for a launch of `width` rows: cluster size times clusters.
 int attention_splits(int sm_count, int width, int kv_heads);

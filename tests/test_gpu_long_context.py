@@ -118,3 +118,50 @@ def test_prompt_tiles_ragged_and_continued(dev, oracle, heads, kv_heads, head):
         assert np.all(np.isfinite(got.logits)), pos
         assert float(np.max(np.abs(got.logits - want))) < LOGIT_BAR
     kv.close()
+
+
+@pytest.mark.parametrize("heads,kv_heads,head", [(8, 2, 64), (4, 1, 128), (2, 2, 128), (8, 1, 64)])
+def test_batch_attention_kernel_on_ragged_batches(oracle, monkeypatch, heads, kv_heads, head):
+    """The tensor-core decode attention for wide batches (one CTA per row and KV head, query heads as the rows
+    of the MMA tile), forced on for a narrow batch: eight sequences at different depths (1 to 130 keys: fewer
+    keys than one tile, exact multiples of a tile, several ring turns), one inactive row, poisoned pool,
+    scattered pages, four steps each; logits against the oracle fed token by token, and the keys the kernel
+    itself appends are read back."""
+    monkeypatch.setenv("JITLLM_B200_BATCH_ATTN_MIN_PAIRS", "1")
+    cfg = _config(heads=heads, kv_heads=kv_heads, head=head, ctx=192)
+    t = GGMLType.Q8_0
+    tensors = jl.synth_model_tensors(cfg, t, seed=33, std=0.05)
+    width, steps = 8, 4
+    depths = [1, 5, 31, 32, 33, 64, 100, 130]
+    with jl.Device(0) as dev:
+        oms = [oracle.Model(cfg, tensors) for _ in range(width)]
+        model = jl.load_model(dev, cfg, tensors, *oms[0].rope_tables(), maxBatch=width)
+        bps = cfg.contextLength // 16
+        kv = model.createKvStorage(jl.KvStorageRequest(width * bps, bps, width, 16, cfg.numberOfLayers, cfg.kvDim))
+        kv.publishBlockTable(np.random.default_rng(5).permutation(width * bps).astype(np.int32))
+        kv.fill(0x7E00)
+        rng = np.random.default_rng(6)
+        for b in range(width):
+            prompt = [int(v) for v in rng.integers(0, cfg.vocabularySize, size=depths[b])]
+            jl.B200InvocationBoundary(model, kvSlot=b, copyLogits=False).prefill(prompt, 0)
+            for pos, tok in enumerate(prompt):
+                oms[b].forward_no_logits(tok, pos)
+        ex = jl.B200BatchExecutor(model)
+        positions = list(depths)
+        active = [True] * width
+        active[3] = False
+        for step in range(steps):
+            toks = [int(v) for v in rng.integers(0, cfg.vocabularySize, size=width)]
+            out, logits = ex.decodeStep(jl.BatchSlots(active, toks, positions, list(range(width))), wantLogits=True)
+            for b in range(width):
+                if not active[b]:
+                    assert out[b] == -1
+                    continue
+                want = oms[b].forward(toks[b], positions[b])
+                assert np.all(np.isfinite(logits[b])), (step, b)
+                assert float(np.max(np.abs(logits[b] - want))) < LOGIT_BAR, (step, b)
+                got_k = kv.readRow("k", b, cfg.numberOfLayers - 1, positions[b]).view(np.float16).astype(np.float32)
+                want_k = oms[b].kcache(cfg.numberOfLayers - 1, positions[b]).view(np.float16).astype(np.float32)
+                assert float(np.max(np.abs(got_k - want_k))) <= 4e-3 * float(np.max(np.abs(want_k))), (step, b)
+                positions[b] += 1
+        kv.close()
