@@ -1006,26 +1006,18 @@ cudaError_t attn_prompt_launch_hd(const AttnArgs &a, int n, cudaStream_t s, bool
 template <int HD, int G>
 struct BatchAttnShape {
     static constexpr int warps = 4;
-    static constexpr int tk = 32;       // keys per tile: eight per warp
-    static constexpr int depth = 4;     // tile buffers: three tiles in flight while one is used
+    static constexpr int tk = 64;       // keys per tile: sixteen per warp
+    static constexpr int depth = 3;     // tile buffers: two tiles in flight while one is used
     static constexpr int ld = HD + 8;
     static constexpr int pages = 256;   // page bases kept in shared memory (4 K keys of 16-token pages)
     static constexpr int tile_halves = tk * ld;
     static constexpr int merge_floats = warps * G * (HD + 2);  // overlays the tiles once the keys are done
-    static constexpr int smem_bytes = depth * 2 * tile_halves * 2 + pages * 8;  // three CTAs per SM at HD = 128
+    static constexpr int smem_bytes = depth * 2 * tile_halves * 2 + pages * 8;  // two CTAs per SM at HD = 128
     static_assert(merge_floats * 4 <= depth * 2 * tile_halves * 2, "the merge area overlays the tile buffers");
 };
 
-// m16n8k8: D (16 x 8, fp32) += A (16 x 8, two registers) * B (8 x 8, one register)
-__device__ __forceinline__ void mma_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(b0));
-}
-
 template <int HD, int G>
-__global__ void __launch_bounds__(BatchAttnShape<HD, G>::warps * 32, 3)
+__global__ void __launch_bounds__(BatchAttnShape<HD, G>::warps * 32, 2)
     attn_batch_kernel(const AttnArgs a) {
     using P = BatchAttnShape<HD, G>;
     constexpr int TK = P::tk, LD = P::ld, KS = HD / 16, DB = HD / 8, NBUF = P::depth;
@@ -1039,6 +1031,7 @@ __global__ void __launch_bounds__(BatchAttnShape<HD, G>::warps * 32, 3)
     const int kvh = blockIdx.x, b = blockIdx.y;
     const int qr = lane >> 2, qc = lane & 3;
     const bool on = a.active == nullptr || a.active[b] != 0;
+    const int trace = trace_begin(kTraceAttn);
     pdl_launch_dependents();
     // positions, slots and the block table are not written by anything in this step (see attn_decode_kernel)
     const int pos = on ? a.positions[b] : -1;
@@ -1087,6 +1080,7 @@ __global__ void __launch_bounds__(BatchAttnShape<HD, G>::warps * 32, 3)
         else cp_async_commit();
     }
     pdl_wait();
+    trace_mark(trace, 2);
     if (!on) return;
     // The G heads' queries, rotated, as rows 0..G-1 of the A operand (hi and lo binary16 parts); rows G..15 are zero.
     uint32_t qhi[KS][2], qlo[KS][2];  // a0 and a2 of each K step: a1 / a3 (rows 8..15) are zero
@@ -1115,6 +1109,7 @@ __global__ void __launch_bounds__(BatchAttnShape<HD, G>::warps * 32, 3)
     for (int db = 0; db < DB; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
     float m = -INFINITY, l = 0.f;  // of row qr (a head when qr < G)
     const float inv_sqrt = 1.0f / sqrtf(static_cast<float>(HD));
+    trace_mark(trace, 3);
     for (int it = 0; it < ntiles; ++it) {
         const int t0 = it * TK, buf = it % NBUF;
         asm volatile("cp.async.wait_group %0;" ::"n"(NBUF - 2) : "memory");  // this thread's copies of tile `it`
@@ -1144,44 +1139,59 @@ __global__ void __launch_bounds__(BatchAttnShape<HD, G>::warps * 32, 3)
             }
             __syncthreads();
         }
-        const int k0 = 8 * warp;  // this warp's eight keys of the tile
+        const int k0 = 16 * warp;  // this warp's sixteen keys of the tile
         if (t0 + k0 > pos) continue;
-        // S = Q K^T: 16 rows (heads) x 8 keys
-        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+        // S = Q K^T: 16 rows (heads) x 16 keys; separate accumulators for the hi and the lo part of q, so that
+        // four chains of MMAs run side by side
+        float sh[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, sl[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int k = 0; k < KS; ++k) {
             const uint32_t ah[4] = {qhi[k][0], 0u, qhi[k][1], 0u}, al[4] = {qlo[k][0], 0u, qlo[k][1], 0u};
-            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(kt + (k0 + qr) * LD + 16 * k + 2 * qc);
-            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(kt + (k0 + qr) * LD + 16 * k + 8 + 2 * qc);
-            mma_16816(sacc, ah, b0, b1);
-            mma_16816(sacc, al, b0, b1);
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(kt + (k0 + nb * 8 + qr) * LD + 16 * k + 2 * qc);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(kt + (k0 + nb * 8 + qr) * LD + 16 * k + 8 + 2 * qc);
+                mma_16816(sh[nb], ah, b0, b1);
+                mma_16816(sl[nb], al, b0, b1);
+            }
         }
         // rows 0..7 are c0 / c1 of each lane: scale, mask the keys after pos, fold into the running soft-max
-        float sv[2];
+        float sv[2][2];
+        float tmax = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) sv[c] = (t0 + k0 + 2 * qc + c <= pos) ? sacc[c] * inv_sqrt : -INFINITY;
-        float tmax = fmaxf(sv[0], sv[1]);
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                sv[nb][c] = (t0 + k0 + nb * 8 + 2 * qc + c <= pos) ? (sh[nb][c] + sl[nb][c]) * inv_sqrt : -INFINITY;
+                tmax = fmaxf(tmax, sv[nb][c]);
+            }
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
         const float mn = fmaxf(m, tmax);
         const float corr = (mn == -INFINITY) ? 1.0f : expf(m - mn);
         m = mn;
-        const float p0 = (m == -INFINITY) ? 0.f : expf(sv[0] - m), p1 = (m == -INFINITY) ? 0.f : expf(sv[1] - m);
-        l = l * corr + p0 + p1;
-        const __half2 ph = __floats2half2_rn(p0, p1);
-        const uint32_t pa0 = *reinterpret_cast<const uint32_t *>(&ph);  // a0: rows 0..7, keys 2 qc, 2 qc + 1; a1 (rows 8..15) is zero
+        l *= corr;
+        uint32_t pa[4] = {0u, 0u, 0u, 0u};  // a0 (keys 0-7) and a2 (keys 8-15) of rows 0..7; a1 / a3 (rows 8..15) stay zero
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+            const float p0 = (m == -INFINITY) ? 0.f : expf(sv[nb][0] - m), p1 = (m == -INFINITY) ? 0.f : expf(sv[nb][1] - m);
+            l += p0 + p1;
+            const __half2 ph = __floats2half2_rn(p0, p1);
+            pa[2 * nb] = *reinterpret_cast<const uint32_t *>(&ph);
+        }
         const uint32_t vt_u32 = tiles_u32 + uint32_t((buf * 2 + 1) * P::tile_halves * 2);
 #pragma unroll
         for (int db = 0; db < DB; ++db) {
             o[db][0] *= corr;
             o[db][1] *= corr;
-            uint32_t b0;
-            const uint32_t addr = vt_u32 + uint32_t(((k0 + (lane & 7)) * LD + db * 8) * 2);
-            asm volatile("ldmatrix.sync.aligned.m8n8.x1.trans.shared.b16 {%0}, [%1];" : "=r"(b0) : "r"(addr));
-            mma_1688(o[db], pa0, 0u, b0);
+            uint32_t b0, b1;
+            const uint32_t addr = vt_u32 + uint32_t(((k0 + (lane & 15)) * LD + db * 8) * 2);
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+            mma_16816(o[db], pa, b0, b1);
         }
     }
     // Merge the four warps (each saw a quarter of every tile's keys): per head the maxima, sums and outputs.
+    trace_mark(trace, 4);
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -1214,6 +1224,7 @@ __global__ void __launch_bounds__(BatchAttnShape<HD, G>::warps * 32, 3)
         }
         attn_store(a, size_t(b), (kvh * G + g) * HD + d, val / L);
     }
+    trace_mark(trace, 5);
 }
 
 template <int HD, int G>
