@@ -718,7 +718,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // Two groups of eight warps take alternate operand stages (group 0 the first 128 columns of
         // every raw stage, group 1 the second): a thread converts a whole 64-column unit of its row,
         // so block headers, scale unpacking and barrier traffic are paid once per 64 weights.
-        pdl_wait();
+        // Converting weights depends on nothing the kernel ahead produces: with pre-split activations these warps fill
+        // the operand ring first and wait for that kernel only before their first epilogue (results, residuals,
+        // the partial-tile workspace). When they convert the activations themselves they wait here.
+        bool waited = false;
+        if (!XT) {
+            pdl_wait();
+            waited = true;
+        }
         constexpr int kGroupThreads = kConvertThreads / 2;
         const int grp = warp >> 3, g_tid = tid & (kGroupThreads - 1);
         const int a_row = g_tid & 127, a_unit = g_tid >> 7;  // a_unit: which 64-column unit of the 128
@@ -900,6 +907,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const bool whole = seg_begin == u_lo && seg_end == u_lo + raw_total;
             const GemmSeg seg = a.seg[tr.seg];
             publish();  // the accumulator cannot finish before the last stage is published
+            if (!waited) {
+                pdl_wait();
+                waited = true;
+            }
 #ifdef JL_TRACE
             const long long tq2 = clock64();
 #endif
