@@ -342,8 +342,9 @@ def run_timeline(jl, args):
     print(f"# one decode step, {args.arch} {args.format}, B={B}, {P + 20} keys; {ms:.3f} ms/step in the trace build; "
           f"{len(step)} launches; times in us, first CTA of each launch")
     print("# mat-vec: A = wait for the kernel ahead, B = stage the activations, C = weight loop, D = epilogue to exit")
-    print("# mat-mat: A = set-up (barriers, tensor memory), B = wait for the kernel ahead and for the first weights, "
-          "C = main loop, D = tail; other kernels stamp entry (and exit) only")
+    print("# mat-mat: A = set-up (barriers, tensor memory), B = wait for the first weights, C = main loop (it fills the "
+          "operand ring, then waits for the kernel ahead before the first results), D = tail; other kernels stamp entry "
+          "(and exit) only")
     print("| launch | kernel | entry | A | B | C | D |")
     print("| ---: | --- | ---: | ---: | ---: | ---: | ---: |")
     per_layer = max(1, (len(step) - 3) // cfg.numberOfLayers)

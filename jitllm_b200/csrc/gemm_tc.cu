@@ -371,8 +371,8 @@ struct GemmSmem {
     static constexpr int b_sub = 2 * NT * 128;         // one 64-column atom of B: hi rows, then lo rows
     static constexpr int b_stage = 2 * b_sub;
     static constexpr int bar_bytes = 384;               // barriers, the tensor-memory address and two flags
-#ifdef JL_TRACE
-    static constexpr int log_bytes = 4096;              // trace build: an event log of 512 words, copied out at the end
+#ifdef JL_TRACE_EVENTS
+    static constexpr int log_bytes = 4096;              // event-log build: a log of 512 words, copied out at the end
 #else
     static constexpr int log_bytes = 0;
 #endif
@@ -504,7 +504,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // 1024-byte aligned base: the swizzle pattern is a function of the shared address.
     uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int ST = S::stages;
-#ifdef JL_TRACE
+    // The per-stage event log of CTA 0 is a build of its own (-DJL_TRACE -DJL_TRACE_EVENTS): its bookkeeping costs
+    // registers that the timeline build would have to spill.
+#ifdef JL_TRACE_EVENTS
     unsigned long long *slog = reinterpret_cast<unsigned long long *>(base + S::log_off);
     const bool logging = blockIdx.x == 0 && a.nseg == 2;
     if (tid < 512) slog[tid] = 0ull;
@@ -558,7 +560,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // the activation-copy thread and the conversion warps do, the weight-copy thread does not.
     pdl_launch_dependents();
 #ifdef JL_TRACE
-    long long tw_raw = 0, tw_free = 0, tw_acc = 0, tw_epi = 0, tw_pub = 0, tw_cvt = 0;
+    unsigned tw_raw = 0, tw_free = 0, tw_acc = 0, tw_epi = 0, tw_pub = 0, tw_cvt = 0;
 #endif
 
     if (warp == kConvertWarps + 1) {
@@ -651,7 +653,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const uint32_t b_lo0 = ((smem_u32(base + S::b_off) >> 4) & 0x3FFFu) | (1u << 16);
             const uint32_t full0 = smem_u32(a_full), free0 = smem_u32(a_free), acc_full_u32 = smem_u32(acc_full);
             int s = 0, done = 0;
-#ifdef JL_TRACE
+#ifdef JL_TRACE_EVENTS
             int qlog = 0;
 #endif
             uint32_t parity = 0, a_col = a_col0, b_lo = b_lo0;
@@ -662,19 +664,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 const int seg_end = u_lo + raw_total < hi ? u_lo + raw_total : hi;
                 const int nstage = 2 * (seg_end - f);  // operand stages of this CTA's share of the tile
 #ifdef JL_TRACE
-                const long long tm2_ = clock64();
+                const unsigned tm2_ = unsigned(clock());
 #endif
                 if (done > 0) ok = GEMM_WAIT(acc_empty, uint32_t(done - 1) & 1u);
 #ifdef JL_TRACE
-                tw_cvt += clock64() - tm2_;
+                tw_cvt += unsigned(clock()) - tm2_;
 #endif
                 for (int k = 0; k < nstage && ok; ++k) {
 #ifdef JL_TRACE
-                    const long long tm0_ = clock64();
+                    const unsigned tm0_ = unsigned(clock());
 #endif
                     ok = mbar_poll_bounded_u32(full0 + 8u * uint32_t(s), parity);
 #ifdef JL_TRACE
-                    tw_pub += clock64() - tm0_;
+                    tw_pub += unsigned(clock()) - tm0_;
 #endif
                     if (!ok) break;
                     SLOG(256 + (qlog - 8) * 2, lane == 0 && qlog >= 8 && qlog < 24);
@@ -683,7 +685,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     umma_stage_f16_tmem_a<2, 4, 6, kAtom, kAtom + 2, kAtom + 4, kAtom + 6>(
                         tmem_d, a_col, b_lo, desc_hi, idesc, free0 + 8u * uint32_t(s), k == 0 ? 0u : 1u);
                     SLOG(256 + (qlog - 8) * 2 + 1, lane == 0 && qlog >= 8 && qlog < 24);
-#ifdef JL_TRACE
+#ifdef JL_TRACE_EVENTS
                     ++qlog;
 #endif
                     if (++s == ST) {
@@ -774,14 +776,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tok0 = (u % n_tiles) * NT;
           for (int it = 0; it < nraw && *abort_flag == 0u; ++it, ++r, ++i) {
 #ifdef JL_TRACE
-            const long long tq0 = clock64();
+            const unsigned tq0 = unsigned(clock());
+#endif
+#ifdef JL_TRACE_EVENTS
             const bool lgw = (tid == 0 || tid == 256 || tid == 96) && i >= 4 && i < 12;
             const int lg = (tid == 0 ? 0 : (tid == 256 ? 80 : 160)) + (i - 4) * 10;
             SLOG(lg, lgw);
 #endif
             ok = mbar_poll_bounded_u32(raw_full0 + 8u * uint32_t(st), raw_par);
 #ifdef JL_TRACE
-            tw_raw += clock64() - tq0;
+            tw_raw += unsigned(clock()) - tq0;
             SLOG(lg + 1, lgw);
             if (i == 0) trace_mark(trace, 3);
 #endif
@@ -806,11 +810,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     }
                 }
 #ifdef JL_TRACE
-                const long long tq1 = clock64();
+                const unsigned tq1 = unsigned(clock());
 #endif
                 if (rev > 0) ok = mbar_poll_bounded_u32(a_free0 + 8u * uint32_t(s), uint32_t(rev - 1) & 1u);
 #ifdef JL_TRACE
-                tw_free += clock64() - tq1;
+                tw_free += unsigned(clock()) - tq1;
                 SLOG(lg + 2, lgw);
 #endif
                 if (ok) {
@@ -819,11 +823,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     tc_fence_after();  // the stage's previous MMAs are complete (a_free): order the store after them
                     const uint32_t col0 = tm_col0 + uint32_t(s) * kTmemAStageCols;
 #ifdef JL_TRACE
-                    const long long tq4 = clock64();
+                    const unsigned tq4 = unsigned(clock());
 #endif
                     publish();  // the previous stage of this group: its stores were issued a whole conversion ago
 #ifdef JL_TRACE
-                    const long long tq5 = clock64();
+                    const unsigned tq5 = unsigned(clock());
                     tw_pub += tq5 - tq4;
 #endif
                     // (Rows past the end of a matrix, in its bottom tile, need no care: the copy engine
@@ -831,7 +835,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     SLOG(lg + 5, lgw);
                     UnitRegs<TYPE> unit_regs;
                     unit_load<TYPE>(row_u32, 2 * j + a_unit, unit_regs);
-#ifdef JL_TRACE
+#ifdef JL_TRACE_EVENTS
                     if (logging && lgw) {  // the stamp waits for the header arithmetic
                         if constexpr (TYPE == kQ4_K) {
                             if (h2_bits(unit_regs.clo2[1]) == 0x12345678u) slog[500] = 1;
@@ -843,7 +847,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     for (int hf = 0; hf < 2; ++hf) {
                         uint32_t cols[16];
                         unit_convert<TYPE>(unit_regs, hf, cols);
-#ifdef JL_TRACE
+#ifdef JL_TRACE_EVENTS
                         if (logging && lgw) {
                             if (cols[15] == 0x12345678u) slog[501] = 1;
                             slog[lg + 7 + hf] = static_cast<unsigned long long>(clock64());
@@ -852,7 +856,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         tmem_st16(col0 + 16u * hf, cols);
                     }
 #ifdef JL_TRACE
-                    tw_cvt += clock64() - tq5;
+                    tw_cvt += unsigned(clock()) - tq5;
                     SLOG(lg + 3, lgw);
 #endif
                 } else {
@@ -912,12 +916,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 waited = true;
             }
 #ifdef JL_TRACE
-            const long long tq2 = clock64();
+            const unsigned tq2 = unsigned(clock());
 #endif
             ok = GEMM_WAIT(acc_full, uint32_t(done) & 1u);
 #ifdef JL_TRACE
-            tw_acc += clock64() - tq2;
-            const long long tq3 = clock64();
+            tw_acc += unsigned(clock()) - tq2;
+            const unsigned tq3 = unsigned(clock());
 #endif
             if (!ok) break;
             ++done;
@@ -978,14 +982,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 }
             }
 #ifdef JL_TRACE
-            tw_epi += clock64() - tq3;
+            tw_epi += unsigned(clock()) - tq3;
 #endif
             f = seg_end;
         }
 #ifdef JL_TRACE
         trace_mark(trace, 4);
-        trace_word(trace, 6, (static_cast<unsigned long long>(tw_raw) << 32) | static_cast<unsigned long long>(tw_free & 0xffffffffll));
-        trace_word(trace, 7, (static_cast<unsigned long long>(tw_acc) << 32) | static_cast<unsigned long long>(tw_epi & 0xffffffffll));
+        trace_word(trace, 6, (static_cast<unsigned long long>(tw_raw) << 32) | static_cast<unsigned long long>(tw_free));
+        trace_word(trace, 7, (static_cast<unsigned long long>(tw_acc) << 32) | static_cast<unsigned long long>(tw_epi));
         if (tid == 0) {  // this CTA's own sums, in the per-CTA cells
             trace_cta_word(5, 0, static_cast<unsigned long long>(tw_pub));
             trace_cta_word(5, 1, static_cast<unsigned long long>(tw_cvt));
@@ -1004,7 +1008,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     tc_fence_before();
     __syncthreads();
     if (warp == kConvertWarps) tmem_dealloc(tmem_d, tmem_cols);
-#ifdef JL_TRACE
+#ifdef JL_TRACE_EVENTS
     if (logging && tid < 512) trace_log(tid, slog[tid]);
 #endif
     trace_mark(trace, 5);
