@@ -57,17 +57,21 @@ def _run(cmd: list[str], verbose: bool) -> None:
         sys.stderr.write(proc.stderr)
 
 
-def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = False, trace: bool = False) -> Path:
+def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = False, trace: bool = False,
+               trace_events: bool = False) -> Path:
     """Compiles every .cu file to its own object (in parallel) and links the shared library.
 
     trace=True builds ``libjitllm_b200_trace.so`` with -DJL_TRACE: the same kernels plus nanosecond
-    stamps that ``jl_debug_trace`` reads back; the default library carries none of that code."""
+    stamps that ``jl_debug_trace`` reads back; the default library carries none of that code.
+    trace_events=True (with trace) adds -DJL_TRACE_EVENTS: the tensor-core kernel's per-stage event log of one
+    CTA, which costs registers and therefore is no part of the timeline build; always rebuilt."""
     LIB.mkdir(exist_ok=True)
     objdir = PKG / "build" / ("trace" if trace else "release")
     objdir.mkdir(parents=True, exist_ok=True)
     target = LIB / ("libjitllm_b200_trace.so" if trace else "libjitllm_b200.so")
     headers = sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "jitllm_b200.h", Path(__file__)]
-    flags = list(NVCC_FLAGS) + (["-DJL_TRACE"] if trace else [])
+    flags = list(NVCC_FLAGS) + (["-DJL_TRACE"] if trace else []) + (["-DJL_TRACE_EVENTS"] if trace and trace_events else [])
+    force = force or (trace and trace_events)
     if ptxas_info:
         flags += ["-Xptxas", "-v"]
     jobs = []
@@ -115,6 +119,6 @@ if __name__ == "__main__":
     elif "--microbench" in sys.argv:
         build_microbench(verbose=True)
     elif "--trace" in sys.argv:
-        build_cuda(force="--force" in sys.argv, verbose=True, trace=True)
+        build_cuda(force="--force" in sys.argv, verbose=True, trace=True, trace_events="--trace-events" in sys.argv)
     else:
         build_all(force="--force" in sys.argv, verbose=True)
