@@ -44,6 +44,7 @@ ARCHS = {
     "8b4": (4096, 14336, 4, 32, 8, 16384, 4096, False),
 }
 BYTES_PER_EL = {"Q4_K": 144 / 256, "Q4_0": 18 / 32, "Q8_0": 34 / 32}
+EXTRA_BYTES_PER_EL = {"Q4_1": 20 / 32, "Q5_K": 176 / 256, "Q6_K": 210 / 256}  # stand-alone operators only
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up kernel for the 8B layer
 # shape, from one ncu capture of that launch (the summary is kept with the other profile summaries)
@@ -77,6 +78,8 @@ def parse_args():
     ap.add_argument("--profile-op", type=int, default=-1,
                     help="launch one matrix-vector operator (0 qkv, 1 out, 2 gate/up, 3 down, 4 vocab) "
                          "--steps times and exit: the small case ncu captures are taken on")
+    ap.add_argument("--sweep-formats", default="Q8_0,Q4_0,Q4_K,Q4_1,Q5_K,Q6_K",
+                    help="comma-separated formats of --sweep")
     ap.add_argument("--prefill-sweep", action="store_true",
                     help="prompt ingestion rate for prompts of 512, 2048 and 8192 tokens, 1 and 4 sequences (the batched "
                          "prefill configuration; use --format Q8_0): one JSON line per case")
@@ -166,20 +169,23 @@ def op_bytes(cfg, fmt, op, shards=1):
 
 
 def run_sweep(jl, args):
-    """Formats {Q8_0, Q4_0, Q4_K} x shapes x N through jl_gemv_dev with device-resident operands. Each
-    case cycles over enough copies of the matrix to exceed L2 (126 MB), so every launch reads HBM."""
+    """Formats {Q8_0, Q4_0, Q4_K} x shapes x N through jl_gemv_dev with device-resident operands, then the
+    stand-alone mat-vec of Q4_1 / Q5_K / Q6_K at N = 1 and 8. Each case cycles over enough copies of the matrix to
+    exceed L2 (126 MB), so every launch reads HBM."""
     import numpy as np
     dev = jl.Device(0)
     peak, peak_kind = measured_peak()
     shapes = ((4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096))
-    for fmt_name in ("Q8_0", "Q4_0", "Q4_K"):
+    for fmt_name in [f for f in args.sweep_formats.split(",") if f]:
         t = jl.GGMLType[fmt_name]
+        extra = fmt_name in EXTRA_BYTES_PER_EL  # no encoder and no tensor-core path: random blocks, N = 1 and 8
         for rows, cols in shapes:
-            w = jl.synth_tensor(t, rows * cols, seed=args.seed + rows + cols)
-            wbytes = rows * cols * BYTES_PER_EL[fmt_name]
+            w = (jl.random_blocks(t, rows * cols, seed=args.seed + rows + cols) if extra
+                 else jl.synth_tensor(t, rows * cols, seed=args.seed + rows + cols))
+            wbytes = rows * cols * (EXTRA_BYTES_PER_EL if extra else BYTES_PER_EL)[fmt_name]
             copies = int(min(32, max(1, -(-300e6 // wbytes))))
             mats = [dev.upload_matrix(t, w, rows, cols) for _ in range(copies)]
-            for n in (1, 8, 32, 512, 2048):
+            for n in ((1, 8) if extra else (1, 8, 32, 512, 2048)):
                 x = np.random.default_rng(args.seed + n).standard_normal((n, cols)).astype(np.float32)
                 xd, yd = dev.alloc(x.nbytes), dev.alloc(n * rows * 4)
                 dev.h2d(xd, x)
@@ -196,7 +202,7 @@ def run_sweep(jl, args):
                 print(json.dumps({"sweep": fmt_name, "rows": rows, "cols": cols, "n": n, "us": round(us, 2),
                                   "bytes": by, "gbs": round(by / us / 1e3, 1), "hbm_frac": round(by / us / 1e3 / peak, 4),
                                   "tflops": round(2.0 * rows * cols * n / us / 1e6, 2), "peak_kind": peak_kind,
-                                  "kernel": "gemv" if n < 8 else "gemm_tc"}), flush=True)
+                                  "kernel": "gemv_extra" if extra else ("gemv" if n < 8 else "gemm_tc")}), flush=True)
                 dev.free(xd)
                 dev.free(yd)
             for m in mats:

@@ -151,11 +151,14 @@ int32_t jl_debug_read(jl_ctx *ctx, const char *name, int32_t row, float *out, in
 
 /* ---- standalone operators (the sweep of quantised GEMV/GEMM shapes) */
 /* Host blocks in, host floats out: element-exact FloatTensor.getFloat
- * (tensor/standard/Q8_0FloatTensor.java:53-61, Q4_0FloatTensor.java:56-79, Q4_KFloatTensor.java:88-122). */
+ * (tensor/standard/Q8_0FloatTensor.java:53-61, Q4_0FloatTensor.java:56-79, Q4_KFloatTensor.java:88-122, and the
+ * formats mixed-precision files add: Q4_1FloatTensor.java:76-99, Q5_KFloatTensor.java:87-127,
+ * Q6_KFloatTensor.java:64-117). ggml_type: Q4_0=2, Q4_1=3, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14. */
 int32_t jl_dequant(jl_ctx *ctx, int32_t ggml_type, const void *blocks, int64_t n_elements,
                    float *out);
 /* y[n][rows] = W[rows][cols] . x[n][cols]; FloatTensor.matmul (tensor/standard/FloatTensor.java:123-140).
- * Host buffers; copies are part of the call. */
+ * Host buffers; copies are part of the call. The same six types as jl_dequant; Q4_1, Q5_K and Q6_K (at most
+ * 49152 columns) take a stand-alone mat-vec kernel and are not accepted as model tensors by jl_upload_tensor. */
 int32_t jl_gemv(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t cols, const void *w_host,
                 const float *x_host, int32_t n, float *y_host);
 /* Device-resident form: upload once, multiply many times. x_dev / y_dev are device pointers. */

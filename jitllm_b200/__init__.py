@@ -20,6 +20,7 @@ from .api import (  # noqa: F401
     load_model,
     precomputeFreqsCis,
     quantize,
+    random_blocks,
     synth_model_tensors,
     synth_tensor,
 )

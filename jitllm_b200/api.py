@@ -47,16 +47,19 @@ class GGMLType(enum.IntEnum):
     F32 = 0
     F16 = 1
     Q4_0 = 2
+    Q4_1 = 3   # Q4_1, Q5_K, Q6_K: dequantize() and matmul() only, not model tensors
     Q8_0 = 8
     Q4_K = 12
+    Q5_K = 13
+    Q6_K = 14
 
     @property
     def block_size(self) -> int:
-        return {0: 1, 1: 1, 2: 32, 8: 32, 12: 256}[int(self)]
+        return {0: 1, 1: 1, 2: 32, 3: 32, 8: 32, 12: 256, 13: 256, 14: 256}[int(self)]
 
     @property
     def type_size(self) -> int:
-        return {0: 4, 1: 2, 2: 18, 8: 34, 12: 144}[int(self)]
+        return {0: 4, 1: 2, 2: 18, 3: 20, 8: 34, 12: 144, 13: 176, 14: 210}[int(self)]
 
     def byte_size_for(self, n_elements: int) -> int:
         assert n_elements % self.block_size == 0
@@ -555,6 +558,23 @@ def synth_tensor(ggml_type: GGMLType, n_elements: int, seed: int, std: float = 0
     if rc != 0:
         raise ValueError("GPUL-CFG-002: synthetic tensor generation failed")
     return out.view(np.float32) if ggml_type == GGMLType.F32 else out
+
+
+def random_blocks(ggml_type: GGMLType, n_elements: int, seed: int, scale: float = 0.01) -> np.ndarray:
+    """Blocks of any block format with random payload bytes and block scales of magnitude `scale` (a random fp16 bit
+    pattern is often infinite): test and benchmark input for the formats that have no encoder here (Q4_1, Q5_K,
+    Q6_K)."""
+    t = GGMLType(ggml_type)
+    if t.block_size == 1 or n_elements % t.block_size:
+        raise ValueError(f"GPUL-CFG-002: {n_elements} elements are no whole number of {t.name} blocks")
+    n = n_elements // t.block_size
+    rng = np.random.default_rng(seed)
+    raw = rng.integers(0, 256, size=(n, t.type_size), dtype=np.uint8)
+    for off in {GGMLType.Q4_0: (0,), GGMLType.Q8_0: (0,), GGMLType.Q4_1: (0, 2), GGMLType.Q4_K: (0, 2),
+                GGMLType.Q5_K: (0, 2), GGMLType.Q6_K: (208,)}[t]:
+        vals = (rng.uniform(0.2, 1.0, n) * scale * rng.choice([-1.0, 1.0], n)).astype(np.float16)
+        raw[:, off:off + 2] = vals.view(np.uint8).reshape(n, 2)
+    return raw.reshape(-1)
 
 
 def quantize(ggml_type: GGMLType, values: np.ndarray, threads: int = 0) -> np.ndarray:

@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "gemv.cuh"
+#include "gemv_extra.cuh"
 #include "ops.cuh"
 #include "sampler.cuh"
 #include "gemm_tc.cuh"
@@ -230,12 +231,18 @@ bool env_flag(const char *name, bool dflt) {
     return !(v[0] == '0' || v[0] == 'n' || v[0] == 'N' || v[0] == 'f' || v[0] == 'F');
 }
 
-int check_shape(jl_ctx *ctx, int type, int64_t rows, int64_t cols, size_t nbytes) {
+// stand_alone: a matrix for jl_gemv / jl_gemv_dev, which also take Q4_1, Q5_K and Q6_K; the model's tensors
+// (jl_upload_tensor) are held to the formats the step kernels read.
+int check_shape(jl_ctx *ctx, int type, int64_t rows, int64_t cols, size_t nbytes, bool stand_alone = false) {
     JL_REQUIRE(ctx, rows > 0 && cols > 0, JL_ERR_INVALID, "rows and cols must be positive, got %lld x %lld",
                (long long)rows, (long long)cols);
-    JL_REQUIRE(ctx, type == kF32 || type == kF16 || is_quant(type), JL_ERR_UNSUPPORTED,
+    if (is_extra_quant(type) && !stand_alone)
+        return fail(ctx, JL_ERR_UNSUPPORTED,
+                    "GGML type %d (Q4_1=3, Q5_K=13, Q6_K=14) is decoded and multiplied by jl_dequant / jl_gemv only; "
+                    "model tensors must be F32=0, F16=1, Q4_0=2, Q8_0=8 or Q4_K=12", type);
+    JL_REQUIRE(ctx, type == kF32 || type == kF16 || is_quant(type) || is_extra_quant(type), JL_ERR_UNSUPPORTED,
                "GGML type %d (supported: F32=0, F16=1, Q4_0=2, Q8_0=8, Q4_K=12)", type);
-    if (is_quant(type))
+    if (is_quant(type) || is_extra_quant(type))
         JL_REQUIRE(ctx, cols % 256 == 0, JL_ERR_UNSUPPORTED,
                    "quantised rows must be a multiple of 256 columns, got %lld", (long long)cols);
     const int64_t need = rows * row_bytes(type, cols);
@@ -1047,6 +1054,7 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->tev0);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->tev1);
     if (e == cudaSuccess) e = gemv_configure();
+    if (e == cudaSuccess) e = gemv_extra_configure();
     if (e == cudaSuccess) e = attention_configure();
     if (e == cudaSuccess) e = gemm_tc_configure();
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->d_status), sizeof(int));
@@ -1893,12 +1901,13 @@ int32_t jl_dequant(jl_ctx *ctx, int32_t ggml_type, const void *blocks, int64_t n
     JL_REQUIRE(ctx, n_elements >= 0, JL_ERR_INVALID, "n_elements must not be negative");
     if (n_elements == 0) return JL_OK;
     JL_REQUIRE(ctx, blocks && out, JL_ERR_INVALID, "blocks and out must not be NULL");
-    JL_REQUIRE(ctx, is_quant(ggml_type), JL_ERR_UNSUPPORTED, "GGML type %d", ggml_type);
-    const int blk = ggml_type == kQ4_K ? 256 : 32;
+    JL_REQUIRE(ctx, is_quant(ggml_type) || is_extra_quant(ggml_type), JL_ERR_UNSUPPORTED,
+               "GGML type %d (supported: Q4_0=2, Q4_1=3, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14)", ggml_type);
+    const int blk = block_elements(ggml_type);
     JL_REQUIRE(ctx, n_elements % blk == 0, JL_ERR_INVALID,
                "n_elements (%lld) must be a whole number of %d-element blocks", (long long)n_elements, blk);
     cudaSetDevice(ctx->device);
-    const size_t in_bytes = size_t(n_elements / blk) * (ggml_type == kQ4_K ? 144 : ggml_type == kQ8_0 ? 34 : 18);
+    const size_t in_bytes = size_t(row_bytes(ggml_type, n_elements));
     void *d_in = nullptr, *d_out = nullptr;
     int rc;
     if ((rc = dev_alloc(ctx, &d_in, in_bytes))) return rc;
@@ -1927,8 +1936,9 @@ int32_t jl_tensor_upload(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t c
     if (!ctx) return JL_ERR_INVALID;
     JL_REQUIRE(ctx, out != nullptr && host_bytes != nullptr, JL_ERR_INVALID, "NULL argument");
     *out = nullptr;
-    JL_REQUIRE(ctx, is_quant(ggml_type), JL_ERR_UNSUPPORTED, "GGML type %d", ggml_type);
-    int rc = check_shape(ctx, ggml_type, rows, cols, nbytes);
+    JL_REQUIRE(ctx, is_quant(ggml_type) || is_extra_quant(ggml_type), JL_ERR_UNSUPPORTED,
+               "GGML type %d (supported: Q4_0=2, Q4_1=3, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14)", ggml_type);
+    int rc = check_shape(ctx, ggml_type, rows, cols, nbytes, /*stand_alone=*/true);
     if (rc) return rc;
     JL_REQUIRE(ctx, rows <= INT32_MAX && cols <= INT32_MAX, JL_ERR_UNSUPPORTED, "matrix too large");
     cudaSetDevice(ctx->device);
@@ -1963,6 +1973,16 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     JL_REQUIRE(ctx, reinterpret_cast<uintptr_t>(x_dev) % 16 == 0 && reinterpret_cast<uintptr_t>(y_dev) % 16 == 0,
                JL_ERR_INVALID, "x_dev and y_dev must be 16-byte aligned");
     cudaSetDevice(ctx->device);
+    if (is_extra_quant(w->t.type)) {
+        // Q4_1 / Q5_K / Q6_K: one launch for all n rows (weights re-read per row from L2 where they fit).
+        JL_REQUIRE(ctx, w->t.cols <= kGemvExtraMaxCols && n <= 65535, JL_ERR_UNSUPPORTED,
+                   "GGML type %d: at most %d columns and 65535 activation rows", w->t.type, kGemvExtraMaxCols);
+        if (n == 0) return JL_OK;
+        JL_CUDA(ctx, gemv_extra_launch(w->t.type, w->t.data, x_dev, y_dev, int(w->t.rows), int(w->t.cols), n, ctx->sm_count,
+                                       ctx->stream));
+        ctx->counters.kernel_launches += 1;
+        return JL_OK;
+    }
     uint64_t launches = 0;
     static const int gemm_min_n = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
     if (n >= gemm_min_n) {
@@ -1991,7 +2011,8 @@ int32_t jl_gemv(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t cols, cons
     if (!ctx) return JL_ERR_INVALID;
     JL_REQUIRE(ctx, w_host && x_host && y_host, JL_ERR_INVALID, "NULL argument");
     JL_REQUIRE(ctx, n >= 0, JL_ERR_INVALID, "n must not be negative");
-    JL_REQUIRE(ctx, is_quant(ggml_type), JL_ERR_UNSUPPORTED, "GGML type %d", ggml_type);
+    JL_REQUIRE(ctx, is_quant(ggml_type) || is_extra_quant(ggml_type), JL_ERR_UNSUPPORTED,
+               "GGML type %d (supported: Q4_0=2, Q4_1=3, Q8_0=8, Q4_K=12, Q5_K=13, Q6_K=14)", ggml_type);
     JL_REQUIRE(ctx, rows > 0 && cols > 0 && cols % 256 == 0, JL_ERR_UNSUPPORTED,
                "rows must be positive and cols a positive multiple of 256");
     if (n == 0) return JL_OK;

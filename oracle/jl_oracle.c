@@ -106,6 +106,12 @@ uint16_t orc_f32_to_f16(float f) {
 #define Q4_0_BYTES 18
 #define Q4_K_BLOCK 256
 #define Q4_K_BYTES 144
+#define Q4_1_BLOCK 32
+#define Q4_1_BYTES 20
+#define Q5_K_BLOCK 256
+#define Q5_K_BYTES 176
+#define Q6_K_BLOCK 256
+#define Q6_K_BYTES 210
 
 static inline uint16_t rd16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
 
@@ -116,6 +122,9 @@ size_t orc_row_bytes(int type, int64_t cols) {
     case ORC_Q8_0: return (size_t)(cols / Q8_0_BLOCK) * Q8_0_BYTES;
     case ORC_Q4_0: return (size_t)(cols / Q4_0_BLOCK) * Q4_0_BYTES;
     case ORC_Q4_K: return (size_t)(cols / Q4_K_BLOCK) * Q4_K_BYTES;
+    case ORC_Q4_1: return (size_t)(cols / Q4_1_BLOCK) * Q4_1_BYTES;
+    case ORC_Q5_K: return (size_t)(cols / Q5_K_BLOCK) * Q5_K_BYTES;
+    case ORC_Q6_K: return (size_t)(cols / Q6_K_BLOCK) * Q6_K_BYTES;
     default: return 0;
     }
 }
@@ -181,6 +190,67 @@ static inline float q4_k_get(const uint8_t *data, int64_t index) {
     return t - u;
 }
 
+/* Q4_1FloatTensor.getFloat, tensor/standard/Q4_1FloatTensor.java:76-99: block = fp16 scale, fp16
+ * minimum, 16 bytes of nibbles packed like Q4_0; nibble * scale + min with an unsigned nibble
+ * (product rounded, then the sum: Java does not contract). */
+static inline float q4_1_get(const uint8_t *data, int64_t index) {
+    const uint8_t *blk = data + (index / Q4_1_BLOCK) * Q4_1_BYTES;
+    int w = (int)(index % Q4_1_BLOCK);
+    float scale = orc_f16_to_f32(rd16(blk));
+    float min = orc_f16_to_f32(rd16(blk + 2));
+    int nibble = w < 16 ? (blk[4 + w] & 0x0F) : ((blk[4 + w - 16] >> 4) & 0x0F);
+    float t = (float)nibble * scale;
+    return t + min;
+}
+
+/* Q5_KFloatTensor.getFloat, tensor/standard/Q5_KFloatTensor.java:87-127: block = d, dmin, 12 bytes of
+ * 6-bit scales / minima packed as in Q4_K, 32 bytes qh (fifth bits), 128 bytes qs (low four bits).
+ * Element e of pair p = e / 64: low nibble (e % 64 < 32) of qs[32 p + e % 32] with bit 2p of
+ * qh[e % 32], or high nibble with bit 2p + 1; ((d * sc) * q) - (dmin * m). */
+static inline float q5_k_get(const uint8_t *data, int64_t index) {
+    const uint8_t *blk = data + (index / Q5_K_BLOCK) * Q5_K_BYTES;
+    int within = (int)(index % Q5_K_BLOCK);
+    float d = orc_f16_to_f32(rd16(blk));
+    float dmin = orc_f16_to_f32(rd16(blk + 2));
+    const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;
+    int pair = within / 64, pos = within % 64;
+    int sub, q, high;
+    if (pos < 32) {
+        sub = pair * 2;
+        q = qs[pair * 32 + pos] & 0xF;
+        high = (qh[pos] >> (pair * 2)) & 1;
+    } else {
+        sub = pair * 2 + 1;
+        q = (qs[pair * 32 + pos - 32] >> 4) & 0xF;
+        high = (qh[pos - 32] >> (pair * 2 + 1)) & 1;
+    }
+    q += high * 16;
+    float t = d * (float)q4k_scale(sub, scales);
+    t = t * (float)q;
+    float u = dmin * (float)q4k_min(sub, scales);
+    return t - u;
+}
+
+/* Q6_KFloatTensor.getFloat, tensor/standard/Q6_KFloatTensor.java:64-117: block = 128 bytes ql, 64 bytes
+ * qh, 16 signed byte scales, fp16 d. Half h = e / 128, group g = (e % 128) / 32, position p = e % 32:
+ * low four bits from ql[64 h + 32 (g & 1) + p] (low nibble for g < 2, high nibble otherwise), top two
+ * bits from qh[32 h + p] >> 2 g, value minus 32; scale index 8 h + 2 g + p / 16;
+ * (d * scale) * q left to right. */
+static inline float q6_k_get(const uint8_t *data, int64_t index) {
+    const uint8_t *blk = data + (index / Q6_K_BLOCK) * Q6_K_BYTES;
+    int within = (int)(index % Q6_K_BLOCK);
+    float d = orc_f16_to_f32(rd16(blk + 208));
+    int half = within / 128, in_half = within % 128;
+    int group = in_half / 32, pos = in_half % 32;
+    const uint8_t *ql = blk + half * 64, *qh = blk + 128 + half * 32;
+    const int8_t *sc = (const int8_t *)(blk + 192 + half * 8);
+    int lo = ql[(group & 1) * 32 + pos];
+    lo = group < 2 ? (lo & 0xF) : (lo >> 4);
+    int q = (lo | (((qh[pos] >> (2 * group)) & 3) << 4)) - 32;
+    float t = d * (float)sc[pos / 16 + 2 * group];
+    return t * (float)q;
+}
+
 float orc_get_float(int type, const void *data, int64_t index) {
     const uint8_t *p = (const uint8_t *)data;
     switch (type) {
@@ -189,6 +259,9 @@ float orc_get_float(int type, const void *data, int64_t index) {
     case ORC_Q8_0: return q8_0_get(p, index);
     case ORC_Q4_0: return q4_0_get(p, index);
     case ORC_Q4_K: return q4_k_get(p, index);
+    case ORC_Q4_1: return q4_1_get(p, index);
+    case ORC_Q5_K: return q5_k_get(p, index);
+    case ORC_Q6_K: return q6_k_get(p, index);
     default: return NAN;
     }
 }
@@ -369,6 +442,59 @@ static float q4_0_vector_dot(const uint8_t *data, int64_t off, const float *x, i
     return result;
 }
 
+/* Q4_1FloatTensor.vectorDot, tensor/standard/Q4_1FloatTensor.java:110-192: per block the lanes carry
+ * the products with the unsigned nibbles and the plain sum of the activations;
+ * val = fma(products, scale, val), then val = fma(activations, min, val). */
+static float q4_1_vector_dot(const uint8_t *data, int64_t off, const float *x, int64_t size, int bits) {
+    float result = 0.f;
+    int64_t j = 0;
+    int64_t align = (-off) & (Q4_1_BLOCK - 1);
+    if (align > size) align = size;
+    if (align > 0) {
+        result += scalar_dot(ORC_Q4_1, data, off, x, align);
+        j += align;
+    }
+    int lanes = bits / 32;
+    float val[8] = {0};
+    const uint8_t *blk = data + ((off + j) / Q4_1_BLOCK) * Q4_1_BYTES;
+    int64_t upper = size / Q4_1_BLOCK * Q4_1_BLOCK;
+    for (; j < upper; j += Q4_1_BLOCK, blk += Q4_1_BYTES) {
+        float scale = orc_f16_to_f32(rd16(blk));
+        float min = orc_f16_to_f32(rd16(blk + 2));
+        float w[32];
+        for (int i = 0; i < 16; i++) {
+            w[i] = (float)(blk[4 + i] & 0xF);
+            w[16 + i] = (float)(blk[4 + i] >> 4);
+        }
+        if (bits == 256) {
+            for (int l = 0; l < 8; l++) {
+                float x0 = x[j + l], x1 = x[j + 8 + l], x2 = x[j + 16 + l], x3 = x[j + 24 + l];
+                float s0 = x0 * w[l], s1 = x1 * w[8 + l], s2 = x2 * w[16 + l], s3 = x3 * w[24 + l];
+                float products = ((s0 + s1) + s2) + s3;
+                float activations = ((x0 + x1) + x2) + x3;
+                val[l] = fmaf(products, scale, val[l]);
+                val[l] = fmaf(activations, min, val[l]);
+            }
+        } else {
+            for (int i = 0; i < 2; i++) {
+                for (int l = 0; l < 4; l++) {
+                    float x0 = x[j + (i * 4 + 0) * 4 + l], x1 = x[j + (i * 4 + 1) * 4 + l];
+                    float x2 = x[j + (i * 4 + 2) * 4 + l], x3 = x[j + (i * 4 + 3) * 4 + l];
+                    float s0 = x0 * w[i * 16 + l], s1 = x1 * w[i * 16 + 4 + l];
+                    float s2 = x2 * w[i * 16 + 8 + l], s3 = x3 * w[i * 16 + 12 + l];
+                    float products = ((s0 + s1) + s2) + s3;
+                    float activations = ((x0 + x1) + x2) + x3;
+                    val[l] = fmaf(products, scale, val[l]);
+                    val[l] = fmaf(activations, min, val[l]);
+                }
+            }
+        }
+    }
+    result += reduce_lanes(val, lanes);
+    if (j < size) result += scalar_dot(ORC_Q4_1, data, off + j, x + j, size - j);
+    return result;
+}
+
 float orc_dot(int type, const void *data, int64_t this_offset, const float *x, int64_t size) {
     const uint8_t *p = (const uint8_t *)data;
     /* Q8_0FloatTensor.java:90-99, Q4_0FloatTensor.java:82-88: vector path only for 128/256-bit
@@ -376,6 +502,7 @@ float orc_dot(int type, const void *data, int64_t this_offset, const float *x, i
     if (g_vector_bits != 0) {
         if (type == ORC_Q8_0) return q8_0_vector_dot(p, this_offset, x, size, g_vector_bits);
         if (type == ORC_Q4_0) return q4_0_vector_dot(p, this_offset, x, size, g_vector_bits);
+        if (type == ORC_Q4_1) return q4_1_vector_dot(p, this_offset, x, size, g_vector_bits);
     }
     return scalar_dot(type, p, this_offset, x, size);
 }
@@ -412,8 +539,10 @@ static void scalar_rows8(int type, const uint8_t *w, size_t row_bytes, const flo
 static void matmul_rows(int type, const uint8_t *w, const float *x, float *out, int r0, int r1,
                         int cols) {
     size_t rb = orc_row_bytes(type, cols);
-    int blocked = (type == ORC_Q8_0 || type == ORC_Q4_0 || type == ORC_Q4_K) &&
-                  (g_vector_bits == 0 || type == ORC_Q4_K);
+    /* Q5_KFloatTensor.java:129-131 and Q6_KFloatTensor.java:119-121 always take scalarDot, like Q4_K. */
+    int always_scalar = type == ORC_Q4_K || type == ORC_Q5_K || type == ORC_Q6_K;
+    int blocked = (type == ORC_Q8_0 || type == ORC_Q4_0 || type == ORC_Q4_1 || always_scalar) &&
+                  (g_vector_bits == 0 || always_scalar);
     if (blocked) {
         for (int r = r0; r < r1; r += RB) {
             int n = r1 - r < RB ? r1 - r : RB;

@@ -30,7 +30,7 @@ extern "C" {
 #endif
 
 /* GGML type ids, format/GGMLType.java:7,13,18-20 (same numbering as the GGUF file format). */
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q8_0 = 8, ORC_Q4_K = 12 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q5_K = 13, ORC_Q6_K = 14 };
 
 /* Summation mode of the quantised dot products, tensor/standard/FloatTensor.java:22-36:
  * 0 = scalar sequential (also what a 512-bit host gets), 128 / 256 = FloatVector lanes. */

@@ -43,3 +43,10 @@ class Pair:
 
     def new_oracle_sequence(self):
         return self._oracle.Model(self.config, self.tensors)
+
+
+def random_blocks(t, n_blocks, rng, scale=0.01):
+    """Random payload bytes with block scales of a sane magnitude (a fully random fp16 scale is often
+    infinite or NaN, which tests nothing but overflow in a dot product)."""
+    t = jl.GGMLType(t)
+    return jl.random_blocks(t, n_blocks * t.block_size, int(rng.integers(0, 2**31)), scale)
