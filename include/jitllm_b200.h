@@ -41,8 +41,13 @@ typedef enum {
     JL_ERR_UNSUPPORTED = 6  /* GPUL-CFG-002: format or shape this build does not handle */
 } jl_status;
 
-/* GGML type ids as stored in GGUF (format/GGMLType.java:7,13,18-20). */
-typedef enum { JL_F32 = 0, JL_F16 = 1, JL_Q4_0 = 2, JL_Q8_0 = 8, JL_Q4_K = 12 } jl_ggml_type;
+/* GGML type ids as stored in GGUF (format/GGMLType.java:7-30). Q4_0, Q8_0 and Q4_K matrices run on the fused
+ * single-row kernels and the tensor-core kernel; Q4_1, Q5_K and Q6_K, which mixed-precision files add for some
+ * tensors, are decoded element-exactly and multiplied by a mat-vec kernel of their own: a model that holds one
+ * takes the row path for every step (one GPU only) and is correct but slower on those matrices. */
+typedef enum {
+    JL_F32 = 0, JL_F16 = 1, JL_Q4_0 = 2, JL_Q4_1 = 3, JL_Q8_0 = 8, JL_Q4_K = 12, JL_Q5_K = 13, JL_Q6_K = 14
+} jl_ggml_type;
 
 /* Tensor roles: the subset of runtime/tensor/TensorRole.java:17-59 a Llama file uses; this is
  * the key of TornadoWeights.tensor(role, layer) (inference/weights/tornado/TornadoWeights.java:95-109). */
@@ -158,7 +163,7 @@ int32_t jl_dequant(jl_ctx *ctx, int32_t ggml_type, const void *blocks, int64_t n
                    float *out);
 /* y[n][rows] = W[rows][cols] . x[n][cols]; FloatTensor.matmul (tensor/standard/FloatTensor.java:123-140).
  * Host buffers; copies are part of the call. The same six types as jl_dequant; Q4_1, Q5_K and Q6_K (at most
- * 49152 columns) take a stand-alone mat-vec kernel and are not accepted as model tensors by jl_upload_tensor. */
+ * 49152 columns) take a mat-vec kernel of their own at every n. */
 int32_t jl_gemv(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t cols, const void *w_host,
                 const float *x_host, int32_t n, float *y_host);
 /* Device-resident form: upload once, multiply many times. x_dev / y_dev are device pointers. */

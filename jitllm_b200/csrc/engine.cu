@@ -60,6 +60,9 @@ struct jl_ctx {
     bool use_graph = true, use_pdl = true;
 
     bool has_model = false, finalized = false;
+    // The model holds a Q4_1 / Q5_K / Q6_K matrix, or Q/K/V (gate/up) of different types: every step, single rows
+    // included, takes the row path, whose projections are launched one matrix at a time.
+    bool mixed = false;
     jl_model_desc desc = {};
     int kv_dim = 0;
     DevTensor global[JL_ROLE_COUNT];
@@ -670,6 +673,24 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
 
 int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
                 uint64_t *launches, int in_kind = -1, bool presplit = false) {
+    if (is_extra_quant(w.type)) {
+        // Q4_1 / Q5_K / Q6_K: the stand-alone mat-vec over the n fp32 rows (every producer of the row path writes
+        // them beside the binary16 parts); a residual is added by a row kernel, through the spare row buffer.
+        if (res != nullptr && (res != y || ctx->part == nullptr || int(w.rows) != ctx->desc.dim))
+            return fail(ctx, JL_ERR_UNSUPPORTED, "residual of a type %d projection", w.type);
+        if (w.cols > kGemvExtraMaxCols)
+            return fail(ctx, JL_ERR_UNSUPPORTED, "type %d matrices are limited to %d columns", w.type, kGemvExtraMaxCols);
+        float *dst = res != nullptr ? ctx->part : y;
+        cudaError_t e = gemv_extra_launch(w.type, w.data, x, dst, int(w.rows), int(w.cols), n, ctx->sm_count, ctx->stream);
+        if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-vector launch failed: %s", cudaGetErrorString(e));
+        ++*launches;
+        if (res != nullptr) {
+            e = add_rows_launch(y, ctx->part, size_t(n) * w.rows, ctx->stream, ctx->use_pdl);
+            if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "residual launch failed: %s", cudaGetErrorString(e));
+            ++*launches;
+        }
+        return JL_OK;
+    }
     const DevTensor *ws[1] = {&w};
     float *ys[1] = {y};
     const float *rs[1] = {res};
@@ -711,7 +732,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             const DevTensor *ws[3] = {&ctx->layer[JL_ROLE_ATTENTION_QUERY][l], &ctx->layer[JL_ROLE_ATTENTION_KEY][l],
                                       &ctx->layer[JL_ROLE_ATTENTION_VALUE][l]};
             float *ys[3] = {ctx->q, ctx->k, ctx->v};
-            const bool same = ws[0]->type == ws[1]->type && ws[0]->type == ws[2]->type;
+            const bool same = ws[0]->type == ws[1]->type && ws[0]->type == ws[2]->type && !is_extra_quant(ws[0]->type);
             if (same) {
                 if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 3, ctx->xb, n, launches, 0, true))) return rc;
             } else {
@@ -773,7 +794,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
         {
             const DevTensor *ws[2] = {&ctx->layer[JL_ROLE_FFN_GATE][l], &ctx->layer[JL_ROLE_FFN_UP][l]};
             float *ys[2] = {ctx->hb, ctx->hb2};
-            if (ws[0]->type == ws[1]->type) {
+            if (ws[0]->type == ws[1]->type && !is_extra_quant(ws[0]->type)) {
                 if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 2, ctx->xb, n, launches, 0, true))) return rc;
             } else {
                 for (int i = 0; i < 2; ++i)
@@ -961,7 +982,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
 // Runs one step: replays the captured graph for this width, capturing it on first use.
 int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
     static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 4; }();
-    const bool rows_path = width >= rows_min;
+    const bool rows_path = width >= rows_min || ctx->mixed;
     const int key = width * 8 + (with_logits ? 1 : 0) + (advance ? 2 : 0) + (rows_path ? 4 : 0);
     uint64_t launches = 0;
     // Under tensor parallelism the first step of each shape runs uncaptured, so that NCCL sets up
@@ -1222,9 +1243,10 @@ int32_t jl_upload_tensor(jl_ctx *ctx, int32_t role, int32_t layer, int32_t ggml_
         JL_REQUIRE(ctx, ggml_type == kF32, JL_ERR_UNSUPPORTED, "norm weights must be F32, got type %d",
                    ggml_type);
     else
-        JL_REQUIRE(ctx, is_quant(ggml_type), JL_ERR_UNSUPPORTED,
-                   "matrix role %d must be Q8_0, Q4_0 or Q4_K, got type %d", role, ggml_type);
-    int rc = check_shape(ctx, ggml_type, rows, cols, nbytes);
+        JL_REQUIRE(ctx, is_quant(ggml_type) || (is_extra_quant(ggml_type) && ctx->tp_size == 1), JL_ERR_UNSUPPORTED,
+                   "matrix role %d must be Q8_0, Q4_0 or Q4_K (on one GPU also Q4_1, Q5_K or Q6_K), got type %d", role,
+                   ggml_type);
+    int rc = check_shape(ctx, ggml_type, rows, cols, nbytes, /*stand_alone=*/true);
     if (rc) return rc;
     cudaSetDevice(ctx->device);
     drop_graphs(ctx);
@@ -1277,6 +1299,7 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
                                               emb.type, ctx->l_vocab, emb.cols));
         }
     }
+    bool mixed = false;
     static const int per_layer_roles[] = {JL_ROLE_ATTENTION_NORM,  JL_ROLE_ATTENTION_QUERY,
                                           JL_ROLE_ATTENTION_KEY,   JL_ROLE_ATTENTION_VALUE,
                                           JL_ROLE_ATTENTION_OUTPUT, JL_ROLE_FFN_NORM,
@@ -1285,13 +1308,21 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     for (int l = 0; l < d.layers; ++l) {
         for (int r : per_layer_roles)
             JL_REQUIRE(ctx, ctx->layer[r][l].data, JL_ERR_STATE, "layer %d is missing tensor role %d", l, r);
+        // The fused single-row kernels want Q, K, V (and gate, up) in one of their three formats and alike; a
+        // layer that is not makes the whole model take the row path (one GPU only).
         const int tq = ctx->layer[JL_ROLE_ATTENTION_QUERY][l].type;
-        JL_REQUIRE(ctx, ctx->layer[JL_ROLE_ATTENTION_KEY][l].type == tq &&
-                            ctx->layer[JL_ROLE_ATTENTION_VALUE][l].type == tq,
-                   JL_ERR_UNSUPPORTED, "layer %d: Q, K and V must share one quantisation type", l);
-        JL_REQUIRE(ctx, ctx->layer[JL_ROLE_FFN_GATE][l].type == ctx->layer[JL_ROLE_FFN_UP][l].type,
-                   JL_ERR_UNSUPPORTED, "layer %d: gate and up must share one quantisation type", l);
+        if (ctx->layer[JL_ROLE_ATTENTION_KEY][l].type != tq || ctx->layer[JL_ROLE_ATTENTION_VALUE][l].type != tq ||
+            ctx->layer[JL_ROLE_FFN_GATE][l].type != ctx->layer[JL_ROLE_FFN_UP][l].type)
+            mixed = true;
+        for (int r : per_layer_roles)
+            if (is_extra_quant(ctx->layer[r][l].type)) mixed = true;
     }
+    if (is_extra_quant(ctx->global[JL_ROLE_TOKEN_EMBEDDING].type) ||
+        (ctx->global[JL_ROLE_OUTPUT].data && is_extra_quant(ctx->global[JL_ROLE_OUTPUT].type)))
+        mixed = true;
+    JL_REQUIRE(ctx, !mixed || ctx->tp_size == 1, JL_ERR_UNSUPPORTED,
+               "tensor parallelism needs Q, K, V (gate, up) of one type per layer and no Q4_1 / Q5_K / Q6_K matrices");
+    ctx->mixed = mixed;
     if (ctx->finalized) return JL_OK;
     cudaSetDevice(ctx->device);
     const size_t B = d.max_batch;
@@ -1330,6 +1361,7 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
             JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[2][i], ctx->hb16, R, ctx->l_hidden, nts[i]));
         }
     }
+    if (ctx->mixed && (rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;
     if (ctx->tp_size > 1) {
         JL_REQUIRE(ctx, ctx->nccl_comm != nullptr, JL_ERR_STATE, "jl_tp_init must come before jl_model_finalize");
         if ((rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;

@@ -132,6 +132,9 @@ int64_t type_row_bytes(int type, uint64_t cols) {
         case JL_Q4_0: return int64_t(cols / 32) * 18;
         case JL_Q8_0: return int64_t(cols / 32) * 34;
         case JL_Q4_K: return int64_t(cols / 256) * 144;
+        case JL_Q4_1: return int64_t(cols / 32) * 20;
+        case JL_Q5_K: return int64_t(cols / 256) * 176;
+        case JL_Q6_K: return int64_t(cols / 256) * 210;
         default: return -1;
     }
 }

@@ -38,7 +38,8 @@ def test_decode_bit_exactly(dev, oracle, t):
 
 
 @pytest.mark.parametrize("t", EXTRA)
-@pytest.mark.parametrize("rows,cols,n", [(4096, 4096, 1), (1000, 14336, 1), (37, 256, 1), (512, 2048, 3)])
+@pytest.mark.parametrize("rows,cols,n", [(4096, 4096, 1), (1000, 14336, 1), (37, 256, 1), (512, 2048, 3), (300, 1024, 5), (256, 4096, 9),
+                                         (64, 14336, 4), (128, 6144, 2)])
 def test_matvec_against_the_oracle(dev, oracle, t, rows, cols, n):
     rng = np.random.default_rng(rows + cols + int(t))
     w = random_blocks(t, rows * cols // t.block_size, rng)
@@ -61,13 +62,15 @@ def test_device_resident_matvec_repeats_bit_identically(dev, oracle, t):
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
-def test_model_tensors_refuse_the_extra_formats():
-    cfg = jl.Configuration(dim=256, hiddenDim=512, numberOfLayers=1, numberOfHeads=4, numberOfKeyValueHeads=2,
+def test_tensor_parallel_models_refuse_the_extra_formats():
+    """One GPU runs such tensors through the row path (tests/test_gpu_mixed_formats.py); a shard of a tensor-parallel
+    model does not take them."""
+    cfg = jl.Configuration(dim=512, hiddenDim=1024, numberOfLayers=1, numberOfHeads=4, numberOfKeyValueHeads=2,
                            vocabularySize=256, contextLength=32)
     with jl.Device(0) as own:
-        model = jl.B200Model(own, cfg)
-        raw = np.zeros(256 * 256 // 256 * 210, dtype=np.uint8)
-        with pytest.raises(ValueError, match="GPUL-CFG-002: unsupported"):
+        model = jl.B200Model(own, cfg, tp=jl.TensorParallel(rank=0, size=2))
+        raw = np.zeros(256 * 512 // 256 * 210, dtype=np.uint8)  # this rank's half of the query rows
+        with pytest.raises(ValueError, match="GPUL-CFG-002: unsupported.*on one GPU"):
             model.uploadTensor(jl.TensorRole.ATTENTION_QUERY, 0, GGMLType.Q6_K, raw, presharded=True)
 
 

@@ -1,0 +1,66 @@
+"""A model whose tensors mix the step kernels' formats with Q4_1 / Q5_K / Q6_K (what mixed-precision files do for
+the value, down and output projections) against the oracle's forwardJava: every step takes the row path, logits
+within the stated 1e-2 max-abs bar, identical greedy tokens."""
+import numpy as np
+import pytest
+
+import jitllm_b200 as jl
+from jitllm_b200 import GGMLType, TensorRole
+from tests.util import Pair, small_config
+
+pytestmark = pytest.mark.gpu
+LOGIT_BAR = 1e-2
+LOGIT_EXPECT = 6e-3  # the row path's binary16 hi + lo activations and weights, as for wide batches
+SCALES = {GGMLType.Q4_1: 4e-3, GGMLType.Q5_K: 4e-5, GGMLType.Q6_K: 3e-5}  # weights of the magnitude of N(0, 0.05)
+
+
+def _mixed(cfg, seed):
+    """Replacement tensors: value and down projections in Q6_K / Q5_K / Q4_1 by layer, the output matrix Q6_K."""
+    out = {}
+    kinds = [GGMLType.Q6_K, GGMLType.Q5_K, GGMLType.Q4_1]
+    for l in range(cfg.numberOfLayers):
+        for j, role in enumerate((TensorRole.ATTENTION_VALUE, TensorRole.FFN_DOWN)):
+            t = kinds[(l + j) % 3]
+            rows, cols = cfg.matrix_shape(role)
+            out[(role, l)] = (t, jl.random_blocks(t, rows * cols, seed + 10 * l + j, SCALES[t]))
+    rows, cols = cfg.matrix_shape(TensorRole.OUTPUT)
+    out[(TensorRole.OUTPUT, -1)] = (GGMLType.Q6_K, jl.random_blocks(GGMLType.Q6_K, rows * cols, seed + 99, SCALES[GGMLType.Q6_K]))
+    return out
+
+
+@pytest.mark.parametrize("head", [64, 128])
+def test_single_sequence_logits_and_tokens(dev, oracle, head):
+    cfg = small_config(layers=3, ctx=64, head=head)
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=31 + head, std=0.05, replace=_mixed(cfg, 500 + head))
+    tokens = np.random.default_rng(6).integers(0, cfg.vocabularySize, size=24)
+    worst = 0.0
+    for pos, tok in enumerate(tokens):
+        want = p.oracle_model.forward(int(tok), pos)
+        res = p.boundary.invoke(int(tok), pos)
+        err = float(np.max(np.abs(res.logits - want)))
+        worst = max(worst, err)
+        assert err < LOGIT_BAR and err < LOGIT_EXPECT, (pos, err)
+        assert res.sampledToken == int(np.argmax(want))
+    assert worst > 0.0  # the two paths are different programs; identical logits would mean one of them did not run
+
+
+def test_batch_of_sequences_and_prompt_path(dev, oracle):
+    cfg = small_config(layers=2, ctx=96)
+    B = 5
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=77, std=0.05, max_batch=B, replace=_mixed(cfg, 700))
+    rng = np.random.default_rng(8)
+    # sequence 0 ingests a prompt through the prompt path, the others start empty
+    prompt = rng.integers(0, cfg.vocabularySize, size=20)
+    seqs = [p.new_oracle_sequence() for _ in range(B)]
+    for pos, tok in enumerate(prompt[:-1]):
+        seqs[0].forward(int(tok), pos)
+    jl.B200InvocationBoundary(p.model, kvSlot=0, copyLogits=False).prefill([int(v) for v in prompt[:-1]], 0)
+    positions = np.array([len(prompt) - 1] + [0] * (B - 1), dtype=np.int32)
+    tokens = np.array([prompt[-1]] + list(rng.integers(0, cfg.vocabularySize, size=B - 1)), dtype=np.int32)
+    for step in range(10):
+        slots = jl.BatchSlots(np.ones(B, dtype=bool), tokens.copy(), positions.copy(), np.arange(B, dtype=np.int32))
+        got = p.executor.decodeStep(slots)
+        want = [int(np.argmax(seqs[b].forward(int(tokens[b]), int(positions[b])))) for b in range(B)]
+        assert list(got) == want, step
+        tokens = np.array(want, dtype=np.int32)
+        positions += 1

@@ -23,9 +23,12 @@ class Pair:
     """The same synthetic model on the oracle and on the GPU, sharing weight bytes and RoPE tables."""
 
     def __init__(self, dev, oracle, config, ggml_type, seed, max_batch=1, slots=None, block_tokens=16,
-                 block_table=None, total_blocks=None, std=0.02):
+                 block_table=None, total_blocks=None, std=0.02, replace=None):
         self.config = config
         self.tensors = jl.synth_model_tensors(config, ggml_type, seed, std=std)
+        for key, value in (replace or {}).items():  # {(role, layer): (type, bytes)}: tensors in another format
+            assert key in self.tensors
+            self.tensors[key] = value
         self.oracle_model = oracle.Model(config, self.tensors)
         cr, ci = self.oracle_model.rope_tables()
         self.model = jl.load_model(dev, config, self.tensors, cr, ci, maxBatch=max_batch)
