@@ -80,6 +80,8 @@ def parse_args():
                          "--steps times and exit: the small case ncu captures are taken on")
     ap.add_argument("--sweep-formats", default="Q8_0,Q4_0,Q4_K,Q4_1,Q5_K,Q6_K",
                     help="comma-separated formats of --sweep")
+    ap.add_argument("--sweep-shapes", default="4096x4096,14336x4096,4096x14336,128256x4096",
+                    help="comma-separated rows x cols of --sweep")
     ap.add_argument("--prefill-sweep", action="store_true",
                     help="prompt ingestion rate for prompts of 512, 2048 and 8192 tokens, 1 and 4 sequences (the batched "
                          "prefill configuration; use --format Q8_0): one JSON line per case")
@@ -175,7 +177,7 @@ def run_sweep(jl, args):
     import numpy as np
     dev = jl.Device(0)
     peak, peak_kind = measured_peak()
-    shapes = ((4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096))
+    shapes = tuple(tuple(int(v) for v in sh.split("x")) for sh in args.sweep_shapes.split(",") if sh)
     for fmt_name in [f for f in args.sweep_formats.split(",") if f]:
         t = jl.GGMLType[fmt_name]
         extra = fmt_name in EXTRA_BYTES_PER_EL  # no encoder and no tensor-core path: random blocks, N = 1 and 8
