@@ -82,6 +82,8 @@ def parse_args():
                     help="comma-separated formats of --sweep")
     ap.add_argument("--sweep-shapes", default="4096x4096,14336x4096,4096x14336,128256x4096",
                     help="comma-separated rows x cols of --sweep")
+    ap.add_argument("--mixed", action="store_true",
+                    help="Q6_K value / down projections (every other layer) and output matrix, as in a mixed-precision file")
     ap.add_argument("--prefill-sweep", action="store_true",
                     help="prompt ingestion rate for prompts of 512, 2048 and 8192 tokens, 1 and 4 sequences (the batched "
                          "prefill configuration; use --format Q8_0): one JSON line per case")
@@ -307,6 +309,55 @@ def run_prefill_sweep(jl, args):
     return 0
 
 
+def run_mixed(jl, args):
+    """Decode rate of a model with the tensor mix of a mixed-precision file next to the same model in one format:
+    the value and down projections of every other layer and the output matrix in Q6_K (random payloads of
+    weight-like magnitude: there is no Q6_K encoder here). One JSON line."""
+    import numpy as np
+    dims = ARCHS[args.arch]
+    cfg = jl.Configuration(dim=dims[0], hiddenDim=dims[1], numberOfLayers=dims[2], numberOfHeads=dims[3],
+                           numberOfKeyValueHeads=dims[4], vocabularySize=dims[5], contextLength=dims[6],
+                           tiedEmbeddings=dims[7])
+    B, P, K = args.batch, args.prompt, max(args.steps, 4)
+    base = jl.synth_model_tensors(cfg, jl.GGMLType[args.format], args.seed, threads=os.cpu_count())
+    R, Q6 = jl.TensorRole, jl.GGMLType.Q6_K
+    mixed = dict(base)
+    q6_bytes = 0
+    for (role, layer) in list(mixed):
+        if (role in (R.ATTENTION_VALUE, R.FFN_DOWN) and layer % 2 == 0) or role == R.OUTPUT:
+            rows, cols = cfg.matrix_shape(role)
+            mixed[(role, layer)] = (Q6, jl.random_blocks(Q6, rows * cols, args.seed + 31 * layer + int(role), 3e-5))
+            q6_bytes += mixed[(role, layer)][1].size
+    cr, ci = jl.precomputeFreqsCis(cfg.contextLength, cfg.headSize, cfg.ropeTheta)
+    out = {}
+    for name, tensors in (("one_format", base), ("mixed", mixed)):
+        dev = jl.Device(0)
+        model = jl.load_model(dev, cfg, tensors, cr, ci, maxBatch=B)
+        bps = cfg.contextLength // 16
+        need = (P + 2 * K + 24 + 15) // 16
+        kv = model.createKvStorage(jl.KvStorageRequest(B * need, bps, B, 16, cfg.numberOfLayers, cfg.kvDim))
+        table = np.full(B * bps, jl.UNMAPPED, dtype=np.int32)
+        for b in range(B):
+            table[b * bps:b * bps + need] = np.arange(b * need, (b + 1) * need)
+        kv.publishBlockTable(table)
+        ex = jl.B200BatchExecutor(model)
+        prompts = np.random.default_rng(args.seed).integers(0, cfg.vocabularySize, size=(B, P))
+        for b in range(B):
+            jl.B200InvocationBoundary(model, kvSlot=b, copyLogits=False).prefill(prompts[b, :P - 1], 0)
+        slots, active = list(range(B)), [True] * B
+        hist = ex.generate(jl.BatchSlots(active, [int(t) for t in prompts[:, P - 1]], [P - 1] * B, slots), 4)
+        dev.synchronize()
+        dev.timer_start()
+        ex.generate(jl.BatchSlots(active, [int(t) for t in hist[-1]], [P + 3] * B, slots), K)
+        ms = dev.timer_stop() / K
+        out[name] = {"ms_per_step": round(ms, 4), "tok_s": round(B * 1000.0 / ms, 1)}
+        kv.close()
+        dev.close()
+    print(json.dumps({"mixed_formats": {"arch": args.arch, "format": args.format, "batch": B, "prompt": P, "steps": K,
+                                        "q6_k_bytes": q6_bytes, **out}}), flush=True)
+    return 0
+
+
 def run_timeline(jl, args):
     """One decode step of --batch sequences as a table of launches, from the stamps the trace build of the
     library leaves (first CTA of every launch: entry, dependency resolved, operands staged, loop done, exit)."""
@@ -383,6 +434,8 @@ def main():
         return run_timeline(jl, args) if rank == 0 else 0
     if args.prefill_sweep:
         return run_prefill_sweep(jl, args) if rank == 0 else 0
+    if args.mixed:
+        return run_mixed(jl, args) if rank == 0 else 0
     if args.profile_matmul:
         if rank != 0:
             return 0

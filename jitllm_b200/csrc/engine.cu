@@ -633,8 +633,35 @@ int attn_splits_for_width(const jl_ctx *ctx, int width) {
 // One tensor-core launch over up to three matrices that share the input rows.
 // in_kind: which pre-split activation buffer x is mirrored in (0 xb by dim, 1 xb by the local query
 // width, 2 hb by the local hidden width), or -1 to let the kernel convert x itself.
+// Batches of at least this many rows, and prompt chunks, take the tensor-core projections.
+int gemm_min_width() {
+    static const int v = [] { const char *e = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return e ? atoi(e) : 4; }();
+    return v;
+}
+
 int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, const float *const *res, int nseg,
                      const float *x, int n, uint64_t *launches, int in_kind = -1, bool presplit = false) {
+    if (ctx->mixed && n < gemm_min_width()) {
+        // A mixed-format model takes the row path for narrow steps too: there its Q4_0 / Q8_0 / Q4_K matrices
+        // are better served by the mat-vec kernel, one launch per row (plain mode: the norm, SwiGLU and arg-max
+        // around it are row kernels on this path; the residual stays in its epilogue).
+        int total = 0;
+        for (int s = 0; s < nseg; ++s) total += int(w[s]->rows);
+        for (int b = 0; b < n; ++b) {
+            GemvArgs a = {};
+            a.nseg = nseg;
+            for (int s = 0; s < nseg; ++s)
+                a.seg[s] = {w[s]->data, y[s] + size_t(b) * w[s]->rows,
+                            res != nullptr && res[s] != nullptr ? res[s] + size_t(b) * w[s]->rows : nullptr, int(w[s]->rows)};
+            a.cols = int(w[0]->cols);
+            a.type = w[0]->type;
+            a.mode = kGemvPlain;
+            a.x = x + size_t(b) * w[0]->cols;
+            int rc = launch_gemv(ctx, a, total, launches);
+            if (rc) return rc;
+        }
+        return JL_OK;
+    }
     GemmArgs g = {};
     if (in_kind >= 0 && ctx->xb16 != nullptr && n <= ctx->row_cap) {
         if (!presplit) {  // otherwise the producing kernel already wrote the hi / lo rows
@@ -981,8 +1008,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
 
 // Runs one step: replays the captured graph for this width, capturing it on first use.
 int run_step(jl_ctx *ctx, int width, bool with_logits, bool advance = false) {
-    static const int rows_min = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return v ? atoi(v) : 4; }();
-    const bool rows_path = width >= rows_min || ctx->mixed;
+    const bool rows_path = width >= gemm_min_width() || ctx->mixed;
     const int key = width * 8 + (with_logits ? 1 : 0) + (advance ? 2 : 0) + (rows_path ? 4 : 0);
     uint64_t launches = 0;
     // Under tensor parallelism the first step of each shape runs uncaptured, so that NCCL sets up

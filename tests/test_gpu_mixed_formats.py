@@ -44,9 +44,9 @@ def test_single_sequence_logits_and_tokens(dev, oracle, head):
     assert worst > 0.0  # the two paths are different programs; identical logits would mean one of them did not run
 
 
-def test_batch_of_sequences_and_prompt_path(dev, oracle):
+@pytest.mark.parametrize("B", [3, 5])  # three rows: a mat-vec per row and matrix; five: the tensor-core kernel
+def test_batch_of_sequences_and_prompt_path(dev, oracle, B):
     cfg = small_config(layers=2, ctx=96)
-    B = 5
     p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=77, std=0.05, max_batch=B, replace=_mixed(cfg, 700))
     rng = np.random.default_rng(8)
     # sequence 0 ingests a prompt through the prompt path, the others start empty
