@@ -64,3 +64,19 @@ def test_batch_of_sequences_and_prompt_path(dev, oracle, B):
         assert list(got) == want, step
         tokens = np.array(want, dtype=np.int32)
         positions += 1
+
+
+def test_tied_q6_k_embedding_serves_as_table_and_output_matrix(dev, oracle):
+    """Tied embeddings in Q6_K: the embedding kernel decodes the token's row element by element and the same matrix
+    is the output projection."""
+    cfg = small_config(layers=2, ctx=48, tied=True)
+    rows, cols = cfg.matrix_shape(TensorRole.TOKEN_EMBEDDING)
+    q6 = GGMLType.Q6_K
+    repl = {(TensorRole.TOKEN_EMBEDDING, -1): (q6, jl.random_blocks(q6, rows * cols, 41, SCALES[q6]))}
+    p = Pair(dev, oracle, cfg, GGMLType.Q8_0, seed=12, std=0.05, replace=repl)
+    tokens = np.random.default_rng(9).integers(0, cfg.vocabularySize, size=12)
+    for pos, tok in enumerate(tokens):
+        want = p.oracle_model.forward(int(tok), pos)
+        res = p.boundary.invoke(int(tok), pos)
+        assert float(np.max(np.abs(res.logits - want))) < LOGIT_EXPECT, pos
+        assert res.sampledToken == int(np.argmax(want))
