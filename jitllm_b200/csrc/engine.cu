@@ -63,6 +63,7 @@ struct jl_ctx {
     // The model holds a Q4_1 / Q5_K / Q6_K matrix, or Q/K/V (gate/up) of different types: every step, single rows
     // included, takes the row path, whose projections are launched one matrix at a time.
     bool mixed = false;
+    bool has_extra = false;  // some matrix is Q4_1 / Q5_K / Q6_K: the row path needs the spare row buffer for residuals
     jl_model_desc desc = {};
     int kv_dim = 0;
     DevTensor global[JL_ROLE_COUNT];
@@ -633,6 +634,12 @@ int attn_splits_for_width(const jl_ctx *ctx, int width) {
 // One tensor-core launch over up to three matrices that share the input rows.
 // in_kind: which pre-split activation buffer x is mirrored in (0 xb by dim, 1 xb by the local query
 // width, 2 hb by the local hidden width), or -1 to let the kernel convert x itself.
+// Matrices the fused single-row step can multiply: F32 norm rows aside, what gemv_plan accepts.
+bool fused_path_takes(const DevTensor &t) {
+    if (!is_extra_quant(t.type)) return true;
+    return gemv_takes(t.type, t.cols) && t.cols <= kGemvMaxCols;
+}
+
 // Batches of at least this many rows, and prompt chunks, take the tensor-core projections.
 int gemm_min_width() {
     static const int v = [] { const char *e = getenv("JITLLM_B200_GEMM_MIN_WIDTH"); return e ? atoi(e) : 4; }();
@@ -700,7 +707,7 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
 
 int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
                 uint64_t *launches, int in_kind = -1, bool presplit = false) {
-    if (is_extra_quant(w.type)) {
+    if (is_extra_quant(w.type) && !(ctx->mixed && n < gemm_min_width() && fused_path_takes(w))) {
         // Q4_1 / Q5_K / Q6_K: the stand-alone mat-vec over the n fp32 rows (every producer of the row path writes
         // them beside the binary16 parts); a residual is added by a row kernel, through the spare row buffer.
         if (res != nullptr && (res != y || ctx->part == nullptr || int(w.rows) != ctx->desc.dim))
@@ -882,20 +889,36 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
         const float *ffn_norm =
             reinterpret_cast<const float *>(ctx->layer[JL_ROLE_FFN_NORM][l].data);
         NvtxRange range("attention", l);
+        const bool qkv_alike = wk.type == wq.type && wv.type == wq.type;
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
-            a.nseg = 3;
-            a.seg[0] = {wq.data, ctx->q + size_t(b) * qdim, nullptr, int(wq.rows)};
-            a.seg[1] = {wk.data, ctx->k + size_t(b) * kv_dim, nullptr, int(wk.rows)};
-            a.seg[2] = {wv.data, ctx->v + size_t(b) * kv_dim, nullptr, int(wv.rows)};
             a.cols = dim;
-            a.type = wq.type;
             a.mode = kGemvPlain;
             a.x = ctx->x + size_t(b) * dim;
             a.norm_w = attn_norm;
             a.eps = d.rms_eps;
             a.active = ctx->d_active + b;
-            if ((rc = launch_gemv(ctx, a, int(wq.rows + wk.rows + wv.rows), launches))) return rc;
+            const GemvSeg segs[3] = {{wq.data, ctx->q + size_t(b) * qdim, nullptr, int(wq.rows)},
+                                     {wk.data, ctx->k + size_t(b) * kv_dim, nullptr, int(wk.rows)},
+                                     {wv.data, ctx->v + size_t(b) * kv_dim, nullptr, int(wv.rows)}};
+            if (qkv_alike) {
+                a.nseg = 3;
+                a.seg[0] = segs[0];
+                a.seg[1] = segs[1];
+                a.seg[2] = segs[2];
+                a.type = wq.type;
+                if ((rc = launch_gemv(ctx, a, int(wq.rows + wk.rows + wv.rows), launches))) return rc;
+            } else {
+                // mixed-precision files keep the value projection in another format: one launch per matrix, each
+                // normalising the row again
+                const int types[3] = {wq.type, wk.type, wv.type};
+                for (int i = 0; i < 3; ++i) {
+                    a.nseg = 1;
+                    a.seg[0] = segs[i];
+                    a.type = types[i];
+                    if ((rc = launch_gemv(ctx, a, segs[i].rows, launches))) return rc;
+                }
+            }
         }
         {
             AttnArgs a = {};
@@ -1325,7 +1348,7 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
                                               emb.type, ctx->l_vocab, emb.cols));
         }
     }
-    bool mixed = false;
+    bool mixed = false, has_extra = false;
     static const int per_layer_roles[] = {JL_ROLE_ATTENTION_NORM,  JL_ROLE_ATTENTION_QUERY,
                                           JL_ROLE_ATTENTION_KEY,   JL_ROLE_ATTENTION_VALUE,
                                           JL_ROLE_ATTENTION_OUTPUT, JL_ROLE_FFN_NORM,
@@ -1334,21 +1357,23 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     for (int l = 0; l < d.layers; ++l) {
         for (int r : per_layer_roles)
             JL_REQUIRE(ctx, ctx->layer[r][l].data, JL_ERR_STATE, "layer %d is missing tensor role %d", l, r);
-        // The fused single-row kernels want Q, K, V (and gate, up) in one of their three formats and alike; a
-        // layer that is not makes the whole model take the row path (one GPU only).
-        const int tq = ctx->layer[JL_ROLE_ATTENTION_QUERY][l].type;
-        if (ctx->layer[JL_ROLE_ATTENTION_KEY][l].type != tq || ctx->layer[JL_ROLE_ATTENTION_VALUE][l].type != tq ||
-            ctx->layer[JL_ROLE_FFN_GATE][l].type != ctx->layer[JL_ROLE_FFN_UP][l].type)
-            mixed = true;
-        for (int r : per_layer_roles)
-            if (is_extra_quant(ctx->layer[r][l].type)) mixed = true;
+        // The fused single-row kernels want every matrix in a format the mat-vec kernel reads (Q6_K among them
+        // where rows are whole 16-byte pieces) and gate and up alike; a layer that is not makes the whole model
+        // take the row path (one GPU only). Q, K and V of different types are launched one by one.
+        if (ctx->layer[JL_ROLE_FFN_GATE][l].type != ctx->layer[JL_ROLE_FFN_UP][l].type) mixed = true;
+        for (int r : per_layer_roles) {
+            if (!fused_path_takes(ctx->layer[r][l])) mixed = true;
+            if (is_extra_quant(ctx->layer[r][l].type)) has_extra = true;
+        }
     }
-    if (is_extra_quant(ctx->global[JL_ROLE_TOKEN_EMBEDDING].type) ||
-        (ctx->global[JL_ROLE_OUTPUT].data && is_extra_quant(ctx->global[JL_ROLE_OUTPUT].type)))
+    // (a table that only serves the embedding kernel may have any type)
+    if (ctx->global[JL_ROLE_OUTPUT].data ? !fused_path_takes(ctx->global[JL_ROLE_OUTPUT])
+                                         : !fused_path_takes(ctx->global[JL_ROLE_TOKEN_EMBEDDING]))
         mixed = true;
     JL_REQUIRE(ctx, !mixed || ctx->tp_size == 1, JL_ERR_UNSUPPORTED,
                "tensor parallelism needs Q, K, V (gate, up) of one type per layer and no Q4_1 / Q5_K / Q6_K matrices");
     ctx->mixed = mixed;
+    ctx->has_extra = has_extra;
     if (ctx->finalized) return JL_OK;
     cudaSetDevice(ctx->device);
     const size_t B = d.max_batch;
@@ -1387,7 +1412,7 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
             JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[2][i], ctx->hb16, R, ctx->l_hidden, nts[i]));
         }
     }
-    if (ctx->mixed && (rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;
+    if ((ctx->mixed || ctx->has_extra) && (rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;
     if (ctx->tp_size > 1) {
         JL_REQUIRE(ctx, ctx->nccl_comm != nullptr, JL_ERR_STATE, "jl_tp_init must come before jl_model_finalize");
         if ((rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;
@@ -2031,8 +2056,10 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     JL_REQUIRE(ctx, reinterpret_cast<uintptr_t>(x_dev) % 16 == 0 && reinterpret_cast<uintptr_t>(y_dev) % 16 == 0,
                JL_ERR_INVALID, "x_dev and y_dev must be 16-byte aligned");
     cudaSetDevice(ctx->device);
-    if (is_extra_quant(w->t.type)) {
-        // Q4_1 / Q5_K / Q6_K: one launch for all n rows (weights re-read per row from L2 where they fit).
+    static const int gemm_min_n0 = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
+    if (is_extra_quant(w->t.type) && !(n < gemm_min_n0 && fused_path_takes(w->t))) {
+        // Q4_1 / Q5_K / Q6_K: one launch for all n rows (weights re-read per row from L2 where they fit); a few rows
+        // of a Q6_K matrix the mat-vec kernel reads go there, below.
         JL_REQUIRE(ctx, w->t.cols <= kGemvExtraMaxCols && n <= 65535, JL_ERR_UNSUPPORTED,
                    "GGML type %d: at most %d columns and 65535 activation rows", w->t.type, kGemvExtraMaxCols);
         if (n == 0) return JL_OK;
@@ -2043,7 +2070,7 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     }
     uint64_t launches = 0;
     static const int gemm_min_n = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
-    if (n >= gemm_min_n) {
+    if (n >= gemm_min_n && !is_extra_quant(w->t.type)) {
         // Wide enough for the tensor cores: one tcgen05 matrix-matrix launch.
         int rc = launch_gemm(ctx, w->t, x_dev, n, y_dev, nullptr, &launches);
         ctx->counters.kernel_launches += launches;

@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, con
     }
     const int nunits = a.cols / 64;
     const int nchunks = pl.nchunks, G = pl.groups, D = pl.stages, PJ = pl.phase_jobs;
-    const uint32_t rowb = uint32_t(nunits) * UB;
+    const uint32_t rowb = Fmt<TYPE>::row_bytes(nunits);
     const uint32_t stage_bytes = S * rowb;
     const int total_jobs = (MODE == kGemvGateUp) ? a.seg[0].rows
                                                  : a.seg[0].rows + (a.nseg > 1 ? a.seg[1].rows : 0) +
@@ -614,7 +614,7 @@ cudaError_t configure_type() {
 }  // namespace
 
 bool gemv_plan(int type, int cols, int total_rows, int mode, int sm_count, GemvPlan *out) {
-    if (!is_quant(type) || cols <= 0 || cols % 256 != 0 || cols > kGemvMaxCols || total_rows <= 0) return false;
+    if (!gemv_takes(type, cols) || cols > kGemvMaxCols || total_rows <= 0) return false;
     const size_t rowb = size_t(row_bytes(type, cols));
     const size_t stage = gemv_rows_per_stage(type) * rowb;
     const int spj = mode == kGemvGateUp ? 2 : 1;
@@ -648,6 +648,7 @@ cudaError_t gemv_configure() {
     cudaError_t e;
     if ((e = configure_type<kQ4_K>()) != cudaSuccess) return e;
     if ((e = configure_type<kQ4_0>()) != cudaSuccess) return e;
+    if ((e = configure_type<kQ6_K>()) != cudaSuccess) return e;
     return configure_type<kQ8_0>();
 }
 
@@ -656,6 +657,7 @@ cudaError_t gemv_launch(const GemvArgs &args, const GemvPlan &plan, cudaStream_t
         case kQ4_K: return launch_mode<kQ4_K>(args, plan, stream, programmatic);
         case kQ4_0: return launch_mode<kQ4_0>(args, plan, stream, programmatic);
         case kQ8_0: return launch_mode<kQ8_0>(args, plan, stream, programmatic);
+        case kQ6_K: return launch_mode<kQ6_K>(args, plan, stream, programmatic);
         default: return cudaErrorInvalidValue;
     }
 }

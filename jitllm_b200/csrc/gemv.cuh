@@ -35,7 +35,7 @@ struct GemvArgs {
     GemvSeg seg[3];
     int nseg;
     int cols;  // multiple of 256, at most kGemvMaxCols
-    int type;  // kQ8_0 / kQ4_0 / kQ4_K
+    int type;  // kQ8_0 / kQ4_0 / kQ4_K, or kQ6_K where gemv_takes() says so
     int mode;
     const float *x;       // cols floats, 16-byte aligned
     const float *norm_w;  // nullable: y = W . (norm_w * (rsqrt(mean(x^2)+eps) * x))
@@ -81,6 +81,13 @@ __host__ __device__ inline int gemv_split(int n, int part, int parts) {
 // Rows per stage (a stage is one bulk copy of whole consecutive rows, completing on one mbarrier
 // phase): two for the 4-bit formats, one for Q8_0 whose rows are twice as long in bytes.
 __host__ __device__ inline int gemv_rows_per_stage(int type) { return type == kQ8_0 ? 1 : 2; }
+
+// The formats this kernel reads: Q8_0, Q4_0, Q4_K, and Q6_K where a row is a whole number of 16-byte pieces
+// (rows are fetched by bulk copies; 210-byte super-blocks make that every eighth: columns a multiple of 2048).
+__host__ __device__ inline bool gemv_takes(int type, int64_t cols) {
+    if (cols <= 0 || cols % 256 != 0) return false;
+    return is_quant(type) || (type == kQ6_K && row_bytes(type, cols) % 16 == 0);
+}
 
 // Chooses group count, pipeline depth and shared-memory layout for one launch shape.
 bool gemv_plan(int type, int cols, int total_rows, int mode, int sm_count, GemvPlan *out);

@@ -12,8 +12,14 @@ constexpr int kUnitBytesQ8 = 68;   // 64 elements: Q8_0 2*34
 template <int TYPE>
 struct Fmt {
     static constexpr int unit_bytes = (TYPE == kQ8_0) ? kUnitBytesQ8 : kUnitBytesQ4;
-    static constexpr int chunk_bytes = 32 * unit_bytes;  // 32 lanes x one unit = 2048 columns
+    // 32 lanes x one unit = 2048 columns; Q6_K: eight 210-byte super-blocks (a unit is a quarter of one and
+    // no byte range of its own)
+    static constexpr int chunk_bytes = (TYPE == kQ6_K) ? 8 * kQ6_KBytes : 32 * unit_bytes;
     static constexpr int streams = (TYPE == kQ8_0) ? 1 : 2;  // rows per stage (gemv_rows_per_stage)
+    // bytes of one row of nunits 64-element units
+    __host__ __device__ static constexpr uint32_t row_bytes(int nunits) {
+        return (TYPE == kQ6_K) ? uint32_t(nunits / 4) * kQ6_KBytes : uint32_t(nunits) * unit_bytes;
+    }
 };
 
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, int b, int c) {
@@ -139,8 +145,71 @@ __device__ __forceinline__ float unit_q8_0(uint32_t chunk, int lane, const UnitX
     return (dA * x.sa) * fA + (dB * x.sb) * fB;
 }
 
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
+// Q6_K (tensor/standard/Q6_KFloatTensor.java:64-117): the unit is quarter p of super-block (lane/4): half h = p / 2
+// of the block, groups 2u and 2u + 1 of that half with u = p & 1 -- the low (u = 0) or high (u = 1) nibbles of the
+// half's 64 ql bytes, bits 4u..4u+3 of its 32 qh bytes, four signed byte scales (one per 16 elements), the block's d.
+// Super-blocks are 210 bytes, so every other one starts two bytes off a word: words are loaded aligned and shifted
+// into place (shift 0 or 16, the same code for both). The six-bit value v becomes the signed byte 4 * (v - 32) as
+// (v ^ 32) << 2 -- flipping bit 5 is v - 32 in six-bit two's complement and the shift moves its sign into bit 7 -- so
+// the integer dot products are exact and four times too large.
+__device__ __forceinline__ float unit_q6_k(uint32_t chunk, int lane, const UnitX &x) {
+    const uint32_t sb = chunk + (lane >> 2) * kQ6_KBytes;
+    const int p = lane & 3, h = p >> 1, u = p & 1;
+    const uint32_t sh = (sb & 2u) * 8u;
+    const uint32_t base = sb & ~3u;
+    uint32_t qh[8];
+    {
+        const uint32_t at = base + 128 + 32 * h;
+        uint32_t prev = lds32(at);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t next = lds32(at + 4 * (i + 1));  // the ninth word still lies inside the block
+            qh[i] = __funnelshift_r(prev, next, sh) >> (4 * u);  // bits 0-1: first group, bits 2-3: second group
+            prev = next;
+        }
+    }
+    const uint32_t sc_at = sb + 192 + 8 * h + 4 * u;
+    const uint32_t sc4 = (lds16(sc_at) | (lds16(sc_at + 2) << 16)) ^ 0x80808080u;  // signed scales, biased by 128
+    const float d = half_bits_to_float(lds16(sb + 208));
+    int acc[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // [16-element scale group][digit]
+    const uint32_t ql_at = base + 64 * h;
+    uint32_t prev = lds32(ql_at);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t next = lds32(ql_at + 4 * (i + 1));
+        const uint32_t nib = (__funnelshift_r(prev, next, sh) >> (4 * u)) & 0x0F0F0F0Fu;
+        prev = next;
+        const uint32_t top = i < 8 ? (qh[i] << 4) : (qh[i - 8] << 2);
+        const uint32_t w4 = ((nib | (top & 0x30303030u)) ^ 0x20202020u) << 2;
+        const int g = i >> 2;  // words 0-3, 4-7: the two scale groups of the first 32 elements; 8-15: of the second
+        if (i < 8) {
+            acc[g][0] = dp4a_s8s8(int(w4), x.a[0][i], acc[g][0]);
+            acc[g][1] = dp4a_s8s8(int(w4), x.a[1][i], acc[g][1]);
+        } else {
+            acc[g][0] = dp4a_s8s8(int(w4), x.b[0][i - 8], acc[g][0]);
+            acc[g][1] = dp4a_s8s8(int(w4), x.b[1][i - 8], acc[g][1]);
+        }
+    }
+    // |acc| <= 16 * 128 * 128 = 2^18, so 256 * acc[.][0] + acc[.][1] stays below 2^27: exact in integers.
+    float t[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) t[g] = static_cast<float>(acc[g][0] * 256 + acc[g][1]);
+    const float s0 = __uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7540u)) - 8388736.0f;  // byte - 128, no conversion
+    const float s1 = __uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7541u)) - 8388736.0f;
+    const float s2 = __uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7542u)) - 8388736.0f;
+    const float s3 = __uint_as_float(__byte_perm(sc4, 0x4B000000u, 0x7543u)) - 8388736.0f;
+    return (0.25f * d) * (x.sa * (s0 * t[0] + s1 * t[1]) + x.sb * (s2 * t[2] + s3 * t[3]));
+}
+
 template <int TYPE>
 __device__ __forceinline__ float unit_dot(uint32_t chunk, int lane, const UnitX &x) {
+    if constexpr (TYPE == kQ6_K) return unit_q6_k(chunk, lane, x);
     if constexpr (TYPE == kQ4_K) return unit_q4_k(chunk, lane, x);
     if constexpr (TYPE == kQ4_0) return unit_q4_0(chunk, lane, x);
     return unit_q8_0(chunk, lane, x);

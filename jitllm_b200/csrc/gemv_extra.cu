@@ -12,8 +12,11 @@
 // or a prompt chunk re-uses every unpacked weight for that many rows). The kernel is bound by
 // instruction issue, not by memory latency (about eight instructions per weight: byte -> float without the
 // slow integer conversion is a permute and a subtraction, then the multiply-add; requesting rows into L2 ahead
-// of the loads changed nothing): 2.0-2.7 TB/s on a 128256 x 4096 matrix. Integer dot products against an
-// 8-bit activation, as the model's own mat-vec does them, are the next step. This is the
+// of the loads changed nothing): 2.0-2.7 TB/s on a 128256 x 4096 matrix. A variant that kept the activation
+// as 8-bit digits in registers (a column slice per warp, dp4a, partial sums meeting in shared memory) had a
+// quarter fewer instructions and no shared-memory reads in its row loop, and was 1.4-2.2x slower: with a slice
+// per warp too few bytes are in flight per SM. What the model's own mat-vec does -- whole rows brought into shared
+// memory by bulk copies, then integer dot products -- is the design that would lift this one. This is the
 // stand-alone operator behind jl_gemv / jl_gemv_dev (HBM-bound: every weight byte is read once); it is
 // not wired into the decode step.
 #include "gemv_extra.cuh"

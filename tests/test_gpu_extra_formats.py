@@ -39,7 +39,7 @@ def test_decode_bit_exactly(dev, oracle, t):
 
 @pytest.mark.parametrize("t", EXTRA)
 @pytest.mark.parametrize("rows,cols,n", [(4096, 4096, 1), (1000, 14336, 1), (37, 256, 1), (512, 2048, 3), (300, 1024, 5), (256, 4096, 9),
-                                         (64, 14336, 4), (128, 6144, 2)])
+                                         (64, 14336, 4), (128, 6144, 2), (96, 16384, 1), (40, 16640, 1), (70, 768, 2), (33, 4352, 1)])
 def test_matvec_against_the_oracle(dev, oracle, t, rows, cols, n):
     rng = np.random.default_rng(rows + cols + int(t))
     w = random_blocks(t, rows * cols // t.block_size, rng)
@@ -48,7 +48,11 @@ def test_matvec_against_the_oracle(dev, oracle, t, rows, cols, n):
     want = oracle.matmul(int(t), w, x if n > 1 else x[0], rows, cols)
     assert got.shape == want.shape
     assert rel_l2(got, want) <= 1e-3
-    assert rel_l2(got, want) <= 2e-5  # what binary32 in another order gives; a wrong nibble is ~1e-1
+    # Q6_K rows that are whole 16-byte pieces (columns a multiple of 2048) go, a few rows at a time, through the
+    # model's own mat-vec kernel: 16-bit fixed-point activations per block (~3e-5). Everything else: binary32 in
+    # another order (~1e-6). A wrong nibble is ~1e-1.
+    fused = t == GGMLType.Q6_K and n < 8 and cols % 2048 == 0
+    assert rel_l2(got, want) <= (1e-4 if fused else 2e-5)
 
 
 @pytest.mark.parametrize("t", EXTRA)

@@ -80,3 +80,45 @@ def test_tied_q6_k_embedding_serves_as_table_and_output_matrix(dev, oracle):
         res = p.boundary.invoke(int(tok), pos)
         assert float(np.max(np.abs(res.logits - want))) < LOGIT_EXPECT, pos
         assert res.sampledToken == int(np.argmax(want))
+
+
+def _q6k_wide(cfg, seed):
+    """Value, down and output matrices in Q6_K on a model whose rows are whole 16-byte pieces in that format."""
+    q6 = GGMLType.Q6_K
+    out = {}
+    for l in range(cfg.numberOfLayers):
+        for j, role in enumerate((TensorRole.ATTENTION_VALUE, TensorRole.FFN_DOWN)):
+            rows, cols = cfg.matrix_shape(role)
+            out[(role, l)] = (q6, jl.random_blocks(q6, rows * cols, seed + 10 * l + j, SCALES[q6]))
+    rows, cols = cfg.matrix_shape(TensorRole.OUTPUT)
+    out[(TensorRole.OUTPUT, -1)] = (q6, jl.random_blocks(q6, rows * cols, seed + 99, SCALES[q6]))
+    return out
+
+
+@pytest.mark.parametrize("B", [1, 2, 5])
+def test_q6_k_on_the_fused_single_row_path(dev, oracle, B):
+    """Columns a multiple of 2048: Q6_K rows can be fetched by bulk copies, so the model keeps the fused single-row
+    step (Q, K, V launched one by one where their types differ) and only wide batches use the row path."""
+    cfg = jl.Configuration(dim=2048, hiddenDim=4096, numberOfLayers=2, numberOfHeads=16, numberOfKeyValueHeads=4,
+                           vocabularySize=1024, contextLength=64)
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=91, std=0.03, max_batch=B, replace=_q6k_wide(cfg, 1200))
+    rng = np.random.default_rng(10 + B)
+    seqs = [p.new_oracle_sequence() for _ in range(B)]
+    tokens = rng.integers(0, cfg.vocabularySize, size=B).astype(np.int32)
+    positions = np.zeros(B, dtype=np.int32)
+    for step in range(8):
+        slots = jl.BatchSlots(np.ones(B, dtype=bool), tokens.copy(), positions.copy(), np.arange(B, dtype=np.int32))
+        before = dev.counters()["kernel_launches"]
+        got, logits = p.executor.decodeStep(slots, wantLogits=True)
+        launches = dev.counters()["kernel_launches"] - before
+        want = [seqs[b].forward(int(tokens[b]), int(positions[b])) for b in range(B)]
+        for b in range(B):
+            err = float(np.max(np.abs(logits[b] - want[b])))
+            # the stated bar, and what the paths are known to give: logits here reach |4|, and the wide batch's
+            # binary16 operands round at 2^-11 relative
+            assert err < LOGIT_BAR and err < max(LOGIT_EXPECT, 2e-3 * float(np.max(np.abs(want[b])))), (step, b, err)
+            assert int(got[b]) == int(np.argmax(want[b])), (step, b)
+        if B < 4:  # embedding, per layer Q, K, V + attention + out + gate/up + down per row, logits per row
+            assert launches == 1 + cfg.numberOfLayers * (6 * B + 1) + B, launches
+        tokens = np.array([int(np.argmax(w)) for w in want], dtype=np.int32)
+        positions += 1
