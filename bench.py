@@ -182,7 +182,8 @@ def run_sweep(jl, args):
     shapes = tuple(tuple(int(v) for v in sh.split("x")) for sh in args.sweep_shapes.split(",") if sh)
     for fmt_name in [f for f in args.sweep_formats.split(",") if f]:
         t = jl.GGMLType[fmt_name]
-        extra = fmt_name in EXTRA_BYTES_PER_EL  # no encoder and no tensor-core path: random blocks, N = 1 and 8
+        extra = fmt_name in EXTRA_BYTES_PER_EL  # no encoder and no tensor-core path: random blocks, N = 1 and 8 (N = 1
+        # in the model's own mat-vec kernel, N = 8 in gemv_extra_kernel)
         for rows, cols in shapes:
             w = (jl.random_blocks(t, rows * cols, seed=args.seed + rows + cols) if extra
                  else jl.synth_tensor(t, rows * cols, seed=args.seed + rows + cols))
@@ -206,7 +207,7 @@ def run_sweep(jl, args):
                 print(json.dumps({"sweep": fmt_name, "rows": rows, "cols": cols, "n": n, "us": round(us, 2),
                                   "bytes": by, "gbs": round(by / us / 1e3, 1), "hbm_frac": round(by / us / 1e3 / peak, 4),
                                   "tflops": round(2.0 * rows * cols * n / us / 1e6, 2), "peak_kind": peak_kind,
-                                  "kernel": ("gemv" if fmt_name == "Q6_K" and n < 8 and cols % 2048 == 0 else "gemv_extra") if extra
+                                  "kernel": ("gemv" if n < 8 and (fmt_name != "Q6_K" or cols % 2048 == 0) else "gemv_extra") if extra
                                   else ("gemv" if n < 8 else "gemm_tc")}), flush=True)
                 dev.free(xd)
                 dev.free(yd)

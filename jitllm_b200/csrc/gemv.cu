@@ -130,7 +130,6 @@ template <int TYPE, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvArgs a, const GemvPlan pl) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int CB = Fmt<TYPE>::chunk_bytes;
-    constexpr int UB = Fmt<TYPE>::unit_bytes;
     constexpr int S = Fmt<TYPE>::streams;               // rows per stage
     constexpr int SPJ = (MODE == kGemvGateUp) ? 2 : 1;  // row streams per job
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -649,6 +648,8 @@ cudaError_t gemv_configure() {
     if ((e = configure_type<kQ4_K>()) != cudaSuccess) return e;
     if ((e = configure_type<kQ4_0>()) != cudaSuccess) return e;
     if ((e = configure_type<kQ6_K>()) != cudaSuccess) return e;
+    if ((e = configure_type<kQ5_K>()) != cudaSuccess) return e;
+    if ((e = configure_type<kQ4_1>()) != cudaSuccess) return e;
     return configure_type<kQ8_0>();
 }
 
@@ -658,6 +659,8 @@ cudaError_t gemv_launch(const GemvArgs &args, const GemvPlan &plan, cudaStream_t
         case kQ4_0: return launch_mode<kQ4_0>(args, plan, stream, programmatic);
         case kQ8_0: return launch_mode<kQ8_0>(args, plan, stream, programmatic);
         case kQ6_K: return launch_mode<kQ6_K>(args, plan, stream, programmatic);
+        case kQ5_K: return launch_mode<kQ5_K>(args, plan, stream, programmatic);
+        case kQ4_1: return launch_mode<kQ4_1>(args, plan, stream, programmatic);
         default: return cudaErrorInvalidValue;
     }
 }

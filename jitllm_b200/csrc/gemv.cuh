@@ -80,13 +80,13 @@ __host__ __device__ inline int gemv_split(int n, int part, int parts) {
 }
 // Rows per stage (a stage is one bulk copy of whole consecutive rows, completing on one mbarrier
 // phase): two for the 4-bit formats, one for Q8_0 whose rows are twice as long in bytes.
-__host__ __device__ inline int gemv_rows_per_stage(int type) { return type == kQ8_0 ? 1 : 2; }
+__host__ __device__ inline int gemv_rows_per_stage(int type) { return type == kQ8_0 ? 1 : 2; }  // = Fmt<type>::streams
 
-// The formats this kernel reads: Q8_0, Q4_0, Q4_K, and Q6_K where a row is a whole number of 16-byte pieces
-// (rows are fetched by bulk copies; 210-byte super-blocks make that every eighth: columns a multiple of 2048).
+// The formats this kernel reads: Q8_0, Q4_0, Q4_K, Q4_1, Q5_K, and Q6_K where a row is a whole number of 16-byte
+// pieces (rows are fetched by bulk copies; 210-byte super-blocks make that every eighth: columns a multiple of 2048).
 __host__ __device__ inline bool gemv_takes(int type, int64_t cols) {
     if (cols <= 0 || cols % 256 != 0) return false;
-    return is_quant(type) || (type == kQ6_K && row_bytes(type, cols) % 16 == 0);
+    return is_quant(type) || ((type == kQ6_K || type == kQ5_K || type == kQ4_1) && row_bytes(type, cols) % 16 == 0);
 }
 
 // Chooses group count, pipeline depth and shared-memory layout for one launch shape.

@@ -11,16 +11,21 @@ constexpr int kUnitBytesQ8 = 68;   // 64 elements: Q8_0 2*34
 
 template <int TYPE>
 struct Fmt {
-    static constexpr int unit_bytes = (TYPE == kQ8_0) ? kUnitBytesQ8 : kUnitBytesQ4;
-    // 32 lanes x one unit = 2048 columns; Q6_K: eight 210-byte super-blocks (a unit is a quarter of one and
-    // no byte range of its own)
-    static constexpr int chunk_bytes = (TYPE == kQ6_K) ? 8 * kQ6_KBytes : 32 * unit_bytes;
+    // bytes of 256 columns: one super-block (Q4_K, Q5_K, Q6_K) or eight blocks (Q4_0, Q4_1, Q8_0). A 64-element
+    // unit is a quarter of that; for Q5_K and Q6_K it is no byte range of its own (the high bits sit apart).
+    static constexpr int group_bytes = TYPE == kQ8_0   ? 8 * kQ8_0Bytes
+                                       : TYPE == kQ6_K ? kQ6_KBytes
+                                       : TYPE == kQ5_K ? kQ5_KBytes
+                                       : TYPE == kQ4_1 ? 8 * kQ4_1Bytes
+                                                       : kQ4_KBytes;  // Q4_K, and Q4_0: 8 x 18
+    static constexpr int unit_bytes = group_bytes / 4;   // meaningful for Q8_0, Q4_0, Q4_1, Q4_K
+    static constexpr int chunk_bytes = 8 * group_bytes;  // 32 lanes x one unit = 2048 columns
     static constexpr int streams = (TYPE == kQ8_0) ? 1 : 2;  // rows per stage (gemv_rows_per_stage)
     // bytes of one row of nunits 64-element units
-    __host__ __device__ static constexpr uint32_t row_bytes(int nunits) {
-        return (TYPE == kQ6_K) ? uint32_t(nunits / 4) * kQ6_KBytes : uint32_t(nunits) * unit_bytes;
-    }
+    __host__ __device__ static constexpr uint32_t row_bytes(int nunits) { return uint32_t(nunits / 4) * group_bytes; }
 };
+static_assert(Fmt<kQ4_K>::unit_bytes == kUnitBytesQ4 && Fmt<kQ4_0>::unit_bytes == kUnitBytesQ4 &&
+                  Fmt<kQ8_0>::unit_bytes == kUnitBytesQ8, "unit sizes");
 
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, int b, int c) {
     int d;
@@ -207,9 +212,81 @@ __device__ __forceinline__ float unit_q6_k(uint32_t chunk, int lane, const UnitX
     return (0.25f * d) * (x.sa * (s0 * t[0] + s1 * t[1]) + x.sb * (s2 * t[2] + s3 * t[3]));
 }
 
+// Q5_K (tensor/standard/Q5_KFloatTensor.java:87-127): Q4_K's layout with 32 bytes of fifth bits between the header
+// and the nibbles: the unit is nibble pair p of super-block (lane/4); bit 2p of qh byte j is the fifth bit of
+// element j of sub-block 2p (low nibbles), bit 2p + 1 that of sub-block 2p + 1 (high nibbles).
+__device__ __forceinline__ float unit_q5_k(uint32_t chunk, int lane, const UnitX &x) {
+    const uint32_t sb = chunk + (lane >> 2) * kQ5_KBytes;
+    const int p = lane & 3;
+    const uint4 hdr = lds128(sb);
+    const uint4 h0 = lds128(sb + 16), h1 = lds128(sb + 32);
+    const uint4 q0 = lds128(sb + 48 + p * 32), q1 = lds128(sb + 64 + p * 32);
+    const float d = half_bits_to_float(hdr.x & 0xFFFFu);
+    const float dmin = half_bits_to_float(hdr.x >> 16);
+    const bool upper = p >= 2;  // the packed 6-bit scales and minima: as in unit_q4_k
+    const int sh = (p & 1) * 16;
+    const uint32_t lo_mask = upper ? 0x0F0Fu : 0x3F3Fu;
+    const uint32_t hi_mask = upper ? 0x3030u : 0u;
+    const uint32_t sc2 = (((upper ? hdr.w : hdr.y) >> sh) & lo_mask) | ((hdr.y >> (sh + 2)) & hi_mask);
+    const uint32_t m2 = (((upper ? (hdr.w >> 4) : hdr.z) >> sh) & lo_mask) | ((hdr.z >> (sh + 2)) & hi_mask);
+    const int sc0 = sc2 & 0xFFu, sc1 = sc2 >> 8;
+    const float m0 = static_cast<float>(m2 & 0xFFu), m1 = static_cast<float>(m2 >> 8);
+    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    int l0 = 0, l1 = 0, h0s = 0, h1s = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t fifth = hw[i] >> (2 * p);
+        const uint32_t lo = (qw[i] & 0x0F0F0F0Fu) | ((fifth << 4) & 0x10101010u);
+        const uint32_t hi = ((qw[i] >> 4) & 0x0F0F0F0Fu) | ((fifth << 3) & 0x10101010u);
+        l0 = dp4a_u8s8(lo, x.a[0][i], l0);
+        l1 = dp4a_u8s8(lo, x.a[1][i], l1);
+        h0s = dp4a_u8s8(hi, x.b[0][i], h0s);
+        h1s = dp4a_u8s8(hi, x.b[1][i], h1s);
+    }
+    // |sum q*X| <= 31 * 128 * 32 < 2^17 per digit, 256 * l0 + l1 < 2^25, times a 6-bit scale < 2^31: exact in integers.
+    const float dots = x.sa * static_cast<float>(sc0 * (l0 * 256 + l1)) + x.sb * static_cast<float>(sc1 * (h0s * 256 + h1s));
+    const float mins = m0 * x.ma + m1 * x.mb;
+    return d * dots - dmin * mins;
+}
+
+// Q4_1 (tensor/standard/Q4_1FloatTensor.java:76-99: w = q * d + m, q unsigned): the unit is two 20-byte blocks = ten
+// aligned words, each block a word of (d, m) and four words of nibbles (low nibbles elements 0-15, high 16-31).
+__device__ __forceinline__ float unit_q4_1(uint32_t chunk, int lane, const UnitX &x) {
+    const uint32_t wp = chunk + lane * 40;
+    uint32_t w[10];
+#pragma unroll
+    for (int i = 0; i < 10; ++i) w[i] = lds32(wp + 4 * i);
+    int l0 = 0, l1 = 0, h0 = 0, h1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = w[1 + i] & 0x0F0F0F0Fu, hi = (w[1 + i] >> 4) & 0x0F0F0F0Fu;
+        l0 = dp4a_u8s8(lo, x.a[0][i], l0);
+        l1 = dp4a_u8s8(lo, x.a[1][i], l1);
+        h0 = dp4a_u8s8(hi, x.a[0][4 + i], h0);
+        h1 = dp4a_u8s8(hi, x.a[1][4 + i], h1);
+    }
+    const float tA = static_cast<float>((l0 + h0) * 256 + (l1 + h1));
+    l0 = l1 = h0 = h1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = w[6 + i] & 0x0F0F0F0Fu, hi = (w[6 + i] >> 4) & 0x0F0F0F0Fu;
+        l0 = dp4a_u8s8(lo, x.b[0][i], l0);
+        l1 = dp4a_u8s8(lo, x.b[1][i], l1);
+        h0 = dp4a_u8s8(hi, x.b[0][4 + i], h0);
+        h1 = dp4a_u8s8(hi, x.b[1][4 + i], h1);
+    }
+    const float tB = static_cast<float>((l0 + h0) * 256 + (l1 + h1));
+    float r = half_bits_to_float(w[0] & 0xFFFFu) * (x.sa * tA) + half_bits_to_float(w[0] >> 16) * x.ma;
+    r += half_bits_to_float(w[5] & 0xFFFFu) * (x.sb * tB) + half_bits_to_float(w[5] >> 16) * x.mb;
+    return r;
+}
+
 template <int TYPE>
 __device__ __forceinline__ float unit_dot(uint32_t chunk, int lane, const UnitX &x) {
     if constexpr (TYPE == kQ6_K) return unit_q6_k(chunk, lane, x);
+    if constexpr (TYPE == kQ5_K) return unit_q5_k(chunk, lane, x);
+    if constexpr (TYPE == kQ4_1) return unit_q4_1(chunk, lane, x);
     if constexpr (TYPE == kQ4_K) return unit_q4_k(chunk, lane, x);
     if constexpr (TYPE == kQ4_0) return unit_q4_0(chunk, lane, x);
     return unit_q8_0(chunk, lane, x);

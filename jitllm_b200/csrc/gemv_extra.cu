@@ -9,16 +9,18 @@
 //   Q6_K  sum_i x_i (d sc (q_i - 32))           = d * sum_g sc_g * sum (q_i - 32) x_i      per 16-element scale group
 //
 // One warp per row of W, eight rows per CTA in flight, one, two or four activation rows staged per CTA (a batch
-// or a prompt chunk re-uses every unpacked weight for that many rows). The kernel is bound by
-// instruction issue, not by memory latency (about eight instructions per weight: byte -> float without the
-// slow integer conversion is a permute and a subtraction, then the multiply-add; requesting rows into L2 ahead
-// of the loads changed nothing): 2.0-2.7 TB/s on a 128256 x 4096 matrix. A variant that kept the activation
-// as 8-bit digits in registers (a column slice per warp, dp4a, partial sums meeting in shared memory) had a
-// quarter fewer instructions and no shared-memory reads in its row loop, and was 1.4-2.2x slower: with a slice
-// per warp too few bytes are in flight per SM. What the model's own mat-vec does -- whole rows brought into shared
-// memory by bulk copies, then integer dot products -- is the design that would lift this one. This is the
-// stand-alone operator behind jl_gemv / jl_gemv_dev (HBM-bound: every weight byte is read once); it is
-// not wired into the decode step.
+// or a prompt chunk re-uses every unpacked weight for that many rows). The kernel is bound by instruction issue and
+// the L1 data pipe, not by memory latency (about eight instructions per weight: byte -> float without the slow
+// integer conversion is a permute and a subtraction, then the multiply-add; narrow global loads because 210-byte
+// blocks are only 2-byte aligned; requesting rows into L2 ahead of the loads changed nothing): 2.0-2.7 TB/s on a
+// 128256 x 4096 matrix. A variant that kept the activation as 8-bit digits in registers (a column slice per warp,
+// dp4a, partial sums meeting in shared memory) had a quarter fewer instructions and no shared-memory reads in its
+// row loop, and was 1.4-2.2x slower: with a slice per warp too few bytes are in flight per SM.
+//
+// Where this kernel runs: batches of four or more rows and prompt chunks of the three formats, eight or more rows
+// of the stand-alone operator, and single Q6_K rows that are not a whole number of 16-byte pieces. Other single rows
+// go through the model's own mat-vec kernel (gemv.cu: whole rows by bulk copies, integer dot products), which
+// reaches 0.7-0.9 of the HBM rate on these formats.
 #include "gemv_extra.cuh"
 
 namespace jl {

@@ -48,10 +48,10 @@ def test_matvec_against_the_oracle(dev, oracle, t, rows, cols, n):
     want = oracle.matmul(int(t), w, x if n > 1 else x[0], rows, cols)
     assert got.shape == want.shape
     assert rel_l2(got, want) <= 1e-3
-    # Q6_K rows that are whole 16-byte pieces (columns a multiple of 2048) go, a few rows at a time, through the
-    # model's own mat-vec kernel: 16-bit fixed-point activations per block (~3e-5). Everything else: binary32 in
-    # another order (~1e-6). A wrong nibble is ~1e-1.
-    fused = t == GGMLType.Q6_K and n < 8 and cols % 2048 == 0
+    # Fewer than eight rows go, row by row, through the model's own mat-vec kernel where a matrix row is a whole
+    # number of 16-byte pieces (Q4_1, Q5_K: always; Q6_K: columns a multiple of 2048): 16-bit fixed-point
+    # activations per block (~3e-5). Everything else: binary32 in another order (~1e-6). A wrong nibble is ~1e-1.
+    fused = n < 8 and (t != GGMLType.Q6_K or cols % 2048 == 0)
     assert rel_l2(got, want) <= (1e-4 if fused else 2e-5)
 
 
