@@ -38,7 +38,17 @@ struct DevTensor {
     size_t bytes = 0;
     bool has_tmap = false;  // quantised with whole 256-column groups: usable by the tensor-core path
     GemmTensorMap tmap = {};
+    // Q6_K only: the copy with padded super-blocks that the tensor map describes (formats.cuh); owned like `data`.
+    uint8_t *padded = nullptr;
+    size_t padded_bytes = 0;
 };
+
+// Frees a tensor's device memory (both copies) and leaves it empty.
+void release_tensor(DevTensor *t) {
+    if (t->data) cudaFree(t->data);
+    if (t->padded) cudaFree(t->padded);
+    *t = DevTensor();
+}
 
 struct StepGraph {
     cudaGraphExec_t exec = nullptr;
@@ -259,9 +269,8 @@ int check_shape(jl_ctx *ctx, int type, int64_t rows, int64_t cols, size_t nbytes
 int upload(jl_ctx *ctx, DevTensor *t, int type, int64_t rows, int64_t cols, const void *host,
            size_t nbytes) {
     if (t->data) {
-        cudaFree(t->data);
-        ctx->counters.weight_bytes -= t->bytes;
-        *t = DevTensor();
+        ctx->counters.weight_bytes -= t->bytes + t->padded_bytes;
+        release_tensor(t);
     }
     void *p = nullptr;
     int rc = dev_alloc(ctx, &p, nbytes);
@@ -287,8 +296,29 @@ int upload(jl_ctx *ctx, DevTensor *t, int type, int64_t rows, int64_t cols, cons
                         (long long)cols, cudaGetErrorString(e));
         }
         t->has_tmap = true;
+    } else if (type == kQ6_K && cols % 256 == 0) {
+        // The tensor-core kernel reads Q6_K from a copy with padded super-blocks (its tensor map needs rows of
+        // 16-byte multiples); the mat-vec kernels and the embedding lookup keep reading the original.
+        const size_t nblocks = size_t(rows) * size_t(cols / 256);
+        void *pp = nullptr;
+        if ((rc = dev_alloc(ctx, &pp, nblocks * kQ6_KPadded))) {
+            release_tensor(t);
+            return rc;
+        }
+        t->padded = static_cast<uint8_t *>(pp);
+        t->padded_bytes = nblocks * kQ6_KPadded;
+        e = pad_q6k_launch(t->data, t->padded, nblocks, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e == cudaSuccess) e = gemm_make_tensor_map(&t->tmap, pp, type, rows, cols);
+        if (e != cudaSuccess) {
+            release_tensor(t);
+            return fail(ctx, JL_ERR_CUDA, "padded copy of a %lld x %lld Q6_K matrix failed: %s", (long long)rows,
+                        (long long)cols, cudaGetErrorString(e));
+        }
+        t->has_tmap = true;
+        ctx->counters.kernel_launches++;
     }
-    ctx->counters.weight_bytes += nbytes;
+    ctx->counters.weight_bytes += nbytes + t->padded_bytes;
     ctx->counters.h2d_bytes += nbytes;
     return JL_OK;
 }
@@ -348,10 +378,8 @@ void free_workspace(jl_ctx *ctx) {
 void free_model(jl_ctx *ctx) {
     free_workspace(ctx);
     for (int r = 0; r < JL_ROLE_COUNT; ++r) {
-        if (ctx->global[r].data) cudaFree(ctx->global[r].data);
-        ctx->global[r] = DevTensor();
-        for (auto &t : ctx->layer[r])
-            if (t.data) cudaFree(t.data);
+        release_tensor(&ctx->global[r]);
+        for (auto &t : ctx->layer[r]) release_tensor(&t);
         ctx->layer[r].clear();
     }
     if (ctx->rope_cos) cudaFree(ctx->rope_cos);
@@ -646,12 +674,64 @@ int gemm_min_width() {
     return v;
 }
 
+// How the row path multiplies n rows by one matrix: the mat-vec kernel row by row (narrow steps of a mixed-format
+// model, formats and row lengths it reads), the tensor-core kernel (wide steps, matrices with a tensor map: Q4_0,
+// Q8_0, Q4_K, and Q6_K through its padded copy), else the stand-alone mat-vec of Q4_1 / Q5_K / Q6_K.
+enum RowsVia { kViaGemv, kViaGemm, kViaExtra };
+RowsVia rows_via(const jl_ctx *ctx, const DevTensor &w, int n) {
+    const bool narrow = ctx->mixed && n < gemm_min_width();
+    if (narrow && fused_path_takes(w)) return kViaGemv;
+    if (!narrow && w.has_tmap) return kViaGemm;
+    return is_extra_quant(w.type) ? kViaExtra : (narrow ? kViaGemv : kViaGemm);
+}
+
 int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, const float *const *res, int nseg,
-                     const float *x, int n, uint64_t *launches, int in_kind = -1, bool presplit = false) {
-    if (ctx->mixed && n < gemm_min_width()) {
-        // A mixed-format model takes the row path for narrow steps too: there its Q4_0 / Q8_0 / Q4_K matrices
-        // are better served by the mat-vec kernel, one launch per row (plain mode: the norm, SwiGLU and arg-max
-        // around it are row kernels on this path; the residual stays in its epilogue).
+                     const float *x, int n, uint64_t *launches, int in_kind = -1, bool presplit = false);
+
+int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
+                uint64_t *launches, int in_kind = -1, bool presplit = false) {
+    if (rows_via(ctx, w, n) == kViaExtra) {
+        // the stand-alone mat-vec over the n fp32 rows (every producer of the row path writes them beside the
+        // binary16 parts); a residual is added by a row kernel, through the spare row buffer
+        if (res != nullptr && (res != y || ctx->part == nullptr || int(w.rows) != ctx->desc.dim))
+            return fail(ctx, JL_ERR_UNSUPPORTED, "residual of a type %d projection", w.type);
+        if (w.cols > kGemvExtraMaxCols)
+            return fail(ctx, JL_ERR_UNSUPPORTED, "type %d matrices are limited to %d columns", w.type, kGemvExtraMaxCols);
+        float *dst = res != nullptr ? ctx->part : y;
+        cudaError_t e = gemv_extra_launch(w.type, w.data, x, dst, int(w.rows), int(w.cols), n, ctx->sm_count, ctx->stream);
+        if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-vector launch failed: %s", cudaGetErrorString(e));
+        ++*launches;
+        if (res != nullptr) {
+            e = add_rows_launch(y, ctx->part, size_t(n) * w.rows, ctx->stream, ctx->use_pdl);
+            if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "residual launch failed: %s", cudaGetErrorString(e));
+            ++*launches;
+        }
+        return JL_OK;
+    }
+    const DevTensor *ws[1] = {&w};
+    float *ys[1] = {y};
+    const float *rs[1] = {res};
+    return launch_gemm_segs(ctx, ws, ys, rs, 1, x, n, launches, in_kind, presplit);
+}
+
+// Several matrices of one type against the same rows (Q, K, V; gate, up) in one launch where one kernel takes them
+// all, else one matrix at a time.
+int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, const float *const *res, int nseg,
+                     const float *x, int n, uint64_t *launches, int in_kind, bool presplit) {
+    const RowsVia via = rows_via(ctx, *w[0], n);
+    bool alike = true;
+    for (int s = 1; s < nseg; ++s) alike = alike && w[s]->type == w[0]->type && rows_via(ctx, *w[s], n) == via;
+    if (!alike || via == kViaExtra) {
+        for (int s = 0; s < nseg; ++s) {
+            int rc = launch_gemm(ctx, *w[s], x, n, y[s], res != nullptr ? res[s] : nullptr, launches, in_kind, presplit);
+            if (rc) return rc;
+        }
+        return JL_OK;
+    }
+    if (via == kViaGemv) {
+        // A mixed-format model takes the row path for narrow steps too: there the mat-vec kernel serves better,
+        // one launch per row (plain mode: the norm, SwiGLU and arg-max around it are row kernels on this path;
+        // the residual stays in its epilogue).
         int total = 0;
         for (int s = 0; s < nseg; ++s) total += int(w[s]->rows);
         for (int b = 0; b < n; ++b) {
@@ -705,32 +785,6 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
     return JL_OK;
 }
 
-int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
-                uint64_t *launches, int in_kind = -1, bool presplit = false) {
-    if (is_extra_quant(w.type) && !(ctx->mixed && n < gemm_min_width() && fused_path_takes(w))) {
-        // Q4_1 / Q5_K / Q6_K: the stand-alone mat-vec over the n fp32 rows (every producer of the row path writes
-        // them beside the binary16 parts); a residual is added by a row kernel, through the spare row buffer.
-        if (res != nullptr && (res != y || ctx->part == nullptr || int(w.rows) != ctx->desc.dim))
-            return fail(ctx, JL_ERR_UNSUPPORTED, "residual of a type %d projection", w.type);
-        if (w.cols > kGemvExtraMaxCols)
-            return fail(ctx, JL_ERR_UNSUPPORTED, "type %d matrices are limited to %d columns", w.type, kGemvExtraMaxCols);
-        float *dst = res != nullptr ? ctx->part : y;
-        cudaError_t e = gemv_extra_launch(w.type, w.data, x, dst, int(w.rows), int(w.cols), n, ctx->sm_count, ctx->stream);
-        if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-vector launch failed: %s", cudaGetErrorString(e));
-        ++*launches;
-        if (res != nullptr) {
-            e = add_rows_launch(y, ctx->part, size_t(n) * w.rows, ctx->stream, ctx->use_pdl);
-            if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "residual launch failed: %s", cudaGetErrorString(e));
-            ++*launches;
-        }
-        return JL_OK;
-    }
-    const DevTensor *ws[1] = {&w};
-    float *ys[1] = {y};
-    const float *rs[1] = {res};
-    return launch_gemm_segs(ctx, ws, ys, rs, 1, x, n, launches, in_kind, presplit);
-}
-
 #define JL_LAUNCH(ctx, call, what)                                                            \
     do {                                                                                      \
         cudaError_t e_ = (call);                                                              \
@@ -766,13 +820,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
             const DevTensor *ws[3] = {&ctx->layer[JL_ROLE_ATTENTION_QUERY][l], &ctx->layer[JL_ROLE_ATTENTION_KEY][l],
                                       &ctx->layer[JL_ROLE_ATTENTION_VALUE][l]};
             float *ys[3] = {ctx->q, ctx->k, ctx->v};
-            const bool same = ws[0]->type == ws[1]->type && ws[0]->type == ws[2]->type && !is_extra_quant(ws[0]->type);
-            if (same) {
-                if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 3, ctx->xb, n, launches, 0, true))) return rc;
-            } else {
-                for (int i = 0; i < 3; ++i)
-                    if ((rc = launch_gemm(ctx, *ws[i], ctx->xb, n, ys[i], nullptr, launches))) return rc;
-            }
+            if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 3, ctx->xb, n, launches, 0, true))) return rc;
         }
         if (!own_sequences)
             JL_LAUNCH(ctx, kv_append_launch(ctx->k, ctx->v, ctx->rope_cos, ctx->rope_sin, ctx->d_positions, ctx->d_slots,
@@ -828,12 +876,7 @@ int enqueue_rows_step(jl_ctx *ctx, int n, bool with_logits, bool advance, uint64
         {
             const DevTensor *ws[2] = {&ctx->layer[JL_ROLE_FFN_GATE][l], &ctx->layer[JL_ROLE_FFN_UP][l]};
             float *ys[2] = {ctx->hb, ctx->hb2};
-            if (ws[0]->type == ws[1]->type && !is_extra_quant(ws[0]->type)) {
-                if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 2, ctx->xb, n, launches, 0, true))) return rc;
-            } else {
-                for (int i = 0; i < 2; ++i)
-                    if ((rc = launch_gemm(ctx, *ws[i], ctx->xb, n, ys[i], nullptr, launches))) return rc;
-            }
+            if ((rc = launch_gemm_segs(ctx, ws, ys, nullptr, 2, ctx->xb, n, launches, 0, true))) return rc;
         }
         JL_LAUNCH(ctx, swiglu_rows_launch(ctx->hb, ctx->hb2, ctx->l_hidden, n, ctx->stream, ctx->hb16,
                                           static_cast<char *>(ctx->hb16) + size_t(ctx->row_cap) * ctx->l_hidden * 2, ctx->use_pdl),
@@ -2040,8 +2083,8 @@ int32_t jl_tensor_free(jl_ctx *ctx, jl_tensor *t) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (t->t.data) {
-        cudaFree(t->t.data);
-        ctx->counters.weight_bytes -= t->t.bytes;
+        ctx->counters.weight_bytes -= t->t.bytes + t->t.padded_bytes;
+        release_tensor(&t->t);
     }
     delete t;
     return JL_OK;
@@ -2057,7 +2100,7 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
                JL_ERR_INVALID, "x_dev and y_dev must be 16-byte aligned");
     cudaSetDevice(ctx->device);
     static const int gemm_min_n0 = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
-    if (is_extra_quant(w->t.type) && !(n < gemm_min_n0 && fused_path_takes(w->t))) {
+    if (is_extra_quant(w->t.type) && !(n < gemm_min_n0 && fused_path_takes(w->t)) && !(n >= gemm_min_n0 && w->t.has_tmap)) {
         // Q4_1 / Q5_K / Q6_K: one launch for all n rows (weights re-read per row from L2 where they fit); a few rows
         // of a Q6_K matrix the mat-vec kernel reads go there, below.
         JL_REQUIRE(ctx, w->t.cols <= kGemvExtraMaxCols && n <= 65535, JL_ERR_UNSUPPORTED,
@@ -2070,7 +2113,7 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     }
     uint64_t launches = 0;
     static const int gemm_min_n = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
-    if (n >= gemm_min_n && !is_extra_quant(w->t.type)) {
+    if (n >= gemm_min_n && w->t.has_tmap) {
         // Wide enough for the tensor cores: one tcgen05 matrix-matrix launch.
         int rc = launch_gemm(ctx, w->t, x_dev, n, y_dev, nullptr, &launches);
         ctx->counters.kernel_launches += launches;

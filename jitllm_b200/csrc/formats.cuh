@@ -16,6 +16,9 @@ constexpr int kQ4_KBlock = 256, kQ4_KBytes = 144;
 constexpr int kQ4_1Block = 32, kQ4_1Bytes = 20;
 constexpr int kQ5_KBlock = 256, kQ5_KBytes = 176;
 constexpr int kQ6_KBlock = 256, kQ6_KBytes = 210;
+// The tensor-core kernel fetches 128-row tiles through a 2-D tensor map, whose rows must be 16-byte multiples: it reads
+// Q6_K matrices from a second copy with every super-block padded to this size (made on upload, same bytes, zero fill).
+constexpr int kQ6_KPadded = 224;
 
 // Every format packs 256 consecutive elements into a 16-byte-aligned group:
 // Q4_K 144 B (one super-block), Q4_0 8 x 18 = 144 B, Q8_0 8 x 34 = 272 B.

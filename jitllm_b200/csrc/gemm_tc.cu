@@ -212,7 +212,7 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 
 template <int TYPE>
 struct RawFmt {
-    static constexpr int row_bytes = (TYPE == kQ8_0) ? 272 : 144;  // 256 columns of one row
+    static constexpr int row_bytes = TYPE == kQ8_0 ? 272 : (TYPE == kQ6_K ? kQ6_KPadded : 144);  // 256 columns of one row
     static constexpr int stage_bytes = kTileM * row_bytes;
 };
 
@@ -247,6 +247,12 @@ struct UnitRegs<kQ4_0> {
 template <>
 struct UnitRegs<kQ8_0> {
     uint32_t base;  // shared address of the unit (two 34-byte blocks); its halves are loaded one at a time
+};
+template <>
+struct UnitRegs<kQ6_K> {
+    uint32_t blk;   // shared address of the (padded) super-block; the unit's halves are loaded one at a time
+    int unit;
+    __half2 d2;     // the super-block scale, exact (it is stored as binary16)
 };
 
 __device__ __forceinline__ __half2 u32_as_half2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
@@ -292,6 +298,11 @@ __device__ __forceinline__ void unit_load(uint32_t row_u32, int unit, UnitRegs<T
         const uint32_t base = row_u32 + unit * 36;
 #pragma unroll
         for (int i = 0; i < 9; ++i) r.t[i] = lds32(base + 4 * i);
+    } else if constexpr (TYPE == kQ6_K) {
+        r.blk = row_u32;
+        r.unit = unit;
+        const uint32_t dw = lds32(row_u32 + 208) & 0xFFFFu;
+        r.d2 = u32_as_half2(dw | (dw << 16));
     } else {
         r.base = row_u32 + unit * 68;
     }
@@ -319,6 +330,39 @@ __device__ __forceinline__ void unit_convert(const UnitRegs<TYPE> &r, int half, 
             const __half2 wo = __hadd2(__hfma2(r.d2, __hfma2(sc2, o, off2), chi2), clo2);
             out[2 * i] = h2_bits(we);
             out[2 * i + 1] = h2_bits(wo);
+        }
+    } else if constexpr (TYPE == kQ6_K) {
+        // tensor/standard/Q6_KFloatTensor.java:64-117. Unit p = 2h + u of the super-block: half h, the groups 2u
+        // (this call's half 0) and 2u + 1 (half 1) of 32 weights: nibble u of ql[64 h + 32 half + j], bits
+        // 4u + 2 half .. +1 of qh[32 h + j], one signed byte scale per 16 weights; w = d * scale * (v - 32).
+        // v - 32 is exact in binary16; d * scale has up to 18 significant bits and is applied as an exact
+        // binary16 pair (hi, lo): w = (v - 32) * hi + (v - 32) * lo, one rounding apart from the small lo product.
+        const int h = r.unit >> 1, u = r.unit & 1;
+        const uint32_t ql_at = r.blk + 64 * h + 32 * half, qh_at = r.blk + 128 + 32 * h;
+        const uint32_t scw = lds32(r.blk + 192 + 8 * h + 4 * u) >> (16 * half);  // bytes 0, 1: this half's two scales
+        const float d = __half2float(__low2half(r.d2));
+        __half2 hi2[2], lo2[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float ds = __fmul_rn(d, static_cast<float>(static_cast<int>(static_cast<int8_t>((scw >> (8 * k)) & 0xFFu))));
+            const __half hi = __float2half_rn(ds);
+            hi2[k] = __half2half2(hi);
+            lo2[k] = __half2half2(__float2half_rn(ds - __half2float(hi)));
+        }
+        const __half2 off = __float2half2_rn(1056.0f);  // 1024 of the byte trick + 32
+        const int qsh = 4 * u + 2 * half;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {  // four words at a time: one 16-byte load of each plane, one scale
+            const uint4 l4 = lds128(ql_at + 16 * q), h4 = lds128(qh_at + 16 * q);
+            const uint32_t lw[4] = {l4.x, l4.y, l4.z, l4.w}, hw[4] = {h4.x, h4.y, h4.z, h4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t v = ((lw[i] >> (4 * u)) & 0x0F0F0F0Fu) | (((hw[i] >> qsh) << 4) & 0x30303030u);
+                const __half2 e = __hsub2(bytes_to_half2_plus1024(v, 0x4240u), off);
+                const __half2 o = __hsub2(bytes_to_half2_plus1024(v, 0x4341u), off);
+                out[8 * q + 2 * i] = h2_bits(__hfma2(e, hi2[q], __hmul2(e, lo2[q])));
+                out[8 * q + 2 * i + 1] = h2_bits(__hfma2(o, hi2[q], __hmul2(o, lo2[q])));
+            }
         }
     } else if constexpr (TYPE == kQ4_0) {
         // tensor/standard/Q4_0FloatTensor.java:56-79: a unit is two 18-byte blocks; element i < 16
@@ -399,6 +443,10 @@ static_assert((2 * 6 + 2 * 8 + 3) * 8 + 64 <= GemmSmem<kQ4_K, 32>::bar_bytes, "b
 static_assert(GemmSmem<kQ8_0, 64>::total <= 227 * 1024 && GemmSmem<kQ4_K, 64>::total <= 227 * 1024 &&
                   GemmSmem<kQ4_K, 16>::total <= 227 * 1024 && GemmSmem<kQ8_0, 32>::total <= 227 * 1024,
               "shared memory budget");
+static_assert(GemmSmem<kQ6_K, 16>::total <= 227 * 1024 && GemmSmem<kQ6_K, 32>::total <= 227 * 1024 &&
+                  GemmSmem<kQ6_K, 64>::total <= 227 * 1024 && GemmSmem<kQ6_K, 128>::total <= 227 * 1024 &&
+                  GemmSmem<kQ6_K, 64>::stages >= 3 && GemmSmem<kQ6_K, 128>::stages >= 2 && GemmSmem<kQ6_K, 128>::raw_stages >= 2,
+              "Q6_K (padded super-blocks) budget");
 static_assert(GemmSmem<kQ8_0, 64>::stages >= 3 && GemmSmem<kQ8_0, 128>::stages >= 2 &&
                   GemmSmem<kQ8_0, 128>::total <= 227 * 1024 && GemmSmem<kQ4_K, 128>::total <= 227 * 1024,
               "pipeline depth");
@@ -1083,7 +1131,9 @@ cudaError_t configure_type() {
 
 cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type, int64_t rows, int64_t cols) {
     static_assert(sizeof(CUtensorMap) == sizeof(GemmTensorMap), "descriptor size");
-    if (!out || !w_dev || !is_quant(type) || rows <= 0 || cols <= 0 || cols % kRawK != 0) return cudaErrorInvalidValue;
+    // (a Q6_K matrix is passed as its padded copy: kQ6_KPadded bytes per super-block)
+    if (!out || !w_dev || !(is_quant(type) || type == kQ6_K) || rows <= 0 || cols <= 0 || cols % kRawK != 0)
+        return cudaErrorInvalidValue;
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1096,8 +1146,8 @@ cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type
         if (q != cudaDriverEntryPointSuccess || fn == nullptr) return cudaErrorNotSupported;
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    const uint64_t rowb = uint64_t(row_bytes(type, cols));
-    const uint32_t raw_bytes = type == kQ8_0 ? 272u : 144u;
+    const uint32_t raw_bytes = type == kQ8_0 ? 272u : (type == kQ6_K ? uint32_t(kQ6_KPadded) : 144u);
+    const uint64_t rowb = type == kQ6_K ? uint64_t(cols / kRawK) * kQ6_KPadded : uint64_t(row_bytes(type, cols));
     const cuuint64_t gdim[2] = {rowb / 4, cuuint64_t(rows)};
     const cuuint64_t gstride[1] = {rowb};
     const cuuint32_t box[2] = {raw_bytes / 4, cuuint32_t(kTileM)};
@@ -1142,6 +1192,7 @@ cudaError_t gemm_tc_configure() {
     cudaError_t e;
     if ((e = configure_type<kQ4_K>()) != cudaSuccess) return e;
     if ((e = configure_type<kQ4_0>()) != cudaSuccess) return e;
+    if ((e = configure_type<kQ6_K>()) != cudaSuccess) return e;
     return configure_type<kQ8_0>();
 }
 
@@ -1174,6 +1225,7 @@ cudaError_t gemm_tc_launch(const GemmArgs &a, cudaStream_t stream) {
             case kQ4_K: e = launch_type<kQ4_K>(part, stream); break;
             case kQ4_0: e = launch_type<kQ4_0>(part, stream); break;
             case kQ8_0: e = launch_type<kQ8_0>(part, stream); break;
+            case kQ6_K: e = launch_type<kQ6_K>(part, stream); break;
             default: return cudaErrorInvalidValue;
         }
         if (e != cudaSuccess) return e;

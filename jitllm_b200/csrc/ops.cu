@@ -29,6 +29,19 @@ __global__ void dequant_kernel(int type, const uint8_t *blocks, int64_t n, float
         out[i] = decode_any(type, blocks, i);
 }
 
+// Q6_K super-blocks (210 bytes) copied into slots of kQ6_KPadded bytes, the tail zeroed: the layout the tensor-core
+// kernel's 2-D tensor map needs (rows that are 16-byte multiples). 16-bit pieces: the source is 2-byte aligned.
+__global__ void pad_q6k_kernel(const uint8_t *src, uint8_t *dst, size_t nblocks) {
+    constexpr int kHalfWords = kQ6_KPadded / 2;
+    const size_t total = nblocks * kHalfWords, stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t blk = i / kHalfWords;
+        const int w = int(i - blk * kHalfWords);
+        const unsigned short v = w < kQ6_KBytes / 2 ? reinterpret_cast<const unsigned short *>(src + blk * kQ6_KBytes)[w] : 0;
+        reinterpret_cast<unsigned short *>(dst + blk * kQ6_KPadded)[w] = v;
+    }
+}
+
 __global__ void fill_kernel(uint32_t *buf, size_t words, uint32_t value) {
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += stride)
@@ -1344,6 +1357,13 @@ cudaError_t embedding_launch(int type, const uint8_t *table, const int32_t *toke
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, embedding_kernel, type, table, tokens, active, x, dim);
+}
+
+cudaError_t pad_q6k_launch(const uint8_t *src, uint8_t *dst, size_t nblocks, cudaStream_t stream) {
+    if (nblocks == 0) return cudaSuccess;
+    const size_t want = (nblocks * (kQ6_KPadded / 2) + 255) / 256;
+    pad_q6k_kernel<<<unsigned(want < 148 * 32 ? want : 148 * 32), 256, 0, stream>>>(src, dst, nblocks);
+    return cudaGetLastError();
 }
 
 cudaError_t dequant_launch(int type, const uint8_t *blocks, int64_t n, float *out,

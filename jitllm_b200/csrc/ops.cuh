@@ -50,6 +50,8 @@ cudaError_t embedding_launch(int type, const uint8_t *table, const int32_t *toke
                              cudaStream_t stream, bool programmatic);
 
 // out[i] = getFloat(i), element-exact.
+// Copies nblocks Q6_K super-blocks into slots of kQ6_KPadded bytes (see formats.cuh).
+cudaError_t pad_q6k_launch(const uint8_t *src, uint8_t *dst, size_t nblocks, cudaStream_t stream);
 cudaError_t dequant_launch(int type, const uint8_t *blocks, int64_t n, float *out,
                            cudaStream_t stream);
 
