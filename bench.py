@@ -190,7 +190,7 @@ def run_sweep(jl, args):
             wbytes = rows * cols * (EXTRA_BYTES_PER_EL if extra else BYTES_PER_EL)[fmt_name]
             copies = int(min(32, max(1, -(-300e6 // wbytes))))
             mats = [dev.upload_matrix(t, w, rows, cols) for _ in range(copies)]
-            for n in ((1, 8) if extra else (1, 8, 32, 512, 2048)):
+            for n in ((1, 8) if extra and fmt_name != "Q6_K" else (1, 8, 32, 512, 2048)):  # Q6_K has a tensor-core path
                 x = np.random.default_rng(args.seed + n).standard_normal((n, cols)).astype(np.float32)
                 xd, yd = dev.alloc(x.nbytes), dev.alloc(n * rows * 4)
                 dev.h2d(xd, x)
@@ -207,7 +207,8 @@ def run_sweep(jl, args):
                 print(json.dumps({"sweep": fmt_name, "rows": rows, "cols": cols, "n": n, "us": round(us, 2),
                                   "bytes": by, "gbs": round(by / us / 1e3, 1), "hbm_frac": round(by / us / 1e3 / peak, 4),
                                   "tflops": round(2.0 * rows * cols * n / us / 1e6, 2), "peak_kind": peak_kind,
-                                  "kernel": ("gemv" if n < 8 and (fmt_name != "Q6_K" or cols % 2048 == 0) else "gemv_extra") if extra
+                                  "kernel": ("gemv" if n < 8 and (fmt_name != "Q6_K" or cols % 2048 == 0) else
+                                             "gemm_tc" if n >= 8 and fmt_name == "Q6_K" else "gemv_extra") if extra
                                   else ("gemv" if n < 8 else "gemm_tc")}), flush=True)
                 dev.free(xd)
                 dev.free(yd)
