@@ -173,24 +173,22 @@ def op_bytes(cfg, fmt, op, shards=1):
 
 
 def run_sweep(jl, args):
-    """Formats {Q8_0, Q4_0, Q4_K} x shapes x N through jl_gemv_dev with device-resident operands, then the
-    stand-alone mat-vec of Q4_1 / Q5_K / Q6_K at N = 1 and 8. Each case cycles over enough copies of the matrix to
-    exceed L2 (126 MB), so every launch reads HBM."""
+    """Formats {Q8_0, Q4_0, Q4_K, Q4_1, Q5_K, Q6_K} x shapes x N through jl_gemv_dev with device-resident operands.
+    Each case cycles over enough copies of the matrix to exceed L2 (126 MB), so every launch reads HBM."""
     import numpy as np
     dev = jl.Device(0)
     peak, peak_kind = measured_peak()
     shapes = tuple(tuple(int(v) for v in sh.split("x")) for sh in args.sweep_shapes.split(",") if sh)
     for fmt_name in [f for f in args.sweep_formats.split(",") if f]:
         t = jl.GGMLType[fmt_name]
-        extra = fmt_name in EXTRA_BYTES_PER_EL  # no encoder and no tensor-core path: random blocks, N = 1 and 8 (N = 1
-        # in the model's own mat-vec kernel, N = 8 in gemv_extra_kernel)
+        extra = fmt_name in EXTRA_BYTES_PER_EL  # no encoder here: random blocks with sane scales
         for rows, cols in shapes:
             w = (jl.random_blocks(t, rows * cols, seed=args.seed + rows + cols) if extra
                  else jl.synth_tensor(t, rows * cols, seed=args.seed + rows + cols))
             wbytes = rows * cols * (EXTRA_BYTES_PER_EL if extra else BYTES_PER_EL)[fmt_name]
             copies = int(min(32, max(1, -(-300e6 // wbytes))))
             mats = [dev.upload_matrix(t, w, rows, cols) for _ in range(copies)]
-            for n in ((1, 8) if extra and fmt_name != "Q6_K" else (1, 8, 32, 512, 2048)):  # Q6_K has a tensor-core path
+            for n in (1, 8, 32, 512, 2048):
                 x = np.random.default_rng(args.seed + n).standard_normal((n, cols)).astype(np.float32)
                 xd, yd = dev.alloc(x.nbytes), dev.alloc(n * rows * 4)
                 dev.h2d(xd, x)
@@ -207,8 +205,7 @@ def run_sweep(jl, args):
                 print(json.dumps({"sweep": fmt_name, "rows": rows, "cols": cols, "n": n, "us": round(us, 2),
                                   "bytes": by, "gbs": round(by / us / 1e3, 1), "hbm_frac": round(by / us / 1e3 / peak, 4),
                                   "tflops": round(2.0 * rows * cols * n / us / 1e6, 2), "peak_kind": peak_kind,
-                                  "kernel": ("gemv" if n < 8 and (fmt_name != "Q6_K" or cols % 2048 == 0) else
-                                             "gemm_tc" if n >= 8 and fmt_name == "Q6_K" else "gemv_extra") if extra
+                                  "kernel": ("gemm_tc" if n >= 8 else "gemv" if fmt_name != "Q6_K" or cols % 2048 == 0 else "gemv_extra") if extra
                                   else ("gemv" if n < 8 else "gemm_tc")}), flush=True)
                 dev.free(xd)
                 dev.free(yd)

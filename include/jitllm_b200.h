@@ -44,9 +44,8 @@ typedef enum {
 /* GGML type ids as stored in GGUF (format/GGMLType.java:7-30). Q4_0, Q8_0 and Q4_K matrices run on the fused
  * single-row kernels and the tensor-core kernel. Q4_1, Q5_K and Q6_K, which mixed-precision files add for some
  * tensors, are decoded element-exactly; they run on the fused single-row kernels too (Q6_K: columns a multiple of
- * 2048); in batches and prompt chunks Q6_K runs on the tensor-core kernel (from a padded second copy on the device),
- * Q4_1 and Q5_K on a mat-vec kernel of their own. A model with other Q6_K row lengths takes the row path for every
- * step. One GPU only. */
+ * 2048) and, in batches and prompt chunks, on the tensor-core kernel (Q6_K from a padded second copy on the device).
+ * A model with other Q6_K row lengths takes the row path for every step. One GPU only. */
 typedef enum {
     JL_F32 = 0, JL_F16 = 1, JL_Q4_0 = 2, JL_Q4_1 = 3, JL_Q8_0 = 8, JL_Q4_K = 12, JL_Q5_K = 13, JL_Q6_K = 14
 } jl_ggml_type;

@@ -287,7 +287,7 @@ int upload(jl_ctx *ctx, DevTensor *t, int type, int64_t rows, int64_t cols, cons
     t->cols = cols;
     t->bytes = nbytes;
     t->has_tmap = false;
-    if (is_quant(type) && cols % 256 == 0) {
+    if ((is_quant(type) || type == kQ4_1 || type == kQ5_K) && cols % 256 == 0) {
         e = gemm_make_tensor_map(&t->tmap, p, type, rows, cols);
         if (e != cudaSuccess) {
             cudaFree(p);

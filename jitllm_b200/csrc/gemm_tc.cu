@@ -212,7 +212,11 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 
 template <int TYPE>
 struct RawFmt {
-    static constexpr int row_bytes = TYPE == kQ8_0 ? 272 : (TYPE == kQ6_K ? kQ6_KPadded : 144);  // 256 columns of one row
+    static constexpr int row_bytes = TYPE == kQ8_0   ? 272  // 256 columns of one row
+                                     : TYPE == kQ6_K ? kQ6_KPadded
+                                     : TYPE == kQ5_K ? kQ5_KBytes
+                                     : TYPE == kQ4_1 ? 8 * kQ4_1Bytes
+                                                     : 144;
     static constexpr int stage_bytes = kTileM * row_bytes;
 };
 
@@ -249,6 +253,19 @@ struct UnitRegs<kQ8_0> {
     uint32_t base;  // shared address of the unit (two 34-byte blocks); its halves are loaded one at a time
 };
 template <>
+struct UnitRegs<kQ5_K> {
+    uint32_t qw[8];            // as Q4_K
+    __half2 d2;
+    __half2 sc2[2], off2[2];
+    __half2 chi2[2], clo2[2];
+    uint32_t qh_at;            // shared address of the super-block's 32 bytes of fifth bits (read again per half)
+    int shift;                 // bit of those bytes that belongs to the unit's low nibbles (the high nibbles' is the next)
+};
+template <>
+struct UnitRegs<kQ4_1> {
+    uint32_t t[10];  // two 20-byte blocks: (d, m), 16 bytes of nibbles, twice
+};
+template <>
 struct UnitRegs<kQ6_K> {
     uint32_t blk;   // shared address of the (padded) super-block; the unit's halves are loaded one at a time
     int unit;
@@ -261,12 +278,18 @@ __device__ __forceinline__ __half2 u32_as_half2(uint32_t v) { return *reinterpre
 // the 64-column unit inside it (0..3).
 template <int TYPE>
 __device__ __forceinline__ void unit_load(uint32_t row_u32, int unit, UnitRegs<TYPE> &r) {
-    if constexpr (TYPE == kQ4_K) {
+    if constexpr (TYPE == kQ4_K || TYPE == kQ5_K) {
         // tensor/standard/Q4_KFloatTensor.java:68-122: unit p holds sub-blocks 2p (low nibbles) and
-        // 2p+1 (high nibbles) of the same 32 bytes; w = (d*sc)*q - dmin*m.
+        // 2p+1 (high nibbles) of the same 32 bytes; w = (d*sc)*q - dmin*m. Q5_K (Q5_KFloatTensor.java:87-127) is
+        // the same with 32 bytes of fifth bits between the header and the nibbles.
+        constexpr int kNibbles = TYPE == kQ5_K ? 48 : 16;
         const uint4 hdr = lds128(row_u32);
-        const uint4 q0 = lds128(row_u32 + 16 + unit * 32);
-        const uint4 q1 = lds128(row_u32 + 32 + unit * 32);
+        const uint4 q0 = lds128(row_u32 + kNibbles + unit * 32);
+        const uint4 q1 = lds128(row_u32 + kNibbles + 16 + unit * 32);
+        if constexpr (TYPE == kQ5_K) {
+            r.qh_at = row_u32 + 16;
+            r.shift = 2 * unit;
+        }
         r.qw[0] = q0.x; r.qw[1] = q0.y; r.qw[2] = q0.z; r.qw[3] = q0.w;
         r.qw[4] = q1.x; r.qw[5] = q1.y; r.qw[6] = q1.z; r.qw[7] = q1.w;
         r.d2 = u32_as_half2(__byte_perm(hdr.x, 0u, 0x1010));
@@ -298,6 +321,10 @@ __device__ __forceinline__ void unit_load(uint32_t row_u32, int unit, UnitRegs<T
         const uint32_t base = row_u32 + unit * 36;
 #pragma unroll
         for (int i = 0; i < 9; ++i) r.t[i] = lds32(base + 4 * i);
+    } else if constexpr (TYPE == kQ4_1) {
+        const uint32_t base = row_u32 + unit * 40;
+#pragma unroll
+        for (int i = 0; i < 10; ++i) r.t[i] = lds32(base + 4 * i);
     } else if constexpr (TYPE == kQ6_K) {
         r.blk = row_u32;
         r.unit = unit;
@@ -330,6 +357,41 @@ __device__ __forceinline__ void unit_convert(const UnitRegs<TYPE> &r, int half, 
             const __half2 wo = __hadd2(__hfma2(r.d2, __hfma2(sc2, o, off2), chi2), clo2);
             out[2 * i] = h2_bits(we);
             out[2 * i + 1] = h2_bits(wo);
+        }
+    } else if constexpr (TYPE == kQ5_K) {
+        // As Q4_K, with the fifth bit dropped into the same mantissa: 1024 + q (low nibbles: bit 4) or 64 + q (high
+        // nibbles, whose mantissa unit is 1/16: bit 8). sc * q stays below 2048, exact in binary16.
+        const uint32_t mask = half == 0 ? 0x000F000Fu : 0x00F000F0u, magic = half == 0 ? 0x64006400u : 0x54005400u;
+        const __half2 sc2 = r.sc2[half], off2 = r.off2[half], chi2 = r.chi2[half], clo2 = r.clo2[half];
+        const uint4 f0 = lds128(r.qh_at), f1 = lds128(r.qh_at + 16);
+        const uint32_t fw[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+        const int fs = r.shift + half;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t f = fw[i] >> fs;  // bit 0 of every byte: the fifth bit of that weight
+            const uint32_t fe = half == 0 ? ((f << 4) & 0x00100010u) : ((f << 8) & 0x01000100u);  // bytes 0 and 2
+            const uint32_t fo = half == 0 ? ((f >> 4) & 0x00100010u) : (f & 0x01000100u);          // bytes 1 and 3
+            const __half2 e = u32_as_half2((r.qw[i] & mask) | fe | magic);
+            const __half2 o = u32_as_half2(((r.qw[i] >> 8) & mask) | fo | magic);
+            const __half2 we = __hadd2(__hfma2(r.d2, __hfma2(sc2, e, off2), chi2), clo2);
+            const __half2 wo = __hadd2(__hfma2(r.d2, __hfma2(sc2, o, off2), chi2), clo2);
+            out[2 * i] = h2_bits(we);
+            out[2 * i + 1] = h2_bits(wo);
+        }
+    } else if constexpr (TYPE == kQ4_1) {
+        // tensor/standard/Q4_1FloatTensor.java:76-99: a unit is two 20-byte blocks; w = q * d + m with an unsigned
+        // nibble, one fused multiply-add on exact inputs.
+        const uint32_t hdr = r.t[5 * half];
+        const __half2 d2 = u32_as_half2(__byte_perm(hdr, 0u, 0x1010)), m2 = u32_as_half2(__byte_perm(hdr, 0u, 0x3232));
+        const __half2 off = __float2half2_rn(1024.0f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t q = r.t[5 * half + 1 + i];
+            const uint32_t l4 = q & 0x0F0F0F0Fu, h4 = (q >> 4) & 0x0F0F0F0Fu;
+            out[2 * i] = h2_bits(__hfma2(__hsub2(bytes_to_half2_plus1024(l4, 0x4240u), off), d2, m2));
+            out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bytes_to_half2_plus1024(l4, 0x4341u), off), d2, m2));
+            out[8 + 2 * i] = h2_bits(__hfma2(__hsub2(bytes_to_half2_plus1024(h4, 0x4240u), off), d2, m2));
+            out[8 + 2 * i + 1] = h2_bits(__hfma2(__hsub2(bytes_to_half2_plus1024(h4, 0x4341u), off), d2, m2));
         }
     } else if constexpr (TYPE == kQ6_K) {
         // tensor/standard/Q6_KFloatTensor.java:64-117. Unit p = 2h + u of the super-block: half h, the groups 2u
@@ -1132,7 +1194,7 @@ cudaError_t configure_type() {
 cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type, int64_t rows, int64_t cols) {
     static_assert(sizeof(CUtensorMap) == sizeof(GemmTensorMap), "descriptor size");
     // (a Q6_K matrix is passed as its padded copy: kQ6_KPadded bytes per super-block)
-    if (!out || !w_dev || !(is_quant(type) || type == kQ6_K) || rows <= 0 || cols <= 0 || cols % kRawK != 0)
+    if (!out || !w_dev || !(is_quant(type) || is_extra_quant(type)) || rows <= 0 || cols <= 0 || cols % kRawK != 0)
         return cudaErrorInvalidValue;
     typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1146,7 +1208,11 @@ cudaError_t gemm_make_tensor_map(GemmTensorMap *out, const void *w_dev, int type
         if (q != cudaDriverEntryPointSuccess || fn == nullptr) return cudaErrorNotSupported;
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    const uint32_t raw_bytes = type == kQ8_0 ? 272u : (type == kQ6_K ? uint32_t(kQ6_KPadded) : 144u);
+    const uint32_t raw_bytes = type == kQ8_0   ? 272u
+                               : type == kQ6_K ? uint32_t(kQ6_KPadded)
+                               : type == kQ5_K ? uint32_t(kQ5_KBytes)
+                               : type == kQ4_1 ? uint32_t(8 * kQ4_1Bytes)
+                                               : 144u;
     const uint64_t rowb = type == kQ6_K ? uint64_t(cols / kRawK) * kQ6_KPadded : uint64_t(row_bytes(type, cols));
     const cuuint64_t gdim[2] = {rowb / 4, cuuint64_t(rows)};
     const cuuint64_t gstride[1] = {rowb};
@@ -1193,6 +1259,8 @@ cudaError_t gemm_tc_configure() {
     if ((e = configure_type<kQ4_K>()) != cudaSuccess) return e;
     if ((e = configure_type<kQ4_0>()) != cudaSuccess) return e;
     if ((e = configure_type<kQ6_K>()) != cudaSuccess) return e;
+    if ((e = configure_type<kQ5_K>()) != cudaSuccess) return e;
+    if ((e = configure_type<kQ4_1>()) != cudaSuccess) return e;
     return configure_type<kQ8_0>();
 }
 
@@ -1226,6 +1294,8 @@ cudaError_t gemm_tc_launch(const GemmArgs &a, cudaStream_t stream) {
             case kQ4_0: e = launch_type<kQ4_0>(part, stream); break;
             case kQ8_0: e = launch_type<kQ8_0>(part, stream); break;
             case kQ6_K: e = launch_type<kQ6_K>(part, stream); break;
+            case kQ5_K: e = launch_type<kQ5_K>(part, stream); break;
+            case kQ4_1: e = launch_type<kQ4_1>(part, stream); break;
             default: return cudaErrorInvalidValue;
         }
         if (e != cudaSuccess) return e;

@@ -17,10 +17,11 @@
 // dp4a, partial sums meeting in shared memory) had a quarter fewer instructions and no shared-memory reads in its
 // row loop, and was 1.4-2.2x slower: with a slice per warp too few bytes are in flight per SM.
 //
-// Where this kernel runs: batches of four or more rows and prompt chunks of Q4_1 and Q5_K matrices (eight or more
-// rows of the stand-alone operator), and single Q6_K rows that are not a whole number of 16-byte pieces. Other
-// single rows go through the model's own mat-vec kernel (gemv.cu: whole rows by bulk copies, integer dot products),
-// which reaches 0.7-0.9 of the HBM rate on these formats, and Q6_K batches through the tensor-core kernel.
+// Where this kernel runs: a few rows (up to seven of the stand-alone operator, up to three of a model step) of a
+// Q6_K matrix whose rows are not a whole number of 16-byte pieces. Other single rows go through the model's own
+// mat-vec kernel (gemv.cu: whole rows by bulk copies, integer dot products), which reaches 0.7-0.9 of the HBM rate on
+// these formats, and batches through the tensor-core kernel. It was the first kernel for these formats and stays as
+// the one that takes any row length.
 #include "gemv_extra.cuh"
 
 namespace jl {

@@ -40,7 +40,7 @@ def test_decode_bit_exactly(dev, oracle, t):
 @pytest.mark.parametrize("t", EXTRA)
 @pytest.mark.parametrize("rows,cols,n", [(4096, 4096, 1), (1000, 14336, 1), (37, 256, 1), (512, 2048, 3), (300, 1024, 5), (256, 4096, 9),
                                          (64, 14336, 4), (128, 6144, 2), (96, 16384, 1), (40, 16640, 1), (70, 768, 2), (33, 4352, 1), (700, 2048, 40), (257, 1024, 130),
-                                         (129, 256, 8)])
+                                         (129, 256, 8), (50, 768, 5), (31, 1280, 7)])
 def test_matvec_against_the_oracle(dev, oracle, t, rows, cols, n):
     rng = np.random.default_rng(rows + cols + int(t))
     w = random_blocks(t, rows * cols // t.block_size, rng)
@@ -53,8 +53,8 @@ def test_matvec_against_the_oracle(dev, oracle, t, rows, cols, n):
     # number of 16-byte pieces (Q4_1, Q5_K: always; Q6_K: columns a multiple of 2048): 16-bit fixed-point
     # activations per block (~3e-5). Everything else: binary32 in another order (~1e-6). A wrong nibble is ~1e-1.
     fused = n < 8 and (t != GGMLType.Q6_K or cols % 2048 == 0)
-    # Eight or more rows of a Q6_K matrix: the tensor-core kernel (binary16 weights and activation parts, ~3e-4).
-    tensor_core = n >= 8 and t == GGMLType.Q6_K
+    # Eight or more rows: the tensor-core kernel (binary16 weights and activation parts, ~3e-4).
+    tensor_core = n >= 8
     assert rel_l2(got, want) <= (6e-4 if tensor_core else 1e-4 if fused else 2e-5)
 
 
