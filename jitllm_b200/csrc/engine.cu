@@ -1420,7 +1420,7 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     if (ctx->finalized) return JL_OK;
     cudaSetDevice(ctx->device);
     const size_t B = d.max_batch;
-    constexpr int kPrefillChunk = 256;
+    constexpr int kPrefillChunk = 512;
     ctx->row_cap = d.max_batch > kPrefillChunk ? d.max_batch : kPrefillChunk;
     const size_t R = ctx->row_cap;
     int rc;
