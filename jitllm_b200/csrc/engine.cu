@@ -1420,7 +1420,14 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     if (ctx->finalized) return JL_OK;
     cudaSetDevice(ctx->device);
     const size_t B = d.max_batch;
-    constexpr int kPrefillChunk = 512;
+    // Rows per prompt chunk (JITLLM_B200_PREFILL_CHUNK: a multiple of 128 between 128 and 2048; default 512). A chunk's
+    // attention walks all earlier keys again, so fewer, larger chunks ingest long prompts faster; the step buffers
+    // grow with it.
+    static const int kPrefillChunk = [] {
+        const char *v = getenv("JITLLM_B200_PREFILL_CHUNK");
+        const int c = v ? atoi(v) : 512;
+        return c >= 128 && c <= 2048 && c % 128 == 0 ? c : 512;
+    }();
     ctx->row_cap = d.max_batch > kPrefillChunk ? d.max_batch : kPrefillChunk;
     const size_t R = ctx->row_cap;
     int rc;
