@@ -21,7 +21,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "lib"
 
 CUDA_SOURCES = ["gemv.cu", "ops.cu", "engine.cu", "static_entry.cu", "gemm_tc.cu", "tp_exchange.cu", "gguf_loader.cu",
-                "sampler.cu", "gemv_extra.cu"]
+                "sampler.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -15,7 +15,6 @@
 #include <vector>
 
 #include "gemv.cuh"
-#include "gemv_extra.cuh"
 #include "ops.cuh"
 #include "sampler.cuh"
 #include "gemm_tc.cuh"
@@ -41,6 +40,8 @@ struct DevTensor {
     // Q6_K only: the copy with padded super-blocks that the tensor map describes (formats.cuh); owned like `data`.
     uint8_t *padded = nullptr;
     size_t padded_bytes = 0;
+    // What the mat-vec kernel reads: the padded copy of a Q6_K matrix, else the matrix as uploaded.
+    const uint8_t *mv() const { return padded != nullptr ? padded : data; }
 };
 
 // Frees a tensor's device memory (both copies) and leaves it empty.
@@ -73,7 +74,6 @@ struct jl_ctx {
     // The model holds a Q4_1 / Q5_K / Q6_K matrix, or Q/K/V (gate/up) of different types: every step, single rows
     // included, takes the row path, whose projections are launched one matrix at a time.
     bool mixed = false;
-    bool has_extra = false;  // some matrix is Q4_1 / Q5_K / Q6_K: the row path needs the spare row buffer for residuals
     jl_model_desc desc = {};
     int kv_dim = 0;
     DevTensor global[JL_ROLE_COUNT];
@@ -665,7 +665,7 @@ int attn_splits_for_width(const jl_ctx *ctx, int width) {
 // Matrices the fused single-row step can multiply: F32 norm rows aside, what gemv_plan accepts.
 bool fused_path_takes(const DevTensor &t) {
     if (!is_extra_quant(t.type)) return true;
-    return gemv_takes(t.type, t.cols) && t.cols <= kGemvMaxCols;
+    return gemv_takes(t.type, t.cols) && t.cols <= kGemvMaxCols && (t.type != kQ6_K || t.padded != nullptr);
 }
 
 // Batches of at least this many rows, and prompt chunks, take the tensor-core projections.
@@ -674,15 +674,12 @@ int gemm_min_width() {
     return v;
 }
 
-// How the row path multiplies n rows by one matrix: the mat-vec kernel row by row (narrow steps of a mixed-format
-// model, formats and row lengths it reads), the tensor-core kernel (wide steps, matrices with a tensor map: Q4_0,
-// Q8_0, Q4_K, and Q6_K through its padded copy), else the stand-alone mat-vec of Q4_1 / Q5_K / Q6_K.
-enum RowsVia { kViaGemv, kViaGemm, kViaExtra };
-RowsVia rows_via(const jl_ctx *ctx, const DevTensor &w, int n) {
-    const bool narrow = ctx->mixed && n < gemm_min_width();
-    if (narrow && fused_path_takes(w)) return kViaGemv;
-    if (!narrow && w.has_tmap) return kViaGemm;
-    return is_extra_quant(w.type) ? kViaExtra : (narrow ? kViaGemv : kViaGemm);
+// How the row path multiplies n rows by one matrix: the mat-vec kernel row by row (narrow steps of a model whose gate
+// and up projections differ in type, which keeps it off the fused single-row step), else the tensor-core kernel
+// (Q6_K through its padded copy).
+enum RowsVia { kViaGemv, kViaGemm };
+RowsVia rows_via(const jl_ctx *ctx, const DevTensor &, int n) {
+    return ctx->mixed && n < gemm_min_width() ? kViaGemv : kViaGemm;
 }
 
 int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, const float *const *res, int nseg,
@@ -690,24 +687,6 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
 
 int launch_gemm(jl_ctx *ctx, const DevTensor &w, const float *x, int n, float *y, const float *res,
                 uint64_t *launches, int in_kind = -1, bool presplit = false) {
-    if (rows_via(ctx, w, n) == kViaExtra) {
-        // the stand-alone mat-vec over the n fp32 rows (every producer of the row path writes them beside the
-        // binary16 parts); a residual is added by a row kernel, through the spare row buffer
-        if (res != nullptr && (res != y || ctx->part == nullptr || int(w.rows) != ctx->desc.dim))
-            return fail(ctx, JL_ERR_UNSUPPORTED, "residual of a type %d projection", w.type);
-        if (w.cols > kGemvExtraMaxCols)
-            return fail(ctx, JL_ERR_UNSUPPORTED, "type %d matrices are limited to %d columns", w.type, kGemvExtraMaxCols);
-        float *dst = res != nullptr ? ctx->part : y;
-        cudaError_t e = gemv_extra_launch(w.type, w.data, x, dst, int(w.rows), int(w.cols), n, ctx->sm_count, ctx->stream);
-        if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "matrix-vector launch failed: %s", cudaGetErrorString(e));
-        ++*launches;
-        if (res != nullptr) {
-            e = add_rows_launch(y, ctx->part, size_t(n) * w.rows, ctx->stream, ctx->use_pdl);
-            if (e != cudaSuccess) return fail(ctx, JL_ERR_CUDA, "residual launch failed: %s", cudaGetErrorString(e));
-            ++*launches;
-        }
-        return JL_OK;
-    }
     const DevTensor *ws[1] = {&w};
     float *ys[1] = {y};
     const float *rs[1] = {res};
@@ -721,7 +700,7 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
     const RowsVia via = rows_via(ctx, *w[0], n);
     bool alike = true;
     for (int s = 1; s < nseg; ++s) alike = alike && w[s]->type == w[0]->type && rows_via(ctx, *w[s], n) == via;
-    if (!alike || via == kViaExtra) {
+    if (!alike) {
         for (int s = 0; s < nseg; ++s) {
             int rc = launch_gemm(ctx, *w[s], x, n, y[s], res != nullptr ? res[s] : nullptr, launches, in_kind, presplit);
             if (rc) return rc;
@@ -738,7 +717,7 @@ int launch_gemm_segs(jl_ctx *ctx, const DevTensor *const *w, float *const *y, co
             GemvArgs a = {};
             a.nseg = nseg;
             for (int s = 0; s < nseg; ++s)
-                a.seg[s] = {w[s]->data, y[s] + size_t(b) * w[s]->rows,
+                a.seg[s] = {w[s]->mv(), y[s] + size_t(b) * w[s]->rows,
                             res != nullptr && res[s] != nullptr ? res[s] + size_t(b) * w[s]->rows : nullptr, int(w[s]->rows)};
             a.cols = int(w[0]->cols);
             a.type = w[0]->type;
@@ -941,9 +920,9 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.norm_w = attn_norm;
             a.eps = d.rms_eps;
             a.active = ctx->d_active + b;
-            const GemvSeg segs[3] = {{wq.data, ctx->q + size_t(b) * qdim, nullptr, int(wq.rows)},
-                                     {wk.data, ctx->k + size_t(b) * kv_dim, nullptr, int(wk.rows)},
-                                     {wv.data, ctx->v + size_t(b) * kv_dim, nullptr, int(wv.rows)}};
+            const GemvSeg segs[3] = {{wq.mv(), ctx->q + size_t(b) * qdim, nullptr, int(wq.rows)},
+                                     {wk.mv(), ctx->k + size_t(b) * kv_dim, nullptr, int(wk.rows)},
+                                     {wv.mv(), ctx->v + size_t(b) * kv_dim, nullptr, int(wv.rows)}};
             if (qkv_alike) {
                 a.nseg = 3;
                 a.seg[0] = segs[0];
@@ -995,9 +974,9 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.nseg = 1;
             float *xr = ctx->x + size_t(b) * dim;
             if (tp && !fused)
-                a.seg[0] = {wo.data, ctx->part + size_t(b) * dim, nullptr, int(wo.rows)};
+                a.seg[0] = {wo.mv(), ctx->part + size_t(b) * dim, nullptr, int(wo.rows)};
             else
-                a.seg[0] = {wo.data, xr, xr, int(wo.rows)};
+                a.seg[0] = {wo.mv(), xr, xr, int(wo.rows)};
             if (fused) tp_fill_reduce(ctx, a, b);
             a.cols = int(wo.cols);
             a.type = wo.type;
@@ -1011,8 +990,8 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
             a.nseg = 2;
-            a.seg[0] = {w1.data, ctx->hb + size_t(b) * hidden, nullptr, int(w1.rows)};
-            a.seg[1] = {w3.data, nullptr, nullptr, int(w3.rows)};
+            a.seg[0] = {w1.mv(), ctx->hb + size_t(b) * hidden, nullptr, int(w1.rows)};
+            a.seg[1] = {w3.mv(), nullptr, nullptr, int(w3.rows)};
             a.cols = dim;
             a.type = w1.type;
             a.mode = kGemvGateUp;
@@ -1027,9 +1006,9 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
             a.nseg = 1;
             float *xr = ctx->x + size_t(b) * dim;
             if (tp && !fused)
-                a.seg[0] = {w2.data, ctx->part + size_t(b) * dim, nullptr, int(w2.rows)};
+                a.seg[0] = {w2.mv(), ctx->part + size_t(b) * dim, nullptr, int(w2.rows)};
             else
-                a.seg[0] = {w2.data, xr, xr, int(w2.rows)};
+                a.seg[0] = {w2.mv(), xr, xr, int(w2.rows)};
             if (fused) tp_fill_reduce(ctx, a, b);
             a.cols = int(w2.cols);
             a.type = w2.type;
@@ -1046,7 +1025,7 @@ int enqueue_step(jl_ctx *ctx, int width, bool with_logits, bool advance, uint64_
         for (int b = 0; b < width; ++b) {
             GemvArgs a = {};
             a.nseg = 1;
-            a.seg[0] = {wc.data, ctx->logits + size_t(b) * ctx->l_vocab, nullptr, int(wc.rows)};
+            a.seg[0] = {wc.mv(), ctx->logits + size_t(b) * ctx->l_vocab, nullptr, int(wc.rows)};
             a.cols = dim;
             a.type = wc.type;
             a.mode = kGemvPlain;
@@ -1167,7 +1146,6 @@ int32_t jl_init(int32_t device_id, jl_ctx **out) {
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->tev0);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->tev1);
     if (e == cudaSuccess) e = gemv_configure();
-    if (e == cudaSuccess) e = gemv_extra_configure();
     if (e == cudaSuccess) e = attention_configure();
     if (e == cudaSuccess) e = gemm_tc_configure();
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ctx->d_status), sizeof(int));
@@ -1391,7 +1369,7 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
                                               emb.type, ctx->l_vocab, emb.cols));
         }
     }
-    bool mixed = false, has_extra = false;
+    bool mixed = false;
     static const int per_layer_roles[] = {JL_ROLE_ATTENTION_NORM,  JL_ROLE_ATTENTION_QUERY,
                                           JL_ROLE_ATTENTION_KEY,   JL_ROLE_ATTENTION_VALUE,
                                           JL_ROLE_ATTENTION_OUTPUT, JL_ROLE_FFN_NORM,
@@ -1404,10 +1382,8 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
         // where rows are whole 16-byte pieces) and gate and up alike; a layer that is not makes the whole model
         // take the row path (one GPU only). Q, K and V of different types are launched one by one.
         if (ctx->layer[JL_ROLE_FFN_GATE][l].type != ctx->layer[JL_ROLE_FFN_UP][l].type) mixed = true;
-        for (int r : per_layer_roles) {
+        for (int r : per_layer_roles)
             if (!fused_path_takes(ctx->layer[r][l])) mixed = true;
-            if (is_extra_quant(ctx->layer[r][l].type)) has_extra = true;
-        }
     }
     // (a table that only serves the embedding kernel may have any type)
     if (ctx->global[JL_ROLE_OUTPUT].data ? !fused_path_takes(ctx->global[JL_ROLE_OUTPUT])
@@ -1416,7 +1392,6 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
     JL_REQUIRE(ctx, !mixed || ctx->tp_size == 1, JL_ERR_UNSUPPORTED,
                "tensor parallelism needs Q, K, V (gate, up) of one type per layer and no Q4_1 / Q5_K / Q6_K matrices");
     ctx->mixed = mixed;
-    ctx->has_extra = has_extra;
     if (ctx->finalized) return JL_OK;
     cudaSetDevice(ctx->device);
     const size_t B = d.max_batch;
@@ -1462,7 +1437,6 @@ int32_t jl_model_finalize(jl_ctx *ctx) {
             JL_CUDA(ctx, gemm_make_activation_map(&ctx->xmaps[2][i], ctx->hb16, R, ctx->l_hidden, nts[i]));
         }
     }
-    if ((ctx->mixed || ctx->has_extra) && (rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;
     if (ctx->tp_size > 1) {
         JL_REQUIRE(ctx, ctx->nccl_comm != nullptr, JL_ERR_STATE, "jl_tp_init must come before jl_model_finalize");
         if ((rc = alloc(reinterpret_cast<void **>(&ctx->part), R * d.dim * 4))) return rc;
@@ -1953,9 +1927,9 @@ int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters)
             const DevTensor &wk = ctx->layer[JL_ROLE_ATTENTION_KEY][l];
             const DevTensor &wv = ctx->layer[JL_ROLE_ATTENTION_VALUE][l];
             a.nseg = 3;
-            a.seg[0] = {wq.data, ctx->q, nullptr, int(wq.rows)};
-            a.seg[1] = {wk.data, ctx->k, nullptr, int(wk.rows)};
-            a.seg[2] = {wv.data, ctx->v, nullptr, int(wv.rows)};
+            a.seg[0] = {wq.mv(), ctx->q, nullptr, int(wq.rows)};
+            a.seg[1] = {wk.mv(), ctx->k, nullptr, int(wk.rows)};
+            a.seg[2] = {wv.mv(), ctx->v, nullptr, int(wv.rows)};
             a.type = wq.type;
             a.x = ctx->x;
             a.norm_w = reinterpret_cast<const float *>(ctx->layer[JL_ROLE_ATTENTION_NORM][l].data);
@@ -1963,7 +1937,7 @@ int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters)
         } else if (op == 1) {
             const DevTensor &wo = ctx->layer[JL_ROLE_ATTENTION_OUTPUT][l];
             a.nseg = 1;
-            a.seg[0] = {wo.data, ctx->tp_size > 1 ? ctx->part : ctx->q, nullptr, int(wo.rows)};
+            a.seg[0] = {wo.mv(), ctx->tp_size > 1 ? ctx->part : ctx->q, nullptr, int(wo.rows)};
             a.cols = int(wo.cols);
             a.type = wo.type;
             a.x = ctx->xb;
@@ -1972,8 +1946,8 @@ int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters)
             const DevTensor &w1 = ctx->layer[JL_ROLE_FFN_GATE][l];
             const DevTensor &w3 = ctx->layer[JL_ROLE_FFN_UP][l];
             a.nseg = 2;
-            a.seg[0] = {w1.data, ctx->hb, nullptr, int(w1.rows)};
-            a.seg[1] = {w3.data, nullptr, nullptr, int(w3.rows)};
+            a.seg[0] = {w1.mv(), ctx->hb, nullptr, int(w1.rows)};
+            a.seg[1] = {w3.mv(), nullptr, nullptr, int(w3.rows)};
             a.type = w1.type;
             a.mode = kGemvGateUp;
             a.x = ctx->x;
@@ -1982,7 +1956,7 @@ int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters)
         } else if (op == 3) {
             const DevTensor &w2 = ctx->layer[JL_ROLE_FFN_DOWN][l];
             a.nseg = 1;
-            a.seg[0] = {w2.data, ctx->tp_size > 1 ? ctx->part : ctx->q, nullptr, int(w2.rows)};
+            a.seg[0] = {w2.mv(), ctx->tp_size > 1 ? ctx->part : ctx->q, nullptr, int(w2.rows)};
             a.cols = int(w2.cols);
             a.type = w2.type;
             a.x = ctx->hb;
@@ -1990,7 +1964,7 @@ int32_t jl_bench_op(jl_ctx *ctx, int32_t op, int32_t first_layer, int32_t iters)
         } else {
             const DevTensor wc = wcls_of(ctx);
             a.nseg = 1;
-            a.seg[0] = {wc.data, ctx->logits, nullptr, int(wc.rows)};
+            a.seg[0] = {wc.mv(), ctx->logits, nullptr, int(wc.rows)};
             a.type = wc.type;
             a.x = ctx->x;
             a.norm_w = reinterpret_cast<const float *>(ctx->global[JL_ROLE_OUTPUT_NORM].data);
@@ -2106,18 +2080,6 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     JL_REQUIRE(ctx, reinterpret_cast<uintptr_t>(x_dev) % 16 == 0 && reinterpret_cast<uintptr_t>(y_dev) % 16 == 0,
                JL_ERR_INVALID, "x_dev and y_dev must be 16-byte aligned");
     cudaSetDevice(ctx->device);
-    static const int gemm_min_n0 = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
-    if (is_extra_quant(w->t.type) && !(n < gemm_min_n0 && fused_path_takes(w->t)) && !(n >= gemm_min_n0 && w->t.has_tmap)) {
-        // Q4_1 / Q5_K / Q6_K: one launch for all n rows (weights re-read per row from L2 where they fit); a few rows
-        // of a Q6_K matrix the mat-vec kernel reads go there, below.
-        JL_REQUIRE(ctx, w->t.cols <= kGemvExtraMaxCols && n <= 65535, JL_ERR_UNSUPPORTED,
-                   "GGML type %d: at most %d columns and 65535 activation rows", w->t.type, kGemvExtraMaxCols);
-        if (n == 0) return JL_OK;
-        JL_CUDA(ctx, gemv_extra_launch(w->t.type, w->t.data, x_dev, y_dev, int(w->t.rows), int(w->t.cols), n, ctx->sm_count,
-                                       ctx->stream));
-        ctx->counters.kernel_launches += 1;
-        return JL_OK;
-    }
     uint64_t launches = 0;
     static const int gemm_min_n = [] { const char *v = getenv("JITLLM_B200_GEMM_MIN_N"); return v ? atoi(v) : 8; }();
     if (n >= gemm_min_n && w->t.has_tmap) {
@@ -2129,7 +2091,7 @@ int32_t jl_gemv_dev(jl_ctx *ctx, const jl_tensor *w, const float *x_dev, int32_t
     for (int b = 0; b < n; ++b) {
         GemvArgs a = {};
         a.nseg = 1;
-        a.seg[0] = {w->t.data, y_dev + size_t(b) * w->t.rows, nullptr, int(w->t.rows)};
+        a.seg[0] = {w->t.mv(), y_dev + size_t(b) * w->t.rows, nullptr, int(w->t.rows)};
         a.cols = int(w->t.cols);
         a.type = w->t.type;
         a.mode = kGemvPlain;

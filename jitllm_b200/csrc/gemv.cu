@@ -614,7 +614,7 @@ cudaError_t configure_type() {
 
 bool gemv_plan(int type, int cols, int total_rows, int mode, int sm_count, GemvPlan *out) {
     if (!gemv_takes(type, cols) || cols > kGemvMaxCols || total_rows <= 0) return false;
-    const size_t rowb = size_t(row_bytes(type, cols));
+    const size_t rowb = size_t(gemv_row_bytes(type, cols));
     const size_t stage = gemv_rows_per_stage(type) * rowb;
     const int spj = mode == kGemvGateUp ? 2 : 1;
     const int jobs = total_rows / spj;

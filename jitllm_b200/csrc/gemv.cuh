@@ -9,7 +9,7 @@ namespace jl {
 
 // One weight matrix of a fused launch (Q, K and V share one launch; gate and up share one).
 struct GemvSeg {
-    const uint8_t *w;  // device, GGUF block layout, rows x cols, 16-byte aligned
+    const uint8_t *w;  // device, GGUF block layout (Q6_K: the copy with padded super-blocks), rows x cols, 16-byte aligned
     float *y;          // device, rows
     const float *res;  // nullable: y[row] = res[row] + dot (may alias y)
     int rows;
@@ -82,11 +82,15 @@ __host__ __device__ inline int gemv_split(int n, int part, int parts) {
 // phase): two for the 4-bit formats, one for Q8_0 whose rows are twice as long in bytes.
 __host__ __device__ inline int gemv_rows_per_stage(int type) { return type == kQ8_0 ? 1 : 2; }  // = Fmt<type>::streams
 
-// The formats this kernel reads: Q8_0, Q4_0, Q4_K, Q4_1, Q5_K, and Q6_K where a row is a whole number of 16-byte
-// pieces (rows are fetched by bulk copies; 210-byte super-blocks make that every eighth: columns a multiple of 2048).
+// The formats this kernel reads: Q8_0, Q4_0, Q4_K, Q4_1, Q5_K, and Q6_K from its padded copy (rows are fetched by bulk
+// copies and must be whole 16-byte pieces: 210-byte super-blocks are not, kQ6_KPadded-byte ones are).
 __host__ __device__ inline bool gemv_takes(int type, int64_t cols) {
     if (cols <= 0 || cols % 256 != 0) return false;
-    return is_quant(type) || ((type == kQ6_K || type == kQ5_K || type == kQ4_1) && row_bytes(type, cols) % 16 == 0);
+    return is_quant(type) || type == kQ6_K || type == kQ5_K || type == kQ4_1;
+}
+// Bytes of one matrix row as this kernel reads it.
+__host__ __device__ inline int64_t gemv_row_bytes(int type, int64_t cols) {
+    return type == kQ6_K ? cols / 256 * kQ6_KPadded : row_bytes(type, cols);
 }
 
 // Chooses group count, pipeline depth and shared-memory layout for one launch shape.

@@ -14,7 +14,7 @@ struct Fmt {
     // bytes of 256 columns: one super-block (Q4_K, Q5_K, Q6_K) or eight blocks (Q4_0, Q4_1, Q8_0). A 64-element
     // unit is a quarter of that; for Q5_K and Q6_K it is no byte range of its own (the high bits sit apart).
     static constexpr int group_bytes = TYPE == kQ8_0   ? 8 * kQ8_0Bytes
-                                       : TYPE == kQ6_K ? kQ6_KBytes
+                                       : TYPE == kQ6_K ? kQ6_KPadded  // read from the copy with padded super-blocks
                                        : TYPE == kQ5_K ? kQ5_KBytes
                                        : TYPE == kQ4_1 ? 8 * kQ4_1Bytes
                                                        : kQ4_KBytes;  // Q4_K, and Q4_0: 8 x 18
@@ -150,55 +150,40 @@ __device__ __forceinline__ float unit_q8_0(uint32_t chunk, int lane, const UnitX
     return (dA * x.sa) * fA + (dB * x.sb) * fB;
 }
 
-__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
-    unsigned short v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-    return v;
-}
-
-// Q6_K (tensor/standard/Q6_KFloatTensor.java:64-117): the unit is quarter p of super-block (lane/4): half h = p / 2
-// of the block, groups 2u and 2u + 1 of that half with u = p & 1 -- the low (u = 0) or high (u = 1) nibbles of the
-// half's 64 ql bytes, bits 4u..4u+3 of its 32 qh bytes, four signed byte scales (one per 16 elements), the block's d.
-// Super-blocks are 210 bytes, so every other one starts two bytes off a word: words are loaded aligned and shifted
-// into place (shift 0 or 16, the same code for both). The six-bit value v becomes the signed byte 4 * (v - 32) as
-// (v ^ 32) << 2 -- flipping bit 5 is v - 32 in six-bit two's complement and the shift moves its sign into bit 7 -- so
-// the integer dot products are exact and four times too large.
+// Q6_K (tensor/standard/Q6_KFloatTensor.java:64-117), read from the copy whose 210-byte super-blocks are padded to
+// kQ6_KPadded bytes (made at upload: rows become whole 16-byte pieces for the bulk copies, and every field is
+// word-aligned). The unit is quarter p of super-block (lane/4): half h = p / 2 of the block, groups 2u and 2u + 1 of
+// that half with u = p & 1 -- the low (u = 0) or high (u = 1) nibbles of the half's 64 ql bytes, bits 4u..4u+3 of its
+// 32 qh bytes, four signed byte scales (one per 16 elements), the block's d. The six-bit value v becomes the signed
+// byte 4 * (v - 32) as (v ^ 32) << 2 -- flipping bit 5 is v - 32 in six-bit two's complement and the shift moves its
+// sign into bit 7 -- so the integer dot products are exact and four times too large.
 __device__ __forceinline__ float unit_q6_k(uint32_t chunk, int lane, const UnitX &x) {
-    const uint32_t sb = chunk + (lane >> 2) * kQ6_KBytes;
+    const uint32_t sb = chunk + (lane >> 2) * kQ6_KPadded;
     const int p = lane & 3, h = p >> 1, u = p & 1;
-    const uint32_t sh = (sb & 2u) * 8u;
-    const uint32_t base = sb & ~3u;
-    uint32_t qh[8];
-    {
-        const uint32_t at = base + 128 + 32 * h;
-        uint32_t prev = lds32(at);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t next = lds32(at + 4 * (i + 1));  // the ninth word still lies inside the block
-            qh[i] = __funnelshift_r(prev, next, sh) >> (4 * u);  // bits 0-1: first group, bits 2-3: second group
-            prev = next;
-        }
-    }
-    const uint32_t sc_at = sb + 192 + 8 * h + 4 * u;
-    const uint32_t sc4 = (lds16(sc_at) | (lds16(sc_at + 2) << 16)) ^ 0x80808080u;  // signed scales, biased by 128
-    const float d = half_bits_to_float(lds16(sb + 208));
+    const uint4 h0 = lds128(sb + 128 + 32 * h), h1 = lds128(sb + 144 + 32 * h);
+    const uint32_t qh[8] = {h0.x >> (4 * u), h0.y >> (4 * u), h0.z >> (4 * u), h0.w >> (4 * u),
+                            h1.x >> (4 * u), h1.y >> (4 * u), h1.z >> (4 * u), h1.w >> (4 * u)};  // bits 0-1, 2-3: the groups
+    const uint32_t sc4 = lds32(sb + 192 + 8 * h + 4 * u) ^ 0x80808080u;  // signed scales, biased by 128
+    const float d = half_bits_to_float(lds32(sb + 208) & 0xFFFFu);
     int acc[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // [16-element scale group][digit]
-    const uint32_t ql_at = base + 64 * h;
-    uint32_t prev = lds32(ql_at);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const uint32_t next = lds32(ql_at + 4 * (i + 1));
-        const uint32_t nib = (__funnelshift_r(prev, next, sh) >> (4 * u)) & 0x0F0F0F0Fu;
-        prev = next;
-        const uint32_t top = i < 8 ? (qh[i] << 4) : (qh[i - 8] << 2);
-        const uint32_t w4 = ((nib | (top & 0x30303030u)) ^ 0x20202020u) << 2;
-        const int g = i >> 2;  // words 0-3, 4-7: the two scale groups of the first 32 elements; 8-15: of the second
-        if (i < 8) {
-            acc[g][0] = dp4a_s8s8(int(w4), x.a[0][i], acc[g][0]);
-            acc[g][1] = dp4a_s8s8(int(w4), x.a[1][i], acc[g][1]);
-        } else {
-            acc[g][0] = dp4a_s8s8(int(w4), x.b[0][i - 8], acc[g][0]);
-            acc[g][1] = dp4a_s8s8(int(w4), x.b[1][i - 8], acc[g][1]);
+    for (int q = 0; q < 4; ++q) {  // four words of ql per load: words 0-7 the first group, 8-15 the second
+        const uint4 l4 = lds128(sb + 64 * h + 16 * q);
+        const uint32_t lw[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = 4 * q + j;
+            const uint32_t nib = (lw[j] >> (4 * u)) & 0x0F0F0F0Fu;
+            const uint32_t top = i < 8 ? (qh[i] << 4) : (qh[i - 8] << 2);
+            const uint32_t w4 = ((nib | (top & 0x30303030u)) ^ 0x20202020u) << 2;
+            const int g = i >> 2;
+            if (i < 8) {
+                acc[g][0] = dp4a_s8s8(int(w4), x.a[0][i], acc[g][0]);
+                acc[g][1] = dp4a_s8s8(int(w4), x.a[1][i], acc[g][1]);
+            } else {
+                acc[g][0] = dp4a_s8s8(int(w4), x.b[0][i - 8], acc[g][0]);
+                acc[g][1] = dp4a_s8s8(int(w4), x.b[1][i - 8], acc[g][1]);
+            }
         }
     }
     // |acc| <= 16 * 128 * 128 = 2^18, so 256 * acc[.][0] + acc[.][1] stays below 2^27: exact in integers.

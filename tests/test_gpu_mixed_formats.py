@@ -1,6 +1,8 @@
-"""A model whose tensors mix the step kernels' formats with Q4_1 / Q5_K / Q6_K (what mixed-precision files do for
-the value, down and output projections) against the oracle's forwardJava: every step takes the row path, logits
-within the stated 1e-2 max-abs bar, identical greedy tokens."""
+"""Models whose tensors mix formats (what mixed-precision files do for the value, down and output projections: Q6_K,
+Q5_K, Q4_1 beside Q4_K) against the oracle's forwardJava: logits within the stated 1e-2 max-abs bar, identical greedy
+tokens -- on the fused single-row step (Q, K, V launched one by one where their types differ), on the tensor-core
+path for batches and prompt chunks, and on the row path a model takes for every step when its gate and up
+projections differ in type."""
 import numpy as np
 import pytest
 
@@ -120,5 +122,32 @@ def test_q6_k_on_the_fused_single_row_path(dev, oracle, B):
             assert int(got[b]) == int(np.argmax(want[b])), (step, b)
         if B < 4:  # embedding, per layer Q, K, V + attention + out + gate/up + down per row, logits per row
             assert launches == 1 + cfg.numberOfLayers * (6 * B + 1) + B, launches
+        tokens = np.array([int(np.argmax(w)) for w in want], dtype=np.int32)
+        positions += 1
+
+
+@pytest.mark.parametrize("B", [1, 3, 5])
+def test_gate_and_up_of_different_types_take_the_row_path(dev, oracle, B):
+    """The fused gate/up launch needs both matrices in one format; a model where they differ runs every step through
+    the row path (narrow steps: the mat-vec kernel per row and matrix, norm / SwiGLU / arg-max as row kernels)."""
+    cfg = small_config(layers=2, ctx=64)
+    repl = {}
+    for l in range(cfg.numberOfLayers):
+        rows, cols = cfg.matrix_shape(TensorRole.FFN_UP)
+        repl[(TensorRole.FFN_UP, l)] = (GGMLType.Q8_0, jl.synth_tensor(GGMLType.Q8_0, rows * cols, seed=300 + l, std=0.05))
+    p = Pair(dev, oracle, cfg, GGMLType.Q4_K, seed=55, std=0.05, max_batch=B, replace=repl)
+    rng = np.random.default_rng(20 + B)
+    seqs = [p.new_oracle_sequence() for _ in range(B)]
+    tokens = rng.integers(0, cfg.vocabularySize, size=B).astype(np.int32)
+    positions = np.zeros(B, dtype=np.int32)
+    for step in range(8):
+        slots = jl.BatchSlots(np.ones(B, dtype=bool), tokens.copy(), positions.copy(), np.arange(B, dtype=np.int32))
+        got, logits = p.executor.decodeStep(slots, wantLogits=True)
+        want = [seqs[b].forward(int(tokens[b]), int(positions[b])) for b in range(B)]
+        for b in range(B):
+            err = float(np.max(np.abs(logits[b] - want[b])))
+            assert err < LOGIT_EXPECT, (step, b)
+            # the device's token is the oracle's, or ties with it within the error of the two logits
+            assert int(got[b]) == int(np.argmax(want[b])) or want[b][int(got[b])] >= float(np.max(want[b])) - 2 * err, (step, b)
         tokens = np.array([int(np.argmax(w)) for w in want], dtype=np.int32)
         positions += 1
