@@ -205,8 +205,7 @@ def run_sweep(jl, args):
                 print(json.dumps({"sweep": fmt_name, "rows": rows, "cols": cols, "n": n, "us": round(us, 2),
                                   "bytes": by, "gbs": round(by / us / 1e3, 1), "hbm_frac": round(by / us / 1e3 / peak, 4),
                                   "tflops": round(2.0 * rows * cols * n / us / 1e6, 2), "peak_kind": peak_kind,
-                                  "kernel": ("gemm_tc" if n >= 8 else "gemv" if fmt_name != "Q6_K" or cols % 2048 == 0 else "gemv_extra") if extra
-                                  else ("gemv" if n < 8 else "gemm_tc")}), flush=True)
+                                  "kernel": "gemv" if n < 8 else "gemm_tc"}), flush=True)
                 dev.free(xd)
                 dev.free(yd)
             for m in mats:

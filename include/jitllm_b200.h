@@ -43,9 +43,8 @@ typedef enum {
 
 /* GGML type ids as stored in GGUF (format/GGMLType.java:7-30). Q4_0, Q8_0 and Q4_K matrices run on the fused
  * single-row kernels and the tensor-core kernel. Q4_1, Q5_K and Q6_K, which mixed-precision files add for some
- * tensors, are decoded element-exactly; they run on the fused single-row kernels too (Q6_K: columns a multiple of
- * 2048) and, in batches and prompt chunks, on the tensor-core kernel (Q6_K from a padded second copy on the device).
- * A model with other Q6_K row lengths takes the row path for every step. One GPU only. */
+ * tensors, are decoded element-exactly and run on the same kernels (Q6_K from a second copy on the device whose
+ * super-blocks are padded to 224 bytes). One GPU only. */
 typedef enum {
     JL_F32 = 0, JL_F16 = 1, JL_Q4_0 = 2, JL_Q4_1 = 3, JL_Q8_0 = 8, JL_Q4_K = 12, JL_Q5_K = 13, JL_Q6_K = 14
 } jl_ggml_type;
@@ -163,8 +162,7 @@ int32_t jl_debug_read(jl_ctx *ctx, const char *name, int32_t row, float *out, in
 int32_t jl_dequant(jl_ctx *ctx, int32_t ggml_type, const void *blocks, int64_t n_elements,
                    float *out);
 /* y[n][rows] = W[rows][cols] . x[n][cols]; FloatTensor.matmul (tensor/standard/FloatTensor.java:123-140).
- * Host buffers; copies are part of the call. The same six types as jl_dequant; Q4_1, Q5_K and Q6_K (at most
- * 49152 columns) take a mat-vec kernel of their own at every n. */
+ * Host buffers; copies are part of the call. The same six types as jl_dequant; at most 32768 columns. */
 int32_t jl_gemv(jl_ctx *ctx, int32_t ggml_type, int64_t rows, int64_t cols, const void *w_host,
                 const float *x_host, int32_t n, float *y_host);
 /* Device-resident form: upload once, multiply many times. x_dev / y_dev are device pointers. */
